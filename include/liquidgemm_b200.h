@@ -1,0 +1,146 @@
+/*
+ * liquidgemm_b200 -- C ABI of the LiquidQuant (LQQ) W4A8 linear path for NVIDIA B200 (sm_100a).
+ *
+ * Every entry point takes plain device pointers and sizes, enqueues work on the CUDA stream it is
+ * given (cudaStream_t passed as void*), never synchronises the device and -- unless its comment
+ * says otherwise -- never allocates.  Return value: 0 on success, a negative LQ_ERR_* code
+ * otherwise (lq_error_string() explains it).  Pointers are borrowed for the duration of the
+ * enqueue only; outputs and workspaces are owned by the caller.
+ *
+ * Each declaration cites the interface of the reference project (liquidgemm, paths relative to
+ * its repository root) that the entry point stands in for.
+ *
+ * Codes shared by several calls
+ *   out_dtype / in_dtype : 0 = bfloat16, 1 = float16, 2 = float32
+ *                          (reference csrc/liquid_gemm/w4a8_wgmma.cu:626-627)
+ */
+#ifndef LIQUIDGEMM_B200_H_
+#define LIQUIDGEMM_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define LQ_API __attribute__((visibility("default")))
+#else
+#define LQ_API
+#endif
+
+#define LQ_OK 0
+#define LQ_ERR_BAD_ARG (-1)      /* null pointer, non-positive size, unknown dtype code            */
+#define LQ_ERR_SHAPE (-2)        /* a divisibility / range precondition of the op does not hold    */
+#define LQ_ERR_WORKSPACE (-3)    /* workspace missing or smaller than lq_*_workspace_bytes()       */
+#define LQ_ERR_CUDA (-4)         /* a CUDA runtime / driver call failed (see lq_last_cuda_error)   */
+#define LQ_ERR_DEVICE (-5)       /* current device is not compute capability 10.x                  */
+#define LQ_ERR_TIMEOUT (-6)      /* a bounded device-side wait gave up (read by lq_poll_status)    */
+
+#define LQ_DT_BF16 0
+#define LQ_DT_F16 1
+#define LQ_DT_F32 2
+
+/* Source layouts accepted by lq_repack_tiles(). */
+#define LQ_SRC_CODES 0           /* [N, K] uint8, one 4-bit code per byte  (LiquidQuantWeight.qweight_u4) */
+#define LQ_SRC_NIBBLES 1         /* [N, K/2] uint8, pack_nibbles() order (even k in the low nibble)       */
+
+/* Library identification and diagnostics (no reference counterpart: the reference reports errors
+ * through TORCH_CHECK exceptions, e.g. csrc/liquid_gemm/gemv2.cu:85-89). */
+LQ_API int lq_abi_version(void);
+LQ_API const char* lq_error_string(int code);
+/* Text of the last CUDA error recorded by this library on the calling thread ("" if none). */
+LQ_API const char* lq_last_cuda_error(void);
+/* 0 when the current device can run the kernels (sm_100), LQ_ERR_DEVICE otherwise. */
+LQ_API int lq_check_device(void);
+/* Reads (and clears) the device-side status word that bounded waits set when they give up.
+ * Synchronises `stream`.  Returns 0 or LQ_ERR_TIMEOUT. */
+LQ_API int lq_poll_status(void* stream);
+
+/* UINT4 -> INT8 reconstruction q_hat = (code*step + a) XOR 0x80.
+ * Replaces torch.ops.liquidgemm.dequant_weight (reference csrc/liquid_gemm/dequant.cu:46-74,
+ * schema csrc/liquid_gemm/torch_bindings.cpp:44-46).  q_u4 is [N,K] one code per byte;
+ * K % 4 == 0, group % 4 == 0, K % group == 0. */
+LQ_API int lq_dequant_weight(const uint8_t* q_u4, const uint8_t* s_u8, const uint8_t* offset_a,
+                      int8_t* out_i8, int N, int K, int group_size, void* stream);
+
+/* Per-token symmetric INT8 activation quantiser: ascale[m] = max(amax,1e-12)/127,
+ * xq = clamp(rint(x / ascale), +-127) with an IEEE division, i.e. bit-identical to
+ * liquidgemm/quant.py:135-141.  Replaces torch.ops.liquidgemm.quant_per_token
+ * (reference csrc/liquid_gemm/epilogue.cu:61-80), whose reciprocal-multiply can differ from
+ * that formula by one count. */
+LQ_API int lq_quant_per_token(const void* x, int in_dtype, int8_t* xq, float* ascale, int M, int K,
+                       void* stream);
+
+/* y[m,n] = (T)((float)acc[m,n] * ascale[m] * s1[n]).
+ * Replaces torch.ops.liquidgemm.scale_epilogue (reference csrc/liquid_gemm/epilogue.cu:82-106). */
+LQ_API int lq_scale_epilogue(const int32_t* acc, const float* ascale, const float* s1, void* y,
+                      int out_dtype, int M, int N, void* stream);
+
+/* Decode GEMV, M <= 16: y = scale_epilogue(x_i8 @ q_hat^T) straight from the row-major
+ * interleaved pack of liquidgemm/ops.py:68-75.  Requires K % 128 == 0 and group_size == 64.
+ * Replaces torch.ops.liquidgemm.w4a8_gemv2 (reference csrc/liquid_gemm/gemv2.cu:82-120). */
+LQ_API int lq_w4a8_gemv(const int8_t* x_i8, const uint8_t* gpack, const uint8_t* s_u8,
+                 const uint8_t* offset_a, const float* ascale, const float* s1, void* y,
+                 int out_dtype, int M, int N, int K, int group_size, void* stream);
+
+/* Same product from the plain pack_nibbles() layout with float32 output, any M.
+ * Replaces torch.ops.liquidgemm.w4a8_gemm (reference csrc/liquid_gemm/w4a8_gemm.cu:183-227).
+ * M <= 16 runs the GEMV; larger M repacks into `workspace` (lq_gemm_v1_workspace_bytes) and runs
+ * the tensor-core kernel.  K % 128 == 0, group_size % 64 == 0. */
+LQ_API size_t lq_gemm_v1_workspace_bytes(int M, int N, int K);
+LQ_API int lq_w4a8_gemm_v1(const int8_t* x_i8, const uint8_t* nibbles, const uint8_t* s_u8,
+                    const uint8_t* offset_a, const float* s1, const float* ascale, float* y,
+                    int M, int N, int K, int group_size, void* workspace, size_t workspace_bytes,
+                    void* stream);
+
+/* Tile-ordered weight blob consumed by the tensor-core GEMM: for every 128-row x 128-k tile,
+ * 8192 bytes of interleaved nibbles followed by 512 bytes of (step, offset) pairs.
+ * Replaces liquidgemm.ops.repack_rs_weight + the wgmma_rs_a_coords op it needs
+ * (reference liquidgemm/ops.py:118-150, csrc/liquid_gemm/w4a8_wgmma.cu:310-331): the layout is
+ * specific to this library, as the reference's is to Hopper register fragments.
+ * K % 128 == 0, group_size % 64 == 0 (and 128 % group_size == 0 or group_size % 128 == 0);
+ * N is padded to a multiple of 128 inside the blob. */
+LQ_API size_t lq_tile_blob_bytes(int N, int K);
+LQ_API int lq_repack_tiles(const uint8_t* src, int src_layout, const uint8_t* s_u8,
+                    const uint8_t* offset_a, uint8_t* blob, int N, int K, int group_size,
+                    void* stream);
+
+/* Split-K factor the GEMM uses for (M,N,K) when the caller passes splitk = 0.
+ * `env_override` carries LIQUIDGEMM_SPLITK (0 = unset); like the reference
+ * (csrc/liquid_gemm/w4a8_wgmma.cu:523-534) it only applies to M <= 128 and is clamped to K/128. */
+LQ_API int lq_gemm_pick_splitk(int M, int N, int K, int env_override);
+/* Bytes of int32 partial planes needed for `splitk` (0 when splitk <= 1). */
+LQ_API size_t lq_gemm_workspace_bytes(int M, int N, int K, int splitk);
+
+/* W4A8 tensor-core GEMM, exact int32 accumulators acc[M,N] = x_i8 @ q_hat^T.
+ * Replaces torch.ops.liquidgemm.w4a8_wgmma_rs (reference csrc/liquid_gemm/w4a8_wgmma.cu:505-570).
+ * Any M >= 1 (token rows beyond M are zero-filled by TMA, not by a padded copy). */
+LQ_API int lq_w4a8_gemm_i32(const int8_t* x_i8, const uint8_t* blob, int32_t* acc, int M, int N, int K,
+                     int splitk, void* workspace, size_t workspace_bytes, void* stream);
+
+/* W4A8 tensor-core GEMM with the fused (split-K reduce +) scale + cast epilogue.
+ * Replaces torch.ops.liquidgemm.w4a8_wgmma_rs_fused
+ * (reference csrc/liquid_gemm/w4a8_wgmma.cu:575-645). */
+LQ_API int lq_w4a8_gemm_fused(const int8_t* x_i8, const uint8_t* blob, const float* ascale,
+                       const float* s1, void* y, int out_dtype, int M, int N, int K, int splitk,
+                       void* workspace, size_t workspace_bytes, void* stream);
+
+/* Plain INT8 x INT8 -> INT32 tensor-core GEMM c[M,N] = a[M,K] @ b[N,K]^T.
+ * Replaces torch.ops.liquidgemm.wgmma_i8_gemm (reference csrc/liquid_gemm/w4a8_wgmma.cu:648-694).
+ * K % 128 == 0; M and N are arbitrary here (the reference needs multiples of 128). */
+LQ_API int lq_i8_gemm_i32(const int8_t* a, const int8_t* b, int32_t* c, int M, int N, int K,
+                   void* stream);
+
+/* Same GEMM with the scale + cast epilogue: y = (T)((float)acc * a_scale[m] * b_scale[n]).
+ * Stands in for the third-party vllm cutlass_scaled_mm call of the plugin's INT8 mode
+ * (reference liquidgemm/vllm_plugin.py:197-204). */
+LQ_API int lq_i8_gemm_scaled(const int8_t* a, const int8_t* b, const float* a_scale,
+                      const float* b_scale, void* y, int out_dtype, int M, int N, int K,
+                      void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LIQUIDGEMM_B200_H_ */

@@ -1,0 +1,65 @@
+// Shared device/host helpers for the liquidgemm_b200 kernels (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/liquidgemm_b200.h"
+
+namespace lq {
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+void record_cuda_error(cudaError_t e, const char* where);   // lq_api.cu
+int check_launch(const char* where);                        // lq_api.cu: cudaGetLastError -> code
+int sm_count();                                             // lq_api.cu: cached per device
+int* status_word();                                         // lq_api.cu: device address of the status word
+
+inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
+
+// ---------------------------------------------------------------------------------------------
+// LQQ arithmetic
+// ---------------------------------------------------------------------------------------------
+// Four codes in the four byte lanes of `w` -> four int8: (code*step + a) XOR 0x80 per lane.
+// code <= 15 and step <= 16 keep every product <= 240 and every sum <= 255, so no lane carries
+// (reference liquidgemm/quant.py:16-22, csrc/liquid_gemm/dequant.cu:39-43).
+__device__ __forceinline__ uint32_t lqq_dequant4(uint32_t codes, uint32_t step, uint32_t a_bcast) {
+  return (codes * step + a_bcast) ^ 0x80808080u;
+}
+
+// The output formula of every fused epilogue: two fp32 multiplies, left to right
+// (reference liquidgemm/quant.py:152, csrc/liquid_gemm/epilogue.cu:57).
+__device__ __forceinline__ float lqq_scale(int acc, float a_scale, float w_scale) {
+  return __fmul_rn(__fmul_rn(__int2float_rn(acc), a_scale), w_scale);
+}
+
+// Store one output element in the dtype selected by `out_dtype` (LQ_DT_*).
+__device__ __forceinline__ void store_out(void* y, size_t idx, float v, int out_dtype) {
+  if (out_dtype == LQ_DT_BF16) {
+    reinterpret_cast<__nv_bfloat16*>(y)[idx] = __float2bfloat16_rn(v);
+  } else if (out_dtype == LQ_DT_F16) {
+    reinterpret_cast<__half*>(y)[idx] = __float2half_rn(v);
+  } else {
+    reinterpret_cast<float*>(y)[idx] = v;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// memory
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint4 ldg_stream_v4(const void* p) {
+  uint4 r;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "l"(p));
+  return r;
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+}  // namespace lq

@@ -1,0 +1,489 @@
+"""``torch.ops.liquidgemm.*`` on B200, plus the Python entry points of liquidgemm/ops.py.
+
+Importing this module loads the C-ABI CUDA library and registers the ten operator schemas of
+the reference (csrc/liquid_gemm/torch_bindings.cpp:43-59) under the same ``liquidgemm``
+namespace, with fake (meta) kernels so that ``torch.compile`` and CUDA-graph capture work
+(reference liquidgemm/ops.py:16-65).  Each CUDA implementation validates its arguments in
+Python -- a bad call raises ``RuntimeError`` before anything reaches the GPU -- allocates its
+output (and split-K workspace) with torch, and calls one ``extern "C"`` function on the current
+stream.  No op synchronises and none falls back to PyTorch arithmetic.
+
+Like the reference, this module is not imported by the package ``__init__``
+(reference liquidgemm/ops.py:3-4).
+"""
+
+from __future__ import annotations
+
+import os
+
+import torch
+
+from . import _lib
+from ._lib import check, lib
+from .quant import LiquidQuantWeight
+from .pack import pack_nibbles
+
+_OUT_DTYPES = {0: torch.bfloat16, 1: torch.float16, 2: torch.float32}
+_DTYPE_CODES = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
+TILE_BYTES = 8704   # one 128x128 weight tile in the blob: 8192 nibble bytes + 512 metadata bytes
+
+# LIQUIDGEMM_SPLITK is read once per process, like the C++ static of the reference
+# (csrc/liquid_gemm/w4a8_wgmma.cu:524-527).
+try:
+    _SPLITK_ENV = max(0, int(os.environ.get("LIQUIDGEMM_SPLITK", "0") or 0))
+except ValueError:
+    _SPLITK_ENV = 0
+
+# --------------------------------------------------------------------------------------
+# schemas (verbatim operator signatures of the reference) and fake kernels
+# --------------------------------------------------------------------------------------
+_SCHEMAS = {
+    "dequant_weight": "(Tensor qweight, Tensor s_u8, Tensor offset_a, int N, int K, int group_size) -> Tensor",
+    "w4a8_gemm": "(Tensor X, Tensor qweight, Tensor s_u8, Tensor offset_a, Tensor s1, Tensor ascale, int N, int K, int group_size) -> Tensor",
+    "quant_per_token": "(Tensor x) -> Tensor[]",
+    "scale_epilogue": "(Tensor acc, Tensor ascale, Tensor s1, int out_dtype) -> Tensor",
+    "wgmma_i8_gemm": "(Tensor a, Tensor b) -> Tensor",
+    "w4a8_wgmma": "(Tensor x_i8, Tensor packed, Tensor s_u8, Tensor off_a, int N, int K, int group_size) -> Tensor",
+    "wgmma_rs_a_coords": "() -> Tensor",
+    "w4a8_wgmma_rs": "(Tensor x_i8, Tensor w, Tensor spack, Tensor s_u8, Tensor off_a, int N, int K, int group_size, bool packed) -> Tensor",
+    "w4a8_wgmma_rs_fused": "(Tensor x_i8, Tensor w, Tensor s_u8, Tensor off_a, Tensor ascale, Tensor s1, int N, int K, int group_size, int out_dtype) -> Tensor",
+    "w4a8_gemv2": "(Tensor x_i8, Tensor gpack, Tensor s_u8, Tensor off_a, Tensor ascale, Tensor s1, int N, int K, int group_size, int out_dtype) -> Tensor",
+    # additions of this library (no reference counterpart): INT8 GEMM with the fused scale epilogue
+    "i8_gemm_scaled": "(Tensor a, Tensor b, Tensor a_scale, Tensor b_scale, int out_dtype) -> Tensor",
+}
+
+_libdef = torch.library.Library("liquidgemm", "DEF")
+for _name, _sig in _SCHEMAS.items():
+    _libdef.define(_name + _sig)
+_impl = torch.library.Library("liquidgemm", "IMPL", "CUDA")
+
+
+def _req(cond: bool, msg: str) -> None:
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: torch.Tensor) -> int:
+    return t.data_ptr()
+
+
+def _dev_ctx(t: torch.Tensor):
+    return torch.cuda.device(t.device)
+
+
+@torch.library.register_fake("liquidgemm::dequant_weight")
+def _f_dequant(qweight, s_u8, offset_a, N, K, group_size):
+    return qweight.new_empty((N, K), dtype=torch.int8)
+
+
+@torch.library.register_fake("liquidgemm::w4a8_gemm")
+def _f_v1(X, qweight, s_u8, offset_a, s1, ascale, N, K, group_size):
+    return X.new_empty((X.shape[0], N), dtype=torch.float32)
+
+
+@torch.library.register_fake("liquidgemm::quant_per_token")
+def _f_qpt(x):
+    M, K = x.shape
+    return [x.new_empty((M, K), dtype=torch.int8), x.new_empty((M,), dtype=torch.float32)]
+
+
+@torch.library.register_fake("liquidgemm::scale_epilogue")
+def _f_epi(acc, ascale, s1, out_dtype):
+    return acc.new_empty(acc.shape, dtype=_OUT_DTYPES[int(out_dtype)])
+
+
+@torch.library.register_fake("liquidgemm::wgmma_i8_gemm")
+def _f_i8(a, b):
+    return a.new_empty((a.shape[0], b.shape[0]), dtype=torch.int32)
+
+
+@torch.library.register_fake("liquidgemm::i8_gemm_scaled")
+def _f_i8s(a, b, a_scale, b_scale, out_dtype):
+    return a.new_empty((a.shape[0], b.shape[0]), dtype=_OUT_DTYPES[int(out_dtype)])
+
+
+@torch.library.register_fake("liquidgemm::w4a8_wgmma")
+def _f_ss(x_i8, packed, s_u8, off_a, N, K, group_size):
+    return x_i8.new_empty((x_i8.shape[0], N), dtype=torch.int32)
+
+
+@torch.library.register_fake("liquidgemm::w4a8_wgmma_rs")
+def _f_rs(x_i8, w, spack, s_u8, off_a, N, K, group_size, packed):
+    return x_i8.new_empty((x_i8.shape[0], N), dtype=torch.int32)
+
+
+@torch.library.register_fake("liquidgemm::w4a8_wgmma_rs_fused")
+def _f_rsf(x_i8, w, s_u8, off_a, ascale, s1, N, K, group_size, out_dtype):
+    return x_i8.new_empty((x_i8.shape[0], N), dtype=_OUT_DTYPES[int(out_dtype)])
+
+
+@torch.library.register_fake("liquidgemm::w4a8_gemv2")
+def _f_gemv(x_i8, gpack, s_u8, off_a, ascale, s1, N, K, group_size, out_dtype):
+    return x_i8.new_empty((x_i8.shape[0], N), dtype=_OUT_DTYPES[int(out_dtype)])
+
+
+# --------------------------------------------------------------------------------------
+# CUDA implementations
+# --------------------------------------------------------------------------------------
+
+def _u8(t, name):
+    _req(t.is_cuda and t.dtype == torch.uint8, f"{name} must be a CUDA uint8 tensor")
+    return t.contiguous()
+
+
+def _f32(t, name):
+    _req(t.is_cuda and t.dtype == torch.float32, f"{name} must be a CUDA float32 tensor")
+    return t.contiguous()
+
+
+def _i8(t, name):
+    _req(t.is_cuda and t.dtype == torch.int8 and t.dim() == 2, f"{name} must be a 2-D CUDA int8 tensor")
+    return t.contiguous()
+
+
+def _dequant_weight(qweight, s_u8, offset_a, N, K, group_size):
+    _req(qweight.is_cuda, "qweight must be CUDA")
+    _req(qweight.dtype == torch.uint8, "qweight must be uint8")
+    _req(s_u8.dtype == torch.uint8 and offset_a.dtype == torch.uint8, "s_u8/offset_a must be uint8")
+    _req(K % 4 == 0, "K must be a multiple of 4")
+    _req(group_size > 0 and group_size % 4 == 0 and K % group_size == 0, "K must be a multiple of group_size")
+    _req(qweight.numel() == N * K, "qweight must hold N*K codes (one per byte)")
+    G = K // group_size
+    _req(s_u8.numel() == N * G and offset_a.numel() == N * G, "s_u8/offset_a must be [N, K/group_size]")
+    qweight, s_u8, offset_a = qweight.contiguous(), _u8(s_u8, "s_u8"), _u8(offset_a, "offset_a")
+    out = torch.empty((N, K), dtype=torch.int8, device=qweight.device)
+    with _dev_ctx(qweight):
+        check(lib.lq_dequant_weight(_ptr(qweight), _ptr(s_u8), _ptr(offset_a), _ptr(out), N, K, group_size,
+                                    _stream()), "dequant_weight")
+    return out
+
+
+def _quant_per_token(x):
+    _req(x.is_cuda and x.dim() == 2, "x must be 2D CUDA")
+    _req(x.dtype in _DTYPE_CODES, "x must be bfloat16, float16 or float32")
+    x = x.contiguous()
+    M, K = x.shape
+    xq = torch.empty((M, K), dtype=torch.int8, device=x.device)
+    ascale = torch.empty((M,), dtype=torch.float32, device=x.device)
+    if M:
+        with _dev_ctx(x):
+            check(lib.lq_quant_per_token(_ptr(x), _DTYPE_CODES[x.dtype], _ptr(xq), _ptr(ascale), M, K, _stream()),
+                  "quant_per_token")
+    return [xq, ascale]
+
+
+def _scale_epilogue(acc, ascale, s1, out_dtype):
+    _req(acc.is_cuda and acc.dim() == 2 and acc.dtype == torch.int32, "acc must be a 2-D CUDA int32 tensor")
+    _req(int(out_dtype) in _OUT_DTYPES, "out_dtype must be 0 (bf16), 1 (fp16) or 2 (fp32)")
+    acc, ascale, s1 = acc.contiguous(), _f32(ascale, "ascale"), _f32(s1, "s1")
+    M, N = acc.shape
+    _req(ascale.numel() == M and s1.numel() == N, "ascale must be [M] and s1 [N]")
+    y = torch.empty((M, N), dtype=_OUT_DTYPES[int(out_dtype)], device=acc.device)
+    if M:
+        with _dev_ctx(acc):
+            check(lib.lq_scale_epilogue(_ptr(acc), _ptr(ascale), _ptr(s1), _ptr(y), int(out_dtype), M, N, _stream()),
+                  "scale_epilogue")
+    return y
+
+
+def _gemv2(x_i8, gpack, s_u8, off_a, ascale, s1, N, K, group_size, out_dtype):
+    x_i8 = _i8(x_i8, "x_i8")
+    _req(gpack.dtype == torch.uint8 and group_size == 64, "gpack must be uint8 and group_size 64")
+    _req(K % 128 == 0, "gemv2 requires K % 128 == 0")
+    M = x_i8.shape[0]
+    _req(M <= 16, "gemv2 is the M<=16 decode path")
+    _req(x_i8.shape[1] == K and gpack.numel() == N * K // 2, "x_i8 must be [M,K] and gpack [N,K/2]")
+    _req(int(out_dtype) in _OUT_DTYPES, "out_dtype must be 0 (bf16), 1 (fp16) or 2 (fp32)")
+    gpack, s_u8, off_a = _u8(gpack, "gpack"), _u8(s_u8, "s_u8"), _u8(off_a, "off_a")
+    ascale, s1 = _f32(ascale, "ascale"), _f32(s1, "s1")
+    _req(s_u8.numel() == N * (K // 64) and off_a.numel() == N * (K // 64), "s_u8/off_a must be [N, K/64]")
+    _req(ascale.numel() == M and s1.numel() == N, "ascale must be [M] and s1 [N]")
+    y = torch.empty((M, N), dtype=_OUT_DTYPES[int(out_dtype)], device=x_i8.device)
+    if M:
+        with _dev_ctx(x_i8):
+            check(lib.lq_w4a8_gemv(_ptr(x_i8), _ptr(gpack), _ptr(s_u8), _ptr(off_a), _ptr(ascale), _ptr(s1), _ptr(y),
+                                   int(out_dtype), M, N, K, group_size, _stream()), "w4a8_gemv2")
+    return y
+
+
+def _splitk_for(M, N, K):
+    return lib.lq_gemm_pick_splitk(M, N, K, _SPLITK_ENV)
+
+
+def _workspace(M, N, K, S, device):
+    nbytes = lib.lq_gemm_workspace_bytes(M, N, K, S)
+    if nbytes == 0:
+        return None, 0
+    ws = torch.empty((nbytes,), dtype=torch.uint8, device=device)
+    return ws, nbytes
+
+
+def _check_blob(w, N, K):
+    _req(w.is_cuda and w.dtype == torch.uint8, "w must be a CUDA uint8 tensor")
+    need = lib.lq_tile_blob_bytes(N, K)
+    _req(need > 0 and w.numel() == need,
+         f"w must be the tile blob of repack_rs_weight for N={N}, K={K} ({need} bytes, got {w.numel()})")
+    return w.contiguous()
+
+
+def gemm_i32(x_i8, blob, N, K, splitk=0):
+    """Exact int32 accumulators from a tile blob; ``splitk=0`` picks the factor automatically."""
+    x_i8 = _i8(x_i8, "x_i8")
+    _req(K % 128 == 0 and x_i8.shape[1] == K, "K%128==0 required and x_i8 must be [M,K]")
+    blob = _check_blob(blob, N, K)
+    M = x_i8.shape[0]
+    acc = torch.empty((M, N), dtype=torch.int32, device=x_i8.device)
+    if M == 0:
+        return acc
+    S = splitk if splitk > 0 else _splitk_for(M, N, K)
+    S = max(1, min(S, K // 128))
+    ws, nbytes = _workspace(M, N, K, S, x_i8.device)
+    with _dev_ctx(x_i8):
+        check(lib.lq_w4a8_gemm_i32(_ptr(x_i8), _ptr(blob), _ptr(acc), M, N, K, S, _ptr(ws) if ws is not None else None,
+                                   nbytes, _stream()), "w4a8_gemm_i32")
+    return acc
+
+
+def gemm_fused(x_i8, blob, ascale, s1, N, K, out_dtype, splitk=0):
+    """Fused W4A8 linear from a tile blob; ``splitk=0`` picks the factor automatically."""
+    x_i8 = _i8(x_i8, "x_i8")
+    _req(K % 128 == 0 and x_i8.shape[1] == K, "K%128==0 required and x_i8 must be [M,K]")
+    _req(int(out_dtype) in _OUT_DTYPES, "out_dtype must be 0 (bf16), 1 (fp16) or 2 (fp32)")
+    blob = _check_blob(blob, N, K)
+    ascale, s1 = _f32(ascale, "ascale"), _f32(s1, "s1")
+    M = x_i8.shape[0]
+    _req(ascale.numel() == M and s1.numel() == N, "ascale must be [M] and s1 [N]")
+    y = torch.empty((M, N), dtype=_OUT_DTYPES[int(out_dtype)], device=x_i8.device)
+    if M == 0:
+        return y
+    S = splitk if splitk > 0 else _splitk_for(M, N, K)
+    S = max(1, min(S, K // 128))
+    ws, nbytes = _workspace(M, N, K, S, x_i8.device)
+    with _dev_ctx(x_i8):
+        check(lib.lq_w4a8_gemm_fused(_ptr(x_i8), _ptr(blob), _ptr(ascale), _ptr(s1), _ptr(y), int(out_dtype), M, N, K,
+                                     S, _ptr(ws) if ws is not None else None, nbytes, _stream()),
+              "w4a8_gemm_fused")
+    return y
+
+
+def _repack_device(src, layout, s_u8, off_a, N, K, group_size):
+    _req(K % 128 == 0, "K%128==0 required")
+    _req(group_size >= 64 and group_size % 64 == 0 and K % group_size == 0, "group_size must be a multiple of 64")
+    src, s_u8, off_a = _u8(src, "weights"), _u8(s_u8, "s_u8"), _u8(off_a, "off_a")
+    G = K // group_size
+    _req(s_u8.numel() == N * G and off_a.numel() == N * G, "s_u8/off_a must be [N, K/group_size]")
+    _req(src.numel() == (N * K if layout == 0 else N * K // 2), "weight tensor has the wrong number of bytes")
+    blob = torch.empty(((N + 127) // 128, K // 128, TILE_BYTES), dtype=torch.uint8, device=src.device)
+    with _dev_ctx(src):
+        check(lib.lq_repack_tiles(_ptr(src), layout, _ptr(s_u8), _ptr(off_a), _ptr(blob), N, K, group_size, _stream()),
+              "repack_tiles")
+    return blob
+
+
+def _wgmma_rs(x_i8, w, spack, s_u8, off_a, N, K, group_size, packed):
+    _req(w.dtype == torch.uint8 and group_size == 64, "w must be uint8 and group_size 64")
+    _req(N % 64 == 0 and K % 128 == 0, "N%64==0 and K%128==0 required")
+    if not packed:
+        # plain pack_nibbles layout: re-tile into scratch first (reference gathers per element,
+        # csrc/liquid_gemm/w4a8_wgmma.cu:424-434)
+        w = _repack_device(w, 1, s_u8, off_a, N, K, group_size)
+    return gemm_i32(x_i8, w.reshape(-1), N, K)
+
+
+def _wgmma_rs_fused(x_i8, w, s_u8, off_a, ascale, s1, N, K, group_size, out_dtype):
+    _req(w.dtype == torch.uint8 and group_size == 64, "w must be uint8 and group_size 64")
+    _req(N % 64 == 0 and K % 128 == 0, "N%64==0 and K%128==0 required")
+    return gemm_fused(x_i8, w.reshape(-1), ascale, s1, N, K, out_dtype)
+
+
+def _wgmma_ss(x_i8, packed, s_u8, off_a, N, K, group_size):
+    _req(group_size == 64, "group_size must be 64")
+    _req(K % 128 == 0, "K must be a multiple of 128")
+    blob = _repack_device(packed, 1, s_u8, off_a, N, K, group_size)
+    return gemm_i32(x_i8, blob.reshape(-1), N, K)
+
+
+def _wgmma_i8(a, b):
+    a, b = _i8(a, "a"), _i8(b, "b")
+    M, K = a.shape
+    N = b.shape[0]
+    _req(b.shape[1] == K, "K mismatch")
+    _req(K % 128 == 0, "K must be a multiple of 128")
+    c = torch.empty((M, N), dtype=torch.int32, device=a.device)
+    if M:
+        with _dev_ctx(a):
+            check(lib.lq_i8_gemm_i32(_ptr(a), _ptr(b), _ptr(c), M, N, K, _stream()), "wgmma_i8_gemm")
+    return c
+
+
+def _i8_gemm_scaled(a, b, a_scale, b_scale, out_dtype):
+    a, b = _i8(a, "a"), _i8(b, "b")
+    M, K = a.shape
+    N = b.shape[0]
+    _req(b.shape[1] == K and K % 128 == 0, "K mismatch or K not a multiple of 128")
+    _req(int(out_dtype) in _OUT_DTYPES, "out_dtype must be 0 (bf16), 1 (fp16) or 2 (fp32)")
+    a_scale, b_scale = _f32(a_scale, "a_scale").reshape(-1), _f32(b_scale, "b_scale").reshape(-1)
+    _req(a_scale.numel() == M and b_scale.numel() == N, "a_scale must have M and b_scale N elements")
+    y = torch.empty((M, N), dtype=_OUT_DTYPES[int(out_dtype)], device=a.device)
+    if M:
+        with _dev_ctx(a):
+            check(lib.lq_i8_gemm_scaled(_ptr(a), _ptr(b), _ptr(a_scale), _ptr(b_scale), _ptr(y), int(out_dtype), M, N,
+                                        K, _stream()), "i8_gemm_scaled")
+    return y
+
+
+def _gemm_v1(X, qweight, s_u8, offset_a, s1, ascale, N, K, group_size):
+    _req(X.is_cuda and qweight.is_cuda, "inputs must be CUDA")
+    _req(X.dtype == torch.int8, "X must be int8")
+    _req(qweight.dtype == torch.uint8, "qweight must be uint8 (nibble-packed)")
+    _req(s1.dtype == torch.float32 and ascale.dtype == torch.float32, "s1/ascale must be float32")
+    _req(group_size == 64, "v1 requires group_size == 64")
+    _req(K % group_size == 0 and K % 2 == 0, "bad K")
+    X, qweight = X.contiguous(), qweight.contiguous()
+    s_u8, offset_a, s1, ascale = _u8(s_u8, "s_u8"), _u8(offset_a, "offset_a"), s1.contiguous(), ascale.contiguous()
+    M = X.shape[0]
+    _req(M <= 16 or K % 128 == 0, "M > 16 requires K % 128 == 0")
+    y = torch.empty((M, N), dtype=torch.float32, device=X.device)
+    if M == 0:
+        return y
+    nbytes = lib.lq_gemm_v1_workspace_bytes(M, N, K)
+    ws = torch.empty((nbytes,), dtype=torch.uint8, device=X.device) if nbytes else None
+    with _dev_ctx(X):
+        check(lib.lq_w4a8_gemm_v1(_ptr(X), _ptr(qweight), _ptr(s_u8), _ptr(offset_a), _ptr(s1), _ptr(ascale), _ptr(y),
+                                  M, N, K, group_size, _ptr(ws) if ws is not None else None, nbytes, _stream()),
+              "w4a8_gemm")
+    return y
+
+
+def tile_coords() -> torch.Tensor:
+    """(row, k) of every code of a 128x128 weight tile in the order dequant thread ``r`` meets them.
+
+    int32 ``[128, 128, 2]``: entry ``[r, e]`` is the coordinate of the e-th value thread ``r``
+    writes to tensor memory (e = 32*chunk + 8*word + 4*half + lane).  Thread r always owns row r
+    and walks k in increasing order; the reference's op of the same name dumps the Hopper
+    register-fragment coordinates instead (csrc/liquid_gemm/w4a8_wgmma.cu:310-331).
+    """
+    r = torch.arange(128, dtype=torch.int32).view(128, 1).expand(128, 128)
+    k = torch.arange(128, dtype=torch.int32).view(1, 128).expand(128, 128)
+    return torch.stack([r, k], dim=-1).contiguous()
+
+
+def _coords():
+    t = tile_coords()
+    return t.cuda() if torch.cuda.is_available() else t
+
+
+_impl.impl("dequant_weight", _dequant_weight)
+_impl.impl("quant_per_token", _quant_per_token)
+_impl.impl("scale_epilogue", _scale_epilogue)
+_impl.impl("w4a8_gemv2", _gemv2)
+_impl.impl("w4a8_wgmma_rs", _wgmma_rs)
+_impl.impl("w4a8_wgmma_rs_fused", _wgmma_rs_fused)
+_impl.impl("w4a8_wgmma", _wgmma_ss)
+_impl.impl("wgmma_i8_gemm", _wgmma_i8)
+_impl.impl("i8_gemm_scaled", _i8_gemm_scaled)
+_impl.impl("w4a8_gemm", _gemm_v1)
+_libdef.impl("wgmma_rs_a_coords", _coords, "CompositeExplicitAutograd")
+
+
+# --------------------------------------------------------------------------------------
+# Python entry points (same names as liquidgemm/ops.py)
+# --------------------------------------------------------------------------------------
+
+def pack_gemv_interleaved(qw: LiquidQuantWeight) -> torch.Tensor:
+    """Row-major ``[N, K/2]`` pack for the GEMV: byte b of octet h is ``w[8h+b] | w[8h+4+b] << 4``
+    so that AND / SHR+AND leave four consecutive k in the byte lanes (reference liquidgemm/ops.py:68-75)."""
+    codes = qw.qweight_u4
+    n, k = codes.shape
+    halves = codes.reshape(n, k // 8, 2, 4)
+    return (halves[:, :, 0] | (halves[:, :, 1] << 4)).to(torch.uint8).reshape(n, k // 2).contiguous()
+
+
+def dequant_weight_i8(qw: LiquidQuantWeight) -> torch.Tensor:
+    """INT8 weights [N, K] reconstructed on the device (reference liquidgemm/ops.py:78-87)."""
+    return torch.ops.liquidgemm.dequant_weight(qw.qweight_u4.cuda(), qw.s_u8.cuda(), qw.offset_a.cuda(),
+                                               qw.N, qw.K, qw.group_size)
+
+
+def repack_rs_weight(qw: LiquidQuantWeight) -> torch.Tensor:
+    """Weight prepack for the tensor-core GEMM: uint8 ``[ceil(N/128), K/128, 8704]`` on the GPU.
+
+    Same role as the reference's fragment-order prepack (liquidgemm/ops.py:118-150) with a layout
+    made for B200: per 128x128 tile, four 32-k chunks of ``[128 rows][16 bytes]`` (interleaved
+    nibbles, so thread r's four shared loads are conflict free and unpack by mask/shift), then
+    ``[128 rows][step0, offset0, step1, offset1]``.  One tile is one contiguous bulk copy.
+    """
+    return _repack_device(qw.qweight_u4.cuda(), 0, qw.s_u8.cuda(), qw.offset_a.cuda(), qw.N, qw.K, qw.group_size)
+
+
+def build_rs_scale_pack(qw: LiquidQuantWeight) -> torch.Tensor:
+    """Per-tile (step, offset) words ``[ceil(N/128), K/128, 128, 4]`` as they sit inside the blob.
+
+    Kept for signature compatibility: the reference built a separate scale pack and then ignored
+    it (liquidgemm/ops.py:153-182, csrc/liquid_gemm/w4a8_wgmma.cu:404); here the words already
+    travel inside the tile blob, so the GEMM ops ignore this argument too.
+    """
+    n, k, g = qw.N, qw.K, qw.group_size
+    nt, kt = (n + 127) // 128, k // 128
+    halves = torch.arange(k // 64, device=qw.s_u8.device) * 64 // g          # group of every 64-k half tile
+    s = qw.s_u8[:, halves].view(n, kt, 2)
+    a = qw.offset_a[:, halves].view(n, kt, 2)
+    words = torch.stack([s[..., 0], a[..., 0], s[..., 1], a[..., 1]], dim=-1)  # [N, KT, 4]
+    out = torch.zeros((nt * 128, kt, 4), dtype=torch.uint8, device=words.device)
+    out[:, :, 0::2] = 1
+    out[:, :, 1::2] = 128
+    out[:n] = words
+    return out.view(nt, 128, kt, 4).permute(0, 2, 1, 3).contiguous()
+
+
+def w4a8_linear_unfused(x_i8, ascale, qw: LiquidQuantWeight, out_dtype: torch.dtype = torch.float16):
+    """Unfused pipeline: dequant kernel -> plain INT8 tensor-core GEMM -> scale epilogue.
+
+    Returns ``(y, acc)`` like the reference (liquidgemm/ops.py:90-115), which uses cuBLASLt for
+    the middle step; here all three steps are kernels of this library.
+    """
+    w_i8 = dequant_weight_i8(qw)
+    acc = torch.ops.liquidgemm.wgmma_i8_gemm(x_i8.cuda().contiguous(), w_i8)
+    y = torch.ops.liquidgemm.scale_epilogue(acc, ascale.cuda().contiguous(), qw.s1.cuda(), _DTYPE_CODES[out_dtype])
+    return y, acc
+
+
+def w4a8_gemm_rs(x_i8, ascale, qw: LiquidQuantWeight, rs_packed: torch.Tensor = None,
+                 out_dtype: torch.dtype = torch.float16):
+    """Tensor-core W4A8 linear, any M: int32 GEMM then the scale epilogue
+    (reference liquidgemm/ops.py:185-201)."""
+    if rs_packed is None:
+        w, packed = pack_nibbles(qw.qweight_u4).cuda().contiguous(), False
+    else:
+        w, packed = rs_packed.cuda(), True
+    acc = torch.ops.liquidgemm.w4a8_wgmma_rs(x_i8.cuda().contiguous(), w, qw.s_u8.cuda(), qw.s_u8.cuda(),
+                                             qw.offset_a.cuda(), qw.N, qw.K, qw.group_size, packed)
+    return torch.ops.liquidgemm.scale_epilogue(acc, ascale.cuda().contiguous(), qw.s1.cuda(), _DTYPE_CODES[out_dtype])
+
+
+def w4a8_gemm(x_i8, ascale, qw: LiquidQuantWeight, out_dtype: torch.dtype = torch.float16):
+    """Fused W4A8 linear from the plain nibble layout, float32 inside, cast on return
+    (reference liquidgemm/ops.py:204-215)."""
+    packed = pack_nibbles(qw.qweight_u4).cuda().contiguous()
+    y = torch.ops.liquidgemm.w4a8_gemm(x_i8.cuda().contiguous(), packed, qw.s_u8.cuda(), qw.offset_a.cuda(),
+                                       qw.s1.cuda(), ascale.cuda(), qw.N, qw.K, qw.group_size)
+    return y.to(out_dtype)
+
+
+def w4a8_linear(x: torch.Tensor, qw_dev: dict, out_dtype: torch.dtype = None) -> torch.Tensor:
+    """One W4A8 linear exactly as the vLLM method runs it: quantise tokens, then GEMV (M <= 16 and a
+    GEMV pack present) or the fused tensor-core GEMM (reference liquidgemm/vllm_plugin.py:183-196).
+
+    ``qw_dev`` holds device tensors ``s1, s_u8, offset_a, N, K`` and ``rs`` (tile blob) and/or ``gp``.
+    """
+    odt = _DTYPE_CODES[out_dtype or x.dtype]
+    x_i8, ascale = torch.ops.liquidgemm.quant_per_token(x)
+    if x_i8.shape[0] <= 16 and qw_dev.get("gp") is not None:
+        return torch.ops.liquidgemm.w4a8_gemv2(x_i8, qw_dev["gp"], qw_dev["s_u8"], qw_dev["offset_a"], ascale,
+                                               qw_dev["s1"], qw_dev["N"], qw_dev["K"], 64, odt)
+    return torch.ops.liquidgemm.w4a8_wgmma_rs_fused(x_i8, qw_dev["rs"], qw_dev["s_u8"], qw_dev["offset_a"], ascale,
+                                                    qw_dev["s1"], qw_dev["N"], qw_dev["K"], 64, odt)
