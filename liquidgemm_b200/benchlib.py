@@ -1,0 +1,191 @@
+"""Secondary measurements printed under ``extras`` by ``bench.py``.
+
+Everything here is timed on the device with CUDA events around CUDA-graph replays, walks rotating
+weight copies larger than L2, and uses seeded synthetic LQQ data generated on the device (timing
+does not depend on the values; parity is the test-suite's job).
+
+* ``sweep``   : per (shape, M) time of the W4A8 op, weight GB/s, TOPS, roofline fraction, and cuBLAS
+                bf16 (``x @ w.T``) on the same GPU -- the comparison the reference publishes
+                (bench/rs_bench.py:44, bench/RESULTS.md:218-224).
+* ``splitk``  : decode-tile GEMM M in {32, 64, 128} on down / gate_up for split-K 1, 2, 4, 8.
+* ``tp70b``   : Llama-3-70B-shape linears column-sharded along N over the ranks, 80 layers x 4
+                linears, with and without an NCCL all-gather of every output.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import ops
+
+SHAPES = {"qkv": (6144, 4096), "gate_up": (28672, 4096), "down": (4096, 14336)}
+SHAPES_70B = {"qkv": (10240, 8192), "o": (8192, 8192), "gate_up": (57344, 8192), "down": (8192, 28672)}
+INT8_DENSE_TOPS = 4500.0   # B200 datasheet, dense
+
+
+def device_lqq(N, K, seed, want_gp=True, want_rs=True):
+    """Random valid LQQ layer generated on the device: codes, steps 1..16, offsets with u <= 255."""
+    from .quant import LiquidQuantWeight
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    codes = torch.randint(0, 16, (N, K), dtype=torch.uint8, device="cuda", generator=g)
+    step = torch.randint(1, 17, (N, K // 64), dtype=torch.int32, device="cuda", generator=g)
+    off = (torch.rand((N, K // 64), device="cuda", generator=g) * (256 - 15 * step).float()).to(torch.int32)
+    off = torch.minimum(off, 255 - 15 * step)
+    s1 = torch.rand(N, device="cuda", generator=g) * 0.01 + 1e-4
+    qw = LiquidQuantWeight(codes, step.to(torch.uint8), off.to(torch.uint8), s1, 64)
+    out = {"s_u8": qw.s_u8, "offset_a": qw.offset_a, "s1": qw.s1, "N": N, "K": K}
+    if want_gp:
+        out["gp"] = ops.pack_gemv_interleaved(qw)
+    if want_rs:
+        out["rs"] = ops.repack_rs_weight(qw).reshape(-1)
+    return out
+
+
+def device_tokens(M, K, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    x = torch.randint(-127, 128, (M, K), dtype=torch.int8, device="cuda", generator=g)
+    sc = torch.rand(M, device="cuda", generator=g) * 0.02 + 0.01
+    return x, sc
+
+
+def graph_time_us(fn, n_items, reps=5):
+    """fn(i) enqueues one launch on weight copy i; returns microseconds per launch under graph replay."""
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        for i in range(min(n_items, 3)):
+            fn(i)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            for i in range(n_items):
+                fn(i)
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(s)
+        for _ in range(reps):
+            g.replay()
+        e1.record(s)
+        torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / (reps * n_items) * 1e3
+
+
+def linear_call(L, x, sc, M, splitk=0, out_dtype=0):
+    if M <= 16 and "gp" in L:
+        return torch.ops.liquidgemm.w4a8_gemv2(x, L["gp"], L["s_u8"], L["offset_a"], sc, L["s1"], L["N"], L["K"], 64,
+                                               out_dtype)
+    return ops.gemm_fused(x, L["rs"], sc, L["s1"], L["N"], L["K"], out_dtype, splitk=splitk)
+
+
+def algorithmic_bytes(M, N, K):
+    return N * K // 2 + 2 * N * K // 64 + 4 * N + M * K + 4 * M + M * N * 2
+
+
+def run_sweep(peaks, Ms=(1, 4, 8, 16, 32, 64, 128, 512, 2048, 8192)):
+    rows = []
+    for name, (N, K) in SHAPES.items():
+        C = max(3, -(-400_000_000 // (N * K // 2)))
+        layers = [device_lqq(N, K, seed=31 * c + len(name)) for c in range(C)]
+        Cb = max(3, -(-300_000_000 // (N * K * 2)))
+        wbf = [torch.randn(N, K, device="cuda", dtype=torch.bfloat16) for _ in range(Cb)]
+        for M in Ms:
+            x, sc = device_tokens(M, K, seed=M)
+            xb = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+            reps = 5 if M < 2048 else 2
+            t = graph_time_us(lambda i: linear_call(layers[i % C], x, sc, M), C, reps)
+            tb = graph_time_us(lambda i: torch.matmul(xb, wbf[i % Cb].t()), Cb, reps)
+            tops = 2.0 * M * N * K / t / 1e6
+            gbs = algorithmic_bytes(M, N, K) / t / 1e3
+            rows.append({"shape": name, "M": M, "us": round(t, 2), "weight_GBps": round(N * K / 2 / t / 1e3, 1),
+                         "alg_GBps": round(gbs, 1), "hbm_frac": round(gbs / peaks["hbm_gbs"], 3),
+                         "TOPS": round(tops, 1), "int8_frac_of_4500": round(tops / INT8_DENSE_TOPS, 3),
+                         "cublas_bf16_us": round(tb, 2), "speedup_vs_cublas_bf16": round(tb / t, 2),
+                         "kernel": "gemv" if M <= 16 else "tcgen05"})
+        del layers, wbf
+        torch.cuda.empty_cache()
+    return rows
+
+
+def run_splitk(peaks):
+    rows = []
+    for name in ("down", "gate_up"):
+        N, K = SHAPES[name]
+        C = max(3, -(-400_000_000 // (N * K // 2)))
+        layers = [device_lqq(N, K, seed=77 * c + 1, want_gp=False) for c in range(C)]
+        for M in (32, 64, 128):
+            x, sc = device_tokens(M, K, seed=M)
+            for S in (1, 2, 4, 8):
+                t = graph_time_us(lambda i: linear_call(layers[i % C], x, sc, M, splitk=S), C)
+                gbs = algorithmic_bytes(M, N, K) / t / 1e3
+                rows.append({"shape": name, "M": M, "splitk": S, "us": round(t, 2), "alg_GBps": round(gbs, 1),
+                             "hbm_frac": round(gbs / peaks["hbm_gbs"], 3)})
+        del layers
+        torch.cuda.empty_cache()
+    return rows
+
+
+def run_tp70b(world, rank, Ms=(1, 64, 2048), layers_in_stack=80, distinct_layers=3):
+    """80-layer stack of the four 70B-shape linears, each column-sharded along N over `world` ranks."""
+    import torch.distributed as dist
+    rows = []
+    names = list(SHAPES_70B)
+    stack = []
+    for l in range(distinct_layers):
+        stack.append({n: device_lqq(SHAPES_70B[n][0] // world, SHAPES_70B[n][1], seed=1000 * rank + 10 * l + i)
+                      for i, n in enumerate(names)})
+    for M in Ms:
+        toks = {n: device_tokens(M, SHAPES_70B[n][1], seed=M + i) for i, n in enumerate(names)}
+        gathered = {n: torch.empty((world, M, SHAPES_70B[n][0] // world), dtype=torch.bfloat16, device="cuda")
+                    for n in names}
+
+        def one_stack(gather):
+            for l in range(layers_in_stack):
+                lay = stack[l % distinct_layers]
+                for n in names:
+                    y = linear_call(lay[n], toks[n][0], toks[n][1], M)
+                    if gather and world > 1:
+                        dist.all_gather_into_tensor(gathered[n], y)
+
+        res = {"M": M}
+        for gather in ((False, True) if world > 1 else (False,)):
+            s = torch.cuda.Stream()
+            with torch.cuda.stream(s):
+                one_stack(gather)
+                torch.cuda.synchronize()
+                use_graph = True
+                try:
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=s):
+                        one_stack(gather)
+                    run = g.replay
+                except Exception:
+                    use_graph = False
+                    run = lambda: one_stack(gather)
+                run()
+                if world > 1:
+                    dist.barrier()
+                torch.cuda.synchronize()
+                reps = 3
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(s)
+                for _ in range(reps):
+                    run()
+                e1.record(s)
+                torch.cuda.synchronize()
+                ms = e0.elapsed_time(e1) / reps
+            t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            res["stack_ms_gather" if gather else "stack_ms_no_gather"] = round(float(t[0]), 3)
+            res["graph"] = use_graph
+        rows.append(res)
+    return rows
+
+
+def run_extras(world, rank, local_rank, peaks):
+    out = {}
+    if world == 1:
+        out["sweep"] = run_sweep(peaks)
+        out["splitk"] = run_splitk(peaks)
+    out["tp70b"] = {"ranks": world, "layers": 80, "rows": run_tp70b(world, rank)}
+    return out

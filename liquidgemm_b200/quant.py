@@ -54,6 +54,11 @@ class LiquidQuantWeight:
                                  self.offset_a.to(device), self.s1.to(device), self.group_size)
 
 
+def _const(like: torch.Tensor, value: float) -> torch.Tensor:
+    """0-dim float32 tensor on the device of ``like`` (see the note on division in quantize_weight)."""
+    return torch.tensor(float(value), dtype=torch.float32, device=like.device)
+
+
 def quantize_weight(W: torch.Tensor, group_size: int = 64) -> LiquidQuantWeight:
     """Quantise ``W`` [N, K] (reference liquidgemm/quant.py:61-100)."""
     if W.dim() != 2:
@@ -64,8 +69,10 @@ def quantize_weight(W: torch.Tensor, group_size: int = 64) -> LiquidQuantWeight:
     n_groups = n_cols // group_size
     w32 = W.detach().to(torch.float32)
 
-    # level 1: one symmetric scale per output channel
-    row_scale = w32.abs().amax(dim=1).clamp_min(1e-12) / INT8_PROTECTIVE_MAX
+    # level 1: one symmetric scale per output channel.  The divisor is a tensor on purpose: torch's
+    # CUDA kernels turn division by a Python scalar into a multiplication by its reciprocal, which
+    # can differ from the CPU result in the last bit; tensor / tensor is an IEEE division everywhere.
+    row_scale = w32.abs().amax(dim=1).clamp_min(1e-12) / _const(w32, INT8_PROTECTIVE_MAX)
     q8 = torch.round(w32 / row_scale.unsqueeze(1))
     q8 = q8.clamp_(-INT8_PROTECTIVE_MAX, INT8_PROTECTIVE_MAX).to(torch.int32)
 
@@ -73,7 +80,9 @@ def quantize_weight(W: torch.Tensor, group_size: int = 64) -> LiquidQuantWeight:
     grouped = q8.view(n_rows, n_groups, group_size)
     g_lo = grouped.amin(dim=2)
     g_hi = grouped.amax(dim=2)
-    step = torch.ceil((g_hi - g_lo).to(torch.float32) / UINT4_MAX).clamp_(1, S_U8_MAX).to(torch.int32)
+    # ceil(range / 15) in integers: identical to the float form for 0 <= range <= 238, on any device
+    step = torch.div(g_hi - g_lo + (UINT4_MAX - 1), UINT4_MAX, rounding_mode="floor").clamp_(1, S_U8_MAX)
+    step = step.to(torch.int32)
     codes = torch.round((grouped - g_lo.unsqueeze(2)).to(torch.float32) / step.unsqueeze(2).to(torch.float32))
     codes = codes.clamp_(0, UINT4_MAX).to(torch.int32)
     offset = (g_lo + 128).to(torch.int32)
@@ -126,7 +135,7 @@ def quantize_activation(X: torch.Tensor):
     if X.dim() != 2:
         raise AssertionError("expected [M, K]")
     x32 = X.detach().to(torch.float32)
-    ascale = x32.abs().amax(dim=1).clamp_min(1e-12) / 127.0
+    ascale = x32.abs().amax(dim=1).clamp_min(1e-12) / _const(x32, 127.0)
     x_i8 = torch.round(x32 / ascale.unsqueeze(1)).clamp_(-127, 127).to(torch.int8)
     return x_i8, ascale.to(torch.float32)
 

