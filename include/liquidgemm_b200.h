@@ -80,15 +80,21 @@ LQ_API int lq_scale_epilogue(const int32_t* acc, const float* ascale, const floa
 
 /* Decode GEMV, M <= 16: y = scale_epilogue(x_i8 @ q_hat^T) straight from the row-major
  * interleaved pack of liquidgemm/ops.py:68-75.  Requires K % 128 == 0 and group_size == 64.
- * Replaces torch.ops.liquidgemm.w4a8_gemv2 (reference csrc/liquid_gemm/gemv2.cu:82-120). */
+ * Replaces torch.ops.liquidgemm.w4a8_gemv2 (reference csrc/liquid_gemm/gemv2.cu:82-120).
+ * lq_w4a8_gemv_variant is the same call with the kernel forced (1 = dp4a, 2 = mma.sync): a
+ * tuning hook for the dispatch table, without a reference counterpart. */
 LQ_API int lq_w4a8_gemv(const int8_t* x_i8, const uint8_t* gpack, const uint8_t* s_u8,
                  const uint8_t* offset_a, const float* ascale, const float* s1, void* y,
                  int out_dtype, int M, int N, int K, int group_size, void* stream);
+LQ_API int lq_w4a8_gemv_variant(const int8_t* x_i8, const uint8_t* gpack, const uint8_t* s_u8,
+                         const uint8_t* offset_a, const float* ascale, const float* s1, void* y,
+                         int out_dtype, int M, int N, int K, int variant, void* stream);
 
 /* Same product from the plain pack_nibbles() layout with float32 output, any M.
  * Replaces torch.ops.liquidgemm.w4a8_gemm (reference csrc/liquid_gemm/w4a8_gemm.cu:183-227).
- * M <= 16 runs the GEMV; larger M repacks into `workspace` (lq_gemm_v1_workspace_bytes) and runs
- * the tensor-core kernel.  K % 128 == 0, group_size % 64 == 0. */
+ * M <= 16 runs the GEMV (K % 64 == 0); larger M re-tiles the weights into `workspace`
+ * (scratch of lq_gemm_v1_workspace_bytes, need not be zeroed) and runs the tensor-core kernel
+ * (K % 128 == 0).  group_size must be 64, as in the reference. */
 LQ_API size_t lq_gemm_v1_workspace_bytes(int M, int N, int K);
 LQ_API int lq_w4a8_gemm_v1(const int8_t* x_i8, const uint8_t* nibbles, const uint8_t* s_u8,
                     const uint8_t* offset_a, const float* s1, const float* ascale, float* y,
@@ -107,11 +113,20 @@ LQ_API int lq_repack_tiles(const uint8_t* src, int src_layout, const uint8_t* s_
                     const uint8_t* offset_a, uint8_t* blob, int N, int K, int group_size,
                     void* stream);
 
-/* Split-K factor the GEMM uses for (M,N,K) when the caller passes splitk = 0.
- * `env_override` carries LIQUIDGEMM_SPLITK (0 = unset); like the reference
- * (csrc/liquid_gemm/w4a8_wgmma.cu:523-534) it only applies to M <= 128 and is clamped to K/128. */
+/* Scheduling of the tensor-core GEMM, selected by the `splitk` argument of the calls below:
+ *   0      stream-K: one persistent CTA per SM, the k-steps of all output tiles are dealt out in
+ *          equal contiguous ranges; tiles cut by a range boundary are reduced through the workspace;
+ *   1      whole tiles only (no reduction, no workspace);
+ *   S > 1  every tile is cut into S equal k-ranges (the split-K factor of the reference,
+ *          csrc/liquid_gemm/w4a8_wgmma.cu:523-534), reduced through the workspace.
+ * Partial sums are int32 and added with atomics, so every setting gives bit-identical results.
+ * lq_gemm_pick_splitk maps LIQUIDGEMM_SPLITK (`env_override`, 0 = unset) to that argument: like
+ * the reference the override only applies to M <= 128 and is clamped to K/128; otherwise 0. */
 LQ_API int lq_gemm_pick_splitk(int M, int N, int K, int env_override);
-/* Bytes of int32 partial planes needed for `splitk` (0 when splitk <= 1). */
+/* Workspace bytes for (M,N,K,splitk).  The workspace must be ALL ZERO when a GEMM call starts and
+ * is all zero again when its kernel ends (the kernel cleans up after itself), so one zero-filled
+ * buffer can serve any number of successive calls on a stream; calls that overlap on the GPU need
+ * separate buffers.  After a LQ_ERR_TIMEOUT the buffer must be cleared by the caller. */
 LQ_API size_t lq_gemm_workspace_bytes(int M, int N, int K, int splitk);
 
 /* W4A8 tensor-core GEMM, exact int32 accumulators acc[M,N] = x_i8 @ q_hat^T.
@@ -126,6 +141,16 @@ LQ_API int lq_w4a8_gemm_i32(const int8_t* x_i8, const uint8_t* blob, int32_t* ac
 LQ_API int lq_w4a8_gemm_fused(const int8_t* x_i8, const uint8_t* blob, const float* ascale,
                        const float* s1, void* y, int out_dtype, int M, int N, int K, int splitk,
                        void* workspace, size_t workspace_bytes, void* stream);
+
+/* The same fused GEMM reading the weights in the row-major interleaved GEMV pack
+ * (liquidgemm/ops.py:68-75: [N, K/2]) with the standard [N, K/64] step / offset arrays, i.e. one
+ * weight format for every M.  No direct reference counterpart (the reference keeps two packs,
+ * liquidgemm/vllm_plugin.py:153-164); it backs torch.ops.liquidgemm.w4a8_gemv2 for the token counts
+ * where tensor cores beat dp4a.  K % 128 == 0, group_size 64. */
+LQ_API int lq_w4a8_gemm_rowmajor(const int8_t* x_i8, const uint8_t* gpack, const uint8_t* s_u8,
+                          const uint8_t* offset_a, const float* ascale, const float* s1, void* y,
+                          int out_dtype, int M, int N, int K, int splitk, void* workspace,
+                          size_t workspace_bytes, void* stream);
 
 /* Plain INT8 x INT8 -> INT32 tensor-core GEMM c[M,N] = a[M,K] @ b[N,K]^T.
  * Replaces torch.ops.liquidgemm.wgmma_i8_gemm (reference csrc/liquid_gemm/w4a8_wgmma.cu:648-694).

@@ -30,6 +30,8 @@ _SIGNATURES = {
     "lq_quant_per_token": (c_int, [P, c_int, P, P, c_int, c_int, P]),
     "lq_scale_epilogue": (c_int, [P, P, P, P, c_int, c_int, c_int, P]),
     "lq_w4a8_gemv": (c_int, [P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P]),
+    "lq_w4a8_gemv_variant": (c_int, [P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P]),
+    "lq_w4a8_gemm_rowmajor": (c_int, [P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, c_size_t, P]),
     "lq_gemm_v1_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "lq_w4a8_gemm_v1": (c_int, [P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, P, c_size_t, P]),
     "lq_tile_blob_bytes": (c_size_t, [c_int, c_int]),

@@ -70,7 +70,7 @@ def graph_time_us(fn, n_items, reps=5):
     return e0.elapsed_time(e1) / (reps * n_items) * 1e3
 
 
-def linear_call(L, x, sc, M, splitk=0, out_dtype=0):
+def linear_call(L, x, sc, M, splitk=None, out_dtype=0):
     if M <= 16 and "gp" in L:
         return torch.ops.liquidgemm.w4a8_gemv2(x, L["gp"], L["s_u8"], L["offset_a"], sc, L["s1"], L["N"], L["K"], 64,
                                                out_dtype)
@@ -114,7 +114,7 @@ def run_splitk(peaks):
         layers = [device_lqq(N, K, seed=77 * c + 1, want_gp=False) for c in range(C)]
         for M in (32, 64, 128):
             x, sc = device_tokens(M, K, seed=M)
-            for S in (1, 2, 4, 8):
+            for S in (0, 1, 2, 4, 8):
                 t = graph_time_us(lambda i: linear_call(layers[i % C], x, sc, M, splitk=S), C)
                 gbs = algorithmic_bytes(M, N, K) / t / 1e3
                 rows.append({"shape": name, "M": M, "splitk": S, "us": round(t, 2), "alg_GBps": round(gbs, 1),

@@ -1,32 +1,40 @@
-// W4A8 tensor-core GEMM for sm_100a: TMA -> in-register LQQ dequant -> TMEM -> tcgen05.mma kind::i8.
+// W4A8 tensor-core GEMM for sm_100a: TMA -> in-register LQQ dequant -> TMEM -> tcgen05.mma kind::i8,
+// as one persistent, warp-specialised kernel with stream-K scheduling.
 //
-// Orientation.  The weights are the MMA "A" operand (128 output channels per CTA, the full
-// tensor-core M), the tokens are the "B" operand (BN = 16..256 per CTA, the MMA N), so small
+// Orientation.  The weights are the MMA "A" operand (128 output channels per tile, the full
+// tensor-core M), the tokens are the "B" operand (BN = 16..256 per tile, the MMA N), so small
 // token counts waste nothing on the 128-wide dimension: Y^T[n, m] = sum_k q_hat[n, k] * x[m, k].
 //
-// One CTA = 6 warps with fixed roles, connected by mbarrier rings:
-//   warp 0      producer : one thread issues, per 128-k step, one bulk copy of the 8704-byte
-//                          weight tile (nibbles + per-row step/offset pairs, contiguous in the
-//                          blob) and one tiled TMA load of the BN x 128 activation box
-//                          (128-byte swizzle; token rows past M are zero-filled by the TMA unit).
-//   warps 2..5  dequant  : thread r owns weight row r of the tile.  It reads its 64 bytes of
-//                          nibbles (4 conflict-free 16-byte shared loads) and its two
-//                          (step, offset) pairs, reconstructs 128 INT8 values with
-//                          AND / SHR+AND + multiply-add + XOR on 32-bit words, and writes them with
-//                          tcgen05.st into TMEM lane r (4 consecutive k per 32-bit column),
-//                          which is exactly the layout tcgen05.mma expects for an A operand
-//                          taken from tensor memory.
-//   warp 1      MMA      : one thread issues four 128 x BN x 32 tcgen05.mma per step (A from
-//                          TMEM, B through a shared-memory descriptor), accumulating int32 in
-//                          TMEM, and commits to the barriers that recycle the stages.
-//   warps 2..5  epilogue : tcgen05.ld of the accumulators (lane = output channel, column = token),
-//                          then either int32 stores (exact accumulators / split-K partial
-//                          planes) or (float)acc * ascale[m] * s1[n] and the cast.
-// Dequant of step i+1..i+NT-1 overlaps the MMAs of step i (NT TMEM operand stages), and the
-// TMA ring runs NS steps ahead of both.
+// Work.  An output tile is 128 channels x BN tokens; it needs KT = K/128 "k-steps".  The grid is
+// one CTA per SM.  All T*KT k-steps of the problem are laid end to end (tile-major) and cut into
+// equal contiguous ranges, one per CTA ("stream-K"): every SM streams the same number of weight
+// bytes whatever the tile count, which is what a bandwidth-bound decode GEMM needs, and prefill
+// loses nothing to wave quantisation.  A CTA's range is a sequence of segments (tile, k-range).
+// A segment that covers its tile's whole K is finished by that CTA alone.  Otherwise the CTA adds
+// its int32 partial sums into a per-tile workspace slot with red.global.add (integer addition is
+// exact in any order, so the result is bit-identical however the tile was cut); the CTA whose
+// contribution completes the tile (a per-slot k-step counter reaches KT) reads the sums back,
+// applies the epilogue and re-zeroes slot and counter, so the workspace is all-zero again when
+// the kernel ends.  A fixed split-K factor can be requested instead (tile = S equal k-ranges).
 //
-// The same kernel with W4 = false takes INT8 weights through a second tensor map and issues the
-// shared-memory form of the MMA; that is the plain INT8 GEMM entry point.
+// Roles inside a CTA (12 warps), connected by mbarrier rings:
+//   warp 0       producer : one thread issues, per k-step, the weight tile (one 8704-byte bulk
+//                           copy from the tile blob, or a tensor-map box from the row-major
+//                           layouts) and the BN x 128 activation box (128-byte swizzle; token rows
+//                           past M are zero-filled by the TMA unit).
+//   warps 4..7   dequant  : thread r owns weight row r of the tile: 64 bytes of nibbles (four
+//                           conflict-free 16-byte shared loads) + two (step, offset) pairs ->
+//                           128 INT8 values by AND / SHR+AND, multiply-add, XOR on 32-bit words ->
+//                           tcgen05.st into TMEM lane r, 4 consecutive k per 32-bit column, which
+//                           is the layout tcgen05.mma reads an A operand from tensor memory in.
+//   warp 1       MMA      : one thread issues four 128 x BN x 32 tcgen05.mma per k-step (A from
+//                           TMEM, B through a shared-memory descriptor) into one of NACC
+//                           accumulators, and commits to the barriers that recycle the stages.
+//   warps 8..11  epilogue : tcgen05.ld (lane = channel, column = token) of a finished
+//                           accumulator while the MMAs of the next segment fill the other one;
+//                           (float)acc * ascale[m] * s1[n] + cast, int32 stores, or the partial
+//                           reduction described above.
+// The TMA ring runs NS k-steps ahead, the dequantised operand ring NT k-steps ahead of the MMAs.
 //
 // Every wait is bounded: when a barrier does not complete within kWaitLimitNs the thread writes
 // a site code to the status word, leaves its loop, and the CTA still reaches the common exit
@@ -40,48 +48,148 @@
 
 namespace lq {
 
-int launch_finish(const int32_t* acc, const float* ascale, const float* s1, void* y, int out_dtype,
-                  int planes, int M, int N, cudaStream_t st);  // lq_elementwise.cu
 int launch_gemv_plain_f32(const int8_t* x, const uint8_t* nibbles, const uint8_t* s_u8,
                           const uint8_t* off_a, const float* ascale, const float* s1, float* y, int M,
                           int N, int K, int G, cudaStream_t st);  // lq_gemv.cu
 
 constexpr int kTileBytes = 8704;     // weight tile in the blob: 8192 nibble bytes + 512 metadata bytes
 constexpr int kI8TileBytes = 16384;  // INT8 weight tile: 128 rows x 128 bytes
-constexpr int kThreads = 192;
+constexpr int kRowBoxBytes = 8192;   // row-major nibble box: 128 rows x 64 bytes
+constexpr int kThreads = 384;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
-constexpr int kOutI32 = 3;           // internal output mode: raw int32 (plane z of acc_out)
+constexpr int kOutI32 = 3;           // internal output mode: raw int32
+
+enum WeightSource { kBlob = 0, kRowMajor = 1, kInt8 = 2 };
 
 struct GemmArgs {
-  const uint8_t* blob;   // W4: tile blob
-  const float* ascale;   // [M]
-  const float* s1;       // [N]
-  void* out;             // scaled output [M,N] or int32 planes [splits][M][N]
+  const uint8_t* blob;     // kBlob: tile blob
+  const uint8_t* s_u8;     // kRowMajor: [N, K/64] steps
+  const uint8_t* off_a;    // kRowMajor: [N, K/64] offsets
+  const float* ascale;     // [M]
+  const float* s1;         // [N]
+  void* out;               // [M, N] in out_mode's type
+  int32_t* slots;          // workspace: per-slot 128 x BN int32 partial sums (all zero between launches)
+  int32_t* counters;       // workspace: per-slot k-steps received so far (all zero between launches)
   int* status;
-  int out_mode;          // LQ_DT_* or kOutI32
+  int out_mode;            // LQ_DT_* or kOutI32
   int M, N, K;
-  int kt_total;          // K / 128
+  int kt_total;            // K / 128
+  int n_tiles, m_tiles;
+  int fixed_split;         // 0: stream-K ranges; S >= 1: every tile is cut into S equal k-ranges
+  long long* trace;        // optional per-CTA cycle counters (32 per CTA) for pipeline studies, or null
+  int debug_skip;          // pipeline studies only (results become wrong): 1 = no tcgen05.st,
+                           // 2 = no epilogue global writes, 4 = no tcgen05.mma, 8 = no activation TMA
 };
 
-template <int BN, int NS, int NT, bool W4>
+// Trace slots (cycles relative to the CTA's first instruction, or accumulated waits).
+enum TraceSlot {
+  kTrSetupDone = 1, kTrFirstTma = 2, kTrLastTma = 3, kTrDeqFirst = 4, kTrDeqLast = 5, kTrMmaFirst = 6,
+  kTrMmaLast = 7, kTrEpiFirst = 8, kTrEpiLast = 9, kTrExit = 10, kTrEpiWhole = 11, kTrEpiPartial = 12,
+  kTrMmaWaitA = 13, kTrMmaWaitFull = 14, kTrMmaWaitAcc = 15, kTrDeqWaitFull = 16, kTrDeqWaitFree = 17,
+  kTrProdWaitEmpty = 18, kTrEpiWaitAcc = 19, kTrSegments = 20, kTrKsteps = 21, kTrDeqCompute = 22,
+  kTrProdIssue = 23, kTrMmaIssue = 24,
+};
+#define LQ_TRACE(slot, value) do { if (args.trace) args.trace[(size_t)blockIdx.x * 32 + (slot)] = (value); } while (0)
+
+template <int BN, int NS, int NT, int NACC, int WSRC>
 struct TcCfg {
   static constexpr int kXStage = BN * 128;
-  static constexpr int kWStage = W4 ? kTileBytes : kI8TileBytes;
-  static constexpr int kAccCols = BN;
-  static constexpr int kACols = W4 ? 32 * NT : 0;
-  static constexpr int kColsNeeded = kAccCols + kACols;
+  static constexpr int kWStage = WSRC == kBlob ? kTileBytes : WSRC == kRowMajor ? kRowBoxBytes : kI8TileBytes;
+  static constexpr int kACols = WSRC == kInt8 ? 0 : 32 * NT;
+  static constexpr int kColsNeeded = NACC * BN + kACols;
   static constexpr int kTmemCols = kColsNeeded <= 32 ? 32 : kColsNeeded <= 64 ? 64 : kColsNeeded <= 128 ? 128
                                    : kColsNeeded <= 256 ? 256 : 512;
-  static constexpr int kBarBytes = (2 * NS + 2 * NT + 1) * 8 + 8;
-  static constexpr int kSmemBytes = 1024 /* alignment slack */ + NS * (kXStage + kWStage) + kBarBytes + BN * 4;
+  static constexpr int kNumBars = 2 * NS + 2 * NT + 2 * NACC;
+  static constexpr int kBarBytes = kNumBars * 8 + 16;
+  static constexpr int kSmemBytes = 1024 /* alignment slack */ + NS * (kXStage + kWStage) + kBarBytes;
   static_assert(kColsNeeded <= 512, "tensor memory budget exceeded");
+  static_assert(kSmemBytes <= 232448, "shared memory budget exceeded");
+  static_assert(kSmemBytes > 116 * 1024, "one CTA per SM is assumed (tensor memory is allocated whole)");
 };
 
-template <int BN, int NS, int NT, bool W4>
+// One unit of a CTA's work: k-steps [kb, ke) of output tile `tile`.
+struct Segment {
+  int tile, kb, ke, slot;
+  bool whole;   // covers the tile's full K: no cross-CTA reduction
+};
+
+// Enumerates the segments of this CTA; every role walks the same sequence.  32-bit arithmetic
+// throughout (tiles * k-steps stays far below 2^31 for any problem that fits the GPU).
+struct SegmentWalk {
+  int kt, split, grid;
+  unsigned u, u_end;   // stream-K: current / last k-step of the range
+  unsigned q, r;       // stream-K: base range length and number of CTAs with one extra k-step
+  unsigned w, w_end;   // fixed split: current / last work item
+
+  __device__ SegmentWalk(const GemmArgs& a, unsigned cta, unsigned grid_) {
+    kt = a.kt_total;
+    split = a.fixed_split;
+    grid = (int)grid_;
+    const unsigned tiles = (unsigned)(a.n_tiles * a.m_tiles);
+    if (split == 0) {
+      const unsigned total = tiles * (unsigned)kt;
+      q = total / grid_;
+      r = total - q * grid_;
+      u = cta * q + (cta < r ? cta : r);
+      u_end = u + q + (cta < r ? 1u : 0u);
+      w = w_end = 0;
+    } else {
+      w = cta;
+      w_end = tiles * (unsigned)split;
+      u = u_end = q = r = 0;
+    }
+  }
+  __device__ int owner_of(unsigned unit) const {   // CTA whose stream-K range contains `unit`
+    const unsigned big = r * (q + 1);
+    return unit < big ? (int)(unit / (q + 1)) : (int)(r + (unit - big) / q);
+  }
+  __device__ bool next(Segment& s) {
+    if (split == 0) {
+      if (u >= u_end) return false;
+      s.tile = (int)(u / (unsigned)kt);
+      s.kb = (int)(u - (unsigned)s.tile * (unsigned)kt);
+      const int left = (int)(u_end - u);
+      s.ke = (kt - s.kb) < left ? kt : s.kb + left;
+      s.whole = (s.kb == 0 && s.ke == kt);
+      s.slot = s.whole ? 0 : owner_of((unsigned)s.tile * (unsigned)kt);
+      u += (unsigned)(s.ke - s.kb);
+      return true;
+    }
+    if (w >= w_end) return false;
+    s.tile = (int)(w / (unsigned)split);
+    const int si = (int)(w - (unsigned)s.tile * (unsigned)split);
+    s.kb = (si * kt) / split;
+    s.ke = ((si + 1) * kt) / split;
+    s.whole = (split == 1);
+    s.slot = s.tile;
+    w += (unsigned)grid;
+    return true;
+  }
+};
+
+// Position in a ring of N stages: stage index and the parity of the pass over the ring.
+template <int N>
+struct Ring {
+  int s = 0;
+  uint32_t ph = 0;
+  __device__ __forceinline__ void advance() {
+    if (++s == N) {
+      s = 0;
+      ph ^= 1u;
+    }
+  }
+};
+
+__device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+#define LQ_CLK() (tracing ? clock64() : 0ll)
+
+template <int BN, int NS, int NT, int NACC, int WSRC>
 __global__ void __launch_bounds__(kThreads, 1)
 w4a8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                const GemmArgs args) {
-  using Cfg = TcCfg<BN, NS, NT, W4>;
+  using Cfg = TcCfg<BN, NS, NT, NACC, WSRC>;
+  constexpr bool kDequant = WSRC != kInt8;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -89,199 +197,452 @@ w4a8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
 
   const uint32_t xs = base;                                  // NS activation stages (1024-aligned)
   const uint32_t ws = xs + NS * Cfg::kXStage;                // NS weight stages
-  const uint32_t bars = ws + NS * Cfg::kWStage;              // barriers
-  const uint32_t bar_full = bars;                            // [NS] TMA landed
-  const uint32_t bar_empty = bars + NS * 8;                  // [NS] stage may be overwritten
-  const uint32_t bar_aready = bars + 2 * NS * 8;             // [NT] dequantised operand in TMEM
-  const uint32_t bar_afree = bars + (2 * NS + NT) * 8;       // [NT] MMAs that read the operand are done
-  const uint32_t bar_acc = bars + (2 * NS + 2 * NT) * 8;     // accumulators final
-  const uint32_t tmem_slot = bar_acc + 8;
-  uint8_t* gen = smem + (bars - base);
-  volatile uint32_t* tmem_slot_p = reinterpret_cast<volatile uint32_t*>(gen + (2 * NS + 2 * NT + 1) * 8);
-  float* ascale_s = reinterpret_cast<float*>(gen + Cfg::kBarBytes);
+  const uint32_t bars = ws + NS * Cfg::kWStage;
+  const uint32_t bar_full = bars;                            // [NS] both TMA copies of the stage landed
+  const uint32_t bar_empty = bar_full + NS * 8;              // [NS] stage may be overwritten
+  const uint32_t bar_aready = bar_empty + NS * 8;            // [NT] dequantised operand is in TMEM
+  const uint32_t bar_afree = bar_aready + NT * 8;            // [NT] MMAs that read the operand are done
+  const uint32_t bar_accfull = bar_afree + NT * 8;           // [NACC] accumulator final
+  const uint32_t bar_accempty = bar_accfull + NACC * 8;      // [NACC] accumulator drained
+  const uint32_t tmem_slot = bar_accempty + NACC * 8;
+  uint8_t* gen_bars = smem + (bars - base);
+  volatile uint32_t* tmem_slot_p = reinterpret_cast<volatile uint32_t*>(gen_bars + Cfg::kNumBars * 8);
+  volatile int* last_flag = reinterpret_cast<volatile int*>(gen_bars + Cfg::kNumBars * 8 + 4);
+  volatile int* wait_flag = reinterpret_cast<volatile int*>(gen_bars + Cfg::kNumBars * 8 + 8);  // [2]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int nt = blockIdx.x, mt = blockIdx.y, z = blockIdx.z, splits = gridDim.z;
-  const int kt_begin = (int)(((long)z * args.kt_total) / splits);
-  const int kt_end = (int)(((long)(z + 1) * args.kt_total) / splits);
-  const int nk = kt_end - kt_begin;
-  const int m0 = mt * BN;
+  const bool tracing = args.trace != nullptr;
+  const long long t_begin = LQ_CLK();
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < NS; ++s) {
-      ptx::mbar_init(bar_full + 8 * s, 1);
-      ptx::mbar_init(bar_empty + 8 * s, W4 ? 129 : 1);
+      ptx::mbar_init(bar_full + 8 * s, 2);                   // one expect_tx arrival per producer thread
+      ptx::mbar_init(bar_empty + 8 * s, kDequant ? 129 : 1);
     }
     for (int t = 0; t < NT; ++t) {
       ptx::mbar_init(bar_aready + 8 * t, 128);
       ptx::mbar_init(bar_afree + 8 * t, 1);
     }
-    ptx::mbar_init(bar_acc, 1);
+    for (int b = 0; b < NACC; ++b) {
+      ptx::mbar_init(bar_accfull + 8 * b, 1);
+      ptx::mbar_init(bar_accempty + 8 * b, 128);
+    }
     ptx::fence_mbar_init();
     ptx::prefetch_tensormap(&tmap_x);
-    if (!W4) ptx::prefetch_tensormap(&tmap_w);
+    if (WSRC != kBlob) ptx::prefetch_tensormap(&tmap_w);
   }
   if (warp == 1) {
     ptx::tmem_alloc(tmem_slot, Cfg::kTmemCols);
     ptx::tmem_relinquish();
   }
-  if (warp >= 2 && args.out_mode != kOutI32) {
-    for (int j = threadIdx.x - 64; j < BN; j += 128) ascale_s[j] = (m0 + j < args.M) ? args.ascale[m0 + j] : 0.f;
-  }
   ptx::tc_fence_before();
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_p;
-  const uint32_t tmem_acc = tmem_base;             // columns [0, BN)
-  const uint32_t tmem_a = tmem_base + BN;          // NT operand stages of 32 columns
+  const uint32_t tmem_a = tmem_base + NACC * BN;   // NT operand stages of 32 columns behind the accumulators
+  if (threadIdx.x == 0) LQ_TRACE(kTrSetupDone, LQ_CLK() - t_begin);
 
-  if (warp == 0) {
-    // ------------------------------------------------------------------ producer
+  if (warp == 0 || warp == 2) {
+    // ------------------------------------------------------------------ producers
+    // warp 0 streams the weight tiles, warp 2 the activation boxes; each thread waits for the
+    // stage to be free and announces its own byte count on the stage's full barrier.
     if (lane == 0) {
-      constexpr uint32_t kTx = Cfg::kXStage + Cfg::kWStage;
+      const bool weights = (warp == 0);
+      SegmentWalk walk(args, blockIdx.x, gridDim.x);
+      Segment sg;
+      Ring<NS> ring;
       int issued = 0;
       bool ok = true;
-      for (int i = 0; i < nk; ++i) {
-        const int s = i % NS;
-        const uint32_t ph = (uint32_t)(i / NS) & 1u;
-        if (!ptx::mbar_wait_bounded(bar_empty + 8 * s, ph ^ 1u, kWaitLimitNs)) {
-          atomicExch(args.status, 101);
-          ok = false;
-          break;
+      long long w_empty = 0, t_issue = 0;
+      while (ok && walk.next(sg)) {
+        const int nt = sg.tile % args.n_tiles, mt = sg.tile / args.n_tiles;
+        const uint8_t* wsrc = WSRC == kBlob ? args.blob + ((size_t)nt * args.kt_total + sg.kb) * kTileBytes : nullptr;
+        for (int kt = sg.kb; kt < sg.ke; ++kt) {
+          const long long tw0 = LQ_CLK();
+          if (!ptx::mbar_wait_bounded(bar_empty + 8 * ring.s, ring.ph ^ 1u, kWaitLimitNs)) {
+            atomicExch(args.status, 101);
+            ok = false;
+            break;
+          }
+          const long long ti0 = LQ_CLK();
+          w_empty += ti0 - tw0;
+          if (issued == 0 && weights) LQ_TRACE(kTrFirstTma, ti0 - t_begin);
+          const uint32_t full = bar_full + 8 * ring.s;
+          if (weights) {
+            ptx::mbar_expect_tx(full, Cfg::kWStage);
+            if (WSRC == kBlob) {
+              ptx::bulk_load(ws + ring.s * Cfg::kWStage, wsrc, kTileBytes, full);
+              wsrc += kTileBytes;
+            } else if (WSRC == kRowMajor) {
+              ptx::tensor_load_2d(ws + ring.s * Cfg::kWStage, &tmap_w, kt * 64, nt * 128, full);
+            } else {
+              ptx::tensor_load_2d(ws + ring.s * Cfg::kWStage, &tmap_w, kt * 128, nt * 128, full);
+            }
+          } else {
+            ptx::mbar_expect_tx(full, Cfg::kXStage);
+            ptx::tensor_load_2d(xs + ring.s * Cfg::kXStage, &tmap_x, kt * 128, mt * BN, full);
+          }
+          t_issue += LQ_CLK() - ti0;
+          ring.advance();
+          ++issued;
         }
-        ptx::mbar_expect_tx(bar_full + 8 * s, kTx);
-        const int kt = kt_begin + i;
-        if (W4) {
-          const uint8_t* src = args.blob + ((size_t)nt * args.kt_total + kt) * kTileBytes;
-          ptx::bulk_load(ws + s * Cfg::kWStage, src, kTileBytes, bar_full + 8 * s);
-        } else {
-          ptx::tensor_load_2d(ws + s * Cfg::kWStage, &tmap_w, kt * 128, nt * 128, bar_full + 8 * s);
-        }
-        ptx::tensor_load_2d(xs + s * Cfg::kXStage, &tmap_x, kt * 128, m0, bar_full + 8 * s);
-        ++issued;
+      }
+      if (weights) {
+        LQ_TRACE(kTrLastTma, LQ_CLK() - t_begin);
+        LQ_TRACE(kTrProdWaitEmpty, w_empty);
+        LQ_TRACE(kTrProdIssue, t_issue);
+        LQ_TRACE(kTrKsteps, issued);
       }
       if (!ok) {
         // copies already issued still write shared memory: let them land before the CTA exits
-        for (int i = issued > NS ? issued - NS : 0; i < issued; ++i)
-          ptx::mbar_wait_bounded(bar_full + 8 * (i % NS), (uint32_t)(i / NS) & 1u, kWaitLimitNs);
+        Ring<NS> back;
+        const int first = issued > NS ? issued - NS : 0;
+        for (int i = 0; i < issued; ++i) {
+          if (i >= first) ptx::mbar_wait_bounded(bar_full + 8 * back.s, back.ph, kWaitLimitNs);
+          back.advance();
+        }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issue
     if (lane == 0) {
       constexpr uint32_t idesc = ptx::idesc_i8(BN);
-      bool ok = true;
-      for (int i = 0; i < nk && ok; ++i) {
-        const int s = i % NS;
-        const uint32_t ph = (uint32_t)(i / NS) & 1u;
-        const int t = i % NT;
-        const uint32_t pht = (uint32_t)(i / NT) & 1u;
-        ok = ptx::mbar_wait_bounded(bar_full + 8 * s, ph, kWaitLimitNs);
-        if (ok && W4) ok = ptx::mbar_wait_bounded(bar_aready + 8 * t, pht, kWaitLimitNs);
-        if (!ok) {
-          atomicExch(args.status, 102);
+      SegmentWalk walk(args, blockIdx.x, gridDim.x);
+      Segment sg;
+      Ring<NS> ring;
+      Ring<NT> aring;
+      Ring<NACC> accring;
+      int seg = 0;
+      bool ok = true, first = true;
+      long long w_a = 0, w_full = 0, w_acc = 0, t_mma = 0;
+      while (ok && walk.next(sg)) {
+        const long long ta0 = LQ_CLK();
+        if (!ptx::mbar_wait_bounded(bar_accempty + 8 * accring.s, accring.ph ^ 1u, kWaitLimitNs)) {
+          atomicExch(args.status, 106);
+          ok = false;
           break;
         }
+        w_acc += LQ_CLK() - ta0;
         ptx::tc_fence_after();
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const uint64_t bdesc = ptx::smem_desc_sw128(xs + s * Cfg::kXStage + j * 32);
-          const uint32_t accumulate = (i > 0 || j > 0) ? 1u : 0u;
-          if (W4) {
-            ptx::mma_i8_ts(tmem_acc, tmem_a + t * 32 + j * 8, bdesc, idesc, accumulate);
-          } else {
-            const uint64_t adesc = ptx::smem_desc_sw128(ws + s * Cfg::kWStage + j * 32);
-            ptx::mma_i8_ss(tmem_acc, adesc, bdesc, idesc, accumulate);
+        const uint32_t tmem_acc = tmem_base + accring.s * BN;
+        for (int kt = sg.kb; kt < sg.ke; ++kt) {
+          const long long tf0 = LQ_CLK();
+          ok = ptx::mbar_wait_bounded(bar_full + 8 * ring.s, ring.ph, kWaitLimitNs);
+          const long long tf1 = LQ_CLK();
+          if (ok && kDequant) ok = ptx::mbar_wait_bounded(bar_aready + 8 * aring.s, aring.ph, kWaitLimitNs);
+          const long long tm0 = LQ_CLK();
+          w_full += tf1 - tf0;
+          w_a += tm0 - tf1;
+          if (!ok) {
+            atomicExch(args.status, 102);
+            break;
           }
+          if (first) {
+            LQ_TRACE(kTrMmaFirst, tm0 - t_begin);
+            first = false;
+          }
+          ptx::tc_fence_after();
+          const uint32_t xb = xs + ring.s * Cfg::kXStage;
+          if (!(args.debug_skip & 4)) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint64_t bdesc = ptx::smem_desc_sw128(xb + j * 32);
+              const uint32_t accumulate = (kt > sg.kb || j > 0) ? 1u : 0u;
+              if (kDequant) {
+                ptx::mma_i8_ts(tmem_acc, tmem_a + aring.s * 32 + j * 8, bdesc, idesc, accumulate);
+              } else {
+                const uint64_t adesc = ptx::smem_desc_sw128(ws + ring.s * Cfg::kWStage + j * 32);
+                ptx::mma_i8_ss(tmem_acc, adesc, bdesc, idesc, accumulate);
+              }
+            }
+          }
+          ptx::tc_commit(bar_empty + 8 * ring.s);
+          if (kDequant) ptx::tc_commit(bar_afree + 8 * aring.s);
+          t_mma += LQ_CLK() - tm0;
+          ring.advance();
+          aring.advance();
         }
-        ptx::tc_commit(bar_empty + 8 * s);
-        if (W4) ptx::tc_commit(bar_afree + 8 * t);
+        if (ok) ptx::tc_commit(bar_accfull + 8 * accring.s);
+        accring.advance();
+        ++seg;
       }
-      if (ok) ptx::tc_commit(bar_acc);
+      LQ_TRACE(kTrMmaLast, LQ_CLK() - t_begin);
+      LQ_TRACE(kTrMmaWaitA, w_a);
+      LQ_TRACE(kTrMmaWaitFull, w_full);
+      LQ_TRACE(kTrMmaWaitAcc, w_acc);
+      LQ_TRACE(kTrSegments, seg);
+      LQ_TRACE(kTrMmaIssue, t_mma);
     }
-  } else {
-    // ------------------------------------------------------------------ dequant, then epilogue
-    const int quad = warp & 3;               // TMEM lane quadrant this warp may access
-    const int row = quad * 32 + lane;        // weight row inside the tile == TMEM lane
-    const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
-    bool ok = true;
-    if (W4) {
-      for (int i = 0; i < nk; ++i) {
-        const int s = i % NS;
-        const uint32_t ph = (uint32_t)(i / NS) & 1u;
-        const int t = i % NT;
-        const uint32_t pht = (uint32_t)(i / NT) & 1u;
-        if (!ptx::mbar_wait_bounded(bar_full + 8 * s, ph, kWaitLimitNs)) {
-          atomicExch(args.status, 103);
-          ok = false;
-          break;
-        }
-        const uint8_t* wst = smem + (ws - base) + s * Cfg::kWStage;
-        uint4 ch[4];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) ch[c] = *reinterpret_cast<const uint4*>(wst + (c * 128 + row) * 16);
-        const uint32_t meta = *reinterpret_cast<const uint32_t*>(wst + 8192 + row * 4);
-        ptx::mbar_arrive(bar_empty + 8 * s);
-
-        if (!ptx::mbar_wait_bounded(bar_afree + 8 * t, pht ^ 1u, kWaitLimitNs)) {
-          atomicExch(args.status, 104);
-          ok = false;
-          break;
-        }
-        ptx::tc_fence_after();
-        const uint32_t step0 = meta & 0xffu, a0 = ((meta >> 8) & 0xffu) * 0x01010101u;
-        const uint32_t step1 = (meta >> 16) & 0xffu, a1 = (meta >> 24) * 0x01010101u;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const uint32_t step = c < 2 ? step0 : step1;
-          const uint32_t ab = c < 2 ? a0 : a1;
-          const uint32_t pk[4] = {ch[c].x, ch[c].y, ch[c].z, ch[c].w};
-          uint32_t v[8];
-#pragma unroll
-          for (int h = 0; h < 4; ++h) {
-            v[2 * h] = lqq_dequant4(pk[h] & 0x0F0F0F0Fu, step, ab);
-            v[2 * h + 1] = lqq_dequant4((pk[h] >> 4) & 0x0F0F0F0Fu, step, ab);
+  } else if (warp >= 4 && warp < 8) {
+    // ------------------------------------------------------------------ dequant
+    if (kDequant) {
+      const int quad = warp & 3;               // TMEM lane quadrant this warp may access
+      const int row = quad * 32 + lane;        // weight row inside the tile == TMEM lane
+      const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
+      const int G = args.K >> 6;
+      SegmentWalk walk(args, blockIdx.x, gridDim.x);
+      Segment sg;
+      Ring<NS> ring;
+      Ring<NT> aring;
+      int pending = -1;                        // operand stage whose tcgen05.st are still in flight
+      bool ok = true, first = true;
+      long long w_full = 0, w_free = 0, t_comp = 0;
+      const bool tracer = (threadIdx.x == 128);
+      while (ok && walk.next(sg)) {
+        const int nt = sg.tile % args.n_tiles;
+        const long n = (long)nt * 128 + row;
+        const bool n_ok = n < args.N;
+        for (int kt = sg.kb; kt < sg.ke; ++kt) {
+          uint32_t meta = 0x80008000u;   // step 0, offset 128: reconstructs to zero
+          if (WSRC == kRowMajor && n_ok) {
+            const uint32_t sp = *reinterpret_cast<const uint16_t*>(args.s_u8 + n * G + 2 * kt);
+            const uint32_t op = *reinterpret_cast<const uint16_t*>(args.off_a + n * G + 2 * kt);
+            meta = (sp & 0xffu) | ((op & 0xffu) << 8) | ((sp >> 8) << 16) | ((op >> 8) << 24);
           }
-          ptx::tmem_st8(tmem_a + lane_addr + t * 32 + c * 8, v);
+          const long long td0 = LQ_CLK();
+          if (!ptx::mbar_wait_bounded(bar_full + 8 * ring.s, ring.ph, kWaitLimitNs)) {
+            atomicExch(args.status, 103);
+            ok = false;
+            break;
+          }
+          const long long td1 = LQ_CLK();
+          w_full += td1 - td0;
+          if (first && tracer) LQ_TRACE(kTrDeqFirst, td1 - t_begin);
+          first = false;
+          const uint8_t* wst = smem + (ws - base) + ring.s * Cfg::kWStage;
+          uint4 ch[4];
+          if (WSRC == kBlob) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) ch[c] = *reinterpret_cast<const uint4*>(wst + (c * 128 + row) * 16);
+            meta = *reinterpret_cast<const uint32_t*>(wst + 8192 + row * 4);
+          } else {
+            // 64-byte rows stored with the 64-byte swizzle: 16-byte chunk c of row r sits at
+            // chunk position c ^ ((r >> 1) & 3)
+            const int sw = (row >> 1) & 3;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) ch[c] = *reinterpret_cast<const uint4*>(wst + row * 64 + ((c ^ sw) << 4));
+          }
+          // The stores of the previous k-step have had the barrier wait and the shared loads above
+          // to complete: publish that operand stage now.
+          if (pending >= 0) {
+            ptx::tc_wait_st();
+            ptx::tc_fence_before();
+            ptx::mbar_arrive(bar_aready + 8 * pending);
+          }
+          ptx::mbar_arrive(bar_empty + 8 * ring.s);   // after the loads above have returned their data
+
+          const long long td2 = LQ_CLK();
+          if (!ptx::mbar_wait_bounded(bar_afree + 8 * aring.s, aring.ph ^ 1u, kWaitLimitNs)) {
+            atomicExch(args.status, 104);
+            ok = false;
+            pending = -1;
+            break;
+          }
+          const long long td3 = LQ_CLK();
+          w_free += td3 - td2;
+          ptx::tc_fence_after();
+          const uint32_t step0 = meta & 0xffu, a0 = ((meta >> 8) & 0xffu) * 0x01010101u;
+          const uint32_t step1 = (meta >> 16) & 0xffu, a1 = (meta >> 24) * 0x01010101u;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const uint32_t step = c < 2 ? step0 : step1;
+            const uint32_t ab = c < 2 ? a0 : a1;
+            const uint32_t pk[4] = {ch[c].x, ch[c].y, ch[c].z, ch[c].w};
+            uint32_t v[8];
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+              v[2 * h] = lqq_dequant4(pk[h] & 0x0F0F0F0Fu, step, ab);
+              v[2 * h + 1] = lqq_dequant4((pk[h] >> 4) & 0x0F0F0F0Fu, step, ab);
+            }
+            if (!(args.debug_skip & 1)) ptx::tmem_st8(tmem_a + lane_addr + aring.s * 32 + c * 8, v);
+          }
+          pending = aring.s;
+          t_comp += LQ_CLK() - td3;
+          ring.advance();
+          aring.advance();
         }
+      }
+      if (pending >= 0) {
         ptx::tc_wait_st();
         ptx::tc_fence_before();
-        ptx::mbar_arrive(bar_aready + 8 * t);
+        ptx::mbar_arrive(bar_aready + 8 * pending);
+      }
+      if (tracer) {
+        LQ_TRACE(kTrDeqLast, LQ_CLK() - t_begin);
+        LQ_TRACE(kTrDeqWaitFull, w_full);
+        LQ_TRACE(kTrDeqWaitFree, w_free);
+        LQ_TRACE(kTrDeqCompute, t_comp);
       }
     }
-    if (ok && !ptx::mbar_wait_bounded(bar_acc, 0u, kWaitLimitNs)) {
-      atomicExch(args.status, 105);
-      ok = false;
-    }
-    if (ok) {
+  } else if (warp >= 8) {
+    // ------------------------------------------------------------------ epilogue
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
+    const int et = threadIdx.x - 256;          // 0..127 inside the epilogue group
+    SegmentWalk walk(args, blockIdx.x, gridDim.x);
+    Segment sg;
+    Ring<NACC> accring;
+    int seg = 0;
+    bool ok = true;
+    long long w_acc = 0, t_whole = 0, t_part = 0;
+    while (ok && walk.next(sg)) {
+      const int b = accring.s;
+      const uint32_t phb = accring.ph;
+      accring.advance();
+      const long long te0 = LQ_CLK();
+      // One thread performs the bounded wait and publishes the outcome, so that the 128 threads
+      // always agree on it (they meet at named barriers below and must never split up).
+      const int fslot = seg & 1;
+      ++seg;
+      if (et == 0) {
+        const bool done = ptx::mbar_wait_bounded(bar_accfull + 8 * b, phb, kWaitLimitNs);
+        if (!done) atomicExch(args.status, 105);
+        wait_flag[fslot] = done ? 1 : 0;
+      }
+      epilogue_barrier();
+      if (wait_flag[fslot] == 0) {
+        ok = false;
+        break;
+      }
       ptx::tc_fence_after();
+      const long long te1 = LQ_CLK();
+      w_acc += te1 - te0;
+      if (seg == 1 && et == 0) LQ_TRACE(kTrEpiFirst, te1 - t_begin);
+      const int nt = sg.tile % args.n_tiles, mt = sg.tile / args.n_tiles;
+      const int m0 = mt * BN;
       const long n = (long)nt * 128 + row;
-      const bool n_ok = n < args.N;
-      const float w_scale = (n_ok && args.out_mode != kOutI32) ? args.s1[n] : 0.f;
-      int32_t* plane = reinterpret_cast<int32_t*>(args.out) + (size_t)z * args.M * args.N;
+      const bool n_ok = n < args.N && !(args.debug_skip & 2);
+      const int cols = (args.M - m0) < BN ? (args.M - m0) : BN;   // valid token columns of this tile
+      const uint32_t tmem_acc = tmem_base + b * BN + lane_addr;
+      const float w_scale = (n_ok && args.out_mode != kOutI32) ? __ldg(args.s1 + n) : 0.f;
+      if (sg.whole) {
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 16) {
-        if (m0 + c0 >= args.M) break;  // uniform over the CTA
-        int v[16];
-        ptx::tmem_ld16(tmem_acc + lane_addr + c0, v);
-        ptx::tc_wait_ld();
-        if (n_ok) {
+        for (int c0 = 0; c0 < cols; c0 += 16) {
+          int v[16];
+          ptx::tmem_ld16(tmem_acc + c0, v);
+          // token scales of the chunk, fetched while the tensor-memory load is in flight
+          float sc[16];
+          if (args.out_mode != kOutI32) {
+            if (c0 + 16 <= cols) {
+              const float4* sp = reinterpret_cast<const float4*>(args.ascale + m0 + c0);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int m = m0 + c0 + j;
-            if (m < args.M) {
-              const size_t idx = (size_t)m * args.N + n;
-              if (args.out_mode == kOutI32) plane[idx] = v[j];
-              else store_out(args.out, idx, lqq_scale(v[j], ascale_s[c0 + j], w_scale), args.out_mode);
+              for (int q4 = 0; q4 < 4; ++q4) {
+                const float4 f = __ldg(sp + q4);
+                sc[4 * q4] = f.x; sc[4 * q4 + 1] = f.y; sc[4 * q4 + 2] = f.z; sc[4 * q4 + 3] = f.w;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) sc[j] = (c0 + j < cols) ? __ldg(args.ascale + m0 + c0 + j) : 0.f;
+            }
+          }
+          ptx::tc_wait_ld();
+          if (c0 + 16 >= cols) {          // last chunk read: the MMA warp may reuse the accumulator
+            ptx::tc_fence_before();
+            ptx::mbar_arrive(bar_accempty + 8 * b);
+          }
+          if (n_ok) {
+            const size_t idx0 = (size_t)(m0 + c0) * args.N + n;
+            if (args.out_mode == kOutI32) {
+              int32_t* o = reinterpret_cast<int32_t*>(args.out) + idx0;
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (c0 + j < cols) o[(size_t)j * args.N] = v[j];
+            } else if (args.out_mode == LQ_DT_BF16) {
+              __nv_bfloat16 r[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) r[j] = __float2bfloat16_rn(lqq_scale(v[j], sc[j], w_scale));
+              __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(args.out) + idx0;
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (c0 + j < cols) o[(size_t)j * args.N] = r[j];
+            } else if (args.out_mode == LQ_DT_F16) {
+              __half r[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) r[j] = __float2half_rn(lqq_scale(v[j], sc[j], w_scale));
+              __half* o = reinterpret_cast<__half*>(args.out) + idx0;
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (c0 + j < cols) o[(size_t)j * args.N] = r[j];
+            } else {
+              float r[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) r[j] = lqq_scale(v[j], sc[j], w_scale);
+              float* o = reinterpret_cast<float*>(args.out) + idx0;
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (c0 + j < cols) o[(size_t)j * args.N] = r[j];
             }
           }
         }
+      } else {
+        int32_t* slot = args.slots + (size_t)sg.slot * (128 * BN);
+#pragma unroll 1
+        for (int c0 = 0; c0 < cols; c0 += 16) {
+          int v[16];
+          ptx::tmem_ld16(tmem_acc + c0, v);
+          ptx::tc_wait_ld();
+          if (c0 + 16 >= cols) {
+            ptx::tc_fence_before();
+            ptx::mbar_arrive(bar_accempty + 8 * b);
+          }
+          if (n_ok) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (c0 + j < cols) atomicAdd(slot + (c0 + j) * 128 + row, v[j]);
+          }
+        }
+        __threadfence();
+        epilogue_barrier();
+        if (et == 0) {
+          const int add = sg.ke - sg.kb;
+          const int before = atomicAdd(args.counters + sg.slot, add);
+          *last_flag = (before + add == args.kt_total) ? 1 : 0;
+        }
+        epilogue_barrier();
+        const bool last = *last_flag != 0;
+        epilogue_barrier();                      // everyone has read the flag before it can be rewritten
+        if (last) {
+          __threadfence();
+          if (n_ok) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < cols; c0 += 16) {
+              int v[16];
+              float sc[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {       // all loads of the chunk first: one L2 round trip
+                int32_t* p = slot + (c0 + j) * 128 + row;
+                v[j] = (c0 + j < cols) ? __ldcg(p) : 0;
+                sc[j] = (c0 + j < cols && args.out_mode != kOutI32) ? __ldg(args.ascale + m0 + c0 + j) : 0.f;
+              }
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                if (c0 + j < cols) {
+                  __stcg(slot + (c0 + j) * 128 + row, 0);
+                  const size_t idx = (size_t)(m0 + c0 + j) * args.N + n;
+                  if (args.out_mode == kOutI32) reinterpret_cast<int32_t*>(args.out)[idx] = v[j];
+                  else store_out(args.out, idx, lqq_scale(v[j], sc[j], w_scale), args.out_mode);
+                }
+              }
+            }
+          }
+          if (et == 0) args.counters[sg.slot] = 0;
+        }
       }
+      if (sg.whole) t_whole += LQ_CLK() - te1;
+      else t_part += LQ_CLK() - te1;
+    }
+    if (et == 0) {
+      LQ_TRACE(kTrEpiLast, LQ_CLK() - t_begin);
+      LQ_TRACE(kTrEpiWhole, t_whole);
+      LQ_TRACE(kTrEpiPartial, t_part);
+      LQ_TRACE(kTrEpiWaitAcc, w_acc);
     }
   }
 
   ptx::tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) LQ_TRACE(kTrExit, LQ_CLK() - t_begin);
   if (warp == 1) {
     __syncwarp();
     ptx::tc_fence_after();
@@ -309,20 +670,22 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// Tensor map over a row-major int8 matrix [rows, K] with a (box_rows x 128-byte) box, 128-byte
-// swizzle and zero fill for out-of-range rows.
-static int make_rowmajor_i8_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
+// Tensor map over a row-major byte matrix [rows, row_bytes] with a (box_rows x box_bytes) box whose
+// rows are stored with the swizzle that matches their length; rows out of range read as zero.
+static int make_byte_matrix_map(CUtensorMap* map, const void* ptr, long rows, long row_bytes, int box_rows,
+                                int box_bytes) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) {
     record_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled entry point not found");
     return LQ_ERR_CUDA;
   }
-  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)K};
-  const cuuint32_t box[2] = {128u, (cuuint32_t)box_rows};
+  const cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
+  const cuuint32_t box[2] = {(cuuint32_t)box_bytes, (cuuint32_t)box_rows};
   const cuuint32_t estr[2] = {1u, 1u};
+  const CUtensorMapSwizzle sw = box_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     record_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled failed");
@@ -331,10 +694,46 @@ static int make_rowmajor_i8_map(CUtensorMap* map, const void* ptr, int rows, int
   return LQ_OK;
 }
 
-template <int BN, int NS, int NT, bool W4>
-static int launch_cfg(const CUtensorMap& tx, const CUtensorMap& tw, const GemmArgs& a, int splits, cudaStream_t st) {
-  using Cfg = TcCfg<BN, NS, NT, W4>;
-  auto kern = &w4a8_tc_kernel<BN, NS, NT, W4>;
+static long long* g_trace_ptr = nullptr;   // set by lq_debug_set_trace (pipeline studies only)
+static int g_debug_skip = 0;
+
+static int pick_bn(int M) {
+  if (M <= 16) return 16;
+  if (M <= 32) return 32;
+  if (M <= 64) return 64;
+  if (M <= 128) return 128;
+  return 192;
+}
+
+struct Plan {
+  int bn, n_tiles, m_tiles, grid, fixed_split;
+  long tiles;
+  size_t slots, ws_bytes;
+};
+
+// splitk: 0 = stream-K over one CTA per SM, 1 = whole tiles only, S > 1 = every tile cut into S ranges.
+static Plan make_plan(int M, int N, int K, int splitk) {
+  Plan p;
+  p.bn = pick_bn(M);
+  p.n_tiles = (N + 127) / 128;
+  p.m_tiles = (M + p.bn - 1) / p.bn;
+  p.tiles = (long)p.n_tiles * p.m_tiles;
+  const int kt = K / 128;
+  const int sms = sm_count();
+  if (splitk > kt) splitk = kt;
+  p.fixed_split = splitk < 0 ? 0 : splitk;
+  const long units = p.fixed_split == 0 ? p.tiles * kt : p.tiles * p.fixed_split;
+  p.grid = (int)(units < sms ? units : sms);
+  p.slots = p.fixed_split == 0 ? (size_t)p.grid : p.fixed_split == 1 ? 0 : (size_t)p.tiles;
+  // slots of 128 x BN int32 followed by one counter per slot (padded to 256 bytes)
+  p.ws_bytes = p.slots == 0 ? 0 : p.slots * (size_t)(128 * p.bn * 4) + ((p.slots * 4 + 255) / 256) * 256;
+  return p;
+}
+
+template <int BN, int NS, int NT, int NACC, int WSRC>
+static int launch_cfg(const CUtensorMap& tx, const CUtensorMap& tw, const GemmArgs& a, int grid, cudaStream_t st) {
+  using Cfg = TcCfg<BN, NS, NT, NACC, WSRC>;
+  auto kern = &w4a8_tc_kernel<BN, NS, NT, NACC, WSRC>;
   static std::once_flag once[64];
   int dev = 0;
   cudaGetDevice(&dev);
@@ -346,82 +745,71 @@ static int launch_cfg(const CUtensorMap& tx, const CUtensorMap& tw, const GemmAr
     record_cuda_error(attr_err, "cudaFuncSetAttribute(w4a8_tc_kernel)");
     return LQ_ERR_CUDA;
   }
-  dim3 grid((a.N + 127) / 128, (a.M + BN - 1) / BN, splits);
   kern<<<grid, kThreads, Cfg::kSmemBytes, st>>>(tx, tw, a);
   return check_launch("w4a8_tc_kernel");
 }
 
-static int pick_bn(int M) {
-  if (M <= 16) return 16;
-  if (M <= 32) return 32;
-  if (M <= 64) return 64;
-  if (M <= 128) return 128;
-  const int rem = M % 256;
-  if (M < 1024 && rem > 0 && rem <= 128) return 128;
-  return 256;
+template <int WSRC>
+static int dispatch_bn(int bn, const CUtensorMap& tx, const CUtensorMap& tw, const GemmArgs& a, int grid,
+                       cudaStream_t st) {
+  constexpr int NT = WSRC == kInt8 ? 1 : 4;
+  if constexpr (WSRC == kInt8) {
+    switch (bn) {
+      case 16: return launch_cfg<16, 9, NT, 2, WSRC>(tx, tw, a, grid, st);
+      case 32: return launch_cfg<32, 9, NT, 2, WSRC>(tx, tw, a, grid, st);
+      case 64: return launch_cfg<64, 8, NT, 2, WSRC>(tx, tw, a, grid, st);
+      case 128: return launch_cfg<128, 6, NT, 2, WSRC>(tx, tw, a, grid, st);
+      default: return launch_cfg<192, 5, NT, 2, WSRC>(tx, tw, a, grid, st);
+    }
+  } else {
+    switch (bn) {
+      case 16: return launch_cfg<16, 16, NT, 2, WSRC>(tx, tw, a, grid, st);
+      case 32: return launch_cfg<32, 14, NT, 2, WSRC>(tx, tw, a, grid, st);
+      case 64: return launch_cfg<64, 12, NT, 2, WSRC>(tx, tw, a, grid, st);
+      case 128: return launch_cfg<128, 8, NT, 2, WSRC>(tx, tw, a, grid, st);
+      default: return launch_cfg<192, 6, NT, 2, WSRC>(tx, tw, a, grid, st);
+    }
+  }
 }
 
-// x: [M,K] int8 tokens.  w: W4 blob or [N,K] int8 weights.
-template <bool W4>
-static int run_gemm(const int8_t* x, const void* w, const float* ascale, const float* s1, void* out, int out_mode,
-                    int M, int N, int K, int splits, cudaStream_t st) {
-  const int bn = pick_bn(M);
+// x: [M,K] int8 tokens.  w: tile blob, row-major interleaved nibbles [N,K/2], or [N,K] int8 weights.
+template <int WSRC>
+static int run_gemm(const int8_t* x, const void* w, const uint8_t* s_u8, const uint8_t* off_a, const float* ascale,
+                    const float* s1, void* out, int out_mode, int M, int N, int K, int splitk, void* wsp,
+                    size_t ws_bytes, cudaStream_t st) {
+  if (int rc = lq_check_device()) return rc;
+  const Plan p = make_plan(M, N, K, splitk);
+  if (p.ws_bytes && (!wsp || ws_bytes < p.ws_bytes)) return LQ_ERR_WORKSPACE;
   CUtensorMap tx, tw;
-  int rc = make_rowmajor_i8_map(&tx, x, M, K, bn);
+  int rc = make_byte_matrix_map(&tx, x, M, K, p.bn, 128);
   if (rc) return rc;
-  if (W4) tw = tx;
-  else if ((rc = make_rowmajor_i8_map(&tw, w, N, K, 128))) return rc;
+  if (WSRC == kBlob) tw = tx;
+  else if (WSRC == kRowMajor) rc = make_byte_matrix_map(&tw, w, N, K / 2, 128, 64);
+  else rc = make_byte_matrix_map(&tw, w, N, K, 128, 128);
+  if (rc) return rc;
   GemmArgs a;
-  a.blob = W4 ? static_cast<const uint8_t*>(w) : nullptr;
+  a.blob = WSRC == kBlob ? static_cast<const uint8_t*>(w) : nullptr;
+  a.s_u8 = s_u8;
+  a.off_a = off_a;
   a.ascale = ascale;
   a.s1 = s1;
   a.out = out;
+  a.slots = static_cast<int32_t*>(wsp);
+  a.counters = p.slots ? reinterpret_cast<int32_t*>(static_cast<uint8_t*>(wsp) + p.slots * (size_t)(128 * p.bn * 4))
+                       : nullptr;
   a.status = status_word();
   a.out_mode = out_mode;
   a.M = M;
   a.N = N;
   a.K = K;
   a.kt_total = K / 128;
+  a.n_tiles = p.n_tiles;
+  a.m_tiles = p.m_tiles;
+  a.fixed_split = p.fixed_split;
+  a.trace = g_trace_ptr;
+  a.debug_skip = g_debug_skip;
   if (!a.status) return LQ_ERR_CUDA;
-  if (W4) {
-    switch (bn) {
-      case 16: return launch_cfg<16, 8, 4, true>(tx, tw, a, splits, st);
-      case 32: return launch_cfg<32, 8, 4, true>(tx, tw, a, splits, st);
-      case 64: return launch_cfg<64, 6, 4, true>(tx, tw, a, splits, st);
-      case 128: return launch_cfg<128, 4, 4, true>(tx, tw, a, splits, st);
-      default: return launch_cfg<256, 5, 4, true>(tx, tw, a, splits, st);
-    }
-  } else {
-    switch (bn) {
-      case 16: return launch_cfg<16, 5, 1, false>(tx, tw, a, splits, st);
-      case 32: return launch_cfg<32, 5, 1, false>(tx, tw, a, splits, st);
-      case 64: return launch_cfg<64, 4, 1, false>(tx, tw, a, splits, st);
-      case 128: return launch_cfg<128, 3, 1, false>(tx, tw, a, splits, st);
-      default: return launch_cfg<256, 4, 1, false>(tx, tw, a, splits, st);
-    }
-  }
-}
-
-static int clamp_splits(int splitk, int M, int N, int K) {
-  if (splitk <= 0) splitk = lq_gemm_pick_splitk(M, N, K, 0);
-  const int kt = K / 128;
-  if (splitk > kt) splitk = kt;
-  return splitk < 1 ? 1 : splitk;
-}
-
-static int w4_common(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, void* out,
-                     int out_mode, int M, int N, int K, int splitk, void* ws, size_t ws_bytes, cudaStream_t st) {
-  if (!x || !blob || !out || M < 0 || N <= 0 || K <= 0) return LQ_ERR_BAD_ARG;
-  if (K % 128) return LQ_ERR_SHAPE;
-  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(blob)) % 16) return LQ_ERR_BAD_ARG;
-  if (M == 0) return LQ_OK;
-  if (int rc = lq_check_device()) return rc;
-  const int S = clamp_splits(splitk, M, N, K);
-  if (S == 1) return run_gemm<true>(x, blob, ascale, s1, out, out_mode, M, N, K, 1, st);
-  if (!ws || ws_bytes < lq_gemm_workspace_bytes(M, N, K, S)) return LQ_ERR_WORKSPACE;
-  int rc = run_gemm<true>(x, blob, nullptr, nullptr, ws, kOutI32, M, N, K, S, st);
-  if (rc) return rc;
-  return launch_finish(static_cast<const int32_t*>(ws), ascale, s1, out, out_mode, S, M, N, st);
+  return dispatch_bn<WSRC>(p.bn, tx, tw, a, p.grid, st);
 }
 
 }  // namespace lq
@@ -430,54 +818,69 @@ using namespace lq;
 
 extern "C" {
 
+// Pipeline-study hook: when set to a device buffer of 32 x 8 bytes per SM, every tensor-core GEMM
+// launch records per-CTA cycle counters there (see TraceSlot).  Pass null to switch it off.
+// `skip` switches pipeline parts off for timing experiments (see GemmArgs::debug_skip); 0 = normal.
+LQ_API void lq_debug_set_trace(void* device_buffer, int skip) {
+  g_trace_ptr = static_cast<long long*>(device_buffer);
+  g_debug_skip = skip;
+}
+
 int lq_gemm_pick_splitk(int M, int N, int K, int env_override) {
-  if (M <= 0 || N <= 0 || K < 128) return 1;
-  const int kt = K / 128;
-  int S = 1;
+  // 0 selects stream-K scheduling, which balances any shape over the SMs; an explicit
+  // LIQUIDGEMM_SPLITK only applies to the decode range, as in the reference.
+  if (M <= 0 || N <= 0 || K < 128) return 0;
   if (env_override > 0 && M <= 128) {
-    S = env_override;
-  } else {
-    // Fill the machine: with T output tiles and 2 resident CTAs per SM, split K until there are
-    // about 2 x SM-count CTAs, keeping at least 8 k-steps per split.
-    const int bn = pick_bn(M);
-    const long tiles = (long)((N + 127) / 128) * ((M + bn - 1) / bn);
-    const long slots = 2L * sm_count();
-    if (tiles * 2 <= slots) {
-      S = (int)(slots / tiles);
-      const int max_by_k = kt / 8 > 0 ? kt / 8 : 1;
-      if (S > max_by_k) S = max_by_k;
-      if (S > 16) S = 16;
-    }
+    const int kt = K / 128;
+    return env_override > kt ? kt : env_override;
   }
-  if (S > kt) S = kt;
-  return S < 1 ? 1 : S;
+  return 0;
 }
 
 size_t lq_gemm_workspace_bytes(int M, int N, int K, int splitk) {
-  (void)K;
-  if (splitk <= 1 || M <= 0 || N <= 0) return 0;
-  return (size_t)splitk * (size_t)M * (size_t)N * sizeof(int32_t);
+  if (M <= 0 || N <= 0 || K < 128) return 0;
+  return make_plan(M, N, K, splitk).ws_bytes;
 }
 
 int lq_w4a8_gemm_i32(const int8_t* x_i8, const uint8_t* blob, int32_t* acc, int M, int N, int K, int splitk,
                      void* workspace, size_t workspace_bytes, void* stream) {
-  return w4_common(x_i8, blob, nullptr, nullptr, acc, kOutI32, M, N, K, splitk, workspace, workspace_bytes,
-                   as_stream(stream));
+  if (!x_i8 || !blob || !acc || M < 0 || N <= 0 || K <= 0) return LQ_ERR_BAD_ARG;
+  if (K % 128) return LQ_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(x_i8) | reinterpret_cast<uintptr_t>(blob)) % 16) return LQ_ERR_BAD_ARG;
+  if (M == 0) return LQ_OK;
+  return run_gemm<kBlob>(x_i8, blob, nullptr, nullptr, nullptr, nullptr, acc, kOutI32, M, N, K, splitk, workspace,
+                         workspace_bytes, as_stream(stream));
 }
 
 int lq_w4a8_gemm_fused(const int8_t* x_i8, const uint8_t* blob, const float* ascale, const float* s1, void* y,
                        int out_dtype, int M, int N, int K, int splitk, void* workspace, size_t workspace_bytes,
                        void* stream) {
-  if (!ascale || !s1 || out_dtype < 0 || out_dtype > 2) return LQ_ERR_BAD_ARG;
-  return w4_common(x_i8, blob, ascale, s1, y, out_dtype, M, N, K, splitk, workspace, workspace_bytes,
-                   as_stream(stream));
+  if (!x_i8 || !blob || !y || !ascale || !s1 || M < 0 || N <= 0 || K <= 0) return LQ_ERR_BAD_ARG;
+  if (out_dtype < 0 || out_dtype > 2) return LQ_ERR_BAD_ARG;
+  if (K % 128) return LQ_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(x_i8) | reinterpret_cast<uintptr_t>(blob)) % 16) return LQ_ERR_BAD_ARG;
+  if (M == 0) return LQ_OK;
+  return run_gemm<kBlob>(x_i8, blob, nullptr, nullptr, ascale, s1, y, out_dtype, M, N, K, splitk, workspace,
+                         workspace_bytes, as_stream(stream));
+}
+
+int lq_w4a8_gemm_rowmajor(const int8_t* x_i8, const uint8_t* gpack, const uint8_t* s_u8, const uint8_t* offset_a,
+                          const float* ascale, const float* s1, void* y, int out_dtype, int M, int N, int K,
+                          int splitk, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!x_i8 || !gpack || !s_u8 || !offset_a || !y || !ascale || !s1 || M < 0 || N <= 0 || K <= 0)
+    return LQ_ERR_BAD_ARG;
+  if (out_dtype < 0 || out_dtype > 2) return LQ_ERR_BAD_ARG;
+  if (K % 128) return LQ_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(x_i8) | reinterpret_cast<uintptr_t>(gpack)) % 16) return LQ_ERR_BAD_ARG;
+  if (M == 0) return LQ_OK;
+  return run_gemm<kRowMajor>(x_i8, gpack, s_u8, offset_a, ascale, s1, y, out_dtype, M, N, K, splitk, workspace,
+                             workspace_bytes, as_stream(stream));
 }
 
 size_t lq_gemm_v1_workspace_bytes(int M, int N, int K) {
   if (M <= 16) return 0;
   const size_t blob = lq_tile_blob_bytes(N, K);
-  const int S = lq_gemm_pick_splitk(M, N, K, 0);
-  return ((blob + 255) / 256) * 256 + lq_gemm_workspace_bytes(M, N, K, S);
+  return ((blob + 255) / 256) * 256 + lq_gemm_workspace_bytes(M, N, K, 1);
 }
 
 int lq_w4a8_gemm_v1(const int8_t* x_i8, const uint8_t* nibbles, const uint8_t* s_u8, const uint8_t* offset_a,
@@ -494,13 +897,11 @@ int lq_w4a8_gemm_v1(const int8_t* x_i8, const uint8_t* nibbles, const uint8_t* s
   }
   if (K % 128) return LQ_ERR_SHAPE;
   if (!workspace || workspace_bytes < lq_gemm_v1_workspace_bytes(M, N, K)) return LQ_ERR_WORKSPACE;
+  // scratch = re-tiled weights only; whole-tile scheduling (splitk 1) needs no reduction slots
   uint8_t* blob = static_cast<uint8_t*>(workspace);
-  const size_t blob_bytes = ((lq_tile_blob_bytes(N, K) + 255) / 256) * 256;
   int rc = lq_repack_tiles(nibbles, LQ_SRC_NIBBLES, s_u8, offset_a, blob, N, K, group_size, stream);
   if (rc) return rc;
-  const int S = lq_gemm_pick_splitk(M, N, K, 0);
-  return w4_common(x_i8, blob, ascale, s1, y, LQ_DT_F32, M, N, K, S, blob + blob_bytes,
-                   workspace_bytes - blob_bytes, st);
+  return run_gemm<kBlob>(x_i8, blob, nullptr, nullptr, ascale, s1, y, LQ_DT_F32, M, N, K, 1, nullptr, 0, st);
 }
 
 static int i8_common(const int8_t* a, const int8_t* b, const float* a_scale, const float* b_scale, void* out,
@@ -509,8 +910,9 @@ static int i8_common(const int8_t* a, const int8_t* b, const float* a_scale, con
   if (K % 128) return LQ_ERR_SHAPE;
   if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) % 16) return LQ_ERR_BAD_ARG;
   if (M == 0) return LQ_OK;
-  if (int rc = lq_check_device()) return rc;
-  return run_gemm<false>(a, b, a_scale, b_scale, out, out_mode, M, N, K, 1, as_stream(stream));
+  // whole-tile scheduling: the plain INT8 entry points take no workspace
+  return run_gemm<kInt8>(a, b, nullptr, nullptr, a_scale, b_scale, out, out_mode, M, N, K, 1, nullptr, 0,
+                         as_stream(stream));
 }
 
 int lq_i8_gemm_i32(const int8_t* a, const int8_t* b, int32_t* c, int M, int N, int K, void* stream) {

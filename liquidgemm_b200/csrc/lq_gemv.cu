@@ -323,7 +323,7 @@ extern "C" int lq_w4a8_gemv(const int8_t* x_i8, const uint8_t* gpack, const uint
 
 // Tuning hook: same contract as lq_w4a8_gemv with the kernel chosen by the caller
 // (1 = dp4a, 2 = mma.sync).  Used by the benchmark sweeps that decide the dispatch table.
-extern "C" LQ_API int lq_w4a8_gemv_variant(const int8_t* x_i8, const uint8_t* gpack, const uint8_t* s_u8,
+extern "C" int lq_w4a8_gemv_variant(const int8_t* x_i8, const uint8_t* gpack, const uint8_t* s_u8,
                                            const uint8_t* offset_a, const float* ascale, const float* s1,
                                            void* y, int out_dtype, int M, int N, int K, int variant,
                                            void* stream) {

@@ -41,8 +41,12 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
 
 // Wait for the phase with the given parity, for at most `limit_ns`.  Returns false when the
 // limit ran out; the caller records a status code and unwinds instead of spinning forever.
+// The timer is only consulted after a few thousand failed polls, so the common case costs one
+// or a handful of try_wait instructions.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint64_t limit_ns) {
-  if (mbar_try_wait(bar, parity)) return true;
+#pragma unroll 1
+  for (int i = 0; i < 4096; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {

@@ -211,15 +211,42 @@ def _gemv2(x_i8, gpack, s_u8, off_a, ascale, s1, N, K, group_size, out_dtype):
 
 
 def _splitk_for(M, N, K):
+    """Scheduling argument for the tensor-core GEMM: 0 (stream-K) unless LIQUIDGEMM_SPLITK applies."""
     return lib.lq_gemm_pick_splitk(M, N, K, _SPLITK_ENV)
 
 
-def _workspace(M, N, K, S, device):
-    nbytes = lib.lq_gemm_workspace_bytes(M, N, K, S)
+# Zero-filled reduction workspaces, one per (device, stream).  The GEMM kernel needs its workspace
+# all-zero on entry and leaves it all-zero on exit, so one buffer serves every call on a stream and
+# keeps a stable address under CUDA-graph capture.  Outgrown buffers are kept alive because a
+# captured graph may still point at them.
+_WORKSPACES: dict = {}
+_RETIRED: list = []
+
+
+def _workspace(nbytes: int, device: torch.device):
     if nbytes == 0:
-        return None, 0
-    ws = torch.empty((nbytes,), dtype=torch.uint8, device=device)
-    return ws, nbytes
+        return None
+    key = (device.index, _stream())
+    ws = _WORKSPACES.get(key)
+    if ws is None or ws.numel() < nbytes:
+        if ws is not None:
+            _RETIRED.append(ws)
+        ws = torch.zeros((max(nbytes, 1 << 22),), dtype=torch.uint8, device=device)
+        _WORKSPACES[key] = ws
+    return ws
+
+
+def _gemm_call(fn_name, x_i8, M, N, K, splitk, call):
+    """Run one tensor-core GEMM entry point with its workspace; clears the workspace if the call fails
+    (a failed kernel may leave partial sums behind)."""
+    S = _splitk_for(M, N, K) if splitk is None else int(splitk)
+    nbytes = lib.lq_gemm_workspace_bytes(M, N, K, S)
+    with _dev_ctx(x_i8):
+        ws = _workspace(nbytes, x_i8.device)
+        rc = call(S, _ptr(ws) if ws is not None else None, ws.numel() if ws is not None else 0, _stream())
+        if rc != 0 and ws is not None:
+            ws.zero_()
+        check(rc, fn_name)
 
 
 def _check_blob(w, N, K):
@@ -230,26 +257,22 @@ def _check_blob(w, N, K):
     return w.contiguous()
 
 
-def gemm_i32(x_i8, blob, N, K, splitk=0):
-    """Exact int32 accumulators from a tile blob; ``splitk=0`` picks the factor automatically."""
+def gemm_i32(x_i8, blob, N, K, splitk=None):
+    """Exact int32 accumulators from a tile blob.  ``splitk``: None = automatic (stream-K unless
+    LIQUIDGEMM_SPLITK applies), 0 = stream-K, 1 = whole tiles, S > 1 = fixed split-K factor."""
     x_i8 = _i8(x_i8, "x_i8")
     _req(K % 128 == 0 and x_i8.shape[1] == K, "K%128==0 required and x_i8 must be [M,K]")
     blob = _check_blob(blob, N, K)
     M = x_i8.shape[0]
     acc = torch.empty((M, N), dtype=torch.int32, device=x_i8.device)
-    if M == 0:
-        return acc
-    S = splitk if splitk > 0 else _splitk_for(M, N, K)
-    S = max(1, min(S, K // 128))
-    ws, nbytes = _workspace(M, N, K, S, x_i8.device)
-    with _dev_ctx(x_i8):
-        check(lib.lq_w4a8_gemm_i32(_ptr(x_i8), _ptr(blob), _ptr(acc), M, N, K, S, _ptr(ws) if ws is not None else None,
-                                   nbytes, _stream()), "w4a8_gemm_i32")
+    if M:
+        _gemm_call("w4a8_gemm_i32", x_i8, M, N, K, splitk,
+                   lambda S, ws, nb, st: lib.lq_w4a8_gemm_i32(_ptr(x_i8), _ptr(blob), _ptr(acc), M, N, K, S, ws, nb, st))
     return acc
 
 
-def gemm_fused(x_i8, blob, ascale, s1, N, K, out_dtype, splitk=0):
-    """Fused W4A8 linear from a tile blob; ``splitk=0`` picks the factor automatically."""
+def gemm_fused(x_i8, blob, ascale, s1, N, K, out_dtype, splitk=None):
+    """Fused W4A8 linear from a tile blob (``splitk`` as in :func:`gemm_i32`)."""
     x_i8 = _i8(x_i8, "x_i8")
     _req(K % 128 == 0 and x_i8.shape[1] == K, "K%128==0 required and x_i8 must be [M,K]")
     _req(int(out_dtype) in _OUT_DTYPES, "out_dtype must be 0 (bf16), 1 (fp16) or 2 (fp32)")
@@ -258,15 +281,30 @@ def gemm_fused(x_i8, blob, ascale, s1, N, K, out_dtype, splitk=0):
     M = x_i8.shape[0]
     _req(ascale.numel() == M and s1.numel() == N, "ascale must be [M] and s1 [N]")
     y = torch.empty((M, N), dtype=_OUT_DTYPES[int(out_dtype)], device=x_i8.device)
-    if M == 0:
-        return y
-    S = splitk if splitk > 0 else _splitk_for(M, N, K)
-    S = max(1, min(S, K // 128))
-    ws, nbytes = _workspace(M, N, K, S, x_i8.device)
-    with _dev_ctx(x_i8):
-        check(lib.lq_w4a8_gemm_fused(_ptr(x_i8), _ptr(blob), _ptr(ascale), _ptr(s1), _ptr(y), int(out_dtype), M, N, K,
-                                     S, _ptr(ws) if ws is not None else None, nbytes, _stream()),
-              "w4a8_gemm_fused")
+    if M:
+        _gemm_call("w4a8_gemm_fused", x_i8, M, N, K, splitk,
+                   lambda S, ws, nb, st: lib.lq_w4a8_gemm_fused(_ptr(x_i8), _ptr(blob), _ptr(ascale), _ptr(s1), _ptr(y),
+                                                                int(out_dtype), M, N, K, S, ws, nb, st))
+    return y
+
+
+def gemm_rowmajor(x_i8, gpack, s_u8, off_a, ascale, s1, N, K, out_dtype, splitk=None):
+    """Fused W4A8 linear on tensor cores straight from the row-major GEMV pack (any M)."""
+    x_i8 = _i8(x_i8, "x_i8")
+    _req(K % 128 == 0 and x_i8.shape[1] == K, "K%128==0 required and x_i8 must be [M,K]")
+    _req(int(out_dtype) in _OUT_DTYPES, "out_dtype must be 0 (bf16), 1 (fp16) or 2 (fp32)")
+    gpack, s_u8, off_a = _u8(gpack, "gpack"), _u8(s_u8, "s_u8"), _u8(off_a, "off_a")
+    ascale, s1 = _f32(ascale, "ascale"), _f32(s1, "s1")
+    M = x_i8.shape[0]
+    _req(gpack.numel() == N * K // 2, "gpack must be [N,K/2]")
+    _req(s_u8.numel() == N * (K // 64) and off_a.numel() == N * (K // 64), "s_u8/off_a must be [N, K/64]")
+    _req(ascale.numel() == M and s1.numel() == N, "ascale must be [M] and s1 [N]")
+    y = torch.empty((M, N), dtype=_OUT_DTYPES[int(out_dtype)], device=x_i8.device)
+    if M:
+        _gemm_call("w4a8_gemm_rowmajor", x_i8, M, N, K, splitk,
+                   lambda S, ws, nb, st: lib.lq_w4a8_gemm_rowmajor(_ptr(x_i8), _ptr(gpack), _ptr(s_u8), _ptr(off_a),
+                                                                   _ptr(ascale), _ptr(s1), _ptr(y), int(out_dtype),
+                                                                   M, N, K, S, ws, nb, st))
     return y
 
 

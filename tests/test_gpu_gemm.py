@@ -108,10 +108,10 @@ def test_fused_equals_unfused_and_oracle(ops, M, out_dtype):
     assert_bits_equal(got, O.w4a8_matmul(x, ascale, qw), out_dtype, "fused vs oracle")
 
 
-@pytest.mark.parametrize("S", [1, 2, 4, 8, 16])
+@pytest.mark.parametrize("S", [0, 1, 2, 4, 8, 16])
 @pytest.mark.parametrize("M", [32, 64, 128])
 def test_explicit_splitk_is_exact(ops, M, S):
-    """Split-K sweep of the decode-tile configuration: any S gives the same bits."""
+    """Split-K sweep of the decode-tile configuration (0 = stream-K): any setting gives the same bits."""
     N, K = 256, 14336
     qw = random_lqq(N, K, 64, seed=S)
     tq = to_torch_qw(qw)
@@ -210,3 +210,30 @@ def test_full_size_prefill_properties(ops, name, M):
 def test_device_status_word_is_clean(ops):
     from liquidgemm_b200._lib import lib
     assert lib.lq_poll_status(torch.cuda.current_stream().cuda_stream) == 0
+
+
+@pytest.mark.parametrize("M", [1, 4, 8, 16, 40, 128, 200])
+@pytest.mark.parametrize("N,K", [(512, 4096), (320, 1152), (4096, 14336)])
+def test_rowmajor_tensor_core_path(ops, M, N, K):
+    """The tensor-core GEMM reading the row-major GEMV pack and the plain [N, K/64] step/offset arrays."""
+    qw = random_lqq(N, K, 64, seed=N + M)
+    tq = to_torch_qw(qw)
+    x, ascale = random_tokens(M, K, seed=M)
+    y = ops.gemm_rowmajor(torch.from_numpy(x).cuda(), ops.pack_gemv_interleaved(tq), tq.s_u8, tq.offset_a,
+                          torch.from_numpy(ascale).cuda(), tq.s1, N, K, 0)
+    assert_bits_equal(y, O.w4a8_matmul(x, ascale, qw), 0, f"rowmajor {M}x{N}x{K}")
+
+
+def test_workspace_is_left_clean(ops):
+    """Stream-K leaves its reduction workspace all-zero, so back-to-back calls stay exact."""
+    N, K, M = 384, 14336, 24
+    qw = random_lqq(N, K, 64, seed=4)
+    tq = to_torch_qw(qw)
+    x, _ = random_tokens(M, K, seed=5)
+    xt = torch.from_numpy(x).cuda()
+    w = ops.repack_rs_weight(tq).reshape(-1)
+    want = _acc(x, qw)
+    for _ in range(3):
+        assert np.array_equal(ops.gemm_i32(xt, w, N, K, splitk=0).cpu().numpy(), want)
+    for ws in ops._WORKSPACES.values():
+        assert int(ws.count_nonzero()) == 0
