@@ -135,7 +135,7 @@ def run_tp70b(world, rank, Ms=(1, 64, 2048), layers_in_stack=80, distinct_layers
                       for i, n in enumerate(names)})
     for M in Ms:
         toks = {n: device_tokens(M, SHAPES_70B[n][1], seed=M + i) for i, n in enumerate(names)}
-        gathered = {n: torch.empty((world, M, SHAPES_70B[n][0] // world), dtype=torch.bfloat16, device="cuda")
+        gathered = {n: torch.empty((world * M, SHAPES_70B[n][0] // world), dtype=torch.bfloat16, device="cuda")
                     for n in names}
 
         def one_stack(gather):

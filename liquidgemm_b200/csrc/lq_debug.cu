@@ -146,3 +146,56 @@ extern "C" LQ_API int lq_debug_sync_cost(const void* src_128k, long long* out16,
   lq::sync_cost_kernel<<<1, 32, 0, lq::as_stream(stream)>>>(static_cast<const uint8_t*>(src_128k), out16);
   return lq::check_launch("sync_cost_kernel");
 }
+
+namespace lq {
+// Pure streaming test: each CTA pulls `steps` blocks of `stage_bytes` (contiguous, CTA-private
+// region of `src`) through a ring of `ns` shared-memory stages with bulk copies; one thread
+// produces, one thread consumes (wait full -> arrive empty).  Upper bound for any TMA-fed kernel.
+__global__ void __launch_bounds__(64, 1)
+tma_stream_kernel(const uint8_t* src, int stage_bytes, int ns, int steps, long long* cycles) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 127u) & ~127u;
+  __shared__ uint64_t bars[64];
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < ns; ++i) {
+      ptx::mbar_init(smem_u32(&bars[i]), 1);
+      ptx::mbar_init(smem_u32(&bars[32 + i]), 1);
+    }
+    ptx::fence_mbar_init();
+  }
+  __syncthreads();
+  const long long t0 = clock64();
+  const uint8_t* my = src + (size_t)blockIdx.x * steps * stage_bytes;
+  if (threadIdx.x == 0) {
+    int s = 0;
+    uint32_t ph = 0;
+    for (int i = 0; i < steps; ++i) {
+      while (!ptx::mbar_try_wait(smem_u32(&bars[32 + s]), ph ^ 1u)) {}
+      ptx::mbar_expect_tx(smem_u32(&bars[s]), stage_bytes);
+      ptx::bulk_load(base + s * stage_bytes, my + (size_t)i * stage_bytes, stage_bytes, smem_u32(&bars[s]));
+      if (++s == ns) { s = 0; ph ^= 1u; }
+    }
+  } else if (threadIdx.x == 32) {
+    int s = 0;
+    uint32_t ph = 0;
+    for (int i = 0; i < steps; ++i) {
+      while (!ptx::mbar_try_wait(smem_u32(&bars[s]), ph)) {}
+      ptx::mbar_arrive(smem_u32(&bars[32 + s]));
+      if (++s == ns) { s = 0; ph ^= 1u; }
+    }
+    cycles[blockIdx.x] = clock64() - t0;
+  }
+  __syncthreads();
+}
+}  // namespace lq
+
+extern "C" LQ_API int lq_debug_tma_stream(const void* src, int stage_bytes, int ns, int steps, int ctas,
+                                          long long* cycles, void* stream) {
+  if (ns < 1 || ns > 32 || stage_bytes % 16 || stage_bytes * ns > 200 * 1024) return LQ_ERR_BAD_ARG;
+  const int smem = stage_bytes * ns + 256;
+  cudaFuncSetAttribute(lq::tma_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 201 * 1024);
+  lq::tma_stream_kernel<<<ctas, 64, smem, lq::as_stream(stream)>>>(static_cast<const uint8_t*>(src), stage_bytes, ns,
+                                                                   steps, cycles);
+  return lq::check_launch("tma_stream_kernel");
+}

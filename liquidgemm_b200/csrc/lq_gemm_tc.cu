@@ -17,12 +17,13 @@
 // applies the epilogue and re-zeroes slot and counter, so the workspace is all-zero again when
 // the kernel ends.  A fixed split-K factor can be requested instead (tile = S equal k-ranges).
 //
-// Roles inside a CTA (12 warps), connected by mbarrier rings:
+// Roles inside a CTA (16 warps), connected by mbarrier rings:
 //   warp 0       producer : one thread issues, per k-step, the weight tile (one 8704-byte bulk
 //                           copy from the tile blob, or a tensor-map box from the row-major
 //                           layouts) and the BN x 128 activation box (128-byte swizzle; token rows
 //                           past M are zero-filled by the TMA unit).
-//   warps 4..7   dequant  : thread r owns weight row r of the tile: 64 bytes of nibbles (four
+//   warps 4..7,  dequant  : two sets take alternate k-steps; thread r owns weight row r of the tile:
+//   12..15                  64 bytes of nibbles (four
 //                           conflict-free 16-byte shared loads) + two (step, offset) pairs ->
 //                           128 INT8 values by AND / SHR+AND, multiply-add, XOR on 32-bit words ->
 //                           tcgen05.st into TMEM lane r, 4 consecutive k per 32-bit column, which
@@ -55,7 +56,7 @@ int launch_gemv_plain_f32(const int8_t* x, const uint8_t* nibbles, const uint8_t
 constexpr int kTileBytes = 8704;     // weight tile in the blob: 8192 nibble bytes + 512 metadata bytes
 constexpr int kI8TileBytes = 16384;  // INT8 weight tile: 128 rows x 128 bytes
 constexpr int kRowBoxBytes = 8192;   // row-major nibble box: 128 rows x 64 bytes
-constexpr int kThreads = 384;
+constexpr int kThreads = 512;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 constexpr int kOutI32 = 3;           // internal output mode: raw int32
 
@@ -179,6 +180,14 @@ struct Ring {
     }
   }
 };
+
+// Bounded barrier wait performed by lane 0 on behalf of a converged warp.
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, int lane) {
+  int done = 1;
+  if (lane == 0) done = ptx::mbar_wait_bounded(bar, parity, kWaitLimitNs) ? 1 : 0;
+  done = __shfl_sync(0xffffffffu, done, 0);
+  return done != 0;
+}
 
 __device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
@@ -373,9 +382,13 @@ w4a8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
       LQ_TRACE(kTrSegments, seg);
       LQ_TRACE(kTrMmaIssue, t_mma);
     }
-  } else if (warp >= 4 && warp < 8) {
+  } else if ((warp >= 4 && warp < 8) || warp >= 12) {
     // ------------------------------------------------------------------ dequant
+    // Two sets of four warps (4..7 and 12..15) take alternate k-steps, so each set has two k-step
+    // periods to hide its shared-load, tcgen05.st and barrier latencies.
     if (kDequant) {
+      const int my_parity = warp >= 12 ? 1 : 0;
+      int step_parity = 0;
       const int quad = warp & 3;               // TMEM lane quadrant this warp may access
       const int row = quad * 32 + lane;        // weight row inside the tile == TMEM lane
       const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
@@ -393,6 +406,13 @@ w4a8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
         const long n = (long)nt * 128 + row;
         const bool n_ok = n < args.N;
         for (int kt = sg.kb; kt < sg.ke; ++kt) {
+          if (step_parity != my_parity) {        // the other set's k-step
+            step_parity ^= 1;
+            ring.advance();
+            aring.advance();
+            continue;
+          }
+          step_parity ^= 1;
           uint32_t meta = 0x80008000u;   // step 0, offset 128: reconstructs to zero
           if (WSRC == kRowMajor && n_ok) {
             const uint32_t sp = *reinterpret_cast<const uint16_t*>(args.s_u8 + n * G + 2 * kt);
@@ -400,7 +420,9 @@ w4a8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
             meta = (sp & 0xffu) | ((op & 0xffu) << 8) | ((sp >> 8) << 16) | ((op >> 8) << 24);
           }
           const long long td0 = LQ_CLK();
-          if (!ptx::mbar_wait_bounded(bar_full + 8 * ring.s, ring.ph, kWaitLimitNs)) {
+          // one lane polls, the warp follows: 128 threads polling the same barrier would crowd the
+          // shared-memory pipeline that the other roles' barrier operations also go through
+          if (!warp_wait(bar_full + 8 * ring.s, ring.ph, lane)) {
             atomicExch(args.status, 103);
             ok = false;
             break;
@@ -432,7 +454,7 @@ w4a8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
           ptx::mbar_arrive(bar_empty + 8 * ring.s);   // after the loads above have returned their data
 
           const long long td2 = LQ_CLK();
-          if (!ptx::mbar_wait_bounded(bar_afree + 8 * aring.s, aring.ph ^ 1u, kWaitLimitNs)) {
+          if (!warp_wait(bar_afree + 8 * aring.s, aring.ph ^ 1u, lane)) {
             atomicExch(args.status, 104);
             ok = false;
             pending = -1;
@@ -443,19 +465,19 @@ w4a8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
           ptx::tc_fence_after();
           const uint32_t step0 = meta & 0xffu, a0 = ((meta >> 8) & 0xffu) * 0x01010101u;
           const uint32_t step1 = (meta >> 16) & 0xffu, a1 = (meta >> 24) * 0x01010101u;
+          uint32_t v[32];
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             const uint32_t step = c < 2 ? step0 : step1;
             const uint32_t ab = c < 2 ? a0 : a1;
             const uint32_t pk[4] = {ch[c].x, ch[c].y, ch[c].z, ch[c].w};
-            uint32_t v[8];
 #pragma unroll
             for (int h = 0; h < 4; ++h) {
-              v[2 * h] = lqq_dequant4(pk[h] & 0x0F0F0F0Fu, step, ab);
-              v[2 * h + 1] = lqq_dequant4((pk[h] >> 4) & 0x0F0F0F0Fu, step, ab);
+              v[8 * c + 2 * h] = lqq_dequant4(pk[h] & 0x0F0F0F0Fu, step, ab);
+              v[8 * c + 2 * h + 1] = lqq_dequant4((pk[h] >> 4) & 0x0F0F0F0Fu, step, ab);
             }
-            if (!(args.debug_skip & 1)) ptx::tmem_st8(tmem_a + lane_addr + aring.s * 32 + c * 8, v);
           }
+          if (!(args.debug_skip & 1)) ptx::tmem_st32(tmem_a + lane_addr + aring.s * 32, v);
           pending = aring.s;
           t_comp += LQ_CLK() - td3;
           ring.advance();
@@ -474,7 +496,7 @@ w4a8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
         LQ_TRACE(kTrDeqCompute, t_comp);
       }
     }
-  } else if (warp >= 8) {
+  } else if (warp >= 8 && warp < 12) {
     // ------------------------------------------------------------------ epilogue
     const int quad = warp & 3;
     const int row = quad * 32 + lane;
