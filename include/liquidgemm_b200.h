@@ -90,6 +90,17 @@ LQ_API int lq_w4a8_gemv_variant(const int8_t* x_i8, const uint8_t* gpack, const 
                          const uint8_t* offset_a, const float* ascale, const float* s1, void* y,
                          int out_dtype, int M, int N, int K, int variant, void* stream);
 
+/* The same GEMV as a persistent stream-K kernel (TMA ring + mma.sync): the fast path behind
+ * torch.ops.liquidgemm.w4a8_gemv2.  It needs a reduction workspace of lq_gemv_workspace_bytes(N, K)
+ * bytes that is ALL ZERO on entry and is left all zero (same contract as lq_gemm_workspace_bytes).
+ * No reference counterpart beyond the op itself (the reference GEMV is one warp per row,
+ * csrc/liquid_gemm/gemv2.cu:21-80). */
+LQ_API size_t lq_gemv_workspace_bytes(int N, int K);
+LQ_API int lq_w4a8_gemv_stream(const int8_t* x_i8, const uint8_t* gpack, const uint8_t* s_u8,
+                        const uint8_t* offset_a, const float* ascale, const float* s1, void* y,
+                        int out_dtype, int M, int N, int K, void* workspace, size_t workspace_bytes,
+                        void* stream);
+
 /* Same product from the plain pack_nibbles() layout with float32 output, any M.
  * Replaces torch.ops.liquidgemm.w4a8_gemm (reference csrc/liquid_gemm/w4a8_gemm.cu:183-227).
  * M <= 16 runs the GEMV (K % 64 == 0); larger M re-tiles the weights into `workspace`
@@ -113,21 +124,26 @@ LQ_API int lq_repack_tiles(const uint8_t* src, int src_layout, const uint8_t* s_
                     const uint8_t* offset_a, uint8_t* blob, int N, int K, int group_size,
                     void* stream);
 
-/* Scheduling of the tensor-core GEMM, selected by the `splitk` argument of the calls below:
- *   0      stream-K: one persistent CTA per SM, the k-steps of all output tiles are dealt out in
- *          equal contiguous ranges; tiles cut by a range boundary are reduced through the workspace;
- *   1      whole tiles only (no reduction, no workspace);
- *   S > 1  every tile is cut into S equal k-ranges (the split-K factor of the reference,
- *          csrc/liquid_gemm/w4a8_wgmma.cu:523-534), reduced through the workspace.
- * Partial sums are int32 and added with atomics, so every setting gives bit-identical results.
+/* Scheduling of the tensor-core GEMM, selected by the `splitk` argument of the calls below.
+ *   M <= 128 (decode tiles): one tile per CTA, two CTAs per SM; every tile is cut into S k-ranges
+ *            whose int32 partial planes one finish kernel reduces, scales and casts -- the split-K
+ *            design of the reference (csrc/liquid_gemm/w4a8_wgmma.cu:39-56, 523-534).
+ *            splitk = 0 picks S from the SM count, splitk = S >= 1 forces it (clamped to K/128).
+ *   M  > 128 (prefill): one persistent CTA per SM.  splitk = 0: stream-K, the k-steps of all tiles
+ *            are dealt out in equal contiguous ranges and tiles cut by a range boundary are
+ *            reduced with int32 atomics; splitk = 1: whole tiles only; S > 1: fixed split.
+ *   splitk = -1 forces the persistent stream-K kernel for any M.
+ * Partial sums are int32, so every setting gives bit-identical results.
  * lq_gemm_pick_splitk maps LIQUIDGEMM_SPLITK (`env_override`, 0 = unset) to that argument: like
  * the reference the override only applies to M <= 128 and is clamped to K/128; otherwise 0. */
 LQ_API int lq_gemm_pick_splitk(int M, int N, int K, int env_override);
-/* Workspace bytes for (M,N,K,splitk).  The workspace must be ALL ZERO when a GEMM call starts and
- * is all zero again when its kernel ends (the kernel cleans up after itself), so one zero-filled
- * buffer can serve any number of successive calls on a stream; calls that overlap on the GPU need
- * separate buffers.  After a LQ_ERR_TIMEOUT the buffer must be cleared by the caller. */
+/* Workspace bytes for (M,N,K,splitk) and its kind: 0 = none, 1 = scratch (any contents; the
+ * decode-tile planes), 2 = reduction buffer of the persistent kernel, which must be ALL ZERO when
+ * a call starts and is all zero again when its kernel ends (the kernel cleans up after itself), so
+ * one zero-filled buffer serves any number of successive calls on a stream; calls that overlap on
+ * the GPU need separate buffers, and after a LQ_ERR_TIMEOUT the caller must clear it. */
 LQ_API size_t lq_gemm_workspace_bytes(int M, int N, int K, int splitk);
+LQ_API int lq_gemm_workspace_kind(int M, int N, int K, int splitk);
 
 /* W4A8 tensor-core GEMM, exact int32 accumulators acc[M,N] = x_i8 @ q_hat^T.
  * Replaces torch.ops.liquidgemm.w4a8_wgmma_rs (reference csrc/liquid_gemm/w4a8_wgmma.cu:505-570).
@@ -146,7 +162,8 @@ LQ_API int lq_w4a8_gemm_fused(const int8_t* x_i8, const uint8_t* blob, const flo
  * (liquidgemm/ops.py:68-75: [N, K/2]) with the standard [N, K/64] step / offset arrays, i.e. one
  * weight format for every M.  No direct reference counterpart (the reference keeps two packs,
  * liquidgemm/vllm_plugin.py:153-164); it backs torch.ops.liquidgemm.w4a8_gemv2 for the token counts
- * where tensor cores beat dp4a.  K % 128 == 0, group_size 64. */
+ * where tensor cores beat dp4a.  K % 128 == 0, group_size 64.  Always the persistent stream-K
+ * kernel (`splitk` is ignored): the workspace is lq_gemm_workspace_bytes(M, N, K, -1), kind 2. */
 LQ_API int lq_w4a8_gemm_rowmajor(const int8_t* x_i8, const uint8_t* gpack, const uint8_t* s_u8,
                           const uint8_t* offset_a, const float* ascale, const float* s1, void* y,
                           int out_dtype, int M, int N, int K, int splitk, void* workspace,

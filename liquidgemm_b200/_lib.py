@@ -32,12 +32,15 @@ _SIGNATURES = {
     "lq_w4a8_gemv": (c_int, [P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P]),
     "lq_w4a8_gemv_variant": (c_int, [P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P]),
     "lq_w4a8_gemm_rowmajor": (c_int, [P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, c_size_t, P]),
+    "lq_gemv_workspace_bytes": (c_size_t, [c_int, c_int]),
+    "lq_w4a8_gemv_stream": (c_int, [P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, P, c_size_t, P]),
     "lq_gemm_v1_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "lq_w4a8_gemm_v1": (c_int, [P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, P, c_size_t, P]),
     "lq_tile_blob_bytes": (c_size_t, [c_int, c_int]),
     "lq_repack_tiles": (c_int, [P, c_int, P, P, P, c_int, c_int, c_int, P]),
     "lq_gemm_pick_splitk": (c_int, [c_int, c_int, c_int, c_int]),
     "lq_gemm_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
+    "lq_gemm_workspace_kind": (c_int, [c_int, c_int, c_int, c_int]),
     "lq_w4a8_gemm_i32": (c_int, [P, P, P, c_int, c_int, c_int, c_int, P, c_size_t, P]),
     "lq_w4a8_gemm_fused": (c_int, [P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, c_size_t, P]),
     "lq_i8_gemm_i32": (c_int, [P, P, P, c_int, c_int, c_int, P]),

@@ -4,6 +4,21 @@
 #include "lq_tc_ptx.cuh"
 
 namespace lq {
+__device__ __forceinline__ bool dbg_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded: gives up after ~2^22 polls so that a wrong experiment ends instead of hanging.
+__device__ __forceinline__ void dbg_wait(uint32_t bar, uint32_t parity, int mode) {
+  for (int i = 0; i < (1 << 22); ++i) {
+    if ((mode & 64) ? dbg_test_wait(bar, parity) : ptx::mbar_try_wait(bar, parity)) return;
+  }
+}
+}  // namespace lq
+
+namespace lq {
 
 // One CTA: `iters` groups of four 128 x N x 32 MMAs into the same accumulator, one commit per group
 // (like one k-step of the GEMM main loop), then a wait for the last commit.  out[blockIdx.x] =
@@ -122,7 +137,7 @@ __global__ void __launch_bounds__(32, 1) sync_cost_kernel(const uint8_t* src, lo
     for (int i = 0; i < 16; ++i) {
       ptx::mbar_expect_tx(b2, 8192);
       ptx::bulk_load(smem_u32(buf), src + (size_t)i * 8192, 8192, b2);
-      while (!ptx::mbar_try_wait(b2, (uint32_t)i & 1u)) {}
+      dbg_wait(b2, (uint32_t)i & 1u, 0);
     }
     t1 = clock64();
     out[5] = (t1 - t0) / 16;                             // expect_tx + 8 KB bulk copy round trip
@@ -136,7 +151,7 @@ __global__ void __launch_bounds__(32, 1) sync_cost_kernel(const uint8_t* src, lo
     for (int i = 0; i < 8; ++i) ptx::bulk_load(smem_u32(buf) + i * 1024, src + (size_t)i * 1024, 1024, b2);
     t1 = clock64();
     out[7] = (t1 - t0) / 8;
-    while (!ptx::mbar_try_wait(b2, 0u)) {}
+    dbg_wait(b2, 0u, 0);
   }
   __syncthreads();
 }
@@ -171,7 +186,7 @@ tma_stream_kernel(const uint8_t* src, int stage_bytes, int ns, int steps, long l
     int s = 0;
     uint32_t ph = 0;
     for (int i = 0; i < steps; ++i) {
-      while (!ptx::mbar_try_wait(smem_u32(&bars[32 + s]), ph ^ 1u)) {}
+      dbg_wait(smem_u32(&bars[32 + s]), ph ^ 1u, 0);
       ptx::mbar_expect_tx(smem_u32(&bars[s]), stage_bytes);
       ptx::bulk_load(base + s * stage_bytes, my + (size_t)i * stage_bytes, stage_bytes, smem_u32(&bars[s]));
       if (++s == ns) { s = 0; ph ^= 1u; }
@@ -180,7 +195,7 @@ tma_stream_kernel(const uint8_t* src, int stage_bytes, int ns, int steps, long l
     int s = 0;
     uint32_t ph = 0;
     for (int i = 0; i < steps; ++i) {
-      while (!ptx::mbar_try_wait(smem_u32(&bars[s]), ph)) {}
+      dbg_wait(smem_u32(&bars[s]), ph, 0);
       ptx::mbar_arrive(smem_u32(&bars[32 + s]));
       if (++s == ns) { s = 0; ph ^= 1u; }
     }
@@ -198,4 +213,167 @@ extern "C" LQ_API int lq_debug_tma_stream(const void* src, int stage_bytes, int 
   lq::tma_stream_kernel<<<ctas, 64, smem, lq::as_stream(stream)>>>(static_cast<const uint8_t*>(src), stage_bytes, ns,
                                                                    steps, cycles);
   return lq::check_launch("tma_stream_kernel");
+}
+
+namespace lq {
+// Skeleton of the GEMM hand-offs without any arithmetic, to cost the synchronisation structure:
+//   thread 0      producer: wait empty -> expect_tx + bulk copy
+//   warps 4..7    "dequant": lane 0 waits full, all 128 threads read 64 bytes, arrive empty,
+//                 (mode & 2) wait afree, arrive aready
+//   thread 32     (mode & 2) "MMA": wait full, wait aready, then release empty/afree either with
+//                 tcgen05.commit (mode & 4) or with plain arrives
+// empty count = 128 (+1 with the MMA thread).  nt = operand ring depth.
+__global__ void __launch_bounds__(256, 1)
+skeleton_kernel(const uint8_t* src, int stage_bytes, int ns, int nt, int steps, int mode, long long* cycles,
+                unsigned* sink) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 127u) & ~127u;
+  const uint8_t* gen = smem_raw + (base - raw_addr);
+  __shared__ uint64_t bars[128];   // full[32], empty[32], aready[32], afree[32]
+  const bool with_mma = mode & 2;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < ns; ++i) {
+      ptx::mbar_init(smem_u32(&bars[i]), 1);
+      ptx::mbar_init(smem_u32(&bars[32 + i]), ((mode & 8) ? 4 : 128) + (with_mma ? 1 : 0));
+    }
+    for (int i = 0; i < nt; ++i) {
+      ptx::mbar_init(smem_u32(&bars[64 + i]), (mode & 8) ? 4 : 128);
+      ptx::mbar_init(smem_u32(&bars[96 + i]), 1);
+    }
+    ptx::fence_mbar_init();
+  }
+  __syncthreads();
+  const long long t0 = clock64();
+  const uint8_t* my = (mode & 32) ? src + (size_t)(blockIdx.x & 7) * 64 * stage_bytes
+                                  : src + (size_t)blockIdx.x * steps * stage_bytes;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if ((mode & 256) ? warp == 0 : threadIdx.x == 0) {
+    int s = 0; uint32_t ph = 0;
+    for (int i = 0; i < steps; ++i) {
+      dbg_wait(smem_u32(&bars[32 + s]), ph ^ 1u, mode);
+      if (lane == 0) ptx::mbar_expect_tx(smem_u32(&bars[s]), stage_bytes);
+      const size_t off = (mode & 32) ? (size_t)(i & 63) * stage_bytes : (size_t)i * stage_bytes;
+      if (lane == 0) ptx::bulk_load(base + s * stage_bytes, my + off, stage_bytes, smem_u32(&bars[s]));
+      if (mode & 256) __syncwarp();
+      if (++s == ns) { s = 0; ph ^= 1u; }
+    }
+  } else if (((mode & 256) ? warp == 1 : threadIdx.x == 32) && with_mma) {
+    int s = 0, t = 0; uint32_t ph = 0, pht = 0;
+    for (int i = 0; i < steps; ++i) {
+      dbg_wait(smem_u32(&bars[s]), ph, mode);
+      dbg_wait(smem_u32(&bars[64 + t]), pht, mode);
+      if (lane == 0) {
+        if (mode & 4) {
+          ptx::tc_commit(smem_u32(&bars[32 + s]));
+          ptx::tc_commit(smem_u32(&bars[96 + t]));
+        } else {
+          ptx::mbar_arrive(smem_u32(&bars[32 + s]));
+          ptx::mbar_arrive(smem_u32(&bars[96 + t]));
+        }
+      }
+      if (mode & 256) __syncwarp();
+      if (++s == ns) { s = 0; ph ^= 1u; }
+      if (++t == nt) { t = 0; pht ^= 1u; }
+    }
+    if (lane == 0) cycles[blockIdx.x] = clock64() - t0;
+  } else if (warp >= 4) {
+    int s = 0, t = 0; uint32_t ph = 0, pht = 0;
+    unsigned acc = 0;
+    const int row = threadIdx.x - 128;
+    for (int i = 0; i < steps; ++i) {
+      if (mode & 128) dbg_wait(smem_u32(&bars[s]), ph, mode);
+      else { if (lane == 0) dbg_wait(smem_u32(&bars[s]), ph, mode); __syncwarp(); }
+      const uint4 v = *reinterpret_cast<const uint4*>(gen + s * stage_bytes + row * 16);
+      acc += v.x ^ v.y ^ v.z ^ v.w;
+      if (mode & 8) { __syncwarp(); if (lane == 0) ptx::mbar_arrive(smem_u32(&bars[32 + s])); }
+      else ptx::mbar_arrive(smem_u32(&bars[32 + s]));
+      if (with_mma) {
+        if (mode & 128) dbg_wait(smem_u32(&bars[96 + t]), pht ^ 1u, mode);
+        else { if (lane == 0) dbg_wait(smem_u32(&bars[96 + t]), pht ^ 1u, mode); __syncwarp(); }
+        if (mode & 8) { if (lane == 0) ptx::mbar_arrive(smem_u32(&bars[64 + t])); }
+        else ptx::mbar_arrive(smem_u32(&bars[64 + t]));
+      }
+      if (++s == ns) { s = 0; ph ^= 1u; }
+      if (++t == nt) { t = 0; pht ^= 1u; }
+    }
+    if (!with_mma && threadIdx.x == 128) cycles[blockIdx.x] = clock64() - t0;
+    if (acc == 0x12345678u) sink[0] = acc;
+  }
+  __syncthreads();
+}
+}  // namespace lq
+
+extern "C" LQ_API int lq_debug_skeleton(const void* src, int stage_bytes, int ns, int nt, int steps, int mode,
+                                        int ctas, long long* cycles, void* stream) {
+  if (ns < 1 || ns > 32 || nt < 1 || nt > 32 || stage_bytes % 16 || stage_bytes * ns > 200 * 1024) return LQ_ERR_BAD_ARG;
+  const int smem = stage_bytes * ns + 256;
+  cudaFuncSetAttribute(lq::skeleton_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 201 * 1024);
+  lq::skeleton_kernel<<<ctas, 256, smem, lq::as_stream(stream)>>>(static_cast<const uint8_t*>(src), stage_bytes, ns, nt,
+                                                                  steps, mode, cycles,
+                                                                  reinterpret_cast<unsigned*>(cycles + ctas));
+  return lq::check_launch("skeleton_kernel");
+}
+
+namespace lq {
+// Streaming test with each stage assembled from `rows` separate bulk copies (one per producer lane)
+// of `row_bytes` each, taken from rows that are `row_stride` bytes apart: the access pattern of a
+// row-major weight matrix fetched as short row pieces.  One consumer thread releases the stages.
+__global__ void __launch_bounds__(64, 1)
+tma_rows_kernel(const uint8_t* src, int rows, int row_bytes, long row_stride, int ns, int steps, int pieces_per_row,
+                long long* cycles) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 127u) & ~127u;
+  __shared__ uint64_t bars[64];
+  const int stage_bytes = rows * row_bytes;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < ns; ++i) {
+      ptx::mbar_init(smem_u32(&bars[i]), 1);
+      ptx::mbar_init(smem_u32(&bars[32 + i]), 1);
+    }
+    ptx::fence_mbar_init();
+  }
+  __syncthreads();
+  const long long t0 = clock64();
+  const int lane = threadIdx.x & 31;
+  if (threadIdx.x < 32) {
+    int s = 0;
+    uint32_t ph = 0;
+    for (int i = 0; i < steps; ++i) {
+      dbg_wait(smem_u32(&bars[32 + s]), ph ^ 1u, 0);
+      if (lane == 0) ptx::mbar_expect_tx(smem_u32(&bars[s]), stage_bytes);
+      __syncwarp();
+      if (lane < rows) {
+        // unit u = blockIdx.x * steps + i: row group u / pieces_per_row, piece u % pieces_per_row
+        const long u = (long)blockIdx.x * steps + i;
+        const long grp = u / pieces_per_row, piece = u % pieces_per_row;
+        const uint8_t* p = src + (grp * rows + lane) * row_stride + piece * row_bytes;
+        ptx::bulk_load(base + s * stage_bytes + lane * row_bytes, p, row_bytes, smem_u32(&bars[s]));
+      }
+      if (++s == ns) { s = 0; ph ^= 1u; }
+    }
+  } else if (threadIdx.x == 32) {
+    int s = 0;
+    uint32_t ph = 0;
+    for (int i = 0; i < steps; ++i) {
+      dbg_wait(smem_u32(&bars[s]), ph, 0);
+      ptx::mbar_arrive(smem_u32(&bars[32 + s]));
+      if (++s == ns) { s = 0; ph ^= 1u; }
+    }
+    cycles[blockIdx.x] = clock64() - t0;
+  }
+  __syncthreads();
+}
+}  // namespace lq
+
+extern "C" LQ_API int lq_debug_tma_rows(const void* src, int rows, int row_bytes, long row_stride, int ns, int steps,
+                                        int pieces_per_row, int ctas, long long* cycles, void* stream) {
+  if (rows < 1 || rows > 32 || ns < 1 || ns > 32 || row_bytes % 16 || (long)rows * row_bytes * ns > 200 * 1024)
+    return LQ_ERR_BAD_ARG;
+  const int smem = rows * row_bytes * ns + 256;
+  cudaFuncSetAttribute(lq::tma_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 201 * 1024);
+  lq::tma_rows_kernel<<<ctas, 64, smem, lq::as_stream(stream)>>>(static_cast<const uint8_t*>(src), rows, row_bytes,
+                                                                 row_stride, ns, steps, pieces_per_row, cycles);
+  return lq::check_launch("tma_rows_kernel");
 }

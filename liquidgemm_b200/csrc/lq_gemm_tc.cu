@@ -46,9 +46,14 @@
 
 #include "lq_common.cuh"
 #include "lq_tc_ptx.cuh"
+#include "lq_sched.cuh"
 
 namespace lq {
 
+int tile_pick_splits(int M, int N, int K);                                   // lq_gemm_tile.cu
+size_t tile_workspace_bytes(int M, int N, int splits);                       // lq_gemm_tile.cu
+int run_tile_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, void* out, int out_mode,
+                  int M, int N, int K, int splits, void* ws, size_t ws_bytes, cudaStream_t st);  // lq_gemm_tile.cu
 int launch_gemv_plain_f32(const int8_t* x, const uint8_t* nibbles, const uint8_t* s_u8,
                           const uint8_t* off_a, const float* ascale, const float* s1, float* y, int M,
                           int N, int K, int G, cudaStream_t st);  // lq_gemv.cu
@@ -96,89 +101,16 @@ template <int BN, int NS, int NT, int NACC, int WSRC>
 struct TcCfg {
   static constexpr int kXStage = BN * 128;
   static constexpr int kWStage = WSRC == kBlob ? kTileBytes : WSRC == kRowMajor ? kRowBoxBytes : kI8TileBytes;
-  static constexpr int kACols = WSRC == kInt8 ? 0 : 32 * NT;
+  static constexpr int kACols = WSRC == kInt8 ? 0 : 32 * NS;   // one operand stage per shared-memory stage
   static constexpr int kColsNeeded = NACC * BN + kACols;
   static constexpr int kTmemCols = kColsNeeded <= 32 ? 32 : kColsNeeded <= 64 ? 64 : kColsNeeded <= 128 ? 128
                                    : kColsNeeded <= 256 ? 256 : 512;
-  static constexpr int kNumBars = 2 * NS + 2 * NT + 2 * NACC;
+  static constexpr int kNumBars = 3 * NS + 2 * NACC;
   static constexpr int kBarBytes = kNumBars * 8 + 16;
   static constexpr int kSmemBytes = 1024 /* alignment slack */ + NS * (kXStage + kWStage) + kBarBytes;
   static_assert(kColsNeeded <= 512, "tensor memory budget exceeded");
   static_assert(kSmemBytes <= 232448, "shared memory budget exceeded");
   static_assert(kSmemBytes > 116 * 1024, "one CTA per SM is assumed (tensor memory is allocated whole)");
-};
-
-// One unit of a CTA's work: k-steps [kb, ke) of output tile `tile`.
-struct Segment {
-  int tile, kb, ke, slot;
-  bool whole;   // covers the tile's full K: no cross-CTA reduction
-};
-
-// Enumerates the segments of this CTA; every role walks the same sequence.  32-bit arithmetic
-// throughout (tiles * k-steps stays far below 2^31 for any problem that fits the GPU).
-struct SegmentWalk {
-  int kt, split, grid;
-  unsigned u, u_end;   // stream-K: current / last k-step of the range
-  unsigned q, r;       // stream-K: base range length and number of CTAs with one extra k-step
-  unsigned w, w_end;   // fixed split: current / last work item
-
-  __device__ SegmentWalk(const GemmArgs& a, unsigned cta, unsigned grid_) {
-    kt = a.kt_total;
-    split = a.fixed_split;
-    grid = (int)grid_;
-    const unsigned tiles = (unsigned)(a.n_tiles * a.m_tiles);
-    if (split == 0) {
-      const unsigned total = tiles * (unsigned)kt;
-      q = total / grid_;
-      r = total - q * grid_;
-      u = cta * q + (cta < r ? cta : r);
-      u_end = u + q + (cta < r ? 1u : 0u);
-      w = w_end = 0;
-    } else {
-      w = cta;
-      w_end = tiles * (unsigned)split;
-      u = u_end = q = r = 0;
-    }
-  }
-  __device__ int owner_of(unsigned unit) const {   // CTA whose stream-K range contains `unit`
-    const unsigned big = r * (q + 1);
-    return unit < big ? (int)(unit / (q + 1)) : (int)(r + (unit - big) / q);
-  }
-  __device__ bool next(Segment& s) {
-    if (split == 0) {
-      if (u >= u_end) return false;
-      s.tile = (int)(u / (unsigned)kt);
-      s.kb = (int)(u - (unsigned)s.tile * (unsigned)kt);
-      const int left = (int)(u_end - u);
-      s.ke = (kt - s.kb) < left ? kt : s.kb + left;
-      s.whole = (s.kb == 0 && s.ke == kt);
-      s.slot = s.whole ? 0 : owner_of((unsigned)s.tile * (unsigned)kt);
-      u += (unsigned)(s.ke - s.kb);
-      return true;
-    }
-    if (w >= w_end) return false;
-    s.tile = (int)(w / (unsigned)split);
-    const int si = (int)(w - (unsigned)s.tile * (unsigned)split);
-    s.kb = (si * kt) / split;
-    s.ke = ((si + 1) * kt) / split;
-    s.whole = (split == 1);
-    s.slot = s.tile;
-    w += (unsigned)grid;
-    return true;
-  }
-};
-
-// Position in a ring of N stages: stage index and the parity of the pass over the ring.
-template <int N>
-struct Ring {
-  int s = 0;
-  uint32_t ph = 0;
-  __device__ __forceinline__ void advance() {
-    if (++s == N) {
-      s = 0;
-      ph ^= 1u;
-    }
-  }
 };
 
 // Bounded barrier wait performed by lane 0 on behalf of a converged warp.
@@ -209,9 +141,8 @@ w4a8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
   const uint32_t bars = ws + NS * Cfg::kWStage;
   const uint32_t bar_full = bars;                            // [NS] both TMA copies of the stage landed
   const uint32_t bar_empty = bar_full + NS * 8;              // [NS] stage may be overwritten
-  const uint32_t bar_aready = bar_empty + NS * 8;            // [NT] dequantised operand is in TMEM
-  const uint32_t bar_afree = bar_aready + NT * 8;            // [NT] MMAs that read the operand are done
-  const uint32_t bar_accfull = bar_afree + NT * 8;           // [NACC] accumulator final
+  const uint32_t bar_aready = bar_empty + NS * 8;            // [NS] dequantised operand is in TMEM
+  const uint32_t bar_accfull = bar_aready + NS * 8;          // [NACC] accumulator final
   const uint32_t bar_accempty = bar_accfull + NACC * 8;      // [NACC] accumulator drained
   const uint32_t tmem_slot = bar_accempty + NACC * 8;
   uint8_t* gen_bars = smem + (bars - base);
@@ -226,11 +157,8 @@ w4a8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
   if (threadIdx.x == 0) {
     for (int s = 0; s < NS; ++s) {
       ptx::mbar_init(bar_full + 8 * s, 2);                   // one expect_tx arrival per producer thread
-      ptx::mbar_init(bar_empty + 8 * s, kDequant ? 129 : 1);
-    }
-    for (int t = 0; t < NT; ++t) {
-      ptx::mbar_init(bar_aready + 8 * t, 128);
-      ptx::mbar_init(bar_afree + 8 * t, 1);
+      ptx::mbar_init(bar_empty + 8 * s, 1);                    // the MMA warp's commit
+      ptx::mbar_init(bar_aready + 8 * s, 128);                 // the 128 threads of one dequant set
     }
     for (int b = 0; b < NACC; ++b) {
       ptx::mbar_init(bar_accfull + 8 * b, 1);
@@ -248,40 +176,41 @@ w4a8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_p;
-  const uint32_t tmem_a = tmem_base + NACC * BN;   // NT operand stages of 32 columns behind the accumulators
+  const uint32_t tmem_a = tmem_base + NACC * BN;   // NS operand stages of 32 columns behind the accumulators
   if (threadIdx.x == 0) LQ_TRACE(kTrSetupDone, LQ_CLK() - t_begin);
 
   if (warp == 0 || warp == 2) {
     // ------------------------------------------------------------------ producers
-    // warp 0 streams the weight tiles, warp 2 the activation boxes; each thread waits for the
-    // stage to be free and announces its own byte count on the stage's full barrier.
-    if (lane == 0) {
-      const bool weights = (warp == 0);
-      SegmentWalk walk(args, blockIdx.x, gridDim.x);
-      Segment sg;
-      Ring<NS> ring;
-      int issued = 0;
-      bool ok = true;
-      long long w_empty = 0, t_issue = 0;
-      while (ok && walk.next(sg)) {
-        const int nt = sg.tile % args.n_tiles, mt = sg.tile / args.n_tiles;
-        const uint8_t* wsrc = WSRC == kBlob ? args.blob + ((size_t)nt * args.kt_total + sg.kb) * kTileBytes : nullptr;
-        for (int kt = sg.kb; kt < sg.ke; ++kt) {
-          const long long tw0 = LQ_CLK();
-          if (!ptx::mbar_wait_bounded(bar_empty + 8 * ring.s, ring.ph ^ 1u, kWaitLimitNs)) {
-            atomicExch(args.status, 101);
-            ok = false;
-            break;
-          }
-          const long long ti0 = LQ_CLK();
-          w_empty += ti0 - tw0;
-          if (issued == 0 && weights) LQ_TRACE(kTrFirstTma, ti0 - t_begin);
-          const uint32_t full = bar_full + 8 * ring.s;
+    // warp 0 streams the weight tiles, warp 2 the activation boxes.  The whole warp walks the loop
+    // and polls (a warp that stays converged costs far less than one lane spinning while 31 wait);
+    // lane 0 alone announces the byte count and issues the copy.
+    const bool weights = (warp == 0);
+    if ((args.debug_skip & 16) && lane != 0) goto role_done;   // experiment: single-lane producer
+    SegmentWalk walk(SchedArgs{args.kt_total, args.n_tiles, args.m_tiles, args.fixed_split}, blockIdx.x, gridDim.x);
+    Segment sg;
+    Ring<NS> ring;
+    int issued = 0;
+    bool ok = true;
+    long long w_empty = 0, t_issue = 0;
+    while (ok && walk.next(sg)) {
+      const int nt = sg.tile % args.n_tiles, mt = sg.tile / args.n_tiles;
+      const uint8_t* wsrc = WSRC == kBlob ? args.blob + ((size_t)nt * args.kt_total + sg.kb) * kTileBytes : nullptr;
+      for (int kt = sg.kb; kt < sg.ke; ++kt) {
+        const long long tw0 = LQ_CLK();
+        if (!ptx::mbar_wait_bounded(bar_empty + 8 * ring.s, ring.ph ^ 1u, kWaitLimitNs)) {
+          atomicExch(args.status, 101);
+          ok = false;
+          break;
+        }
+        const long long ti0 = LQ_CLK();
+        w_empty += ti0 - tw0;
+        if (issued == 0 && weights && lane == 0) LQ_TRACE(kTrFirstTma, ti0 - t_begin);
+        const uint32_t full = bar_full + 8 * ring.s;
+        if (lane == 0) {
           if (weights) {
             ptx::mbar_expect_tx(full, Cfg::kWStage);
             if (WSRC == kBlob) {
               ptx::bulk_load(ws + ring.s * Cfg::kWStage, wsrc, kTileBytes, full);
-              wsrc += kTileBytes;
             } else if (WSRC == kRowMajor) {
               ptx::tensor_load_2d(ws + ring.s * Cfg::kWStage, &tmap_w, kt * 64, nt * 128, full);
             } else {
@@ -291,66 +220,65 @@ w4a8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
             ptx::mbar_expect_tx(full, Cfg::kXStage);
             ptx::tensor_load_2d(xs + ring.s * Cfg::kXStage, &tmap_x, kt * 128, mt * BN, full);
           }
-          t_issue += LQ_CLK() - ti0;
-          ring.advance();
-          ++issued;
         }
+        if (WSRC == kBlob) wsrc += kTileBytes;
+        t_issue += LQ_CLK() - ti0;
+        ring.advance();
+        ++issued;
       }
-      if (weights) {
-        LQ_TRACE(kTrLastTma, LQ_CLK() - t_begin);
-        LQ_TRACE(kTrProdWaitEmpty, w_empty);
-        LQ_TRACE(kTrProdIssue, t_issue);
-        LQ_TRACE(kTrKsteps, issued);
-      }
-      if (!ok) {
-        // copies already issued still write shared memory: let them land before the CTA exits
-        Ring<NS> back;
-        const int first = issued > NS ? issued - NS : 0;
-        for (int i = 0; i < issued; ++i) {
-          if (i >= first) ptx::mbar_wait_bounded(bar_full + 8 * back.s, back.ph, kWaitLimitNs);
-          back.advance();
-        }
+    }
+    if (weights && lane == 0) {
+      LQ_TRACE(kTrLastTma, LQ_CLK() - t_begin);
+      LQ_TRACE(kTrProdWaitEmpty, w_empty);
+      LQ_TRACE(kTrProdIssue, t_issue);
+      LQ_TRACE(kTrKsteps, issued);
+    }
+    if (!ok) {
+      // copies already issued still write shared memory: let them land before the CTA exits
+      Ring<NS> back;
+      const int first = issued > NS ? issued - NS : 0;
+      for (int i = 0; i < issued; ++i) {
+        if (i >= first) ptx::mbar_wait_bounded(bar_full + 8 * back.s, back.ph, kWaitLimitNs);
+        back.advance();
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issue
-    if (lane == 0) {
-      constexpr uint32_t idesc = ptx::idesc_i8(BN);
-      SegmentWalk walk(args, blockIdx.x, gridDim.x);
-      Segment sg;
-      Ring<NS> ring;
-      Ring<NT> aring;
-      Ring<NACC> accring;
-      int seg = 0;
-      bool ok = true, first = true;
-      long long w_a = 0, w_full = 0, w_acc = 0, t_mma = 0;
-      while (ok && walk.next(sg)) {
-        const long long ta0 = LQ_CLK();
-        if (!ptx::mbar_wait_bounded(bar_accempty + 8 * accring.s, accring.ph ^ 1u, kWaitLimitNs)) {
-          atomicExch(args.status, 106);
-          ok = false;
+    // The whole warp waits; lane 0 issues.  With dequantisation the only wait per k-step is on the
+    // operand barrier: the dequant warps saw the stage's full barrier (weights and activations)
+    // before they produced the operand, so "operand ready" implies "activations landed".
+    constexpr uint32_t idesc = ptx::idesc_i8(BN);
+    if ((args.debug_skip & 32) && lane != 0) goto role_done;   // experiment: single-lane MMA role
+    SegmentWalk walk(SchedArgs{args.kt_total, args.n_tiles, args.m_tiles, args.fixed_split}, blockIdx.x, gridDim.x);
+    Segment sg;
+    Ring<NS> ring;
+    Ring<NACC> accring;
+    int seg = 0;
+    bool ok = true, first = true;
+    long long w_a = 0, w_acc = 0, t_mma = 0;
+    while (ok && walk.next(sg)) {
+      const long long ta0 = LQ_CLK();
+      if (!ptx::mbar_wait_bounded(bar_accempty + 8 * accring.s, accring.ph ^ 1u, kWaitLimitNs)) {
+        atomicExch(args.status, 106);
+        ok = false;
+        break;
+      }
+      w_acc += LQ_CLK() - ta0;
+      ptx::tc_fence_after();
+      const uint32_t tmem_acc = tmem_base + accring.s * BN;
+      for (int kt = sg.kb; kt < sg.ke; ++kt) {
+        const long long tf0 = LQ_CLK();
+        ok = ptx::mbar_wait_bounded((kDequant ? bar_aready : bar_full) + 8 * ring.s, ring.ph, kWaitLimitNs);
+        const long long tm0 = LQ_CLK();
+        w_a += tm0 - tf0;
+        if (!ok) {
+          atomicExch(args.status, 102);
           break;
         }
-        w_acc += LQ_CLK() - ta0;
+        if (first && lane == 0) LQ_TRACE(kTrMmaFirst, tm0 - t_begin);
+        first = false;
         ptx::tc_fence_after();
-        const uint32_t tmem_acc = tmem_base + accring.s * BN;
-        for (int kt = sg.kb; kt < sg.ke; ++kt) {
-          const long long tf0 = LQ_CLK();
-          ok = ptx::mbar_wait_bounded(bar_full + 8 * ring.s, ring.ph, kWaitLimitNs);
-          const long long tf1 = LQ_CLK();
-          if (ok && kDequant) ok = ptx::mbar_wait_bounded(bar_aready + 8 * aring.s, aring.ph, kWaitLimitNs);
-          const long long tm0 = LQ_CLK();
-          w_full += tf1 - tf0;
-          w_a += tm0 - tf1;
-          if (!ok) {
-            atomicExch(args.status, 102);
-            break;
-          }
-          if (first) {
-            LQ_TRACE(kTrMmaFirst, tm0 - t_begin);
-            first = false;
-          }
-          ptx::tc_fence_after();
+        if (lane == 0) {
           const uint32_t xb = xs + ring.s * Cfg::kXStage;
           if (!(args.debug_skip & 4)) {
 #pragma unroll
@@ -358,26 +286,27 @@ w4a8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
               const uint64_t bdesc = ptx::smem_desc_sw128(xb + j * 32);
               const uint32_t accumulate = (kt > sg.kb || j > 0) ? 1u : 0u;
               if (kDequant) {
-                ptx::mma_i8_ts(tmem_acc, tmem_a + aring.s * 32 + j * 8, bdesc, idesc, accumulate);
+                ptx::mma_i8_ts(tmem_acc, tmem_a + ring.s * 32 + j * 8, bdesc, idesc, accumulate);
               } else {
                 const uint64_t adesc = ptx::smem_desc_sw128(ws + ring.s * Cfg::kWStage + j * 32);
                 ptx::mma_i8_ss(tmem_acc, adesc, bdesc, idesc, accumulate);
               }
             }
           }
+          // one commit recycles the shared-memory stage and the tensor-memory operand stage: the
+          // dequant warps have finished with both before they signalled "operand ready"
           ptx::tc_commit(bar_empty + 8 * ring.s);
-          if (kDequant) ptx::tc_commit(bar_afree + 8 * aring.s);
-          t_mma += LQ_CLK() - tm0;
-          ring.advance();
-          aring.advance();
         }
-        if (ok) ptx::tc_commit(bar_accfull + 8 * accring.s);
-        accring.advance();
-        ++seg;
+        t_mma += LQ_CLK() - tm0;
+        ring.advance();
       }
+      if (ok && lane == 0) ptx::tc_commit(bar_accfull + 8 * accring.s);
+      accring.advance();
+      ++seg;
+    }
+    if (lane == 0) {
       LQ_TRACE(kTrMmaLast, LQ_CLK() - t_begin);
       LQ_TRACE(kTrMmaWaitA, w_a);
-      LQ_TRACE(kTrMmaWaitFull, w_full);
       LQ_TRACE(kTrMmaWaitAcc, w_acc);
       LQ_TRACE(kTrSegments, seg);
       LQ_TRACE(kTrMmaIssue, t_mma);
@@ -385,7 +314,11 @@ w4a8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
   } else if ((warp >= 4 && warp < 8) || warp >= 12) {
     // ------------------------------------------------------------------ dequant
     // Two sets of four warps (4..7 and 12..15) take alternate k-steps, so each set has two k-step
-    // periods to hide its shared-load, tcgen05.st and barrier latencies.
+    // periods to hide its shared-load and tcgen05.st latencies.  Operand stage s lives in tensor
+    // memory columns [32 s, 32 s + 32) and is tied to shared-memory stage s: when the stage's full
+    // barrier fires for k-step i, the producer had seen the commit of k-step i - NS, so the MMAs
+    // that read the previous contents of both are complete and no separate "operand free"
+    // barrier is needed.
     if (kDequant) {
       const int my_parity = warp >= 12 ? 1 : 0;
       int step_parity = 0;
@@ -393,13 +326,11 @@ w4a8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
       const int row = quad * 32 + lane;        // weight row inside the tile == TMEM lane
       const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
       const int G = args.K >> 6;
-      SegmentWalk walk(args, blockIdx.x, gridDim.x);
+      SegmentWalk walk(SchedArgs{args.kt_total, args.n_tiles, args.m_tiles, args.fixed_split}, blockIdx.x, gridDim.x);
       Segment sg;
       Ring<NS> ring;
-      Ring<NT> aring;
-      int pending = -1;                        // operand stage whose tcgen05.st are still in flight
       bool ok = true, first = true;
-      long long w_full = 0, w_free = 0, t_comp = 0;
+      long long w_full = 0, t_comp = 0;
       const bool tracer = (threadIdx.x == 128);
       while (ok && walk.next(sg)) {
         const int nt = sg.tile % args.n_tiles;
@@ -409,7 +340,6 @@ w4a8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
           if (step_parity != my_parity) {        // the other set's k-step
             step_parity ^= 1;
             ring.advance();
-            aring.advance();
             continue;
           }
           step_parity ^= 1;
@@ -420,9 +350,7 @@ w4a8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
             meta = (sp & 0xffu) | ((op & 0xffu) << 8) | ((sp >> 8) << 16) | ((op >> 8) << 24);
           }
           const long long td0 = LQ_CLK();
-          // one lane polls, the warp follows: 128 threads polling the same barrier would crowd the
-          // shared-memory pipeline that the other roles' barrier operations also go through
-          if (!warp_wait(bar_full + 8 * ring.s, ring.ph, lane)) {
+          if (!ptx::mbar_wait_bounded(bar_full + 8 * ring.s, ring.ph, kWaitLimitNs)) {
             atomicExch(args.status, 103);
             ok = false;
             break;
@@ -431,6 +359,7 @@ w4a8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
           w_full += td1 - td0;
           if (first && tracer) LQ_TRACE(kTrDeqFirst, td1 - t_begin);
           first = false;
+          ptx::tc_fence_after();
           const uint8_t* wst = smem + (ws - base) + ring.s * Cfg::kWStage;
           uint4 ch[4];
           if (WSRC == kBlob) {
@@ -444,25 +373,6 @@ w4a8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
 #pragma unroll
             for (int c = 0; c < 4; ++c) ch[c] = *reinterpret_cast<const uint4*>(wst + row * 64 + ((c ^ sw) << 4));
           }
-          // The stores of the previous k-step have had the barrier wait and the shared loads above
-          // to complete: publish that operand stage now.
-          if (pending >= 0) {
-            ptx::tc_wait_st();
-            ptx::tc_fence_before();
-            ptx::mbar_arrive(bar_aready + 8 * pending);
-          }
-          ptx::mbar_arrive(bar_empty + 8 * ring.s);   // after the loads above have returned their data
-
-          const long long td2 = LQ_CLK();
-          if (!warp_wait(bar_afree + 8 * aring.s, aring.ph ^ 1u, lane)) {
-            atomicExch(args.status, 104);
-            ok = false;
-            pending = -1;
-            break;
-          }
-          const long long td3 = LQ_CLK();
-          w_free += td3 - td2;
-          ptx::tc_fence_after();
           const uint32_t step0 = meta & 0xffu, a0 = ((meta >> 8) & 0xffu) * 0x01010101u;
           const uint32_t step1 = (meta >> 16) & 0xffu, a1 = (meta >> 24) * 0x01010101u;
           uint32_t v[32];
@@ -477,22 +387,20 @@ w4a8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
               v[8 * c + 2 * h + 1] = lqq_dequant4((pk[h] >> 4) & 0x0F0F0F0Fu, step, ab);
             }
           }
-          if (!(args.debug_skip & 1)) ptx::tmem_st32(tmem_a + lane_addr + aring.s * 32, v);
-          pending = aring.s;
-          t_comp += LQ_CLK() - td3;
+          if (!(args.debug_skip & 1)) ptx::tmem_st32(tmem_a + lane_addr + ring.s * 32, v);
+          // Publish at once: the other dequant set covers the next k-step while these stores drain.
+          // (Deferring this to the set's next iteration would tie MMA i to the arrival of the TMA
+          // data of k-step i + 2 and eat two stages of prefetch depth.)
+          ptx::tc_wait_st();
+          ptx::tc_fence_before();
+          ptx::mbar_arrive(bar_aready + 8 * ring.s);
+          t_comp += LQ_CLK() - td1;
           ring.advance();
-          aring.advance();
         }
-      }
-      if (pending >= 0) {
-        ptx::tc_wait_st();
-        ptx::tc_fence_before();
-        ptx::mbar_arrive(bar_aready + 8 * pending);
       }
       if (tracer) {
         LQ_TRACE(kTrDeqLast, LQ_CLK() - t_begin);
         LQ_TRACE(kTrDeqWaitFull, w_full);
-        LQ_TRACE(kTrDeqWaitFree, w_free);
         LQ_TRACE(kTrDeqCompute, t_comp);
       }
     }
@@ -502,7 +410,7 @@ w4a8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
     const int row = quad * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
     const int et = threadIdx.x - 256;          // 0..127 inside the epilogue group
-    SegmentWalk walk(args, blockIdx.x, gridDim.x);
+    SegmentWalk walk(SchedArgs{args.kt_total, args.n_tiles, args.m_tiles, args.fixed_split}, blockIdx.x, gridDim.x);
     Segment sg;
     Ring<NACC> accring;
     int seg = 0;
@@ -662,6 +570,7 @@ w4a8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
     }
   }
 
+role_done:
   ptx::tc_fence_before();
   __syncthreads();
   if (threadIdx.x == 0) LQ_TRACE(kTrExit, LQ_CLK() - t_begin);
@@ -694,7 +603,7 @@ static EncodeTiledFn encode_fn() {
 
 // Tensor map over a row-major byte matrix [rows, row_bytes] with a (box_rows x box_bytes) box whose
 // rows are stored with the swizzle that matches their length; rows out of range read as zero.
-static int make_byte_matrix_map(CUtensorMap* map, const void* ptr, long rows, long row_bytes, int box_rows,
+int make_byte_matrix_map(CUtensorMap* map, const void* ptr, long rows, long row_bytes, int box_rows,
                                 int box_bytes) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) {
@@ -719,7 +628,10 @@ static int make_byte_matrix_map(CUtensorMap* map, const void* ptr, long rows, lo
 static long long* g_trace_ptr = nullptr;   // set by lq_debug_set_trace (pipeline studies only)
 static int g_debug_skip = 0;
 
-static int pick_bn(int M) {
+static int pick_bn(int M, int K = 0) {
+  // long K amortises an exposed epilogue: one 256-token accumulator (best MMA rate, fewest token
+  // re-reads); short K: two 192-token accumulators so that the epilogue overlaps the next tile
+  if (M > 128 && K >= 8192) return 256;
   if (M <= 16) return 16;
   if (M <= 32) return 32;
   if (M <= 64) return 64;
@@ -728,6 +640,7 @@ static int pick_bn(int M) {
 }
 
 struct Plan {
+  int cfg;   // kernel configuration key (differs from bn only in experiments)
   int bn, n_tiles, m_tiles, grid, fixed_split;
   long tiles;
   size_t slots, ws_bytes;
@@ -736,7 +649,8 @@ struct Plan {
 // splitk: 0 = stream-K over one CTA per SM, 1 = whole tiles only, S > 1 = every tile cut into S ranges.
 static Plan make_plan(int M, int N, int K, int splitk) {
   Plan p;
-  p.bn = pick_bn(M);
+  p.bn = pick_bn(M, K);
+  p.cfg = p.bn;
   p.n_tiles = (N + 127) / 128;
   p.m_tiles = (M + p.bn - 1) / p.bn;
   p.tiles = (long)p.n_tiles * p.m_tiles;
@@ -774,22 +688,25 @@ static int launch_cfg(const CUtensorMap& tx, const CUtensorMap& tw, const GemmAr
 template <int WSRC>
 static int dispatch_bn(int bn, const CUtensorMap& tx, const CUtensorMap& tw, const GemmArgs& a, int grid,
                        cudaStream_t st) {
-  constexpr int NT = WSRC == kInt8 ? 1 : 4;
+  constexpr int NT = 1;   // unused: operand stages follow the shared-memory ring
   if constexpr (WSRC == kInt8) {
     switch (bn) {
       case 16: return launch_cfg<16, 9, NT, 2, WSRC>(tx, tw, a, grid, st);
       case 32: return launch_cfg<32, 9, NT, 2, WSRC>(tx, tw, a, grid, st);
       case 64: return launch_cfg<64, 8, NT, 2, WSRC>(tx, tw, a, grid, st);
       case 128: return launch_cfg<128, 6, NT, 2, WSRC>(tx, tw, a, grid, st);
+      case 256: return launch_cfg<256, 4, NT, 1, WSRC>(tx, tw, a, grid, st);
       default: return launch_cfg<192, 5, NT, 2, WSRC>(tx, tw, a, grid, st);
     }
   } else {
+    // tensor memory: 2 * BN accumulator columns + 32 * NS operand columns <= 512
     switch (bn) {
-      case 16: return launch_cfg<16, 16, NT, 2, WSRC>(tx, tw, a, grid, st);
+      case 16: return launch_cfg<16, 14, NT, 2, WSRC>(tx, tw, a, grid, st);
       case 32: return launch_cfg<32, 14, NT, 2, WSRC>(tx, tw, a, grid, st);
       case 64: return launch_cfg<64, 12, NT, 2, WSRC>(tx, tw, a, grid, st);
       case 128: return launch_cfg<128, 8, NT, 2, WSRC>(tx, tw, a, grid, st);
-      default: return launch_cfg<192, 6, NT, 2, WSRC>(tx, tw, a, grid, st);
+      case 256: return launch_cfg<256, 5, NT, 1, WSRC>(tx, tw, a, grid, st);
+      default: return launch_cfg<192, 4, NT, 2, WSRC>(tx, tw, a, grid, st);
     }
   }
 }
@@ -831,7 +748,7 @@ static int run_gemm(const int8_t* x, const void* w, const uint8_t* s_u8, const u
   a.trace = g_trace_ptr;
   a.debug_skip = g_debug_skip;
   if (!a.status) return LQ_ERR_CUDA;
-  return dispatch_bn<WSRC>(p.bn, tx, tw, a, p.grid, st);
+  return dispatch_bn<WSRC>(p.cfg, tx, tw, a, p.grid, st);
 }
 
 }  // namespace lq
@@ -859,31 +776,60 @@ int lq_gemm_pick_splitk(int M, int N, int K, int env_override) {
   return 0;
 }
 
+// Which kernel serves (M, splitk): the two-CTAs-per-SM decode-tile kernel with `splits` int32 planes
+// (M <= 128), or the persistent kernel (stream-K for splitk 0 / -1, fixed split otherwise).
+struct Route {
+  bool tile;
+  int splits;
+};
+static Route route_for(int M, int N, int K, int splitk) {
+  const int kt = K / 128;
+  if (splitk == -1) return {false, 0};
+  if (M <= 128) {
+    int S = splitk > 0 ? splitk : tile_pick_splits(M, N, K);
+    if (S > kt) S = kt;
+    return {true, S < 1 ? 1 : S};
+  }
+  return {false, splitk};
+}
+
 size_t lq_gemm_workspace_bytes(int M, int N, int K, int splitk) {
   if (M <= 0 || N <= 0 || K < 128) return 0;
-  return make_plan(M, N, K, splitk).ws_bytes;
+  const Route r = route_for(M, N, K, splitk);
+  return r.tile ? tile_workspace_bytes(M, N, r.splits) : make_plan(M, N, K, r.splits).ws_bytes;
+}
+
+int lq_gemm_workspace_kind(int M, int N, int K, int splitk) {
+  if (lq_gemm_workspace_bytes(M, N, K, splitk) == 0) return 0;
+  return route_for(M, N, K, splitk).tile ? 1 : 2;
+}
+
+static int blob_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, void* out, int out_mode,
+                     int M, int N, int K, int splitk, void* ws, size_t ws_bytes, cudaStream_t st) {
+  if (!x || !blob || !out || M < 0 || N <= 0 || K <= 0) return LQ_ERR_BAD_ARG;
+  if (K % 128) return LQ_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(blob)) % 16) return LQ_ERR_BAD_ARG;
+  if (M == 0) return LQ_OK;
+  const Route r = route_for(M, N, K, splitk);
+  if (r.tile) {
+    if (int rc = lq_check_device()) return rc;
+    return run_tile_gemm(x, blob, ascale, s1, out, out_mode, M, N, K, r.splits, ws, ws_bytes, st);
+  }
+  return run_gemm<kBlob>(x, blob, nullptr, nullptr, ascale, s1, out, out_mode, M, N, K, r.splits, ws, ws_bytes, st);
 }
 
 int lq_w4a8_gemm_i32(const int8_t* x_i8, const uint8_t* blob, int32_t* acc, int M, int N, int K, int splitk,
                      void* workspace, size_t workspace_bytes, void* stream) {
-  if (!x_i8 || !blob || !acc || M < 0 || N <= 0 || K <= 0) return LQ_ERR_BAD_ARG;
-  if (K % 128) return LQ_ERR_SHAPE;
-  if ((reinterpret_cast<uintptr_t>(x_i8) | reinterpret_cast<uintptr_t>(blob)) % 16) return LQ_ERR_BAD_ARG;
-  if (M == 0) return LQ_OK;
-  return run_gemm<kBlob>(x_i8, blob, nullptr, nullptr, nullptr, nullptr, acc, kOutI32, M, N, K, splitk, workspace,
-                         workspace_bytes, as_stream(stream));
+  return blob_gemm(x_i8, blob, nullptr, nullptr, acc, kOutI32, M, N, K, splitk, workspace, workspace_bytes,
+                   as_stream(stream));
 }
 
 int lq_w4a8_gemm_fused(const int8_t* x_i8, const uint8_t* blob, const float* ascale, const float* s1, void* y,
                        int out_dtype, int M, int N, int K, int splitk, void* workspace, size_t workspace_bytes,
                        void* stream) {
-  if (!x_i8 || !blob || !y || !ascale || !s1 || M < 0 || N <= 0 || K <= 0) return LQ_ERR_BAD_ARG;
-  if (out_dtype < 0 || out_dtype > 2) return LQ_ERR_BAD_ARG;
-  if (K % 128) return LQ_ERR_SHAPE;
-  if ((reinterpret_cast<uintptr_t>(x_i8) | reinterpret_cast<uintptr_t>(blob)) % 16) return LQ_ERR_BAD_ARG;
-  if (M == 0) return LQ_OK;
-  return run_gemm<kBlob>(x_i8, blob, nullptr, nullptr, ascale, s1, y, out_dtype, M, N, K, splitk, workspace,
-                         workspace_bytes, as_stream(stream));
+  if (!ascale || !s1 || out_dtype < 0 || out_dtype > 2) return LQ_ERR_BAD_ARG;
+  return blob_gemm(x_i8, blob, ascale, s1, y, out_dtype, M, N, K, splitk, workspace, workspace_bytes,
+                   as_stream(stream));
 }
 
 int lq_w4a8_gemm_rowmajor(const int8_t* x_i8, const uint8_t* gpack, const uint8_t* s_u8, const uint8_t* offset_a,
@@ -895,7 +841,8 @@ int lq_w4a8_gemm_rowmajor(const int8_t* x_i8, const uint8_t* gpack, const uint8_
   if (K % 128) return LQ_ERR_SHAPE;
   if ((reinterpret_cast<uintptr_t>(x_i8) | reinterpret_cast<uintptr_t>(gpack)) % 16) return LQ_ERR_BAD_ARG;
   if (M == 0) return LQ_OK;
-  return run_gemm<kRowMajor>(x_i8, gpack, s_u8, offset_a, ascale, s1, y, out_dtype, M, N, K, splitk, workspace,
+  (void)splitk;   // always stream-K: workspace = lq_gemm_workspace_bytes(M, N, K, -1)
+  return run_gemm<kRowMajor>(x_i8, gpack, s_u8, offset_a, ascale, s1, y, out_dtype, M, N, K, 0, workspace,
                              workspace_bytes, as_stream(stream));
 }
 

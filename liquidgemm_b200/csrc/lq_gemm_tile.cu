@@ -1,0 +1,348 @@
+// Decode-tile W4A8 GEMM (17 <= M <= 128): one 128-channel x BN-token tile per CTA, two CTAs per SM.
+//
+// The persistent stream-K kernel keeps one CTA per SM; for a handful of k-steps per CTA its
+// single MMA-issuing thread and the cross-CTA reduction tail dominate.  With small token tiles the
+// shared-memory and tensor-memory footprint of a tile is small enough for two CTAs per SM, whose
+// load, dequant, MMA-issue and epilogue latencies overlap each other, which measured 1.5-2x
+// faster in this range.  Long-K shapes are cut into `splits` k-ranges (blockIdx.z); each CTA then
+// writes an int32 partial plane and one finish kernel reduces the planes and applies
+// (float)acc * ascale[m] * s1[n] (the reference's design, csrc/liquid_gemm/w4a8_wgmma.cu:39-56,
+// 523-534); with one split the epilogue is fused in the GEMM kernel.
+//
+// Per CTA: warp 0 = TMA producer (8704-byte bulk copy of the weight tile + BN x 128 token box per
+// k-step), warp 1 = TMEM allocation and tcgen05.mma issue (A operand from tensor memory), warps
+// 2..5 = dequant (thread r owns weight row r -> TMEM lane r) and epilogue.  All waits are bounded.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "lq_common.cuh"
+#include "lq_tc_ptx.cuh"
+
+namespace lq {
+
+int launch_finish(const int32_t* acc, const float* ascale, const float* s1, void* y, int out_dtype,
+                  int planes, int M, int N, cudaStream_t st);  // lq_elementwise.cu
+int make_byte_matrix_map(CUtensorMap* map, const void* ptr, long rows, long row_bytes, int box_rows,
+                         int box_bytes);  // lq_gemm_tc.cu
+
+namespace tile {
+
+constexpr int kTileBytes = 8704;
+constexpr int kI8TileBytes = 16384;
+constexpr int kThreads = 192;
+constexpr uint64_t kWaitLimitNs = 2000000000ull;
+constexpr int kOutI32 = 3;
+
+struct GemmArgs {
+  const uint8_t* blob;   // W4: tile blob
+  const float* ascale;   // [M]
+  const float* s1;       // [N]
+  void* out;             // scaled output [M,N] or int32 planes [splits][M][N]
+  int* status;
+  int out_mode;          // LQ_DT_* or kOutI32
+  int M, N, K;
+  int kt_total;          // K / 128
+};
+
+template <int BN, int NS, int NT, bool W4>
+struct TcCfg {
+  static constexpr int kXStage = BN * 128;
+  static constexpr int kWStage = W4 ? kTileBytes : kI8TileBytes;
+  static constexpr int kAccCols = BN;
+  static constexpr int kACols = W4 ? 32 * NT : 0;
+  static constexpr int kColsNeeded = kAccCols + kACols;
+  static constexpr int kTmemCols = kColsNeeded <= 32 ? 32 : kColsNeeded <= 64 ? 64 : kColsNeeded <= 128 ? 128
+                                   : kColsNeeded <= 256 ? 256 : 512;
+  static constexpr int kBarBytes = (2 * NS + 2 * NT + 1) * 8 + 8;
+  static constexpr int kSmemBytes = 1024 /* alignment slack */ + NS * (kXStage + kWStage) + kBarBytes + BN * 4;
+  static_assert(kColsNeeded <= 512, "tensor memory budget exceeded");
+};
+
+template <int BN, int NS, int NT, bool W4>
+__global__ void __launch_bounds__(kThreads, 1)
+w4a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
+               const GemmArgs args) {
+  using Cfg = TcCfg<BN, NS, NT, W4>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw_addr);
+
+  const uint32_t xs = base;                                  // NS activation stages (1024-aligned)
+  const uint32_t ws = xs + NS * Cfg::kXStage;                // NS weight stages
+  const uint32_t bars = ws + NS * Cfg::kWStage;              // barriers
+  const uint32_t bar_full = bars;                            // [NS] TMA landed
+  const uint32_t bar_empty = bars + NS * 8;                  // [NS] stage may be overwritten
+  const uint32_t bar_aready = bars + 2 * NS * 8;             // [NT] dequantised operand in TMEM
+  const uint32_t bar_afree = bars + (2 * NS + NT) * 8;       // [NT] MMAs that read the operand are done
+  const uint32_t bar_acc = bars + (2 * NS + 2 * NT) * 8;     // accumulators final
+  const uint32_t tmem_slot = bar_acc + 8;
+  uint8_t* gen = smem + (bars - base);
+  volatile uint32_t* tmem_slot_p = reinterpret_cast<volatile uint32_t*>(gen + (2 * NS + 2 * NT + 1) * 8);
+  float* ascale_s = reinterpret_cast<float*>(gen + Cfg::kBarBytes);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nt = blockIdx.x, mt = blockIdx.y, z = blockIdx.z, splits = gridDim.z;
+  const int kt_begin = (int)(((long)z * args.kt_total) / splits);
+  const int kt_end = (int)(((long)(z + 1) * args.kt_total) / splits);
+  const int nk = kt_end - kt_begin;
+  const int m0 = mt * BN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NS; ++s) {
+      ptx::mbar_init(bar_full + 8 * s, 1);
+      ptx::mbar_init(bar_empty + 8 * s, W4 ? 129 : 1);
+    }
+    for (int t = 0; t < NT; ++t) {
+      ptx::mbar_init(bar_aready + 8 * t, 128);
+      ptx::mbar_init(bar_afree + 8 * t, 1);
+    }
+    ptx::mbar_init(bar_acc, 1);
+    ptx::fence_mbar_init();
+    ptx::prefetch_tensormap(&tmap_x);
+    if (!W4) ptx::prefetch_tensormap(&tmap_w);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  if (warp >= 2 && args.out_mode != kOutI32) {
+    for (int j = threadIdx.x - 64; j < BN; j += 128) ascale_s[j] = (m0 + j < args.M) ? args.ascale[m0 + j] : 0.f;
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_p;
+  const uint32_t tmem_acc = tmem_base;             // columns [0, BN)
+  const uint32_t tmem_a = tmem_base + BN;          // NT operand stages of 32 columns
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      constexpr uint32_t kTx = Cfg::kXStage + Cfg::kWStage;
+      int issued = 0;
+      bool ok = true;
+      for (int i = 0; i < nk; ++i) {
+        const int s = i % NS;
+        const uint32_t ph = (uint32_t)(i / NS) & 1u;
+        if (!ptx::mbar_wait_bounded(bar_empty + 8 * s, ph ^ 1u, kWaitLimitNs)) {
+          atomicExch(args.status, 101);
+          ok = false;
+          break;
+        }
+        ptx::mbar_expect_tx(bar_full + 8 * s, kTx);
+        const int kt = kt_begin + i;
+        if (W4) {
+          const uint8_t* src = args.blob + ((size_t)nt * args.kt_total + kt) * kTileBytes;
+          ptx::bulk_load(ws + s * Cfg::kWStage, src, kTileBytes, bar_full + 8 * s);
+        } else {
+          ptx::tensor_load_2d(ws + s * Cfg::kWStage, &tmap_w, kt * 128, nt * 128, bar_full + 8 * s);
+        }
+        ptx::tensor_load_2d(xs + s * Cfg::kXStage, &tmap_x, kt * 128, m0, bar_full + 8 * s);
+        ++issued;
+      }
+      if (!ok) {
+        // copies already issued still write shared memory: let them land before the CTA exits
+        for (int i = issued > NS ? issued - NS : 0; i < issued; ++i)
+          ptx::mbar_wait_bounded(bar_full + 8 * (i % NS), (uint32_t)(i / NS) & 1u, kWaitLimitNs);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issue
+    if (lane == 0) {
+      constexpr uint32_t idesc = ptx::idesc_i8(BN);
+      bool ok = true;
+      for (int i = 0; i < nk && ok; ++i) {
+        const int s = i % NS;
+        const uint32_t ph = (uint32_t)(i / NS) & 1u;
+        const int t = i % NT;
+        const uint32_t pht = (uint32_t)(i / NT) & 1u;
+        ok = ptx::mbar_wait_bounded(bar_full + 8 * s, ph, kWaitLimitNs);
+        if (ok && W4) ok = ptx::mbar_wait_bounded(bar_aready + 8 * t, pht, kWaitLimitNs);
+        if (!ok) {
+          atomicExch(args.status, 102);
+          break;
+        }
+        ptx::tc_fence_after();
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint64_t bdesc = ptx::smem_desc_sw128(xs + s * Cfg::kXStage + j * 32);
+          const uint32_t accumulate = (i > 0 || j > 0) ? 1u : 0u;
+          if (W4) {
+            ptx::mma_i8_ts(tmem_acc, tmem_a + t * 32 + j * 8, bdesc, idesc, accumulate);
+          } else {
+            const uint64_t adesc = ptx::smem_desc_sw128(ws + s * Cfg::kWStage + j * 32);
+            ptx::mma_i8_ss(tmem_acc, adesc, bdesc, idesc, accumulate);
+          }
+        }
+        ptx::tc_commit(bar_empty + 8 * s);
+        if (W4) ptx::tc_commit(bar_afree + 8 * t);
+      }
+      if (ok) ptx::tc_commit(bar_acc);
+    }
+  } else {
+    // ------------------------------------------------------------------ dequant, then epilogue
+    const int quad = warp & 3;               // TMEM lane quadrant this warp may access
+    const int row = quad * 32 + lane;        // weight row inside the tile == TMEM lane
+    const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
+    bool ok = true;
+    if (W4) {
+      for (int i = 0; i < nk; ++i) {
+        const int s = i % NS;
+        const uint32_t ph = (uint32_t)(i / NS) & 1u;
+        const int t = i % NT;
+        const uint32_t pht = (uint32_t)(i / NT) & 1u;
+        if (!ptx::mbar_wait_bounded(bar_full + 8 * s, ph, kWaitLimitNs)) {
+          atomicExch(args.status, 103);
+          ok = false;
+          break;
+        }
+        const uint8_t* wst = smem + (ws - base) + s * Cfg::kWStage;
+        uint4 ch[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) ch[c] = *reinterpret_cast<const uint4*>(wst + (c * 128 + row) * 16);
+        const uint32_t meta = *reinterpret_cast<const uint32_t*>(wst + 8192 + row * 4);
+        ptx::mbar_arrive(bar_empty + 8 * s);
+
+        if (!ptx::mbar_wait_bounded(bar_afree + 8 * t, pht ^ 1u, kWaitLimitNs)) {
+          atomicExch(args.status, 104);
+          ok = false;
+          break;
+        }
+        ptx::tc_fence_after();
+        const uint32_t step0 = meta & 0xffu, a0 = ((meta >> 8) & 0xffu) * 0x01010101u;
+        const uint32_t step1 = (meta >> 16) & 0xffu, a1 = (meta >> 24) * 0x01010101u;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const uint32_t step = c < 2 ? step0 : step1;
+          const uint32_t ab = c < 2 ? a0 : a1;
+          const uint32_t pk[4] = {ch[c].x, ch[c].y, ch[c].z, ch[c].w};
+          uint32_t v[8];
+#pragma unroll
+          for (int h = 0; h < 4; ++h) {
+            v[2 * h] = lqq_dequant4(pk[h] & 0x0F0F0F0Fu, step, ab);
+            v[2 * h + 1] = lqq_dequant4((pk[h] >> 4) & 0x0F0F0F0Fu, step, ab);
+          }
+          ptx::tmem_st8(tmem_a + lane_addr + t * 32 + c * 8, v);
+        }
+        ptx::tc_wait_st();
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(bar_aready + 8 * t);
+      }
+    }
+    if (ok && !ptx::mbar_wait_bounded(bar_acc, 0u, kWaitLimitNs)) {
+      atomicExch(args.status, 105);
+      ok = false;
+    }
+    if (ok) {
+      ptx::tc_fence_after();
+      const long n = (long)nt * 128 + row;
+      const bool n_ok = n < args.N;
+      const float w_scale = (n_ok && args.out_mode != kOutI32) ? args.s1[n] : 0.f;
+      int32_t* plane = reinterpret_cast<int32_t*>(args.out) + (size_t)z * args.M * args.N;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        if (m0 + c0 >= args.M) break;  // uniform over the CTA
+        int v[16];
+        ptx::tmem_ld16(tmem_acc + lane_addr + c0, v);
+        ptx::tc_wait_ld();
+        if (n_ok) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int m = m0 + c0 + j;
+            if (m < args.M) {
+              const size_t idx = (size_t)m * args.N + n;
+              if (args.out_mode == kOutI32) plane[idx] = v[j];
+              else store_out(args.out, idx, lqq_scale(v[j], ascale_s[c0 + j], w_scale), args.out_mode);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+template <int BN, int NS, int NT, bool W4>
+static int launch_cfg(const CUtensorMap& tx, const CUtensorMap& tw, const GemmArgs& a, int splits, cudaStream_t st) {
+  using Cfg = TcCfg<BN, NS, NT, W4>;
+  auto kern = &w4a8_tile_kernel<BN, NS, NT, W4>;
+  static std::once_flag once[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  cudaError_t attr_err = cudaSuccess;
+  std::call_once(once[dev & 63], [&]() {
+    attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+  });
+  if (attr_err != cudaSuccess) {
+    record_cuda_error(attr_err, "cudaFuncSetAttribute(w4a8_tile_kernel)");
+    return LQ_ERR_CUDA;
+  }
+  dim3 grid((a.N + 127) / 128, (a.M + BN - 1) / BN, splits);
+  kern<<<grid, kThreads, Cfg::kSmemBytes, st>>>(tx, tw, a);
+  return check_launch("w4a8_tile_kernel");
+}
+
+static int tile_bn(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128; }
+
+}  // namespace tile
+
+// Split factor for the decode-tile kernel: fill about two CTAs per SM, at least 8 k-steps per split.
+int tile_pick_splits(int M, int N, int K) {
+  const int kt = K / 128;
+  const long tiles = (long)((N + 127) / 128) * ((M + tile::tile_bn(M) - 1) / tile::tile_bn(M));
+  const long slots = 2L * sm_count();
+  int S = 1;
+  if (tiles * 2 <= slots) {
+    S = (int)(slots / tiles);
+    const int max_by_k = kt / 8 > 0 ? kt / 8 : 1;
+    if (S > max_by_k) S = max_by_k;
+    if (S > 16) S = 16;
+  }
+  return S < 1 ? 1 : (S > kt ? kt : S);
+}
+
+size_t tile_workspace_bytes(int M, int N, int splits) {
+  return splits <= 1 ? 0 : (size_t)splits * (size_t)M * (size_t)N * sizeof(int32_t);
+}
+
+// out_mode: LQ_DT_* or 3 (raw int32).  M <= 128.  `ws` holds `splits` int32 planes (need not be zeroed).
+int run_tile_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, void* out, int out_mode,
+                  int M, int N, int K, int splits, void* ws, size_t ws_bytes, cudaStream_t st) {
+  using namespace tile;
+  if (splits > 1 && (!ws || ws_bytes < tile_workspace_bytes(M, N, splits))) return LQ_ERR_WORKSPACE;
+  const int bn = tile_bn(M);
+  CUtensorMap tx;
+  int rc = make_byte_matrix_map(&tx, x, M, K, bn, 128);
+  if (rc) return rc;
+  GemmArgs a;
+  a.blob = blob;
+  a.ascale = splits > 1 ? nullptr : ascale;
+  a.s1 = splits > 1 ? nullptr : s1;
+  a.out = splits > 1 ? ws : out;
+  a.status = status_word();
+  a.out_mode = splits > 1 ? kOutI32 : out_mode;
+  a.M = M;
+  a.N = N;
+  a.K = K;
+  a.kt_total = K / 128;
+  if (!a.status) return LQ_ERR_CUDA;
+  switch (bn) {
+    case 16: rc = launch_cfg<16, 8, 4, true>(tx, tx, a, splits, st); break;
+    case 32: rc = launch_cfg<32, 8, 4, true>(tx, tx, a, splits, st); break;
+    case 64: rc = launch_cfg<64, 6, 4, true>(tx, tx, a, splits, st); break;
+    default: rc = launch_cfg<128, 4, 4, true>(tx, tx, a, splits, st); break;
+  }
+  if (rc || splits <= 1) return rc;
+  return launch_finish(static_cast<const int32_t*>(ws), ascale, s1, out, out_mode, splits, M, N, st);
+}
+
+}  // namespace lq

@@ -203,10 +203,54 @@ def _gemv2(x_i8, gpack, s_u8, off_a, ascale, s1, N, K, group_size, out_dtype):
     _req(s_u8.numel() == N * (K // 64) and off_a.numel() == N * (K // 64), "s_u8/off_a must be [N, K/64]")
     _req(ascale.numel() == M and s1.numel() == N, "ascale must be [M] and s1 [N]")
     y = torch.empty((M, N), dtype=_OUT_DTYPES[int(out_dtype)], device=x_i8.device)
-    if M:
-        with _dev_ctx(x_i8):
+    if M == 0:
+        return y
+    # Kernel choice by measurement on B200 (weights in the row-major pack):
+    #   M <= 2, or M <= 4 with short K : warp-per-row-pair dp4a kernel straight from global memory
+    #   M <= 4 with long K             : persistent TMA-ring dp4a kernel (stream-K)
+    #   larger M                       : dp4a runs out of issue slots; big matrices use the warp-MMA
+    #                                    kernel, the others the tensor-core kernel on the same pack
+    with _dev_ctx(x_i8):
+        if M <= 2 or (M <= 4 and K < 8192):
             check(lib.lq_w4a8_gemv(_ptr(x_i8), _ptr(gpack), _ptr(s_u8), _ptr(off_a), _ptr(ascale), _ptr(s1), _ptr(y),
                                    int(out_dtype), M, N, K, group_size, _stream()), "w4a8_gemv2")
+        elif M <= 4:
+            ws = _workspace(lib.lq_gemv_workspace_bytes(N, K), x_i8.device)
+            rc = lib.lq_w4a8_gemv_stream(_ptr(x_i8), _ptr(gpack), _ptr(s_u8), _ptr(off_a), _ptr(ascale), _ptr(s1),
+                                         _ptr(y), int(out_dtype), M, N, K, _ptr(ws), ws.numel(), _stream())
+            if rc != 0:
+                ws.zero_()
+            check(rc, "w4a8_gemv2")
+        elif N * K >= (1 << 26):
+            check(lib.lq_w4a8_gemv(_ptr(x_i8), _ptr(gpack), _ptr(s_u8), _ptr(off_a), _ptr(ascale), _ptr(s1), _ptr(y),
+                                   int(out_dtype), M, N, K, group_size, _stream()), "w4a8_gemv2")
+        else:
+            nbytes = lib.lq_gemm_workspace_bytes(M, N, K, -1)
+            ws = _workspace(nbytes, x_i8.device)
+            rc = lib.lq_w4a8_gemm_rowmajor(_ptr(x_i8), _ptr(gpack), _ptr(s_u8), _ptr(off_a), _ptr(ascale), _ptr(s1),
+                                           _ptr(y), int(out_dtype), M, N, K, 0, _ptr(ws), ws.numel(), _stream())
+            if rc != 0:
+                ws.zero_()
+            check(rc, "w4a8_gemv2")
+    return y
+
+
+def gemv_stream(x_i8, gpack, s_u8, off_a, ascale, s1, N, K, out_dtype):
+    """The persistent TMA-ring GEMV kernel for any M <= 16 (tuning / test entry point)."""
+    x_i8 = _i8(x_i8, "x_i8")
+    M = x_i8.shape[0]
+    _req(M <= 16 and K % 128 == 0, "M <= 16 and K % 128 == 0 required")
+    gpack, s_u8, off_a = _u8(gpack, "gpack"), _u8(s_u8, "s_u8"), _u8(off_a, "off_a")
+    ascale, s1 = _f32(ascale, "ascale"), _f32(s1, "s1")
+    y = torch.empty((M, N), dtype=_OUT_DTYPES[int(out_dtype)], device=x_i8.device)
+    if M:
+        with _dev_ctx(x_i8):
+            ws = _workspace(lib.lq_gemv_workspace_bytes(N, K), x_i8.device)
+            rc = lib.lq_w4a8_gemv_stream(_ptr(x_i8), _ptr(gpack), _ptr(s_u8), _ptr(off_a), _ptr(ascale), _ptr(s1),
+                                         _ptr(y), int(out_dtype), M, N, K, _ptr(ws), ws.numel(), _stream())
+            if rc != 0:
+                ws.zero_()
+            check(rc, "gemv_stream")
     return y
 
 
@@ -237,14 +281,19 @@ def _workspace(nbytes: int, device: torch.device):
 
 
 def _gemm_call(fn_name, x_i8, M, N, K, splitk, call):
-    """Run one tensor-core GEMM entry point with its workspace; clears the workspace if the call fails
-    (a failed kernel may leave partial sums behind)."""
+    """Run one tensor-core GEMM entry point with the workspace its scheduling needs: fresh scratch for
+    the decode-tile planes, or the cached zero-filled reduction buffer of the persistent kernel (cleared
+    again if the call fails, since a failed kernel may leave partial sums behind)."""
     S = _splitk_for(M, N, K) if splitk is None else int(splitk)
     nbytes = lib.lq_gemm_workspace_bytes(M, N, K, S)
+    kind = lib.lq_gemm_workspace_kind(M, N, K, S)
     with _dev_ctx(x_i8):
-        ws = _workspace(nbytes, x_i8.device)
+        if kind == 1:
+            ws = torch.empty((nbytes,), dtype=torch.uint8, device=x_i8.device)
+        else:
+            ws = _workspace(nbytes, x_i8.device)
         rc = call(S, _ptr(ws) if ws is not None else None, ws.numel() if ws is not None else 0, _stream())
-        if rc != 0 and ws is not None:
+        if rc != 0 and ws is not None and kind == 2:
             ws.zero_()
         check(rc, fn_name)
 
@@ -259,7 +308,7 @@ def _check_blob(w, N, K):
 
 def gemm_i32(x_i8, blob, N, K, splitk=None):
     """Exact int32 accumulators from a tile blob.  ``splitk``: None = automatic (stream-K unless
-    LIQUIDGEMM_SPLITK applies), 0 = stream-K, 1 = whole tiles, S > 1 = fixed split-K factor."""
+    LIQUIDGEMM_SPLITK applies), S >= 1 = that split-K factor, -1 = force the persistent stream-K kernel."""
     x_i8 = _i8(x_i8, "x_i8")
     _req(K % 128 == 0 and x_i8.shape[1] == K, "K%128==0 required and x_i8 must be [M,K]")
     blob = _check_blob(blob, N, K)
@@ -301,7 +350,7 @@ def gemm_rowmajor(x_i8, gpack, s_u8, off_a, ascale, s1, N, K, out_dtype, splitk=
     _req(ascale.numel() == M and s1.numel() == N, "ascale must be [M] and s1 [N]")
     y = torch.empty((M, N), dtype=_OUT_DTYPES[int(out_dtype)], device=x_i8.device)
     if M:
-        _gemm_call("w4a8_gemm_rowmajor", x_i8, M, N, K, splitk,
+        _gemm_call("w4a8_gemm_rowmajor", x_i8, M, N, K, -1,
                    lambda S, ws, nb, st: lib.lq_w4a8_gemm_rowmajor(_ptr(x_i8), _ptr(gpack), _ptr(s_u8), _ptr(off_a),
                                                                    _ptr(ascale), _ptr(s1), _ptr(y), int(out_dtype),
                                                                    M, N, K, S, ws, nb, st))
@@ -520,8 +569,19 @@ def w4a8_linear(x: torch.Tensor, qw_dev: dict, out_dtype: torch.dtype = None) ->
     """
     odt = _DTYPE_CODES[out_dtype or x.dtype]
     x_i8, ascale = torch.ops.liquidgemm.quant_per_token(x)
-    if x_i8.shape[0] <= 16 and qw_dev.get("gp") is not None:
+    if use_gemv(x_i8.shape[0], qw_dev["N"], qw_dev["K"], qw_dev.get("gp") is not None, qw_dev.get("rs") is not None):
         return torch.ops.liquidgemm.w4a8_gemv2(x_i8, qw_dev["gp"], qw_dev["s_u8"], qw_dev["offset_a"], ascale,
                                                qw_dev["s1"], qw_dev["N"], qw_dev["K"], 64, odt)
     return torch.ops.liquidgemm.w4a8_wgmma_rs_fused(x_i8, qw_dev["rs"], qw_dev["s_u8"], qw_dev["offset_a"], ascale,
                                                     qw_dev["s1"], qw_dev["N"], qw_dev["K"], 64, odt)
+
+
+def use_gemv(M: int, N: int, K: int, have_gp: bool, have_rs: bool) -> bool:
+    """Decode dispatch measured on B200: the GEMV pack wins for one or two tokens (and up to four on
+    matrices of qkv size); from there on the two-CTAs-per-SM tensor-core tile kernel on the tile blob
+    is faster.  The reference switches at M <= 16 (liquidgemm/vllm_plugin.py:189)."""
+    if not have_gp or M > 16:
+        return False
+    if not have_rs:
+        return True
+    return M <= 2 or (M <= 4 and N * K <= (1 << 25))

@@ -103,7 +103,8 @@ def apply_layer(layer: torch.nn.Module, x: torch.Tensor, bias: Optional[torch.Te
     odt = _DT.get(x.dtype, 0)
     x_i8, ascale = torch.ops.liquidgemm.quant_per_token(x2)
     if w4:
-        if getattr(layer, "lq_gemv", False) and x_i8.shape[0] <= 16:
+        from .ops import use_gemv
+        if getattr(layer, "lq_gemv", False) and use_gemv(x_i8.shape[0], n, layer.lq_K, True, True):
             y = torch.ops.liquidgemm.w4a8_gemv2(x_i8, layer.lq_gp, layer.lq_s_u8, layer.lq_offset_a, ascale,
                                                 layer.lq_s1, n, layer.lq_K, group_size, odt)
         else:

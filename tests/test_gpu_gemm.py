@@ -108,12 +108,12 @@ def test_fused_equals_unfused_and_oracle(ops, M, out_dtype):
     assert_bits_equal(got, O.w4a8_matmul(x, ascale, qw), out_dtype, "fused vs oracle")
 
 
-@pytest.mark.parametrize("S", [0, 1, 2, 4, 8, 16])
+@pytest.mark.parametrize("S", [-1, 0, 1, 2, 4, 8, 16])
 @pytest.mark.parametrize("M", [32, 64, 128])
 def test_explicit_splitk_is_exact(ops, M, S):
-    """Split-K sweep of the decode-tile configuration (0 = stream-K): any setting gives the same bits."""
+    """Split-K sweep of the decode-tile configuration (0 = automatic, -1 = persistent stream-K): any setting gives the same bits."""
     N, K = 256, 14336
-    qw = random_lqq(N, K, 64, seed=S)
+    qw = random_lqq(N, K, 64, seed=S + 2)
     tq = to_torch_qw(qw)
     x, ascale = random_tokens(M, K, seed=M)
     w = ops.repack_rs_weight(tq).reshape(-1)
@@ -234,6 +234,21 @@ def test_workspace_is_left_clean(ops):
     w = ops.repack_rs_weight(tq).reshape(-1)
     want = _acc(x, qw)
     for _ in range(3):
-        assert np.array_equal(ops.gemm_i32(xt, w, N, K, splitk=0).cpu().numpy(), want)
+        assert np.array_equal(ops.gemm_i32(xt, w, N, K, splitk=-1).cpu().numpy(), want)
     for ws in ops._WORKSPACES.values():
         assert int(ws.count_nonzero()) == 0
+
+
+@pytest.mark.parametrize("M", [200, 2048])
+@pytest.mark.parametrize("S", [-1, 0, 1, 3])
+def test_prefill_scheduling_modes_are_exact(ops, M, S):
+    """Persistent kernel: stream-K, whole tiles and a fixed split give the same bits (M > 128)."""
+    N, K = 640, 2048
+    qw = random_lqq(N, K, 64, seed=S + 7)
+    tq = to_torch_qw(qw)
+    x, ascale = random_tokens(M, K, seed=M)
+    w = ops.repack_rs_weight(tq).reshape(-1)
+    xt, at = torch.from_numpy(x).cuda(), torch.from_numpy(ascale).cuda()
+    assert np.array_equal(ops.gemm_i32(xt, w, N, K, splitk=S).cpu().numpy(), _acc(x, qw))
+    y = ops.gemm_fused(xt, w, at, tq.s1, N, K, 1, splitk=S)
+    assert_bits_equal(y, O.w4a8_matmul(x, ascale, qw), 1, f"M={M} S={S}")

@@ -40,7 +40,10 @@ def test_size_helpers_without_gpu():
     assert lib.lq_gemm_pick_splitk(256, 4096, 14336, 4) == 0     # ... and not above
     assert lib.lq_gemm_pick_splitk(64, 4096, 256, 8) == 2        # clamped to K/128
     assert lib.lq_gemm_workspace_bytes(64, 4096, 14336, 1) == 0
-    assert lib.lq_gemm_workspace_bytes(64, 4096, 14336, 4) > 0
+    assert lib.lq_gemm_workspace_bytes(64, 4096, 14336, 4) == 4 * 64 * 4096 * 4
+    assert lib.lq_gemm_workspace_kind(64, 4096, 14336, 4) == 1
+    assert lib.lq_gemm_workspace_kind(2048, 4096, 14336, 0) == 2
+    assert lib.lq_gemm_workspace_kind(2048, 4096, 14336, 1) == 0
 
 
 def test_bad_arguments_return_codes_without_touching_the_gpu():
