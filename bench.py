@@ -4,8 +4,8 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--no-extras]
 
 One *step* is one pass of the decode sweep: M in {1, 4, 8, 16} over the three Llama-3.1-8B linear
-shapes (qkv 6144x4096, gate_up 28672x4096, down 4096x14336) = 12 launches of the M <= 16 entry
-point ``torch.ops.liquidgemm.w4a8_gemv2``.  Weights are seeded synthetic LQQ data of those
+shapes (qkv 6144x4096, gate_up 28672x4096, down 4096x14336) = 12 linears through the decode
+dispatch of the plugin (``w4a8_gemv2`` for one or two tokens, the fused tensor-core op above).  Weights are seeded synthetic LQQ data of those
 shapes (no checkpoint is read); every launch uses the next of several weight copies so that the
 bytes it streams were evicted from L2 long before (working set > 2 x 126 MB).
 
@@ -226,8 +226,8 @@ def build_device_sets(torch, ops, n_sets, seed_base):
             codes, step, off, s1 = synth_lqq_codes(N, K, seed=seed_base + 17 * c + len(name))
             qw = LiquidQuantWeight(torch.from_numpy(codes).cuda(), torch.from_numpy(step).cuda(),
                                    torch.from_numpy(off).cuda(), torch.from_numpy(s1).cuda(), 64)
-            layer[name] = {"gp": ops.pack_gemv_interleaved(qw), "s_u8": qw.s_u8, "offset_a": qw.offset_a,
-                           "s1": qw.s1, "N": N, "K": K}
+            layer[name] = {"gp": ops.pack_gemv_interleaved(qw), "rs": ops.repack_rs_weight(qw).reshape(-1),
+                           "s_u8": qw.s_u8, "offset_a": qw.offset_a, "s1": qw.s1, "N": N, "K": K}
             del qw, codes
         sets.append(layer)
     return sets
@@ -279,11 +279,19 @@ def main():
                                "out_host": torch.empty(M, N, dtype=torch.float16).pin_memory()}
     launches = [(name, M) for M in SWEEP_M for name in SHAPES]
 
+    def decode_linear(L, xq, sc, M, out_dtype):
+        """The decode dispatch of the plugin (liquidgemm_b200.ops.use_gemv): GEMV pack for one or two
+        tokens, the tensor-core tile kernel on the tile blob from there on."""
+        if ops.use_gemv(M, L["N"], L["K"], True, True):
+            return torch.ops.liquidgemm.w4a8_gemv2(xq, L["gp"], L["s_u8"], L["offset_a"], sc, L["s1"], L["N"], L["K"],
+                                                   64, out_dtype)
+        return torch.ops.liquidgemm.w4a8_wgmma_rs_fused(xq, L["rs"], L["s_u8"], L["offset_a"], sc, L["s1"], L["N"],
+                                                        L["K"], 64, out_dtype)
+
     def enqueue_sweep(c):
         for name, M in launches:
             L, a = sets[c][name], acts[(name, M)]
-            torch.ops.liquidgemm.w4a8_gemv2(a["xq"], L["gp"], L["s_u8"], L["offset_a"], a["sc"], L["s1"],
-                                            L["N"], L["K"], 64, OUT_BF16)
+            decode_linear(L, a["xq"], a["sc"], M, OUT_BF16)
 
     stream = torch.cuda.Stream()
     graphs = []
@@ -323,8 +331,7 @@ def main():
             L, a = sets[c][name], acts[(name, M)]
             xd = a["host"].cuda(non_blocking=True)
             xq, sc = torch.ops.liquidgemm.quant_per_token(xd)
-            y = torch.ops.liquidgemm.w4a8_gemv2(xq, L["gp"], L["s_u8"], L["offset_a"], sc, L["s1"], L["N"], L["K"],
-                                                64, 1)
+            y = decode_linear(L, xq, sc, M, 1)
             a["out_host"].copy_(y, non_blocking=True)
 
     e2e_steps = max(3, min(args.steps, 50))
@@ -347,6 +354,12 @@ def main():
     ms, e2e_ms = float(t_ms[0]), float(t_ms[1])
     status = lib.lq_poll_status(torch.cuda.current_stream().cuda_stream)
 
+    def kernels_of(name, M):
+        N, K = SHAPES[name]
+        if ops.use_gemv(M, N, K, True, True):
+            return 1
+        return 2 if lib.lq_gemm_workspace_bytes(M, N, K, 0) > 0 else 1
+    launches_per_step = sum(kernels_of(n, M) for n, M in launches)
     wbytes = sweep_weight_bytes()
     abytes = sum(algorithmic_bytes(M, *SHAPES[n]) for n, M in launches)
     step_s = ms / 1e3 / args.steps
@@ -356,11 +369,23 @@ def main():
 
     extras = {}
     if not args.no_extras:
-        try:
-            from liquidgemm_b200 import benchlib
-            extras = benchlib.run_extras(world, rank, local_rank, peaks)
-        except Exception as exc:  # extras never invalidate the headline numbers
-            extras = {"error": repr(exc)}
+        if world == 1:
+            # the secondary configurations run in a child process: nothing they do can touch the
+            # numbers measured above
+            try:
+                env = dict(os.environ, CUDA_VISIBLE_DEVICES=os.environ.get("CUDA_VISIBLE_DEVICES", str(local_rank)))
+                out = subprocess.run([sys.executable, "-m", "liquidgemm_b200.benchlib", str(peaks["hbm_gbs"])], cwd=ROOT,
+                                     env=env, capture_output=True, text=True, timeout=900)
+                extras = json.loads(out.stdout.strip().splitlines()[-1]) if out.returncode == 0 else {
+                    "error": (out.stderr or "")[-400:]}
+            except Exception as exc:
+                extras = {"error": repr(exc)}
+        else:
+            try:
+                from liquidgemm_b200 import benchlib
+                extras = benchlib.run_extras(world, rank, local_rank, peaks)
+            except Exception as exc:
+                extras = {"error": repr(exc)}
 
     cpu = None
     if rank == 0 and world == 1:
@@ -380,14 +405,14 @@ def main():
                        "sharding": "each rank owns a full set of output channels (N-sharded, no collective)"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / peaks["hbm_gbs"], "traffic": None,
-                         "of": peaks["source"], "kernel": "gemv_dp4a_kernel / gemv_mma_kernel (12-launch sweep)",
+                         "of": peaks["source"], "kernel": "gemv_dp4a_kernel (M <= 2 or qkv M = 4) + w4a8_tile_kernel [+ finish_kernel] (12-op sweep)",
                          "algorithmic_bytes_per_step": abytes},
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": UNIT,
                     "h2d_bytes_per_step": sum(M * SHAPES[n][1] * 2 for n, M in launches),
                     "d2h_bytes_per_step": sum(M * SHAPES[n][0] * 2 for n, M in launches),
                     "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
-            "gpu_launches": len(launches) * args.steps,
+            "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks, "device_status": status, "extras": extras,
         }
         print(json.dumps(line), flush=True)

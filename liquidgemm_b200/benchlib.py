@@ -189,3 +189,12 @@ def run_extras(world, rank, local_rank, peaks):
         out["splitk"] = run_splitk(peaks)
     out["tp70b"] = {"ranks": world, "layers": 80, "rows": run_tp70b(world, rank)}
     return out
+
+
+if __name__ == "__main__":
+    # ``python -m liquidgemm_b200.benchlib <hbm_gbs>``: single-GPU extras as one JSON object on stdout.
+    # bench.py runs this in a child process so that the headline numbers never depend on it.
+    import json
+    import sys
+    torch.cuda.set_device(0)
+    print(json.dumps(run_extras(1, 0, 0, {"hbm_gbs": float(sys.argv[1]) if len(sys.argv) > 1 else 6451.8})))

@@ -210,6 +210,7 @@ w4a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
           ok = false;
           break;
         }
+        __syncwarp();   // lanes leave the poll loops one by one; tcgen05.st / wait::st need the warp converged
         ptx::tc_fence_after();
         const uint32_t step0 = meta & 0xffu, a0 = ((meta >> 8) & 0xffu) * 0x01010101u;
         const uint32_t step1 = (meta >> 16) & 0xffu, a1 = (meta >> 24) * 0x01010101u;
@@ -235,6 +236,7 @@ w4a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
       atomicExch(args.status, 105);
       ok = false;
     }
+    __syncwarp();
     if (ok) {
       ptx::tc_fence_after();
       const long n = (long)nt * 128 + row;
