@@ -1,0 +1,112 @@
+"""Pipeline microbenchmarks for the sm_100a building blocks of the W4A8 kernels.
+
+    python -m liquidgemm_b200.microbench mma_rate     # tcgen05.mma kind::i8 issue-to-issue cost
+    python -m liquidgemm_b200.microbench sync_cost    # mbarrier / commit / bulk-copy instruction costs
+    python -m liquidgemm_b200.microbench tma_stream   # HBM streaming rate of ring-buffered bulk copies
+    python -m liquidgemm_b200.microbench tma_rows     # the same with one bulk copy per weight row
+
+Each one launches a measurement-only kernel exported by the native library (``lq_debug_*``); none of
+them is on a product path.  They need a B200; every device-side wait in them is bounded.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import sys
+
+import numpy as np
+import torch
+
+from ._lib import lib
+
+_I, _P, _L = ctypes.c_int, ctypes.c_void_p, ctypes.c_long
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def mma_rate(iters: int = 2000) -> None:
+    """Cycles between back-to-back 128 x N x 32 int8 MMAs, A in tensor memory (TS) or shared (SS)."""
+    fn = lib.lq_debug_mma_rate
+    fn.argtypes, fn.restype = [_I] * 4 + [_P, _P], _I
+    for ctas in (1, 148):
+        for ts in (1, 0):
+            for n in (16, 64, 128, 192, 256):
+                out = torch.zeros(ctas * 2, dtype=torch.int64, device="cuda")
+                for _ in range(2):
+                    assert fn(n, iters, ts, ctas, out.data_ptr(), _stream()) == 0
+                torch.cuda.synchronize()
+                o = out.cpu().numpy().reshape(ctas, 2)
+                cyc = float(np.median(o[:, 0])) / (iters * 4)
+                issue = float(np.median(o[:, 1])) / (iters * 4)
+                print(f"ctas={ctas:3d} {'TS' if ts else 'SS'} N={n:3d}: {cyc:7.1f} cycles/MMA (issue {issue:6.1f})"
+                      f"  -> {128 * n * 32 / cyc:7.0f} MAC/clk/SM", flush=True)
+
+
+def sync_cost() -> None:
+    """Cycle cost of the synchronisation instructions the GEMM pipeline is built from."""
+    fn = lib.lq_debug_sync_cost
+    fn.argtypes, fn.restype = [_P] * 3, _I
+    src = torch.zeros(1 << 20, dtype=torch.uint8, device="cuda")
+    out = torch.zeros(16, dtype=torch.int64, device="cuda")
+    names = ["loop64", "clock64", "trywait_fresh", "arrive", "trywait_done", "bulk8k_roundtrip", "commit",
+             "bulk_issue", "ok"]
+    for _ in range(3):
+        assert fn(src.data_ptr(), out.data_ptr(), None) == 0
+        torch.cuda.synchronize()
+        print(dict(zip(names, out.cpu().tolist())), flush=True)
+
+
+def tma_stream(total_bytes: int = 400_000_000) -> None:
+    """One producer thread per CTA streams contiguous stages through a ring of `ns` buffers."""
+    fn = lib.lq_debug_tma_stream
+    fn.argtypes, fn.restype = [_P, _I, _I, _I, _I, _P, _P], _I
+    src = torch.zeros(1 << 30, dtype=torch.uint8, device="cuda")
+    cyc = torch.zeros(148, dtype=torch.int64, device="cuda")
+    for stage, ns in [(8704, 16), (8704, 8), (8704, 4), (17408, 8), (32768, 5), (4352, 32), (8704, 20)]:
+        steps = total_bytes // (148 * stage)
+        for _ in range(2):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            assert fn(src.data_ptr(), stage, ns, steps, 148, cyc.data_ptr(), None) == 0
+            e1.record()
+            torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3
+        nbytes = 148 * steps * stage
+        print(f"stage {stage:6d} B x {ns:2d} buffers: {us:8.1f} us  {nbytes / us / 1e6:6.2f} TB/s  "
+              f"cycles/stage {float(np.median(cyc.cpu().numpy())) / steps:7.1f}", flush=True)
+
+
+def tma_rows(total_bytes: int = 400_000_000) -> None:
+    """A stage made of `rows` separate bulk copies of `row_bytes` each (a row-major weight slice)
+    instead of one contiguous copy; `pieces` splits every row into that many copies."""
+    fn = lib.lq_debug_tma_rows
+    fn.argtypes, fn.restype = [_P, _I, _I, _L, _I, _I, _I, _I, _P, _P], _I
+    src = torch.zeros(1 << 30, dtype=torch.uint8, device="cuda")
+    cyc = torch.zeros(148, dtype=torch.int64, device="cuda")
+    for rows, row_bytes, stride, ns, pieces in [(8, 2048, 2048, 9, 1), (8, 1024, 2048, 18, 2), (16, 1024, 2048, 9, 2),
+                                                (8, 2048, 7168, 9, 3), (32, 512, 2048, 9, 4), (4, 4096, 4096, 9, 1),
+                                                (16, 512, 2048, 18, 4)]:
+        stage = rows * row_bytes
+        steps = total_bytes // (148 * stage)
+        for _ in range(2):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            rc = fn(src.data_ptr(), rows, row_bytes, stride, ns, steps, pieces, 148, cyc.data_ptr(), None)
+            e1.record()
+            torch.cuda.synchronize()
+            assert rc == 0, rc
+        us = e0.elapsed_time(e1) * 1e3
+        print(f"{rows:2d} rows x {row_bytes:4d} B (stride {stride}, {pieces} copies/row) x {ns:2d} buffers: "
+              f"{us:8.1f} us  {148 * steps * stage / us / 1e6:6.2f} TB/s  "
+              f"cycles/stage {float(np.median(cyc.cpu().numpy())) / steps:7.1f}", flush=True)
+
+
+_CASES = {"mma_rate": mma_rate, "sync_cost": sync_cost, "tma_stream": tma_stream, "tma_rows": tma_rows}
+
+if __name__ == "__main__":
+    which = sys.argv[1:] or list(_CASES)
+    for name in which:
+        print(f"== {name}", flush=True)
+        _CASES[name]()
