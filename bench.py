@@ -11,7 +11,7 @@ bytes it streams were evicted from L2 long before (working set > 2 x 126 MB).
 
 The JSON line printed by rank 0 carries
   value     weight GB/s (packed weight bytes N*K/2 per launch / device time), whole job
-  e2e       the same metric through the public op with HOST buffers: per launch a pinned fp16
+  e2e       the same metric through the host-buffer C entry point (lq_w4a8_linear_host): per launch a pinned fp16
             activation copy to the device, quant_per_token + GEMV, and the result copied back
   roofline  algorithmic bytes of the sweep / device time, against the measured HBM copy rate
   cpu_baseline  the CPU oracle (C, OpenMP) on the same sweep, timed on this host
@@ -280,8 +280,8 @@ def main():
     launches = [(name, M) for M in SWEEP_M for name in SHAPES]
 
     def decode_linear(L, xq, sc, M, out_dtype):
-        """The decode dispatch of the plugin (liquidgemm_b200.ops.use_gemv): GEMV pack for one or two
-        tokens, the tensor-core tile kernel on the tile blob from there on."""
+        """The decode dispatch of the plugin (liquidgemm_b200.ops.use_gemv): the row-major GEMV pack on
+        small matrices with up to four tokens, everything else from the tile blob."""
         if ops.use_gemv(M, L["N"], L["K"], True, True):
             return torch.ops.liquidgemm.w4a8_gemv2(xq, L["gp"], L["s_u8"], L["offset_a"], sc, L["s1"], L["N"], L["K"],
                                                    64, out_dtype)
@@ -329,10 +329,7 @@ def main():
     def e2e_step(c):
         for name, M in launches:
             L, a = sets[c][name], acts[(name, M)]
-            xd = a["host"].cuda(non_blocking=True)
-            xq, sc = torch.ops.liquidgemm.quant_per_token(xd)
-            y = decode_linear(L, xq, sc, M, 1)
-            a["out_host"].copy_(y, non_blocking=True)
+            ops.w4a8_linear_host(a["host"], L, a["out_host"])
 
     e2e_steps = max(3, min(args.steps, 50))
     with torch.cuda.stream(stream):
@@ -354,12 +351,7 @@ def main():
     ms, e2e_ms = float(t_ms[0]), float(t_ms[1])
     status = lib.lq_poll_status(torch.cuda.current_stream().cuda_stream)
 
-    def kernels_of(name, M):
-        N, K = SHAPES[name]
-        if ops.use_gemv(M, N, K, True, True):
-            return 1
-        return 2 if lib.lq_gemm_workspace_bytes(M, N, K, 0) > 0 else 1
-    launches_per_step = sum(kernels_of(n, M) for n, M in launches)
+    launches_per_step = len(launches)   # every linear of the sweep is one kernel launch
     wbytes = sweep_weight_bytes()
     abytes = sum(algorithmic_bytes(M, *SHAPES[n]) for n, M in launches)
     step_s = ms / 1e3 / args.steps
@@ -405,7 +397,7 @@ def main():
                        "sharding": "each rank owns a full set of output channels (N-sharded, no collective)"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / peaks["hbm_gbs"], "traffic": None,
-                         "of": peaks["source"], "kernel": "gemv_dp4a_kernel (M <= 2 or qkv M = 4) + w4a8_tile_kernel [+ finish_kernel] (12-op sweep)",
+                         "of": peaks["source"], "kernel": "w4a8_skinny_kernel (M = 8, 16) + gemv_blob_kernel (M <= 4) + gemv_dp4a_kernel (qkv, M <= 4): the 12-op sweep",
                          "algorithmic_bytes_per_step": abytes},
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": UNIT,

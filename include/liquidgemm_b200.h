@@ -101,6 +101,31 @@ LQ_API int lq_w4a8_gemv_stream(const int8_t* x_i8, const uint8_t* gpack, const u
                         int out_dtype, int M, int N, int K, void* workspace, size_t workspace_bytes,
                         void* stream);
 
+/* The decode GEMV (1..8 tokens) fed from the GEMM's tile blob instead of a GEMV-specific pack, so a
+ * layer keeps ONE copy of its 4-bit weights for every batch size (the reference's GEMV mode stores
+ * a second, row-major copy: liquidgemm/vllm_plugin.py:157-164).  Stream-K over 2 CTAs per SM with a
+ * bulk-copy ring and dp4a.  `workspace`: lq_gemv_blob_workspace_bytes() bytes, ALL ZERO on entry, left
+ * all zero.  x_i8 and blob must be 16-byte aligned; K % 128 == 0; any N (the blob pads rows).
+ * Serves torch.ops.liquidgemm.w4a8_wgmma_rs_fused for small M
+ * (reference csrc/liquid_gemm/w4a8_wgmma.cu:575-645). */
+LQ_API size_t lq_gemv_blob_workspace_bytes(void);
+LQ_API int lq_w4a8_gemv_blob(const void* x_i8, const void* blob, const void* ascale, const void* s1,
+                             void* out, int out_dtype, int M, int N, int K, void* workspace,
+                             size_t workspace_bytes, void* stream);
+
+/* One whole linear layer for HOST activations and a HOST output: upload, per-token quantise, fused
+ * W4A8 linear from the tile blob (automatic kernel choice by M), download, all enqueued on `stream`
+ * by this one call; nothing is synchronised.  x_host [M,K] in x_dtype and y_host [M,N] in out_dtype
+ * should be pinned for the copies to be asynchronous.  `scratch`: device memory of
+ * lq_linear_host_scratch_bytes() bytes, 256-byte aligned, holding the device copies; `workspace`
+ * as for lq_w4a8_gemm_fused with splitk 0.  Stands for the Python-side .cuda() moves around the
+ * reference's operators (liquidgemm/ops.py:185-201, liquidgemm/vllm_plugin.py:174-206). */
+LQ_API size_t lq_linear_host_scratch_bytes(int M, int N, int K, int x_dtype, int out_dtype);
+LQ_API int lq_w4a8_linear_host(const void* x_host, int x_dtype, const void* blob, const void* s1,
+                               void* y_host, int out_dtype, int M, int N, int K, void* scratch,
+                               size_t scratch_bytes, void* workspace, size_t workspace_bytes,
+                               void* stream);
+
 /* Same product from the plain pack_nibbles() layout with float32 output, any M.
  * Replaces torch.ops.liquidgemm.w4a8_gemm (reference csrc/liquid_gemm/w4a8_gemm.cu:183-227).
  * M <= 16 runs the GEMV (K % 64 == 0); larger M re-tiles the weights into `workspace`

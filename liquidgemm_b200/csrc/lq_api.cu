@@ -1,5 +1,6 @@
 // Library-level plumbing of the C ABI: error reporting, device checks, the device status word.
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -47,6 +48,14 @@ static int current_device() {
 int sm_count() {
   int dev = current_device();
   return dev < 0 || g_sm_count[dev] <= 0 ? 148 : g_sm_count[dev];
+}
+
+bool pdl_enabled() {
+  static const bool on = []() {
+    const char* e = getenv("LIQUIDGEMM_PDL");
+    return !(e && e[0] == '0');
+  }();
+  return on;
 }
 
 int* status_word() {

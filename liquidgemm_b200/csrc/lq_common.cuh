@@ -20,6 +20,27 @@ int* status_word();                                         // lq_api.cu: device
 
 inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 
+// Launch with programmatic stream serialisation: the kernel may start while the previous kernel
+// of the stream is still draining, and must execute griddepcontrol.wait (dependency_wait()) before
+// it touches anything an earlier kernel may have written or may still read-modify-write.  Switched
+// off with LIQUIDGEMM_PDL=0 (then this is an ordinary launch).
+bool pdl_enabled();                                         // lq_api.cu
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_overlapped(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                     Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
 // ---------------------------------------------------------------------------------------------
 // LQQ arithmetic
 // ---------------------------------------------------------------------------------------------
@@ -57,6 +78,12 @@ __device__ __forceinline__ uint4 ldg_stream_v4(const void* p) {
                : "l"(p));
   return r;
 }
+
+// Programmatic dependent launch, device side.  allow_dependents(): the next kernel of the stream may be
+// scheduled once every CTA of this grid has executed it.  dependency_wait(): returns when all earlier
+// kernels of the stream have completed and their writes are visible (no-op for an ordinary launch).
+__device__ __forceinline__ void allow_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));

@@ -40,8 +40,12 @@ mma_rate_kernel(int n, int iters, int a_in_tmem, long long* out) {
   for (int i = threadIdx.x; i < (32768 + 16384) / 4; i += blockDim.x)
     reinterpret_cast<uint32_t*>(smem_raw + (base - raw_addr))[i] = 0x01020304u * (i + 1);
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  // a_in_tmem bit 1: allocate 256 columns (accumulator <= 128 wide) so two CTAs share an SM
+  const uint32_t cols = (a_in_tmem & 2) ? 256u : 512u;
+  const uint32_t a_col = cols / 2;
+  a_in_tmem &= 1;
   if (threadIdx.x < 32) {
-    ptx::tmem_alloc(smem_u32(&tmem_slot), 512);
+    ptx::tmem_alloc(smem_u32(&tmem_slot), cols);
     ptx::tmem_relinquish();
   }
   ptx::tc_fence_before();
@@ -55,7 +59,7 @@ mma_rate_kernel(int n, int iters, int a_in_tmem, long long* out) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const uint64_t bdesc = ptx::smem_desc_sw128(base + j * 32);
-        if (a_in_tmem) ptx::mma_i8_ts(tmem_base, tmem_base + 256 + j * 8, bdesc, idesc, 1u);
+        if (a_in_tmem) ptx::mma_i8_ts(tmem_base, tmem_base + a_col + j * 8, bdesc, idesc, 1u);
         else ptx::mma_i8_ss(tmem_base, ptx::smem_desc_sw128(base + 32768 + j * 32), bdesc, idesc, 1u);
       }
     }
@@ -70,7 +74,7 @@ mma_rate_kernel(int n, int iters, int a_in_tmem, long long* out) {
   __syncthreads();
   if (threadIdx.x < 32) {
     ptx::tc_fence_after();
-    ptx::tmem_dealloc(tmem_base, 512);
+    ptx::tmem_dealloc(tmem_base, cols);
   }
 }
 
@@ -79,6 +83,7 @@ mma_rate_kernel(int n, int iters, int a_in_tmem, long long* out) {
 // out: device buffer of 2 x ctas int64: total cycles and cycles spent issuing, per CTA.
 extern "C" LQ_API int lq_debug_mma_rate(int n, int iters, int a_in_tmem, int ctas, long long* out, void* stream) {
   if (n < 16 || n > 256 || n % 16 || iters <= 0 || ctas <= 0 || !out) return LQ_ERR_BAD_ARG;
+  if ((a_in_tmem & 2) && n > 128) return LQ_ERR_BAD_ARG;
   const int smem = 1024 + 32768 + 16384;
   static bool attr_done = false;
   if (!attr_done) {

@@ -1,0 +1,431 @@
+// W4A8 tensor-core GEMM for decode batches (M <= 128 tokens): HBM-bound, so built like a streaming
+// copy with tensor cores attached.  Replaces the reference's split-K WGMMA path for small M
+// (csrc/liquid_gemm/w4a8_wgmma.cu:333-503 with the split rule at :523-534 and the finish kernel :39-56).
+//
+//  * Work = the (n-tile, k-tile) grid of 8704-byte blob tiles, cut into equal contiguous ranges, one
+//    per CTA, two CTAs per SM (stream-K): every SM streams the same number of weight bytes whatever
+//    N and K are, in ONE launch (no second reduction kernel).
+//  * warp 0  producer: one thread keeps a ring of NS stages in flight: a contiguous bulk copy of the
+//            weight tile and a 128-byte-swizzled tensor-map box of the BN x 128 token slice.
+//  * warps 2..9  two dequant sets taking alternate k-tiles; thread r of a set owns weight row r:
+//            64 bytes of nibbles -> 128 INT8 (AND / SHR+AND / IMAD / XOR on 4-lane words) ->
+//            tcgen05.st into tensor-memory lane r (the MMA's A operand, 4 consecutive k per column).
+//  * warp 1  MMA: one thread issues four 128 x BN x 32 tcgen05.mma kind::i8 per k-tile (A from tensor
+//            memory, B = tokens through a shared-memory descriptor); its commit recycles the stage.
+//            A single CTA cannot issue these faster than one per ~94 cycles, two CTAs per SM overlap.
+//  * Epilogue by the dequant warps: tcgen05.ld (lane = channel, column = token); a segment that
+//    covers its tile's whole K is scaled and stored directly, otherwise the int32 partial sums are
+//    added into a zeroed workspace slot with red.global.add and the CTA that completes the tile's
+//    k-tile count reads them back, stores and re-zeroes.  Integer sums are exact in any order.
+//  * Launched with programmatic stream serialisation: weight tiles are requested before the wait for
+//    the previous kernel of the stream, tokens / outputs / workspace are touched only after it.
+// Every wait is bounded; a thread whose wait expires records a site code, stops waiting and still
+// runs the rest of its control flow, so the CTA reaches the exit where tensor memory is released.
+
+#include <cuda.h>
+#include <stdint.h>
+
+#include <cstdlib>
+#include <mutex>
+
+#include "lq_common.cuh"
+#include "lq_sched.cuh"
+#include "lq_tc_ptx.cuh"
+
+namespace lq {
+
+int make_byte_matrix_map(CUtensorMap* map, const void* ptr, long rows, long row_bytes, int box_rows,
+                         int box_bytes);   // lq_gemm_tc.cu
+
+namespace skinny {
+
+constexpr int kTileBytes = 8704;
+constexpr int kDequant = 256;              // two sets of 128
+constexpr int kThreads = 64 + kDequant;
+constexpr uint64_t kWaitLimitNs = 2000000000ull;
+constexpr int kOutI32 = 3;
+
+struct Args {
+  const uint8_t* blob;
+  const float* ascale;   // [M]
+  const float* s1;       // [N]
+  void* out;             // [M, N]
+  int32_t* slots;        // [grid][BN][128] partial sums, zero between launches
+  int32_t* counters;     // [grid]
+  int* status;
+  int out_mode;          // LQ_DT_* or kOutI32
+  int M, N, K, kt_total, n_tiles;
+  int debug_skip;        // pipeline studies only (results become wrong): 1 no tcgen05.st, 2 no MMA, 4 no dequant ALU
+};
+
+// One ring of NS stages couples shared memory (weight tile + token box) and the tensor-memory operand
+// stage: three barriers per k-tile (full, operand ready, empty) is the cheapest protocol measured;
+// every extra handshake per k-tile costs more than the buffer space it frees earlier.  Measured on
+// B200: about 70-100 KB of copies in flight per SM saturate HBM, deeper rings are slower.
+template <int BN, int NS>
+struct Cfg {
+  static constexpr int kXStage = BN * 128;
+  static constexpr int kACols = 32 * NS;   // one operand stage per shared-memory stage
+  static constexpr int kColsNeeded = BN + kACols;
+  static constexpr int kTmemCols = kColsNeeded <= 128 ? 128 : kColsNeeded <= 256 ? 256 : 512;
+  static constexpr int kNumBars = 3 * NS + 2;
+  static constexpr int kSmemBytes = 1024 + NS * (kXStage + kTileBytes) + kNumBars * 8 + 16;
+  static_assert(kColsNeeded <= 256, "two CTAs per SM share 512 tensor-memory columns");
+  static_assert(kSmemBytes <= 113 * 1024, "two CTAs per SM share the shared memory");
+};
+
+__device__ __forceinline__ void dequant_barrier() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+template <int BN, int NS>
+__global__ void __launch_bounds__(kThreads, 2)
+w4a8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args) {
+  using C = Cfg<BN, NS>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw);
+
+  const uint32_t xs = base;                          // NS token boxes (1024-aligned for the swizzle)
+  const uint32_t ws = xs + NS * C::kXStage;          // NS weight tiles
+  const uint32_t bar_full = ws + NS * kTileBytes;    // [NS] both copies of the stage landed
+  const uint32_t bar_empty = bar_full + NS * 8;      // [NS] the stage's MMAs are done
+  const uint32_t bar_aready = bar_empty + NS * 8;    // [NS] dequantised operand is in tensor memory
+  const uint32_t bar_accfull = bar_aready + NS * 8;  // the segment's accumulator is final
+  const uint32_t bar_accfree = bar_accfull + 8;      // the accumulator has been read
+  const uint32_t tmem_slot = bar_accfree + 8;
+  volatile uint32_t* tmem_slot_p = reinterpret_cast<volatile uint32_t*>(smem + (tmem_slot - base));
+  volatile int* last_flag = reinterpret_cast<volatile int*>(smem + (tmem_slot - base) + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NS; ++s) {
+      ptx::mbar_init(bar_full + 8 * s, 1);
+      ptx::mbar_init(bar_empty + 8 * s, 1);
+      ptx::mbar_init(bar_aready + 8 * s, 128);
+    }
+    ptx::mbar_init(bar_accfull, 1);
+    ptx::mbar_init(bar_accfree, kDequant);
+    ptx::fence_mbar_init();
+    ptx::prefetch_tensormap(&tmap_x);
+  }
+  __syncthreads();
+  allow_dependents();   // the next kernel of the stream may start prefetching its weights
+
+  SegmentWalk walk(SchedArgs{args.kt_total, args.n_tiles, 1, 0}, blockIdx.x, gridDim.x);
+  Segment sg;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      constexpr uint32_t kTx = (uint32_t)(kTileBytes + C::kXStage);
+      Ring<NS> ring;
+      int issued = 0;
+      bool ok = true;
+      // Weight tiles do not depend on the previous kernel of the stream, the tokens do: the first NS
+      // weight tiles are requested at once, then comes the wait for the previous kernel, then the
+      // token boxes of those stages.
+      int early_kt[NS];
+      bool dependency_met = false;
+      auto meet_dependency = [&]() {
+        dependency_wait();
+        dependency_met = true;
+        const int n = issued < NS ? issued : NS;
+        for (int j = 0; j < n; ++j)
+          ptx::tensor_load_2d(xs + j * C::kXStage, &tmap_x, early_kt[j] * 128, 0, bar_full + 8 * j);
+      };
+      while (ok && walk.next(sg)) {
+        const uint8_t* src = args.blob + ((size_t)sg.tile * args.kt_total + sg.kb) * kTileBytes;
+        for (int kt = sg.kb; kt < sg.ke; ++kt, src += kTileBytes) {
+          if (issued == NS) meet_dependency();
+          if (!ptx::mbar_wait_bounded(bar_empty + 8 * ring.s, ring.ph ^ 1u, kWaitLimitNs)) {
+            atomicExch(args.status, 401);
+            ok = false;
+            break;
+          }
+          const uint32_t full = bar_full + 8 * ring.s;
+          ptx::mbar_expect_tx(full, kTx);
+          ptx::bulk_load(ws + ring.s * kTileBytes, src, kTileBytes, full);
+          if (issued < NS) early_kt[issued] = kt;
+          else ptx::tensor_load_2d(xs + ring.s * C::kXStage, &tmap_x, kt * 128, 0, full);
+          ring.advance();
+          ++issued;
+        }
+      }
+      if (!dependency_met) meet_dependency();
+      // Copies in flight write shared memory: they must have landed before the CTA may exit.
+      const int pending = issued < NS ? issued : NS;
+      for (int j = 0; j < pending; ++j) {
+        const int i = issued - pending + j;
+        ptx::mbar_wait_bounded(bar_full + 8 * (i % NS), (uint32_t)(i / NS) & 1u, kWaitLimitNs);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ tensor memory + MMA issue
+    ptx::tmem_alloc(tmem_slot, C::kTmemCols);
+    ptx::tmem_relinquish();
+    ptx::tc_fence_before();
+    asm volatile("bar.sync 2, 288;" ::: "memory");   // publishes the allocation to the dequant warps
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot_p;
+    const uint32_t tmem_acc = tmem_base;
+    const uint32_t tmem_a = tmem_base + BN;
+    if (lane == 0) {
+      constexpr uint32_t idesc = ptx::idesc_i8(BN);
+      Ring<NS> ring;
+      bool ok = true;
+      uint32_t seg = 0;
+      while (walk.next(sg)) {
+        if (seg > 0 && ok && !ptx::mbar_wait_bounded(bar_accfree, (seg - 1) & 1u, kWaitLimitNs)) {
+          atomicExch(args.status, 402);
+          ok = false;
+        }
+        for (int kt = sg.kb; kt < sg.ke; ++kt) {
+          // "operand ready" implies "token box landed": the dequant set saw the stage's full barrier
+          if (ok && !ptx::mbar_wait_bounded(bar_aready + 8 * ring.s, ring.ph, kWaitLimitNs)) {
+            atomicExch(args.status, 403);
+            ok = false;
+          }
+          ptx::tc_fence_after();
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint64_t bdesc = ptx::smem_desc_sw128(xs + ring.s * C::kXStage + j * 32);
+            if (!(args.debug_skip & 2))
+              ptx::mma_i8_ts(tmem_acc, tmem_a + ring.s * 32 + j * 8, bdesc, idesc, (kt > sg.kb || j > 0) ? 1u : 0u);
+          }
+          ptx::tc_commit(bar_empty + 8 * ring.s);
+          ring.advance();
+        }
+        ptx::tc_commit(bar_accfull);
+        ++seg;
+      }
+    }
+    __syncwarp();
+    // tensor memory is released after every role is done
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, C::kTmemCols);
+    return;
+  } else {
+    // ------------------------------------------------------------------ dequant sets, then epilogue
+    const int d = threadIdx.x - 64;
+    const int set = d >> 7;                   // takes the k-tiles whose running index is set (mod 2)
+    const int quad = warp & 3;                // tensor-memory lane quadrant this warp may access
+    const int row = quad * 32 + lane;         // weight row inside the tile == tensor-memory lane
+    const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
+    asm volatile("bar.sync 2, 288;" ::: "memory");
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot_p;
+    const uint32_t tmem_acc = tmem_base + lane_addr;
+    const uint32_t tmem_a = tmem_base + BN + lane_addr;
+    Ring<NS> ring;
+    bool ok = true;
+    uint32_t step = 0;   // running k-tile index of this CTA
+    uint32_t seg = 0;
+    bool waited_dependency = false;
+
+    while (walk.next(sg)) {
+#pragma unroll 1
+      for (int kt = sg.kb; kt < sg.ke; ++kt, ++step, ring.advance()) {
+        if ((int)(step & 1u) != set) continue;
+        if (ok && !ptx::mbar_wait_bounded(bar_full + 8 * ring.s, ring.ph, kWaitLimitNs)) {
+          atomicExch(args.status, 404);
+          ok = false;
+        }
+        const uint8_t* wst = smem + (ws - base) + ring.s * kTileBytes;
+        uint4 ch[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) ch[c] = *reinterpret_cast<const uint4*>(wst + (c * 128 + row) * 16);
+        const uint32_t meta = *reinterpret_cast<const uint32_t*>(wst + 8192 + row * 4);
+        __syncwarp();   // lanes leave the poll loop one by one; tcgen05.st / wait::st need the warp converged
+        const uint32_t step0 = meta & 0xffu, a0 = ((meta >> 8) & 0xffu) * 0x01010101u;
+        const uint32_t step1 = (meta >> 16) & 0xffu, a1 = (meta >> 24) * 0x01010101u;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const uint32_t st = c < 2 ? step0 : step1;
+          const uint32_t ab = c < 2 ? a0 : a1;
+          const uint32_t pk[4] = {ch[c].x, ch[c].y, ch[c].z, ch[c].w};
+          uint32_t v[8];
+#pragma unroll
+          for (int h = 0; h < 4; ++h) {
+            if (args.debug_skip & 4) {
+              v[2 * h] = pk[h];
+              v[2 * h + 1] = pk[h] + st;
+            } else {
+              v[2 * h] = lqq_dequant4(pk[h] & 0x0F0F0F0Fu, st, ab);
+              v[2 * h + 1] = lqq_dequant4((pk[h] >> 4) & 0x0F0F0F0Fu, st, ab);
+            }
+          }
+          if (!(args.debug_skip & 1)) ptx::tmem_st8(tmem_a + ring.s * 32 + c * 8, v);
+          else if (v[0] + v[3] == 0x12345u) atomicExch(args.status, 499);
+        }
+        ptx::tc_wait_st();
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(bar_aready + 8 * ring.s);
+      }
+
+      // ---- epilogue of the segment: set g takes the 16-column chunks g, g+2, ...
+      if (ok && !ptx::mbar_wait_bounded(bar_accfull, seg & 1u, kWaitLimitNs)) {
+        atomicExch(args.status, 405);
+        ok = false;
+      }
+      __syncwarp();
+      ptx::tc_fence_after();
+      if (!waited_dependency) {
+        dependency_wait();   // outputs and the reduction workspace belong to earlier kernels until here
+        waited_dependency = true;
+      }
+      const long n = (long)sg.tile * 128 + row;
+      const bool n_ok = n < args.N;
+      const bool scaled = args.out_mode != kOutI32;
+      int32_t* slot = args.slots + (size_t)sg.slot * (BN * 128);
+      const float w_scale = (n_ok && scaled) ? args.s1[n] : 0.f;
+#pragma unroll 1
+      for (int c0 = set * 16; c0 < BN; c0 += 32) {
+        if (c0 >= args.M) break;   // uniform over the warp
+        int v[16];
+        ptx::tmem_ld16(tmem_acc + c0, v);
+        ptx::tc_wait_ld();
+        if (!n_ok) continue;
+        if (sg.whole) {
+          float sc[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) sc[j] = (scaled && c0 + j < args.M) ? __ldg(args.ascale + c0 + j) : 0.f;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (c0 + j < args.M) {
+              const size_t idx = (size_t)(c0 + j) * args.N + n;
+              if (scaled) store_out(args.out, idx, lqq_scale(v[j], sc[j], w_scale), args.out_mode);
+              else reinterpret_cast<int32_t*>(args.out)[idx] = v[j];
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (c0 + j < args.M) atomicAdd(slot + (c0 + j) * 128 + row, v[j]);
+        }
+      }
+      __syncwarp();
+      ptx::tc_fence_before();
+      ptx::mbar_arrive(bar_accfree);
+      ++seg;
+
+      if (!sg.whole) {
+        __threadfence();
+        dequant_barrier();
+        if (d == 0) {
+          const int add = sg.ke - sg.kb;
+          const int before = atomicAdd(args.counters + sg.slot, add);
+          *last_flag = (before + add == args.kt_total) ? 1 : 0;
+        }
+        dequant_barrier();
+        const bool last = *last_flag != 0;
+        dequant_barrier();   // everyone has read the flag before it can be rewritten
+        if (last) {
+          __threadfence();
+          if (n_ok) {
+#pragma unroll 1
+            for (int c0 = set * 16; c0 < BN; c0 += 32) {
+              if (c0 >= args.M) break;
+              int v[16];
+              float sc[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {   // all loads of the chunk first: one L2 round trip
+                v[j] = (c0 + j < args.M) ? __ldcg(slot + (c0 + j) * 128 + row) : 0;
+                sc[j] = (scaled && c0 + j < args.M) ? __ldg(args.ascale + c0 + j) : 0.f;
+              }
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                if (c0 + j < args.M) {
+                  __stcg(slot + (c0 + j) * 128 + row, 0);
+                  const size_t idx = (size_t)(c0 + j) * args.N + n;
+                  if (scaled) store_out(args.out, idx, lqq_scale(v[j], sc[j], w_scale), args.out_mode);
+                  else reinterpret_cast<int32_t*>(args.out)[idx] = v[j];
+                }
+              }
+            }
+          }
+          if (d == 0) args.counters[sg.slot] = 0;
+        }
+      }
+    }
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+}
+
+template <int BN, int NS>
+static int launch(const CUtensorMap& tx, const Args& a, int grid, cudaStream_t st) {
+  using C = Cfg<BN, NS>;
+  auto kern = &w4a8_skinny_kernel<BN, NS>;
+  static std::once_flag once[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  cudaError_t e = cudaSuccess;
+  std::call_once(once[dev & 63], [&]() {
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+  });
+  if (e == cudaSuccess) e = launch_overlapped(kern, dim3(grid), dim3(kThreads), (size_t)C::kSmemBytes, st, tx, a);
+  if (e != cudaSuccess) {
+    record_cuda_error(e, "w4a8_skinny_kernel launch");
+    return LQ_ERR_CUDA;
+  }
+  return check_launch("w4a8_skinny_kernel");
+}
+
+static int g_debug_skip = 0;
+
+static int bn_for(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128; }
+
+static int grid_for(int N, int K) {
+  const long units = (long)((N + 127) / 128) * (K / 128);
+  const long slots = 2L * sm_count();
+  return (int)(units < slots ? units : slots);
+}
+
+}  // namespace skinny
+
+size_t skinny_workspace_bytes(int M, int N, int K) {
+  const size_t grid = (size_t)skinny::grid_for(N, K);
+  return grid * (size_t)(skinny::bn_for(M) * 128 * 4) + grid * 4;
+}
+
+// out_mode: LQ_DT_* or 3 (raw int32).  M <= 128.  `ws`: skinny_workspace_bytes(), all zero, left all zero.
+int run_skinny_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, void* out,
+                    int out_mode, int M, int N, int K, void* ws, size_t ws_bytes, cudaStream_t st) {
+  using namespace skinny;
+  if (!ws || ws_bytes < skinny_workspace_bytes(M, N, K)) return LQ_ERR_WORKSPACE;
+  const int bn = bn_for(M);
+  const int grid = grid_for(N, K);
+  CUtensorMap tx;
+  int rc = make_byte_matrix_map(&tx, x, M, K, bn, 128);
+  if (rc) return rc;
+  Args a;
+  a.blob = blob;
+  a.ascale = ascale;
+  a.s1 = s1;
+  a.out = out;
+  a.slots = static_cast<int32_t*>(ws);
+  a.counters = a.slots + (size_t)grid * (bn * 128);
+  a.status = status_word();
+  a.out_mode = out_mode;
+  a.M = M;
+  a.N = N;
+  a.K = K;
+  a.kt_total = K / 128;
+  a.n_tiles = (N + 127) / 128;
+  a.debug_skip = g_debug_skip;
+  if (!a.status) return LQ_ERR_CUDA;
+  switch (bn) {
+    case 16: return launch<16, 6>(tx, a, grid, st);
+    case 32: return launch<32, 6>(tx, a, grid, st);
+    case 64: return launch<64, 5>(tx, a, grid, st);
+    default: return launch<128, 4>(tx, a, grid, st);
+  }
+}
+
+}  // namespace lq
+
+// Pipeline-study hook (timing experiments only; results become wrong when non-zero).
+extern "C" LQ_API void lq_debug_set_skinny_skip(int mask) { lq::skinny::g_debug_skip = mask; }

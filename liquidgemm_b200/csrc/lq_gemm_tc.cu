@@ -54,6 +54,12 @@ int tile_pick_splits(int M, int N, int K);                                   // 
 size_t tile_workspace_bytes(int M, int N, int splits);                       // lq_gemm_tile.cu
 int run_tile_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, void* out, int out_mode,
                   int M, int N, int K, int splits, void* ws, size_t ws_bytes, cudaStream_t st);  // lq_gemm_tile.cu
+size_t skinny_workspace_bytes(int M, int N, int K);                          // lq_gemm_skinny.cu
+int run_skinny_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, void* out,
+                    int out_mode, int M, int N, int K, void* ws, size_t ws_bytes, cudaStream_t st);  // lq_gemm_skinny.cu
+size_t gemv_blob_workspace_bytes(int N, int K);                              // lq_gemv_blob.cu
+int run_gemv_blob_ws(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, void* out,
+                     int out_dtype, int M, int N, int K, void* ws, size_t ws_bytes, cudaStream_t st);  // lq_gemv_blob.cu
 int launch_gemv_plain_f32(const int8_t* x, const uint8_t* nibbles, const uint8_t* s_u8,
                           const uint8_t* off_a, const float* ascale, const float* s1, float* y, int M,
                           int N, int K, int G, cudaStream_t st);  // lq_gemv.cu
@@ -779,23 +785,32 @@ int lq_gemm_pick_splitk(int M, int N, int K, int env_override) {
 // Which kernel serves (M, splitk): the two-CTAs-per-SM decode-tile kernel with `splits` int32 planes
 // (M <= 128), or the persistent kernel (stream-K for splitk 0 / -1, fixed split otherwise).
 struct Route {
-  bool tile;
+  bool tile;     // decode-tile kernel with `splits` int32 planes (explicit split-K request, M <= 128)
+  bool skinny;   // streaming stream-K kernel for M <= 128 (the default for decode batches)
   int splits;
 };
+// Up to this many tokens the dp4a streaming GEMV over the blob beats the tensor-core kernel (measured on
+// the Llama-3.1-8B shapes); it only produces scaled outputs, the int32 entry point always uses tensor cores.
+constexpr int kGemvBlobMaxM = 4;
+
 static Route route_for(int M, int N, int K, int splitk) {
   const int kt = K / 128;
-  if (splitk == -1) return {false, 0};
+  if (splitk == -1) return {false, false, 0};
   if (M <= 128) {
-    int S = splitk > 0 ? splitk : tile_pick_splits(M, N, K);
-    if (S > kt) S = kt;
-    return {true, S < 1 ? 1 : S};
+    if (splitk == 0) return {false, true, 0};
+    int S = splitk > kt ? kt : splitk;
+    return {true, false, S < 1 ? 1 : S};
   }
-  return {false, splitk};
+  return {false, false, splitk};
 }
 
 size_t lq_gemm_workspace_bytes(int M, int N, int K, int splitk) {
   if (M <= 0 || N <= 0 || K < 128) return 0;
   const Route r = route_for(M, N, K, splitk);
+  if (r.skinny) {
+    const size_t a = skinny_workspace_bytes(M, N, K), b = M <= kGemvBlobMaxM ? gemv_blob_workspace_bytes(N, K) : 0;
+    return a > b ? a : b;
+  }
   return r.tile ? tile_workspace_bytes(M, N, r.splits) : make_plan(M, N, K, r.splits).ws_bytes;
 }
 
@@ -811,6 +826,12 @@ static int blob_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, 
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(blob)) % 16) return LQ_ERR_BAD_ARG;
   if (M == 0) return LQ_OK;
   const Route r = route_for(M, N, K, splitk);
+  if (r.skinny) {
+    if (int rc = lq_check_device()) return rc;
+    if (M <= kGemvBlobMaxM && out_mode != kOutI32)
+      return run_gemv_blob_ws(x, blob, ascale, s1, out, out_mode, M, N, K, ws, ws_bytes, st);
+    return run_skinny_gemm(x, blob, ascale, s1, out, out_mode, M, N, K, ws, ws_bytes, st);
+  }
   if (r.tile) {
     if (int rc = lq_check_device()) return rc;
     return run_tile_gemm(x, blob, ascale, s1, out, out_mode, M, N, K, r.splits, ws, ws_bytes, st);

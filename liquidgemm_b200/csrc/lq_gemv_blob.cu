@@ -1,0 +1,387 @@
+// Decode GEMV over the tile blob (the GEMM's weight format): y[m,n] = scale * sum_k x[m,k] * q^[n,k]
+// for 1..8 tokens, replacing the reference's fused GEMV (csrc/liquid_gemm/gemv2.cu:21-120) without a
+// second copy of the weights in a GEMV-specific layout.
+//
+// HBM-bound streaming design:
+//  * the (n-tile, k-tile) grid of 8704-byte blob tiles is cut into equal contiguous ranges, one per
+//    CTA, two CTAs per SM ("stream-K"): every SM streams the same number of bytes whatever N and K;
+//  * one producer thread per CTA keeps a ring of NS tiles in flight with contiguous bulk copies
+//    (cp.async.bulk + mbarrier complete_tx), plus one 128-byte copy per token for the activations;
+//  * 256 consumer threads: thread (row r, group h) reconstructs the 64 weights of row r in 64-wide
+//    group h of the k-tile (AND / SHR+AND / IMAD / XOR on words of 4 lanes) and feeds dp4a against the
+//    tokens' words, which every lane reads from shared memory at the same address (broadcast);
+//  * int32 partial sums of an n-tile cut by a range boundary are added with red.global.add into a
+//    zeroed slot; the CTA that completes the tile's k-tile count applies the scale epilogue and
+//    re-zeroes slot and counter.  Integer addition commutes, so the result is bit-identical for every
+//    grid size.
+// Every wait is bounded: on expiry the thread records a site code in the status word, stops waiting
+// and runs the rest of its control flow (barriers included) so the CTA still exits.
+
+#include <stdint.h>
+
+#include <mutex>
+
+#include "lq_common.cuh"
+#include "lq_sched.cuh"
+#include "lq_tc_ptx.cuh"
+
+namespace lq {
+namespace gblob {
+
+constexpr int kTileBytes = 8704;   // 4 chunks x [128 rows][16 B] + [128 rows][step0, off0, step1, off1]
+constexpr int kConsumers = 256;
+constexpr int kThreads = 32 + kConsumers;
+constexpr uint64_t kWaitLimitNs = 2000000000ull;
+
+struct Args {
+  const uint8_t* blob;
+  const int8_t* x;       // [M, K]
+  const float* ascale;   // [M]
+  const float* s1;       // [N]
+  void* out;             // [M, N]
+  int32_t* slots;        // [grid][MT][128] partial sums, zero between launches
+  int32_t* counters;     // [grid] k-tiles added to the slot, zero between launches
+  int* status;
+  int out_dtype;
+  int M, N, K, kt_total, n_tiles;
+  long long* trace;      // pipeline studies: [grid][4] globaltimer stamps, or null
+};
+
+template <int MT, int NS>
+struct Cfg {
+  static constexpr int kXStage = MT * 128;
+  static constexpr int kStage = kTileBytes + kXStage;
+  static constexpr int kRedBytes = MT * 128 * 4;
+  static constexpr int kSmemBytes = 128 + NS * kStage + 2 * NS * 8 + kRedBytes + 16;
+};
+
+__device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+__device__ __forceinline__ int dp4a_s8(uint32_t w, uint32_t x, int acc) {
+  int d;
+  asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(w), "r"(x), "r"(acc));
+  return d;
+}
+
+template <int MT, int NS>
+__global__ void __launch_bounds__(kThreads, 2) gemv_blob_kernel(const Args args) {
+  using C = Cfg<MT, NS>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 127u) & ~127u;
+  uint8_t* smem = smem_raw + (base - raw);
+
+  const uint32_t ws = base;                                // NS weight tiles
+  const uint32_t xs = ws + NS * kTileBytes;                // NS token slices [MT][128 B]
+  const uint32_t bar_full = xs + NS * C::kXStage;
+  const uint32_t bar_empty = bar_full + NS * 8;
+  int32_t* red = reinterpret_cast<int32_t*>(smem + (bar_empty + NS * 8 - base));   // [MT][128]
+  volatile int* last_flag = reinterpret_cast<volatile int*>(red + MT * 128);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int M = args.M;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NS; ++s) {
+      ptx::mbar_init(bar_full + 8 * s, 1);
+      ptx::mbar_init(bar_empty + 8 * s, kConsumers);
+    }
+    ptx::fence_mbar_init();
+  }
+  __syncthreads();
+
+  allow_dependents();   // the next kernel of the stream may start prefetching its weights
+
+  SchedArgs sa;
+  sa.kt_total = args.kt_total;
+  sa.n_tiles = args.n_tiles;
+  sa.m_tiles = 1;
+  sa.fixed_split = 0;
+  SegmentWalk walk(sa, blockIdx.x, gridDim.x);
+  Segment sg;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      const uint32_t tx = (uint32_t)(kTileBytes + M * 128);
+      Ring<NS> ring;
+      int issued = 0;
+      bool ok = true;
+      // The weights never depend on the previous kernel of the stream, the tokens do: the first NS
+      // weight tiles are requested at once, the wait for the previous kernel comes after that, and
+      // only then the token slices of those stages.
+      int early_kt[NS];
+      bool dependency_met = false;
+      auto meet_dependency = [&]() {
+        dependency_wait();
+        dependency_met = true;
+        const int n = issued < NS ? issued : NS;
+        for (int j = 0; j < n; ++j) {
+          const int8_t* xsrc = args.x + (size_t)early_kt[j] * 128;
+          for (int m = 0; m < M; ++m)
+            ptx::bulk_load(xs + j * C::kXStage + m * 128, xsrc + (size_t)m * args.K, 128, bar_full + 8 * j);
+        }
+      };
+      while (ok && walk.next(sg)) {
+        const uint8_t* src = args.blob + ((size_t)sg.tile * args.kt_total + sg.kb) * kTileBytes;
+        for (int kt = sg.kb; kt < sg.ke; ++kt, src += kTileBytes) {
+          if (issued == NS) meet_dependency();
+          if (!ptx::mbar_wait_bounded(bar_empty + 8 * ring.s, ring.ph ^ 1u, kWaitLimitNs)) {
+            atomicExch(args.status, 301);
+            ok = false;
+            break;
+          }
+          const uint32_t full = bar_full + 8 * ring.s;
+          ptx::mbar_expect_tx(full, tx);
+          ptx::bulk_load(ws + ring.s * kTileBytes, src, kTileBytes, full);
+          if (issued < NS) {
+            early_kt[issued] = kt;
+          } else {
+            const int8_t* xsrc = args.x + (size_t)kt * 128;
+            for (int m = 0; m < M; ++m)
+              ptx::bulk_load(xs + ring.s * C::kXStage + m * 128, xsrc + (size_t)m * args.K, 128, full);
+          }
+          ring.advance();
+          ++issued;
+        }
+      }
+      if (!dependency_met) meet_dependency();
+      // Copies in flight write shared memory: they must have landed before the CTA may exit.  On
+      // the normal path the consumers have waited for every one of them already.
+      const int pending = issued < NS ? issued : NS;
+      for (int j = 0; j < pending; ++j) {
+        const int i = issued - pending + j;
+        ptx::mbar_wait_bounded(bar_full + 8 * (i % NS), (uint32_t)(i / NS) & 1u, kWaitLimitNs);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ consumers
+    const int c = threadIdx.x - 32;
+    const int row = c & 127;
+    const int h = c >> 7;   // 64-wide group of the k-tile handled by this thread
+    const uint32_t w_off = (uint32_t)((2 * h) * 128 + row) * 16;
+    const uint32_t meta_off = 8192u + (uint32_t)row * 4 + 2 * h;
+    Ring<NS> ring;
+    bool ok = true;
+    const bool tracing = args.trace != nullptr && c == 0;
+    dependency_wait();   // outputs, the reduction workspace and the tokens belong to earlier kernels until here
+    if (tracing) args.trace[blockIdx.x * 4 + 0] = (long long)ptx::globaltimer_ns();
+    bool first = true;
+
+    while (walk.next(sg)) {
+      int acc[MT];
+#pragma unroll
+      for (int m = 0; m < MT; ++m) acc[m] = 0;
+
+#pragma unroll 1
+      for (int kt = sg.kb; kt < sg.ke; ++kt) {
+        if (ok && !ptx::mbar_wait_bounded(bar_full + 8 * ring.s, ring.ph, kWaitLimitNs)) {
+          atomicExch(args.status, 302);
+          ok = false;
+        }
+        if (first) {
+          if (tracing) args.trace[blockIdx.x * 4 + 1] = (long long)ptx::globaltimer_ns();
+          first = false;
+        }
+        const uint8_t* wst = smem + (ws - base) + ring.s * kTileBytes;
+        const uint4 c0 = *reinterpret_cast<const uint4*>(wst + w_off);
+        const uint4 c1 = *reinterpret_cast<const uint4*>(wst + w_off + 2048);
+        const uint32_t meta = *reinterpret_cast<const uint16_t*>(wst + meta_off);
+        const uint32_t step = meta & 0xffu;
+        const uint32_t ab = (meta >> 8) * 0x01010101u;
+        const uint32_t pk[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+        uint32_t v[16];   // v[2j], v[2j+1]: weights k = 8j..8j+3, 8j+4..8j+7 of the group
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          v[2 * j] = lqq_dequant4(pk[j] & 0x0F0F0F0Fu, step, ab);
+          v[2 * j + 1] = lqq_dequant4((pk[j] >> 4) & 0x0F0F0F0Fu, step, ab);
+        }
+        const uint8_t* xst = smem + (xs - base) + ring.s * C::kXStage + 64 * h;
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+          const uint4* xp = reinterpret_cast<const uint4*>(xst + m * 128);
+          int a = acc[m], b = 0;   // two chains: dp4a latency, not issue, would bound one
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const uint4 xv = xp[q];
+            a = dp4a_s8(v[4 * q], xv.x, a);
+            b = dp4a_s8(v[4 * q + 1], xv.y, b);
+            a = dp4a_s8(v[4 * q + 2], xv.z, a);
+            b = dp4a_s8(v[4 * q + 3], xv.w, b);
+          }
+          acc[m] = a + b;
+        }
+        ptx::mbar_arrive(bar_empty + 8 * ring.s);
+        ring.advance();
+      }
+
+      if (tracing) args.trace[blockIdx.x * 4 + 2] = (long long)ptx::globaltimer_ns();   // last main loop end
+      // ---- reduce the two k-groups of every row, then finish or publish the partial sums
+      if (h == 1) {
+#pragma unroll
+        for (int m = 0; m < MT; ++m) red[m * 128 + row] = acc[m];
+      }
+      consumer_barrier();
+      const long n = (long)sg.tile * 128 + row;
+      const bool mine = (h == 0) && n < args.N;
+      if (h == 0) {
+#pragma unroll
+        for (int m = 0; m < MT; ++m) acc[m] += red[m * 128 + row];
+      }
+      if (sg.whole) {
+        if (mine) {
+          const float w_scale = args.s1[n];
+#pragma unroll
+          for (int m = 0; m < MT; ++m)
+            if (m < M) store_out(args.out, (size_t)m * args.N + n, lqq_scale(acc[m], args.ascale[m], w_scale),
+                                 args.out_dtype);
+        }
+        consumer_barrier();   // `red` may be rewritten by the next segment
+      } else {
+        int32_t* slot = args.slots + (size_t)sg.slot * (MT * 128);
+        if (mine) {
+#pragma unroll
+          for (int m = 0; m < MT; ++m)
+            if (m < M) atomicAdd(slot + m * 128 + row, acc[m]);
+        }
+        __threadfence();
+        consumer_barrier();
+        if (c == 0) {
+          const int add = sg.ke - sg.kb;
+          const int before = atomicAdd(args.counters + sg.slot, add);
+          *last_flag = (before + add == args.kt_total) ? 1 : 0;
+        }
+        consumer_barrier();
+        const bool last = *last_flag != 0;
+        consumer_barrier();   // everyone has read the flag before it can be rewritten
+        if (last) {
+          __threadfence();
+          if (mine) {
+            const float w_scale = args.s1[n];
+            int t[MT];
+#pragma unroll
+            for (int m = 0; m < MT; ++m) t[m] = (m < M) ? __ldcg(slot + m * 128 + row) : 0;
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+              if (m < M) {
+                __stcg(slot + m * 128 + row, 0);
+                store_out(args.out, (size_t)m * args.N + n, lqq_scale(t[m], args.ascale[m], w_scale),
+                          args.out_dtype);
+              }
+            }
+          }
+          if (c == 0) args.counters[sg.slot] = 0;
+        }
+      }
+    }
+    if (tracing) args.trace[blockIdx.x * 4 + 3] = (long long)ptx::globaltimer_ns();
+  }
+  __syncthreads();
+}
+
+template <int MT, int NS>
+static int launch(const Args& a, int grid, cudaStream_t st) {
+  using C = Cfg<MT, NS>;
+  auto kern = &gemv_blob_kernel<MT, NS>;
+  static std::once_flag once[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  cudaError_t e = cudaSuccess;
+  std::call_once(once[dev & 63], [&]() {
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+  });
+  if (e != cudaSuccess) {
+    record_cuda_error(e, "cudaFuncSetAttribute(gemv_blob_kernel)");
+    return LQ_ERR_CUDA;
+  }
+  e = launch_overlapped(kern, dim3(grid), dim3(kThreads), (size_t)C::kSmemBytes, st, a);
+  if (e != cudaSuccess) {
+    record_cuda_error(e, "gemv_blob_kernel launch");
+    return LQ_ERR_CUDA;
+  }
+  return check_launch("gemv_blob_kernel");
+}
+
+static long long* g_trace = nullptr;
+
+static int grid_for(int N, int K) {
+  const long units = (long)((N + 127) / 128) * (K / 128);
+  const long slots = 2L * sm_count();
+  return (int)(units < slots ? units : slots);
+}
+
+}  // namespace gblob
+
+// Workspace bytes for a launch grid of `grid` CTAs (partial-sum slots, then counters).
+static size_t gemv_blob_ws_bytes(int grid) { return (size_t)grid * (8 * 128 * 4) + (size_t)grid * 4; }
+
+size_t gemv_blob_workspace_bytes(int N, int K) { return gemv_blob_ws_bytes(gblob::grid_for(N, K)); }
+
+// Same call with the workspace as one buffer (slots, then counters), for the GEMM entry points.
+int run_gemv_blob_ws(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, void* out,
+                     int out_dtype, int M, int N, int K, void* ws, size_t ws_bytes, cudaStream_t st);
+
+int run_gemv_blob(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, void* out,
+                  int out_dtype, int M, int N, int K, int32_t* slots, int32_t* counters, cudaStream_t st) {
+  using namespace gblob;
+  Args a;
+  a.blob = blob;
+  a.x = x;
+  a.ascale = ascale;
+  a.s1 = s1;
+  a.out = out;
+  a.slots = slots;
+  a.counters = counters;
+  a.status = status_word();
+  a.out_dtype = out_dtype;
+  a.M = M;
+  a.N = N;
+  a.K = K;
+  a.kt_total = K / 128;
+  a.n_tiles = (N + 127) / 128;
+  a.trace = g_trace;
+  if (!a.status) return LQ_ERR_CUDA;
+  const int grid = grid_for(N, K);
+  if (M <= 1) return launch<1, 8>(a, grid, st);
+  if (M <= 2) return launch<2, 8>(a, grid, st);
+  if (M <= 4) return launch<4, 8>(a, grid, st);
+  return launch<8, 7>(a, grid, st);
+}
+
+int run_gemv_blob_ws(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, void* out,
+                     int out_dtype, int M, int N, int K, void* ws, size_t ws_bytes, cudaStream_t st) {
+  const int grid = gblob::grid_for(N, K);
+  if (!ws || ws_bytes < gemv_blob_ws_bytes(grid)) return LQ_ERR_WORKSPACE;
+  int32_t* slots = static_cast<int32_t*>(ws);
+  return run_gemv_blob(x, blob, ascale, s1, out, out_dtype, M, N, K, slots, slots + (size_t)grid * (8 * 128), st);
+}
+
+}  // namespace lq
+
+using namespace lq;
+
+extern "C" {
+
+// Pipeline-study hook: device buffer of 4 x int64 per CTA (2 x SM count CTAs) that receives
+// globaltimer stamps (start, first tile landed, last main loop done, exit); null switches it off.
+LQ_API void lq_debug_set_blob_trace(void* device_buffer) { gblob::g_trace = static_cast<long long*>(device_buffer); }
+
+LQ_API size_t lq_gemv_blob_workspace_bytes(void) { return gemv_blob_ws_bytes(2 * sm_count()); }
+
+LQ_API int lq_w4a8_gemv_blob(const void* x_i8, const void* blob, const void* ascale, const void* s1, void* out,
+                             int out_dtype, int M, int N, int K, void* workspace, size_t workspace_bytes,
+                             void* stream) {
+  if (!x_i8 || !blob || !ascale || !s1 || !out) return LQ_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(x_i8) | reinterpret_cast<uintptr_t>(blob)) & 15u) return LQ_ERR_BAD_ARG;
+  if (out_dtype < LQ_DT_BF16 || out_dtype > LQ_DT_F32) return LQ_ERR_BAD_ARG;
+  if (M < 1 || M > 8 || N < 1 || K < 128 || K % 128) return LQ_ERR_SHAPE;
+  const int grid = gblob::grid_for(N, K);
+  if (!workspace || workspace_bytes < gemv_blob_ws_bytes(grid)) return LQ_ERR_WORKSPACE;
+  int32_t* slots = static_cast<int32_t*>(workspace);
+  int32_t* counters = slots + (size_t)grid * (8 * 128);
+  return run_gemv_blob(static_cast<const int8_t*>(x_i8), static_cast<const uint8_t*>(blob),
+                       static_cast<const float*>(ascale), static_cast<const float*>(s1), out, out_dtype, M, N, K,
+                       slots, counters, as_stream(stream));
+}
+
+}  // extern "C"

@@ -337,6 +337,28 @@ def gemm_fused(x_i8, blob, ascale, s1, N, K, out_dtype, splitk=None):
     return y
 
 
+def gemv_blob(x_i8, blob, ascale, s1, N, K, out_dtype):
+    """Decode GEMV (M <= 8) straight from the GEMM's tile blob: the streaming dp4a kernel."""
+    x_i8 = _i8(x_i8, "x_i8")
+    _req(K % 128 == 0 and x_i8.shape[1] == K, "K%128==0 required and x_i8 must be [M,K]")
+    _req(int(out_dtype) in _OUT_DTYPES, "out_dtype must be 0 (bf16), 1 (fp16) or 2 (fp32)")
+    blob = _check_blob(blob, N, K)
+    ascale, s1 = _f32(ascale, "ascale"), _f32(s1, "s1")
+    M = x_i8.shape[0]
+    _req(M <= 8, "gemv_blob is the M <= 8 decode path")
+    _req(ascale.numel() == M and s1.numel() == N, "ascale must be [M] and s1 [N]")
+    y = torch.empty((M, N), dtype=_OUT_DTYPES[int(out_dtype)], device=x_i8.device)
+    if M:
+        with _dev_ctx(x_i8):
+            ws = _workspace(lib.lq_gemv_blob_workspace_bytes(), x_i8.device)
+            rc = lib.lq_w4a8_gemv_blob(_ptr(x_i8), _ptr(blob), _ptr(ascale), _ptr(s1), _ptr(y), int(out_dtype),
+                                       M, N, K, _ptr(ws), ws.numel(), _stream())
+            if rc != 0:
+                ws.zero_()
+            check(rc, "gemv_blob")
+    return y
+
+
 def gemm_rowmajor(x_i8, gpack, s_u8, off_a, ascale, s1, N, K, out_dtype, splitk=None):
     """Fused W4A8 linear on tensor cores straight from the row-major GEMV pack (any M)."""
     x_i8 = _i8(x_i8, "x_i8")
@@ -576,12 +598,56 @@ def w4a8_linear(x: torch.Tensor, qw_dev: dict, out_dtype: torch.dtype = None) ->
                                                     qw_dev["s1"], qw_dev["N"], qw_dev["K"], 64, odt)
 
 
+_HOST_SCRATCH: dict = {}
+
+
+def w4a8_linear_host(x_host: torch.Tensor, qw_dev: dict, y_host: torch.Tensor = None,
+                     out_dtype: torch.dtype = None, device=None) -> torch.Tensor:
+    """The same linear for activations and outputs in HOST memory (pinned for asynchronous copies):
+    upload, quantise, linear from the tile blob ``qw_dev["rs"]`` and download are enqueued on the current
+    stream by ONE native call.  Returns ``y_host`` (allocated pinned when not given); the caller
+    synchronises the stream before reading it."""
+    _req(not x_host.is_cuda and x_host.dim() == 2 and x_host.is_contiguous(), "x_host must be a contiguous CPU [M,K] tensor")
+    _req(x_host.dtype in _DTYPE_CODES, "x_host must be bf16, fp16 or fp32")
+    M, K = x_host.shape
+    N = qw_dev["N"]
+    _req(K == qw_dev["K"] and K % 128 == 0, "K mismatch or K % 128 != 0")
+    odt = out_dtype or x_host.dtype
+    if y_host is None:
+        y_host = torch.empty((M, N), dtype=odt, pin_memory=True)
+    _req(not y_host.is_cuda and y_host.is_contiguous() and tuple(y_host.shape) == (M, N) and y_host.dtype == odt,
+         "y_host must be a contiguous CPU [M,N] tensor of the output dtype")
+    if M == 0:
+        return y_host
+    blob, s1 = qw_dev["rs"], qw_dev["s1"]
+    dev = blob.device if device is None else torch.device(device)
+    xc, oc = _DTYPE_CODES[x_host.dtype], _DTYPE_CODES[odt]
+    with torch.cuda.device(dev):
+        stream = _stream()
+        need = lib.lq_linear_host_scratch_bytes(M, N, K, xc, oc)
+        key = (dev.index, stream)
+        scratch = _HOST_SCRATCH.get(key)
+        if scratch is None or scratch.numel() < need:
+            scratch = torch.empty((max(need, 1 << 22),), dtype=torch.uint8, device=dev)
+            _HOST_SCRATCH[key] = scratch
+        nws = lib.lq_gemm_workspace_bytes(M, N, K, 0)
+        ws = _workspace(nws, dev)
+        rc = lib.lq_w4a8_linear_host(x_host.data_ptr(), xc, _ptr(blob), _ptr(s1), y_host.data_ptr(), oc, M, N, K,
+                                     _ptr(scratch), scratch.numel(), _ptr(ws) if ws is not None else None,
+                                     ws.numel() if ws is not None else 0, stream)
+        if rc != 0 and ws is not None:
+            ws.zero_()
+        check(rc, "w4a8_linear_host")
+    return y_host
+
+
 def use_gemv(M: int, N: int, K: int, have_gp: bool, have_rs: bool) -> bool:
-    """Decode dispatch measured on B200: the GEMV pack wins for one or two tokens (and up to four on
-    matrices of qkv size); from there on the two-CTAs-per-SM tensor-core tile kernel on the tile blob
-    is faster.  The reference switches at M <= 16 (liquidgemm/vllm_plugin.py:189)."""
+    """Decode dispatch measured on B200: the row-major GEMV pack only wins on small matrices (qkv
+    size) with up to four tokens, where fixed costs dominate and a kernel without a reduction stage is
+    ahead; everything else is served from the tile blob (streaming dp4a GEMV up to four tokens, the
+    tensor-core kernel from there on).  The reference switches at M <= 16 (liquidgemm/vllm_plugin.py:189)."""
     if not have_gp or M > 16:
         return False
     if not have_rs:
         return True
-    return M <= 2 or (M <= 4 and N * K <= (1 << 25))
+    return M <= 4 and N * K <= (1 << 25)
