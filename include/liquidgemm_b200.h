@@ -113,6 +113,22 @@ LQ_API int lq_w4a8_gemv_blob(const void* x_i8, const void* blob, const void* asc
                              void* out, int out_dtype, int M, int N, int K, void* workspace,
                              size_t workspace_bytes, void* stream);
 
+/* lq_w4a8_gemv_blob without a workspace argument: the reduction scratch is an array inside the
+ * library's device image (2 099 200 bytes, enough for 512 CTAs = devices of up to 256 SMs), so the
+ * call needs no buffer from any allocator.  This entry point has no counterpart in the reference.
+ *  - Limits: M <= 8, K % 128 == 0, x_i8 and blob 16-byte aligned as for lq_w4a8_gemv_blob; a device
+ *    whose 2 x SM count exceeds 512 is refused with LQ_ERR_WORKSPACE (text in lq_last_cuda_error()).
+ *  - The FIRST call on each device (with that device current) looks the array up and clears it with
+ *    a synchronous cudaMemset: make that first call outside any stream capture and outside
+ *    latency-critical sections; later calls only enqueue the kernel.
+ *  - The array must be all zero when a call starts and every successful call leaves it all zero.
+ *    There is one array per device: two calls that overlap in time on the same device (different
+ *    streams or threads) race on it and give wrong sums; serialise them.  Between calls the array
+ *    simply keeps what the last call left (zeros after a successful one). */
+LQ_API int lq_w4a8_gemv_blob_static(const void* x_i8, const void* blob, const void* ascale,
+                                    const void* s1, void* out, int out_dtype, int M, int N, int K,
+                                    void* stream);
+
 /* One whole linear layer for HOST activations and a HOST output: upload, per-token quantise, fused
  * W4A8 linear from the tile blob (automatic kernel choice by M), download, all enqueued on `stream`
  * by this one call; nothing is synchronised.  x_host [M,K] in x_dtype and y_host [M,N] in out_dtype

@@ -36,6 +36,7 @@ _SIGNATURES = {
     "lq_w4a8_gemv_stream": (c_int, [P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, P, c_size_t, P]),
     "lq_gemv_blob_workspace_bytes": (c_size_t, []),
     "lq_w4a8_gemv_blob": (c_int, [P, P, P, P, P, c_int, c_int, c_int, c_int, P, c_size_t, P]),
+    "lq_w4a8_gemv_blob_static": (c_int, [P, P, P, P, P, c_int, c_int, c_int, c_int, P]),
     "lq_linear_host_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "lq_w4a8_linear_host": (c_int, [P, c_int, P, P, P, c_int, c_int, c_int, c_int, P, c_size_t, P, c_size_t, P]),
     "lq_gemm_v1_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),

@@ -384,4 +384,65 @@ LQ_API int lq_w4a8_gemv_blob(const void* x_i8, const void* blob, const void* asc
                        slots, counters, as_stream(stream));
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same GEMV with its reduction scratch inside the library image instead of a caller buffer.
+// ---------------------------------------------------------------------------------------------
+}  // extern "C"
+
+namespace lq {
+namespace gblob {
+
+// Room for 512 CTAs (two per SM on up to 256 SMs): 512 x (8 tokens x 128 rows x 4 B) of partial
+// sums followed by 512 counters, 2 099 200 bytes of device memory that exist as long as the
+// library is loaded.  The loader zero-fills it; the kernel leaves it zero-filled.
+constexpr int kStaticMaxCtas = 512;
+constexpr size_t kStaticSlotBytes = (size_t)kStaticMaxCtas * 8 * 128 * 4;
+constexpr size_t kStaticBytes = kStaticSlotBytes + (size_t)kStaticMaxCtas * 4;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticBytes];
+
+static void* g_static_ptr[64];
+static cudaError_t g_static_err[64];
+static std::once_flag g_static_once[64];
+
+// First use on a device (that device current): resolve the array's address and clear it once.
+static void* static_scratch_for_current_device() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::call_once(g_static_once[dev], [dev]() {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e == cudaSuccess) e = cudaMemset(p, 0, kStaticBytes);
+    g_static_err[dev] = e;
+    g_static_ptr[dev] = e == cudaSuccess ? p : nullptr;
+    if (e != cudaSuccess) record_cuda_error(e, "static GEMV scratch set-up");
+  });
+  return g_static_ptr[dev];
+}
+
+}  // namespace gblob
+}  // namespace lq
+
+extern "C" {
+
+LQ_API int lq_w4a8_gemv_blob_static(const void* x_i8, const void* blob, const void* ascale, const void* s1,
+                                    void* out, int out_dtype, int M, int N, int K, void* stream) {
+  if (!x_i8 || !blob || !ascale || !s1 || !out) return LQ_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(x_i8) | reinterpret_cast<uintptr_t>(blob)) & 15u) return LQ_ERR_BAD_ARG;
+  if (out_dtype < LQ_DT_BF16 || out_dtype > LQ_DT_F32) return LQ_ERR_BAD_ARG;
+  if (M < 1 || M > 8 || N < 1 || K < 128 || K % 128) return LQ_ERR_SHAPE;
+  const int grid = gblob::grid_for(N, K);
+  if (grid > gblob::kStaticMaxCtas) {
+    record_cuda_error(cudaErrorInvalidValue,
+                      "lq_w4a8_gemv_blob_static: the built-in scratch holds 512 CTAs (devices up to 256 SMs)");
+    return LQ_ERR_WORKSPACE;
+  }
+  void* p = gblob::static_scratch_for_current_device();
+  if (!p) return LQ_ERR_CUDA;
+  int32_t* slots = static_cast<int32_t*>(p);
+  int32_t* counters = reinterpret_cast<int32_t*>(static_cast<unsigned char*>(p) + gblob::kStaticSlotBytes);
+  return run_gemv_blob(static_cast<const int8_t*>(x_i8), static_cast<const uint8_t*>(blob),
+                       static_cast<const float*>(ascale), static_cast<const float*>(s1), out, out_dtype, M, N, K,
+                       slots, counters, as_stream(stream));
+}
+
 }  // extern "C"
