@@ -114,7 +114,7 @@ LQ_API int lq_w4a8_gemv_blob(const void* x_i8, const void* blob, const void* asc
                              size_t workspace_bytes, void* stream);
 
 /* lq_w4a8_gemv_blob without a workspace argument: the reduction scratch is an array inside the
- * library's device image (2 099 200 bytes, enough for 512 CTAs = devices of up to 256 SMs), so the
+ * library's device image (4 194 304 bytes, enough for 512 CTAs = devices of up to 256 SMs), so the
  * call needs no buffer from any allocator.  This entry point has no counterpart in the reference.
  *  - Limits: M <= 8, K % 128 == 0, x_i8 and blob 16-byte aligned as for lq_w4a8_gemv_blob; a device
  *    whose 2 x SM count exceeds 512 is refused with LQ_ERR_WORKSPACE (text in lq_last_cuda_error()).

@@ -14,9 +14,10 @@
 //            memory, B = tokens through a shared-memory descriptor); its commit recycles the stage.
 //            A single CTA cannot issue these faster than one per ~94 cycles, two CTAs per SM overlap.
 //  * Epilogue by the dequant warps: tcgen05.ld (lane = channel, column = token); a segment that
-//    covers its tile's whole K is scaled and stored directly, otherwise the int32 partial sums are
-//    added into a zeroed workspace slot with red.global.add and the CTA that completes the tile's
-//    k-tile count reads them back, stores and re-zeroes.  Integer sums are exact in any order.
+//    covers its tile's whole K is scaled and stored directly; otherwise the partial sums of the CTAs
+//    that share the tile meet in a zeroed workspace word per output element through ONE returning
+//    64-bit atomic add that carries the k-tile count along with the sum, and whoever completes the
+//    count stores the output and re-zeroes the word.  Integer sums are exact in any order.
 //  * Launched with programmatic stream serialisation: weight tiles are requested before the wait for
 //    the previous kernel of the stream, tokens / outputs / workspace are touched only after it.
 // Every wait is bounded; a thread whose wait expires records a site code, stops waiting and still
@@ -50,8 +51,7 @@ struct Args {
   const float* ascale;   // [M]
   const float* s1;       // [N]
   void* out;             // [M, N]
-  int32_t* slots;        // [grid][BN][128] partial sums, zero between launches
-  int32_t* counters;     // [grid]
+  unsigned long long* slots;   // [grid][BN][128] packed (k-tile count, biased partial sum), zero between launches
   int* status;
   int out_mode;          // LQ_DT_* or kOutI32
   int M, N, K, kt_total, n_tiles;
@@ -69,7 +69,10 @@ struct Cfg {
   static constexpr int kColsNeeded = BN + kACols;
   static constexpr int kTmemCols = kColsNeeded <= 128 ? 128 : kColsNeeded <= 256 ? 256 : 512;
   static constexpr int kNumBars = 3 * NS + 2;
-  static constexpr int kSmemBytes = 1024 + NS * (kXStage + kTileBytes) + kNumBars * 8 + 16;
+  static constexpr int kUsedBytes = 1024 + NS * (kXStage + kTileBytes) + kNumBars * 8 + 16;
+  // more than a third of the SM's shared memory, so that never three CTAs (of this and of the next
+  // kernel, under programmatic dependent launch) share an SM while another SM holds one
+  static constexpr int kSmemBytes = kUsedBytes > 78 * 1024 ? kUsedBytes : 78 * 1024;
   static_assert(kColsNeeded <= 256, "two CTAs per SM share 512 tensor-memory columns");
   static_assert(kSmemBytes <= 113 * 1024, "two CTAs per SM share the shared memory");
 };
@@ -94,7 +97,6 @@ w4a8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args) 
   const uint32_t bar_accfree = bar_accfull + 8;      // the accumulator has been read
   const uint32_t tmem_slot = bar_accfree + 8;
   volatile uint32_t* tmem_slot_p = reinterpret_cast<volatile uint32_t*>(smem + (tmem_slot - base));
-  volatile int* last_flag = reinterpret_cast<volatile int*>(smem + (tmem_slot - base) + 4);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -279,76 +281,64 @@ w4a8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args) 
       const long n = (long)sg.tile * 128 + row;
       const bool n_ok = n < args.N;
       const bool scaled = args.out_mode != kOutI32;
-      int32_t* slot = args.slots + (size_t)sg.slot * (BN * 128);
+      unsigned long long* slot = args.slots + (size_t)sg.slot * (BN * 128);
       const float w_scale = (n_ok && scaled) ? args.s1[n] : 0.f;
+      const long long nk = sg.ke - sg.kb;
 #pragma unroll 1
       for (int c0 = set * 16; c0 < BN; c0 += 32) {
         if (c0 >= args.M) break;   // uniform over the warp
         int v[16];
         ptx::tmem_ld16(tmem_acc + c0, v);
         ptx::tc_wait_ld();
+        if (c0 + 32 >= BN || c0 + 32 >= args.M) {   // last chunk of this set: the accumulator may be reused
+          __syncwarp();
+          ptx::tc_fence_before();
+          ptx::mbar_arrive(bar_accfree);
+        }
         if (!n_ok) continue;
-        if (sg.whole) {
-          float sc[16];
+        float sc[16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) sc[j] = (scaled && c0 + j < args.M) ? __ldg(args.ascale + c0 + j) : 0.f;
+        for (int j = 0; j < 16; ++j) sc[j] = (scaled && c0 + j < args.M) ? __ldg(args.ascale + c0 + j) : 0.f;
+        if (!sg.whole) {
+          // One returning 64-bit atomic per element does the cross-CTA reduction: the word holds the
+          // k-tiles added so far (bits 40..) and the sum of the contributions, each biased by 2^21 per
+          // k-tile so that it is non-negative and never borrows from the count.  The thread whose add
+          // completes the tile's count holds the full sum in the value it got back: it stores the
+          // output and re-zeroes the word.  No fence, no counter, no read-back.
+          unsigned long long old[16];
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            if (c0 + j < args.M) {
-              const size_t idx = (size_t)(c0 + j) * args.N + n;
-              if (scaled) store_out(args.out, idx, lqq_scale(v[j], sc[j], w_scale), args.out_mode);
-              else reinterpret_cast<int32_t*>(args.out)[idx] = v[j];
+            const unsigned long long add = (unsigned long long)((long long)v[j] + (nk << 21)) |
+                                           ((unsigned long long)nk << 40);
+            old[j] = (c0 + j < args.M) ? atomicAdd(slot + (c0 + j) * 128 + row, add) : 0ull;
+          }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const bool done = (c0 + j < args.M) && ((long long)(old[j] >> 40) + nk == (long long)args.kt_total);
+            if (done) {
+              __stcg(slot + (c0 + j) * 128 + row, 0ull);
+              v[j] = (int)((long long)(old[j] & ((1ull << 40) - 1)) + (long long)v[j] + (nk << 21) -
+                           ((long long)args.kt_total << 21));
+            } else {
+              sc[j] = __int_as_float(0x7fc00000);   // marks "not finished here"
             }
           }
-        } else {
+        }
 #pragma unroll
-          for (int j = 0; j < 16; ++j)
-            if (c0 + j < args.M) atomicAdd(slot + (c0 + j) * 128 + row, v[j]);
+        for (int j = 0; j < 16; ++j) {
+          if (c0 + j < args.M && (sg.whole || sc[j] == sc[j])) {
+            const size_t idx = (size_t)(c0 + j) * args.N + n;
+            if (scaled) store_out(args.out, idx, lqq_scale(v[j], sc[j], w_scale), args.out_mode);
+            else reinterpret_cast<int32_t*>(args.out)[idx] = v[j];
+          }
         }
       }
-      __syncwarp();
-      ptx::tc_fence_before();
-      ptx::mbar_arrive(bar_accfree);
+      if (set * 16 >= BN || set * 16 >= args.M) {   // this set had no chunk: it still releases the accumulator
+        __syncwarp();
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(bar_accfree);
+      }
       ++seg;
-
-      if (!sg.whole) {
-        __threadfence();
-        dequant_barrier();
-        if (d == 0) {
-          const int add = sg.ke - sg.kb;
-          const int before = atomicAdd(args.counters + sg.slot, add);
-          *last_flag = (before + add == args.kt_total) ? 1 : 0;
-        }
-        dequant_barrier();
-        const bool last = *last_flag != 0;
-        dequant_barrier();   // everyone has read the flag before it can be rewritten
-        if (last) {
-          __threadfence();
-          if (n_ok) {
-#pragma unroll 1
-            for (int c0 = set * 16; c0 < BN; c0 += 32) {
-              if (c0 >= args.M) break;
-              int v[16];
-              float sc[16];
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {   // all loads of the chunk first: one L2 round trip
-                v[j] = (c0 + j < args.M) ? __ldcg(slot + (c0 + j) * 128 + row) : 0;
-                sc[j] = (scaled && c0 + j < args.M) ? __ldg(args.ascale + c0 + j) : 0.f;
-              }
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                if (c0 + j < args.M) {
-                  __stcg(slot + (c0 + j) * 128 + row, 0);
-                  const size_t idx = (size_t)(c0 + j) * args.N + n;
-                  if (scaled) store_out(args.out, idx, lqq_scale(v[j], sc[j], w_scale), args.out_mode);
-                  else reinterpret_cast<int32_t*>(args.out)[idx] = v[j];
-                }
-              }
-            }
-          }
-          if (d == 0) args.counters[sg.slot] = 0;
-        }
-      }
     }
   }
   ptx::tc_fence_before();
@@ -388,7 +378,7 @@ static int grid_for(int N, int K) {
 
 size_t skinny_workspace_bytes(int M, int N, int K) {
   const size_t grid = (size_t)skinny::grid_for(N, K);
-  return grid * (size_t)(skinny::bn_for(M) * 128 * 4) + grid * 4;
+  return grid * (size_t)(skinny::bn_for(M) * 128 * 8);
 }
 
 // out_mode: LQ_DT_* or 3 (raw int32).  M <= 128.  `ws`: skinny_workspace_bytes(), all zero, left all zero.
@@ -406,8 +396,7 @@ int run_skinny_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, c
   a.ascale = ascale;
   a.s1 = s1;
   a.out = out;
-  a.slots = static_cast<int32_t*>(ws);
-  a.counters = a.slots + (size_t)grid * (bn * 128);
+  a.slots = static_cast<unsigned long long*>(ws);
   a.status = status_word();
   a.out_mode = out_mode;
   a.M = M;

@@ -793,12 +793,18 @@ struct Route {
 // the Llama-3.1-8B shapes); it only produces scaled outputs, the int32 entry point always uses tensor cores.
 constexpr int kGemvBlobMaxM = 4;
 
+// Decode batches up to this size use the single-launch streaming kernel; its one-atomic-per-element
+// reduction is the cheapest way to join split tiles while a CTA holds few tokens, but from about 64
+// tokens on the int32 planes + finish pass of the tile kernel are faster (measured on B200).
+constexpr int kSkinnyMaxM = 32;
+
 static Route route_for(int M, int N, int K, int splitk) {
   const int kt = K / 128;
   if (splitk == -1) return {false, false, 0};
   if (M <= 128) {
-    if (splitk == 0) return {false, true, 0};
-    int S = splitk > kt ? kt : splitk;
+    if (splitk == 0 && M <= kSkinnyMaxM) return {false, true, 0};
+    int S = splitk > 0 ? splitk : tile_pick_splits(M, N, K);
+    if (S > kt) S = kt;
     return {true, false, S < 1 ? 1 : S};
   }
   return {false, false, splitk};

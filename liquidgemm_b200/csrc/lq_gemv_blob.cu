@@ -10,10 +10,10 @@
 //  * 256 consumer threads: thread (row r, group h) reconstructs the 64 weights of row r in 64-wide
 //    group h of the k-tile (AND / SHR+AND / IMAD / XOR on words of 4 lanes) and feeds dp4a against the
 //    tokens' words, which every lane reads from shared memory at the same address (broadcast);
-//  * int32 partial sums of an n-tile cut by a range boundary are added with red.global.add into a
-//    zeroed slot; the CTA that completes the tile's k-tile count applies the scale epilogue and
-//    re-zeroes slot and counter.  Integer addition commutes, so the result is bit-identical for every
-//    grid size.
+//  * the partial sums of an n-tile cut by a range boundary meet in a zeroed workspace word per
+//    output element through ONE returning 64-bit atomic add that carries the k-tile count along with
+//    the sum; whoever completes the count stores the output and re-zeroes the word.  Integer addition
+//    commutes, so the result is bit-identical for every grid size.
 // Every wait is bounded: on expiry the thread records a site code in the status word, stops waiting
 // and runs the rest of its control flow (barriers included) so the CTA still exits.
 
@@ -39,8 +39,7 @@ struct Args {
   const float* ascale;   // [M]
   const float* s1;       // [N]
   void* out;             // [M, N]
-  int32_t* slots;        // [grid][MT][128] partial sums, zero between launches
-  int32_t* counters;     // [grid] k-tiles added to the slot, zero between launches
+  unsigned long long* slots;   // [grid][MT][128] packed (k-tile count, biased partial sum), zero between launches
   int* status;
   int out_dtype;
   int M, N, K, kt_total, n_tiles;
@@ -52,7 +51,12 @@ struct Cfg {
   static constexpr int kXStage = MT * 128;
   static constexpr int kStage = kTileBytes + kXStage;
   static constexpr int kRedBytes = MT * 128 * 4;
-  static constexpr int kSmemBytes = 128 + NS * kStage + 2 * NS * 8 + kRedBytes + 16;
+  static constexpr int kUsedBytes = 128 + NS * kStage + 2 * NS * 8 + kRedBytes + 16;
+  // Never three CTAs on one SM: with programmatic dependent launch the next kernel's CTAs fill whatever
+  // fits, and an SM that holds three streams while its neighbour holds one makes the slowest CTA
+  // (hence the kernel) much later than the average one.  Asking for more than a third of the SM's
+  // shared memory caps residency at two.
+  static constexpr int kSmemBytes = kUsedBytes > 78 * 1024 ? kUsedBytes : 78 * 1024;
 };
 
 __device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
@@ -76,7 +80,6 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_blob_kernel(const Args args)
   const uint32_t bar_full = xs + NS * C::kXStage;
   const uint32_t bar_empty = bar_full + NS * 8;
   int32_t* red = reinterpret_cast<int32_t*>(smem + (bar_empty + NS * 8 - base));   // [MT][128]
-  volatile int* last_flag = reinterpret_cast<volatile int*>(red + MT * 128);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int M = args.M;
@@ -165,7 +168,12 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_blob_kernel(const Args args)
     bool ok = true;
     const bool tracing = args.trace != nullptr && c == 0;
     dependency_wait();   // outputs, the reduction workspace and the tokens belong to earlier kernels until here
-    if (tracing) args.trace[blockIdx.x * 4 + 0] = (long long)ptx::globaltimer_ns();
+    if (tracing) {
+      uint32_t smid;
+      asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+      args.trace[blockIdx.x * 4 + 0] = (long long)ptx::globaltimer_ns();
+      args.trace[(size_t)gridDim.x * 4 + blockIdx.x] = smid;   // SM ids behind the stamps
+    }
     bool first = true;
 
     while (walk.next(sg)) {
@@ -238,40 +246,36 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_blob_kernel(const Args args)
         }
         consumer_barrier();   // `red` may be rewritten by the next segment
       } else {
-        int32_t* slot = args.slots + (size_t)sg.slot * (MT * 128);
+        // One returning 64-bit atomic per element does the whole cross-CTA reduction: the word holds
+        // the number of k-tiles added so far (bits 40..) and the sum of the contributions, each
+        // biased by 2^21 per k-tile so that it is non-negative and never borrows from the count.
+        // The thread whose add completes the tile's k-tile count holds the full sum in the value it
+        // got back, stores the output and re-zeroes the word: no fence, no counter, no read-back.
+        unsigned long long* slot = args.slots + (size_t)sg.slot * (MT * 128);
         if (mine) {
+          const float w_scale = args.s1[n];
+          const long long nk = sg.ke - sg.kb;
+          float a_scale[MT];
+          unsigned long long old[MT];
 #pragma unroll
-          for (int m = 0; m < MT; ++m)
-            if (m < M) atomicAdd(slot + m * 128 + row, acc[m]);
-        }
-        __threadfence();
-        consumer_barrier();
-        if (c == 0) {
-          const int add = sg.ke - sg.kb;
-          const int before = atomicAdd(args.counters + sg.slot, add);
-          *last_flag = (before + add == args.kt_total) ? 1 : 0;
-        }
-        consumer_barrier();
-        const bool last = *last_flag != 0;
-        consumer_barrier();   // everyone has read the flag before it can be rewritten
-        if (last) {
-          __threadfence();
-          if (mine) {
-            const float w_scale = args.s1[n];
-            int t[MT];
+          for (int m = 0; m < MT; ++m) a_scale[m] = (m < M) ? args.ascale[m] : 0.f;
 #pragma unroll
-            for (int m = 0; m < MT; ++m) t[m] = (m < M) ? __ldcg(slot + m * 128 + row) : 0;
+          for (int m = 0; m < MT; ++m) {
+            const unsigned long long add = (unsigned long long)((long long)acc[m] + (nk << 21)) |
+                                           ((unsigned long long)nk << 40);
+            old[m] = (m < M) ? atomicAdd(slot + m * 128 + row, add) : 0ull;
+          }
 #pragma unroll
-            for (int m = 0; m < MT; ++m) {
-              if (m < M) {
-                __stcg(slot + m * 128 + row, 0);
-                store_out(args.out, (size_t)m * args.N + n, lqq_scale(t[m], args.ascale[m], w_scale),
-                          args.out_dtype);
-              }
+          for (int m = 0; m < MT; ++m) {
+            if (m < M && (long long)(old[m] >> 40) + nk == (long long)args.kt_total) {
+              const long long total = (long long)(old[m] & ((1ull << 40) - 1)) + (long long)acc[m] + (nk << 21) -
+                                      ((long long)args.kt_total << 21);
+              __stcg(slot + m * 128 + row, 0ull);
+              store_out(args.out, (size_t)m * args.N + n, lqq_scale((int)total, a_scale[m], w_scale), args.out_dtype);
             }
           }
-          if (c == 0) args.counters[sg.slot] = 0;
         }
+        consumer_barrier();   // `red` may be rewritten by the next segment
       }
     }
     if (tracing) args.trace[blockIdx.x * 4 + 3] = (long long)ptx::globaltimer_ns();
@@ -312,17 +316,17 @@ static int grid_for(int N, int K) {
 
 }  // namespace gblob
 
-// Workspace bytes for a launch grid of `grid` CTAs (partial-sum slots, then counters).
-static size_t gemv_blob_ws_bytes(int grid) { return (size_t)grid * (8 * 128 * 4) + (size_t)grid * 4; }
+// Workspace bytes for a launch grid of `grid` CTAs: one 64-bit word per (token <= 8, row) of a slot.
+static size_t gemv_blob_ws_bytes(int grid) { return (size_t)grid * (8 * 128 * 8); }
 
 size_t gemv_blob_workspace_bytes(int N, int K) { return gemv_blob_ws_bytes(gblob::grid_for(N, K)); }
 
-// Same call with the workspace as one buffer (slots, then counters), for the GEMM entry points.
+// Same call with a size-checked workspace, for the GEMM entry points.
 int run_gemv_blob_ws(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, void* out,
                      int out_dtype, int M, int N, int K, void* ws, size_t ws_bytes, cudaStream_t st);
 
 int run_gemv_blob(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, void* out,
-                  int out_dtype, int M, int N, int K, int32_t* slots, int32_t* counters, cudaStream_t st) {
+                  int out_dtype, int M, int N, int K, unsigned long long* slots, cudaStream_t st) {
   using namespace gblob;
   Args a;
   a.blob = blob;
@@ -331,7 +335,6 @@ int run_gemv_blob(const int8_t* x, const uint8_t* blob, const float* ascale, con
   a.s1 = s1;
   a.out = out;
   a.slots = slots;
-  a.counters = counters;
   a.status = status_word();
   a.out_dtype = out_dtype;
   a.M = M;
@@ -352,8 +355,7 @@ int run_gemv_blob_ws(const int8_t* x, const uint8_t* blob, const float* ascale, 
                      int out_dtype, int M, int N, int K, void* ws, size_t ws_bytes, cudaStream_t st) {
   const int grid = gblob::grid_for(N, K);
   if (!ws || ws_bytes < gemv_blob_ws_bytes(grid)) return LQ_ERR_WORKSPACE;
-  int32_t* slots = static_cast<int32_t*>(ws);
-  return run_gemv_blob(x, blob, ascale, s1, out, out_dtype, M, N, K, slots, slots + (size_t)grid * (8 * 128), st);
+  return run_gemv_blob(x, blob, ascale, s1, out, out_dtype, M, N, K, static_cast<unsigned long long*>(ws), st);
 }
 
 }  // namespace lq
@@ -363,7 +365,8 @@ using namespace lq;
 extern "C" {
 
 // Pipeline-study hook: device buffer of 4 x int64 per CTA (2 x SM count CTAs) that receives
-// globaltimer stamps (start, first tile landed, last main loop done, exit); null switches it off.
+// globaltimer stamps (start, first tile landed, last main loop done, exit), followed by one int64 SM id
+// per CTA; null switches it off.
 LQ_API void lq_debug_set_blob_trace(void* device_buffer) { gblob::g_trace = static_cast<long long*>(device_buffer); }
 
 LQ_API size_t lq_gemv_blob_workspace_bytes(void) { return gemv_blob_ws_bytes(2 * sm_count()); }
@@ -377,11 +380,9 @@ LQ_API int lq_w4a8_gemv_blob(const void* x_i8, const void* blob, const void* asc
   if (M < 1 || M > 8 || N < 1 || K < 128 || K % 128) return LQ_ERR_SHAPE;
   const int grid = gblob::grid_for(N, K);
   if (!workspace || workspace_bytes < gemv_blob_ws_bytes(grid)) return LQ_ERR_WORKSPACE;
-  int32_t* slots = static_cast<int32_t*>(workspace);
-  int32_t* counters = slots + (size_t)grid * (8 * 128);
   return run_gemv_blob(static_cast<const int8_t*>(x_i8), static_cast<const uint8_t*>(blob),
                        static_cast<const float*>(ascale), static_cast<const float*>(s1), out, out_dtype, M, N, K,
-                       slots, counters, as_stream(stream));
+                       static_cast<unsigned long long*>(workspace), as_stream(stream));
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -392,12 +393,11 @@ LQ_API int lq_w4a8_gemv_blob(const void* x_i8, const void* blob, const void* asc
 namespace lq {
 namespace gblob {
 
-// Room for 512 CTAs (two per SM on up to 256 SMs): 512 x (8 tokens x 128 rows x 4 B) of partial
-// sums followed by 512 counters, 2 099 200 bytes of device memory that exist as long as the
-// library is loaded.  The loader zero-fills it; the kernel leaves it zero-filled.
+// Room for 512 CTAs (two per SM on up to 256 SMs): 512 x (8 tokens x 128 rows x 8 B) reduction
+// words, 4 194 304 bytes of device memory that exist as long as the library is loaded.  The loader
+// zero-fills it; the kernel leaves it zero-filled.
 constexpr int kStaticMaxCtas = 512;
-constexpr size_t kStaticSlotBytes = (size_t)kStaticMaxCtas * 8 * 128 * 4;
-constexpr size_t kStaticBytes = kStaticSlotBytes + (size_t)kStaticMaxCtas * 4;
+constexpr size_t kStaticBytes = (size_t)kStaticMaxCtas * 8 * 128 * 8;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticBytes];
 
 static void* g_static_ptr[64];
@@ -438,11 +438,9 @@ LQ_API int lq_w4a8_gemv_blob_static(const void* x_i8, const void* blob, const vo
   }
   void* p = gblob::static_scratch_for_current_device();
   if (!p) return LQ_ERR_CUDA;
-  int32_t* slots = static_cast<int32_t*>(p);
-  int32_t* counters = reinterpret_cast<int32_t*>(static_cast<unsigned char*>(p) + gblob::kStaticSlotBytes);
   return run_gemv_blob(static_cast<const int8_t*>(x_i8), static_cast<const uint8_t*>(blob),
                        static_cast<const float*>(ascale), static_cast<const float*>(s1), out, out_dtype, M, N, K,
-                       slots, counters, as_stream(stream));
+                       static_cast<unsigned long long*>(p), as_stream(stream));
 }
 
 }  // extern "C"
