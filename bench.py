@@ -280,8 +280,8 @@ def main():
     launches = [(name, M) for M in SWEEP_M for name in SHAPES]
 
     def decode_linear(L, xq, sc, M, out_dtype):
-        """The decode dispatch of the plugin (liquidgemm_b200.ops.use_gemv): the row-major GEMV pack on
-        small matrices with up to four tokens, everything else from the tile blob."""
+        """The decode dispatch of the plugin (liquidgemm_b200.ops.use_gemv): everything is served from
+        the tile blob; the row-major GEMV pack is only a fallback for layers without a blob."""
         if ops.use_gemv(M, L["N"], L["K"], True, True):
             return torch.ops.liquidgemm.w4a8_gemv2(xq, L["gp"], L["s_u8"], L["offset_a"], sc, L["s1"], L["N"], L["K"],
                                                    64, out_dtype)
@@ -397,7 +397,7 @@ def main():
                        "sharding": "each rank owns a full set of output channels (N-sharded, no collective)"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / peaks["hbm_gbs"], "traffic": None,
-                         "of": peaks["source"], "kernel": "w4a8_skinny_kernel (M = 8, 16) + gemv_blob_kernel (M <= 4) + gemv_dp4a_kernel (qkv, M <= 4): the 12-op sweep",
+                         "of": peaks["source"], "kernel": "w4a8_skinny_kernel (M = 8, 16) + gemv_blob_kernel (M = 1, 4): the 12-op sweep",
                          "algorithmic_bytes_per_step": abytes},
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": UNIT,

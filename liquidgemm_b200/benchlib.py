@@ -71,7 +71,7 @@ def graph_time_us(fn, n_items, reps=5):
 
 
 def linear_call(L, x, sc, M, splitk=None, out_dtype=0):
-    if M <= 16 and "gp" in L:
+    if ops.use_gemv(M, L["N"], L["K"], "gp" in L, "rs" in L):
         return torch.ops.liquidgemm.w4a8_gemv2(x, L["gp"], L["s_u8"], L["offset_a"], sc, L["s1"], L["N"], L["K"], 64,
                                                out_dtype)
     return ops.gemm_fused(x, L["rs"], sc, L["s1"], L["N"], L["K"], out_dtype, splitk=splitk)
@@ -85,7 +85,7 @@ def run_sweep(peaks, Ms=(1, 4, 8, 16, 32, 64, 128, 512, 2048, 8192)):
     rows = []
     for name, (N, K) in SHAPES.items():
         C = max(3, -(-400_000_000 // (N * K // 2)))
-        layers = [device_lqq(N, K, seed=31 * c + len(name)) for c in range(C)]
+        layers = [device_lqq(N, K, seed=31 * c + len(name), want_gp=False) for c in range(C)]
         Cb = max(3, -(-300_000_000 // (N * K * 2)))
         wbf = [torch.randn(N, K, device="cuda", dtype=torch.bfloat16) for _ in range(Cb)]
         for M in Ms:
@@ -100,7 +100,7 @@ def run_sweep(peaks, Ms=(1, 4, 8, 16, 32, 64, 128, 512, 2048, 8192)):
                          "alg_GBps": round(gbs, 1), "hbm_frac": round(gbs / peaks["hbm_gbs"], 3),
                          "TOPS": round(tops, 1), "int8_frac_of_4500": round(tops / INT8_DENSE_TOPS, 3),
                          "cublas_bf16_us": round(tb, 2), "speedup_vs_cublas_bf16": round(tb / t, 2),
-                         "kernel": "gemv" if M <= 16 else "tcgen05"})
+                         "kernel": "dp4a stream" if M <= 4 else "tcgen05"})
         del layers, wbf
         torch.cuda.empty_cache()
     return rows

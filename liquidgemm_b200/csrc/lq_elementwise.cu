@@ -71,6 +71,9 @@ __global__ void __launch_bounds__(256)
 quant_per_token_kernel(const T* __restrict__ x, int8_t* __restrict__ xq, float* __restrict__ ascale,
                        int K) {
   __shared__ float red[32];
+  // The linear that consumes these tokens is launched with programmatic stream serialisation: let it
+  // start streaming its weights now; it waits for this grid before it reads the tokens.
+  allow_dependents();
   const long m = blockIdx.x;
   const T* xr = x + m * K;
   int8_t* qr = xq + m * K;

@@ -642,12 +642,10 @@ def w4a8_linear_host(x_host: torch.Tensor, qw_dev: dict, y_host: torch.Tensor = 
 
 
 def use_gemv(M: int, N: int, K: int, have_gp: bool, have_rs: bool) -> bool:
-    """Decode dispatch measured on B200: the row-major GEMV pack only wins on small matrices (qkv
-    size) with up to four tokens, where fixed costs dominate and a kernel without a reduction stage is
-    ahead; everything else is served from the tile blob (streaming dp4a GEMV up to four tokens, the
-    tensor-core kernel from there on).  The reference switches at M <= 16 (liquidgemm/vllm_plugin.py:189)."""
+    """Whether the row-major GEMV pack should serve this call.  Measured on B200 the kernels that read
+    the tile blob (streaming dp4a GEMV up to four tokens, tensor-core kernel above) are faster for every
+    decode shape, so the GEMV pack is only used by a layer that has nothing else.  The reference
+    switches to its GEMV at M <= 16 (liquidgemm/vllm_plugin.py:189)."""
     if not have_gp or M > 16:
         return False
-    if not have_rs:
-        return True
-    return M <= 4 and N * K <= (1 << 25)
+    return not have_rs

@@ -4,8 +4,9 @@ Same registration name, classes, layer buffers and environment switches as the r
 (liquidgemm/vllm_plugin.py), so ``LLM(model, quantization="liquidgemm")`` keeps working:
 
 * ``LIQUIDGEMM_W4=1``    store 4-bit weights and run the fused W4A8 tensor-core GEMM;
-* ``LIQUIDGEMM_GEMV=1``  additionally keep the row-major GEMV pack and use the decode GEMV for
-                         M <= 16 (reference liquidgemm/vllm_plugin.py:157-164);
+* ``LIQUIDGEMM_GEMV=1``  decode GEMV for small M (reference liquidgemm/vllm_plugin.py:157-164); here it
+                         is served from the same tile blob as the GEMM, so it costs no extra memory
+                         and is in fact always on;
 * ``LIQUIDGEMM_SPLITK``  split-K override for M <= 128, read once by :mod:`liquidgemm_b200.ops`.
 
 Differences that follow from the hardware target: the minimum capability is 100 (sm_100a), and
@@ -80,8 +81,12 @@ def prepare_layer(layer: torch.nn.Module, group_size: int, w4: bool, gemv: bool)
         layer.register_buffer("lq_rs", ops.repack_rs_weight(qw).to(dev))
         layer.register_buffer("lq_s_u8", qw.s_u8.to(dev))
         layer.register_buffer("lq_offset_a", qw.offset_a.to(dev))
+        # LIQUIDGEMM_GEMV=1 asks for the decode GEMV.  Here the GEMV reads the tile blob, so the flag
+        # needs no second copy of the weights (the reference stores `lq_gp`, doubling weight memory:
+        # liquidgemm/vllm_plugin.py:157-164); LIQUIDGEMM_GEMV_PACK=1 still builds that row-major pack
+        # for callers that want to drive torch.ops.liquidgemm.w4a8_gemv2 themselves.
         layer.lq_gemv = bool(gemv and qw.K % 128 == 0 and group_size == 64)
-        if layer.lq_gemv:
+        if layer.lq_gemv and os.environ.get("LIQUIDGEMM_GEMV_PACK") == "1":
             layer.register_buffer("lq_gp", ops.pack_gemv_interleaved(qw).to(dev))
     else:
         w_i8 = torch.ops.liquidgemm.dequant_weight(qw.qweight_u4.to(dev), qw.s_u8.to(dev), qw.offset_a.to(dev),
@@ -104,7 +109,7 @@ def apply_layer(layer: torch.nn.Module, x: torch.Tensor, bias: Optional[torch.Te
     x_i8, ascale = torch.ops.liquidgemm.quant_per_token(x2)
     if w4:
         from .ops import use_gemv
-        if getattr(layer, "lq_gemv", False) and use_gemv(x_i8.shape[0], n, layer.lq_K, True, True):
+        if use_gemv(x_i8.shape[0], n, layer.lq_K, hasattr(layer, "lq_gp"), True):
             y = torch.ops.liquidgemm.w4a8_gemv2(x_i8, layer.lq_gp, layer.lq_s_u8, layer.lq_offset_a, ascale,
                                                 layer.lq_s1, n, layer.lq_K, group_size, odt)
         else:
