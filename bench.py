@@ -233,6 +233,11 @@ def build_device_sets(torch, ops, n_sets, seed_base):
     return sets
 
 
+# DRAM read+write bytes per launch / algorithmic bytes per launch, mean of six ncu captures of the decode
+# kernels (three shapes each of gemv_blob_kernel and w4a8_skinny_kernel); summary under profiles/.
+NCU_TRAFFIC_RATIO = 1.016
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -396,7 +401,7 @@ def main():
                        "l2": f"{n_sets} weight copies rotate (302 MB working set > 2 x L2); step captured in a CUDA graph",
                        "sharding": "each rank owns a full set of output channels (N-sharded, no collective)"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                         "frac": achieved / peaks["hbm_gbs"], "traffic": None,
+                         "frac": achieved / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_RATIO * abytes,
                          "of": peaks["source"], "kernel": "w4a8_skinny_kernel (M = 8, 16) + gemv_blob_kernel (M = 1, 4): the 12-op sweep",
                          "algorithmic_bytes_per_step": abytes},
             "cpu_baseline": cpu,
