@@ -54,7 +54,8 @@ struct Args {
   unsigned long long* slots;   // [grid][BN][128] packed (k-tile count, biased partial sum), zero between launches
   int* status;
   int out_mode;          // LQ_DT_* or kOutI32
-  int M, N, K, kt_total, n_tiles;
+  int M, N, K, kt_total, n_tiles, fixed_split;
+  long long* trace;      // pipeline studies: [grid][4] globaltimer stamps, or null
   int debug_skip;        // pipeline studies only (results become wrong): 1 no tcgen05.st, 2 no MMA, 4 no dequant ALU
 };
 
@@ -114,7 +115,7 @@ w4a8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args) 
   __syncthreads();
   allow_dependents();   // the next kernel of the stream may start prefetching its weights
 
-  SegmentWalk walk(SchedArgs{args.kt_total, args.n_tiles, 1, 0}, blockIdx.x, gridDim.x);
+  SegmentWalk walk(SchedArgs{args.kt_total, args.n_tiles, 1, args.fixed_split}, blockIdx.x, gridDim.x);
   Segment sg;
 
   if (warp == 0) {
@@ -226,14 +227,31 @@ w4a8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args) 
     uint32_t step = 0;   // running k-tile index of this CTA
     uint32_t seg = 0;
     bool waited_dependency = false;
+    const bool tracing = args.trace != nullptr && d == 0;
+    bool first = true;
+    if (tracing) args.trace[blockIdx.x * 4 + 0] = (long long)ptx::globaltimer_ns();
 
     while (walk.next(sg)) {
+      // the channel scale is a weight: fetch it now, it is needed right after the last MMA
+      const long n = (long)sg.tile * 128 + row;
+      const bool n_ok = n < args.N;
+      const bool scaled = args.out_mode != kOutI32;
+      const float w_scale = (n_ok && scaled) ? __ldg(args.s1 + n) : 0.f;
 #pragma unroll 1
       for (int kt = sg.kb; kt < sg.ke; ++kt, ++step, ring.advance()) {
         if ((int)(step & 1u) != set) continue;
         if (ok && !ptx::mbar_wait_bounded(bar_full + 8 * ring.s, ring.ph, kWaitLimitNs)) {
           atomicExch(args.status, 404);
           ok = false;
+        }
+        if (first) {
+          // The stage holds tokens, so the producer is past its wait for the previous kernel: pull the
+          // token scales (that kernel's output) into L1 now, the epilogue reads them under time pressure.
+          if (tracing) args.trace[blockIdx.x * 4 + 1] = (long long)ptx::globaltimer_ns();
+          first = false;
+          dependency_wait();
+          waited_dependency = true;
+          if (scaled && d * 32 < args.M) asm volatile("prefetch.global.L1 [%0];" ::"l"(args.ascale + d * 32));
         }
         const uint8_t* wst = smem + (ws - base) + ring.s * kTileBytes;
         uint4 ch[4];
@@ -267,6 +285,7 @@ w4a8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args) 
         ptx::mbar_arrive(bar_aready + 8 * ring.s);
       }
 
+      if (tracing) args.trace[blockIdx.x * 4 + 2] = (long long)ptx::globaltimer_ns();   // last dequant done
       // ---- epilogue of the segment: set g takes the 16-column chunks g, g+2, ...
       if (ok && !ptx::mbar_wait_bounded(bar_accfull, seg & 1u, kWaitLimitNs)) {
         atomicExch(args.status, 405);
@@ -278,11 +297,7 @@ w4a8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args) 
         dependency_wait();   // outputs and the reduction workspace belong to earlier kernels until here
         waited_dependency = true;
       }
-      const long n = (long)sg.tile * 128 + row;
-      const bool n_ok = n < args.N;
-      const bool scaled = args.out_mode != kOutI32;
       unsigned long long* slot = args.slots + (size_t)sg.slot * (BN * 128);
-      const float w_scale = (n_ok && scaled) ? args.s1[n] : 0.f;
       const long long nk = sg.ke - sg.kb;
 #pragma unroll 1
       for (int c0 = set * 16; c0 < BN; c0 += 32) {
@@ -340,6 +355,7 @@ w4a8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args) 
       }
       ++seg;
     }
+    if (tracing) args.trace[blockIdx.x * 4 + 3] = (long long)ptx::globaltimer_ns();
   }
   ptx::tc_fence_before();
   __syncthreads();
@@ -365,20 +381,18 @@ static int launch(const CUtensorMap& tx, const Args& a, int grid, cudaStream_t s
 }
 
 static int g_debug_skip = 0;
+static long long* g_trace = nullptr;
 
 static int bn_for(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128; }
 
-static int grid_for(int N, int K) {
-  const long units = (long)((N + 127) / 128) * (K / 128);
-  const long slots = 2L * sm_count();
-  return (int)(units < slots ? units : slots);
-}
+static DecodePlan plan_for(int N, int K) { return decode_plan((N + 127) / 128, K / 128, 2 * sm_count()); }
 
 }  // namespace skinny
 
 size_t skinny_workspace_bytes(int M, int N, int K) {
-  const size_t grid = (size_t)skinny::grid_for(N, K);
-  return grid * (size_t)(skinny::bn_for(M) * 128 * 8);
+  (void)N;
+  (void)K;
+  return (size_t)(2 * sm_count()) * (size_t)(skinny::bn_for(M) * 128 * 8);   // one slot per resident CTA
 }
 
 // out_mode: LQ_DT_* or 3 (raw int32).  M <= 128.  `ws`: skinny_workspace_bytes(), all zero, left all zero.
@@ -387,7 +401,8 @@ int run_skinny_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, c
   using namespace skinny;
   if (!ws || ws_bytes < skinny_workspace_bytes(M, N, K)) return LQ_ERR_WORKSPACE;
   const int bn = bn_for(M);
-  const int grid = grid_for(N, K);
+  const DecodePlan plan = plan_for(N, K);
+  const int grid = plan.grid;
   CUtensorMap tx;
   int rc = make_byte_matrix_map(&tx, x, M, K, bn, 128);
   if (rc) return rc;
@@ -404,7 +419,9 @@ int run_skinny_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, c
   a.K = K;
   a.kt_total = K / 128;
   a.n_tiles = (N + 127) / 128;
+  a.fixed_split = plan.fixed_split;
   a.debug_skip = g_debug_skip;
+  a.trace = g_trace;
   if (!a.status) return LQ_ERR_CUDA;
   switch (bn) {
     case 16: return launch<16, 6>(tx, a, grid, st);
@@ -418,3 +435,9 @@ int run_skinny_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, c
 
 // Pipeline-study hook (timing experiments only; results become wrong when non-zero).
 extern "C" LQ_API void lq_debug_set_skinny_skip(int mask) { lq::skinny::g_debug_skip = mask; }
+
+// Pipeline-study hook: device buffer of 4 x int64 per CTA receiving globaltimer stamps of dequant
+// thread 0 (start, first tile landed, last dequant done, exit); null switches it off.
+extern "C" LQ_API void lq_debug_set_skinny_trace(void* device_buffer) {
+  lq::skinny::g_trace = static_cast<long long*>(device_buffer);
+}

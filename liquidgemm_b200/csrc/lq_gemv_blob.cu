@@ -42,7 +42,7 @@ struct Args {
   unsigned long long* slots;   // [grid][MT][128] packed (k-tile count, biased partial sum), zero between launches
   int* status;
   int out_dtype;
-  int M, N, K, kt_total, n_tiles;
+  int M, N, K, kt_total, n_tiles, fixed_split;
   long long* trace;      // pipeline studies: [grid][4] globaltimer stamps, or null
 };
 
@@ -99,7 +99,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_blob_kernel(const Args args)
   sa.kt_total = args.kt_total;
   sa.n_tiles = args.n_tiles;
   sa.m_tiles = 1;
-  sa.fixed_split = 0;
+  sa.fixed_split = args.fixed_split;
   SegmentWalk walk(sa, blockIdx.x, gridDim.x);
   Segment sg;
 
@@ -175,8 +175,13 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_blob_kernel(const Args args)
       args.trace[(size_t)gridDim.x * 4 + blockIdx.x] = smid;   // SM ids behind the stamps
     }
     bool first = true;
+    float a_scale[MT];   // token scales: read once, they are needed right after the last tile
+#pragma unroll
+    for (int m = 0; m < MT; ++m) a_scale[m] = (m < M) ? __ldg(args.ascale + m) : 0.f;
 
     while (walk.next(sg)) {
+      const long n = (long)sg.tile * 128 + row;
+      const float w_scale = (n < args.N) ? __ldg(args.s1 + n) : 0.f;   // a weight: fetched ahead of the loop
       int acc[MT];
 #pragma unroll
       for (int m = 0; m < MT; ++m) acc[m] = 0;
@@ -230,7 +235,6 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_blob_kernel(const Args args)
         for (int m = 0; m < MT; ++m) red[m * 128 + row] = acc[m];
       }
       consumer_barrier();
-      const long n = (long)sg.tile * 128 + row;
       const bool mine = (h == 0) && n < args.N;
       if (h == 0) {
 #pragma unroll
@@ -238,10 +242,9 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_blob_kernel(const Args args)
       }
       if (sg.whole) {
         if (mine) {
-          const float w_scale = args.s1[n];
 #pragma unroll
           for (int m = 0; m < MT; ++m)
-            if (m < M) store_out(args.out, (size_t)m * args.N + n, lqq_scale(acc[m], args.ascale[m], w_scale),
+            if (m < M) store_out(args.out, (size_t)m * args.N + n, lqq_scale(acc[m], a_scale[m], w_scale),
                                  args.out_dtype);
         }
         consumer_barrier();   // `red` may be rewritten by the next segment
@@ -253,12 +256,8 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_blob_kernel(const Args args)
         // got back, stores the output and re-zeroes the word: no fence, no counter, no read-back.
         unsigned long long* slot = args.slots + (size_t)sg.slot * (MT * 128);
         if (mine) {
-          const float w_scale = args.s1[n];
           const long long nk = sg.ke - sg.kb;
-          float a_scale[MT];
           unsigned long long old[MT];
-#pragma unroll
-          for (int m = 0; m < MT; ++m) a_scale[m] = (m < M) ? args.ascale[m] : 0.f;
 #pragma unroll
           for (int m = 0; m < MT; ++m) {
             const unsigned long long add = (unsigned long long)((long long)acc[m] + (nk << 21)) |
@@ -308,18 +307,19 @@ static int launch(const Args& a, int grid, cudaStream_t st) {
 
 static long long* g_trace = nullptr;
 
-static int grid_for(int N, int K) {
-  const long units = (long)((N + 127) / 128) * (K / 128);
-  const long slots = 2L * sm_count();
-  return (int)(units < slots ? units : slots);
-}
+static DecodePlan plan_for(int N, int K) { return decode_plan((N + 127) / 128, K / 128, 2 * sm_count()); }
+static int grid_for(int N, int K) { return plan_for(N, K).grid; }
 
 }  // namespace gblob
 
 // Workspace bytes for a launch grid of `grid` CTAs: one 64-bit word per (token <= 8, row) of a slot.
 static size_t gemv_blob_ws_bytes(int grid) { return (size_t)grid * (8 * 128 * 8); }
 
-size_t gemv_blob_workspace_bytes(int N, int K) { return gemv_blob_ws_bytes(gblob::grid_for(N, K)); }
+size_t gemv_blob_workspace_bytes(int N, int K) {
+  (void)N;
+  (void)K;
+  return gemv_blob_ws_bytes(2 * sm_count());   // one slot per resident CTA
+}
 
 // Same call with a size-checked workspace, for the GEMM entry points.
 int run_gemv_blob_ws(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, void* out,
@@ -342,6 +342,7 @@ int run_gemv_blob(const int8_t* x, const uint8_t* blob, const float* ascale, con
   a.K = K;
   a.kt_total = K / 128;
   a.n_tiles = (N + 127) / 128;
+  a.fixed_split = plan_for(N, K).fixed_split;
   a.trace = g_trace;
   if (!a.status) return LQ_ERR_CUDA;
   const int grid = grid_for(N, K);

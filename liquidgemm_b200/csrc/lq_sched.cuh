@@ -70,6 +70,24 @@ struct SegmentWalk {
   }
 };
 
+// Work split of the streaming decode kernels over `slots` resident CTAs.  With few output tiles every
+// tile is cut into S equal k-ranges, one CTA each: a CTA then has exactly one segment, so no CTA pays
+// the segment epilogue twice.  With many tiles the k-tiles of all tiles are laid end to end and cut
+// into equal contiguous ranges (stream-K): perfectly balanced bytes, at the price of a second
+// segment in most CTAs.
+struct DecodePlan {
+  int grid, fixed_split;
+};
+inline DecodePlan decode_plan(int n_tiles, int kt, int slots) {
+  if (n_tiles * 2 <= slots) {
+    int S = slots / n_tiles;
+    if (S > kt) S = kt;
+    return {n_tiles * S, S};
+  }
+  const long units = (long)n_tiles * kt;
+  return {(int)(units < slots ? units : slots), 0};
+}
+
 // Position in a ring of N stages: stage index and the parity of the pass over the ring.
 template <int N>
 struct Ring {

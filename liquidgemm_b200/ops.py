@@ -599,45 +599,64 @@ def w4a8_linear(x: torch.Tensor, qw_dev: dict, out_dtype: torch.dtype = None) ->
 
 
 _HOST_SCRATCH: dict = {}
+_HOST_SIZES: dict = {}
 
 
 def w4a8_linear_host(x_host: torch.Tensor, qw_dev: dict, y_host: torch.Tensor = None,
-                     out_dtype: torch.dtype = None, device=None) -> torch.Tensor:
+                     out_dtype: torch.dtype = None) -> torch.Tensor:
     """The same linear for activations and outputs in HOST memory (pinned for asynchronous copies):
     upload, quantise, linear from the tile blob ``qw_dev["rs"]`` and download are enqueued on the current
-    stream by ONE native call.  Returns ``y_host`` (allocated pinned when not given); the caller
-    synchronises the stream before reading it."""
-    _req(not x_host.is_cuda and x_host.dim() == 2 and x_host.is_contiguous(), "x_host must be a contiguous CPU [M,K] tensor")
-    _req(x_host.dtype in _DTYPE_CODES, "x_host must be bf16, fp16 or fp32")
+    stream of the blob's device by ONE native call.  Returns ``y_host`` (allocated pinned when not
+    given); the caller synchronises the stream before reading it.
+
+    The wrapper is on the per-layer critical path of a host-driven decode loop, so it caches what does
+    not change between calls (buffer sizes per shape, the scratch per stream) and does no tensor work."""
+    if x_host.is_cuda or x_host.dim() != 2 or not x_host.is_contiguous() or x_host.dtype not in _DTYPE_CODES:
+        raise RuntimeError("liquidgemm_b200: x_host must be a contiguous CPU [M,K] tensor of bf16, fp16 or fp32")
     M, K = x_host.shape
     N = qw_dev["N"]
-    _req(K == qw_dev["K"] and K % 128 == 0, "K mismatch or K % 128 != 0")
     odt = out_dtype or x_host.dtype
+    if K != qw_dev["K"] or K % 128:
+        raise RuntimeError("liquidgemm_b200: K mismatch or K % 128 != 0")
     if y_host is None:
         y_host = torch.empty((M, N), dtype=odt, pin_memory=True)
-    _req(not y_host.is_cuda and y_host.is_contiguous() and tuple(y_host.shape) == (M, N) and y_host.dtype == odt,
-         "y_host must be a contiguous CPU [M,N] tensor of the output dtype")
+    elif y_host.is_cuda or y_host.dtype != odt or y_host.shape[0] != M or y_host.shape[1] != N or \
+            not y_host.is_contiguous():
+        raise RuntimeError("liquidgemm_b200: y_host must be a contiguous CPU [M,N] tensor of the output dtype")
     if M == 0:
         return y_host
     blob, s1 = qw_dev["rs"], qw_dev["s1"]
-    dev = blob.device if device is None else torch.device(device)
+    dev = blob.device
     xc, oc = _DTYPE_CODES[x_host.dtype], _DTYPE_CODES[odt]
-    with torch.cuda.device(dev):
-        stream = _stream()
-        need = lib.lq_linear_host_scratch_bytes(M, N, K, xc, oc)
+    sizes = _HOST_SIZES.get((M, N, K, xc, oc))
+    if sizes is None:
+        sizes = _HOST_SIZES[(M, N, K, xc, oc)] = (lib.lq_linear_host_scratch_bytes(M, N, K, xc, oc),
+                                                  lib.lq_gemm_workspace_bytes(M, N, K, 0))
+    need, nws = sizes
+    switch = torch.cuda.current_device() != dev.index
+    if switch:
+        prev = torch.cuda.current_device()
+        torch.cuda.set_device(dev)
+    try:
+        stream = torch.cuda.current_stream().cuda_stream
         key = (dev.index, stream)
         scratch = _HOST_SCRATCH.get(key)
         if scratch is None or scratch.numel() < need:
             scratch = torch.empty((max(need, 1 << 22),), dtype=torch.uint8, device=dev)
             _HOST_SCRATCH[key] = scratch
-        nws = lib.lq_gemm_workspace_bytes(M, N, K, 0)
-        ws = _workspace(nws, dev)
-        rc = lib.lq_w4a8_linear_host(x_host.data_ptr(), xc, _ptr(blob), _ptr(s1), y_host.data_ptr(), oc, M, N, K,
-                                     _ptr(scratch), scratch.numel(), _ptr(ws) if ws is not None else None,
-                                     ws.numel() if ws is not None else 0, stream)
-        if rc != 0 and ws is not None:
-            ws.zero_()
-        check(rc, "w4a8_linear_host")
+        ws = _WORKSPACES.get(key)
+        if nws and (ws is None or ws.numel() < nws):
+            ws = _workspace(nws, dev)
+        rc = lib.lq_w4a8_linear_host(x_host.data_ptr(), xc, blob.data_ptr(), s1.data_ptr(), y_host.data_ptr(), oc,
+                                     M, N, K, scratch.data_ptr(), scratch.numel(),
+                                     ws.data_ptr() if nws else None, ws.numel() if nws else 0, stream)
+        if rc != 0:
+            if nws:
+                ws.zero_()
+            check(rc, "w4a8_linear_host")
+    finally:
+        if switch:
+            torch.cuda.set_device(prev)
     return y_host
 
 
