@@ -385,7 +385,7 @@ static long long* g_trace = nullptr;
 
 static int bn_for(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128; }
 
-static DecodePlan plan_for(int N, int K) { return decode_plan((N + 127) / 128, K / 128, 2 * sm_count()); }
+static DecodePlan plan_for(int N, int K) { return decode_plan((N + 127) / 128, K / 128, 2 * sm_count(), true); }
 
 }  // namespace skinny
 

@@ -307,7 +307,7 @@ static int launch(const Args& a, int grid, cudaStream_t st) {
 
 static long long* g_trace = nullptr;
 
-static DecodePlan plan_for(int N, int K) { return decode_plan((N + 127) / 128, K / 128, 2 * sm_count()); }
+static DecodePlan plan_for(int N, int K) { return decode_plan((N + 127) / 128, K / 128, 2 * sm_count(), false); }
 static int grid_for(int N, int K) { return plan_for(N, K).grid; }
 
 }  // namespace gblob

@@ -74,12 +74,14 @@ struct SegmentWalk {
 // tile is cut into S equal k-ranges, one CTA each: a CTA then has exactly one segment, so no CTA pays
 // the segment epilogue twice.  With many tiles the k-tiles of all tiles are laid end to end and cut
 // into equal contiguous ranges (stream-K): perfectly balanced bytes, at the price of a second
-// segment in most CTAs.
+// segment in most CTAs.  Between slots/2 and slots tiles the choice is the kernel's: whole tiles
+// leave some SMs with one CTA (measured better for the tensor-core kernel, whose segment epilogue is
+// expensive), stream-K keeps all CTAs equal (measured better for the dp4a GEMV).
 struct DecodePlan {
   int grid, fixed_split;
 };
-inline DecodePlan decode_plan(int n_tiles, int kt, int slots) {
-  if (n_tiles * 2 <= slots) {
+inline DecodePlan decode_plan(int n_tiles, int kt, int slots, bool whole_tiles_up_to_slots) {
+  if (n_tiles * 2 <= slots || (whole_tiles_up_to_slots && n_tiles <= slots)) {
     int S = slots / n_tiles;
     if (S > kt) S = kt;
     return {n_tiles * S, S};
