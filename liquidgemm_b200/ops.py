@@ -603,11 +603,13 @@ _HOST_SIZES: dict = {}
 
 
 def w4a8_linear_host(x_host: torch.Tensor, qw_dev: dict, y_host: torch.Tensor = None,
-                     out_dtype: torch.dtype = None) -> torch.Tensor:
+                     out_dtype: torch.dtype = None, stream: "torch.cuda.Stream" = None) -> torch.Tensor:
     """The same linear for activations and outputs in HOST memory (pinned for asynchronous copies):
-    upload, quantise, linear from the tile blob ``qw_dev["rs"]`` and download are enqueued on the current
-    stream of the blob's device by ONE native call.  Returns ``y_host`` (allocated pinned when not
-    given); the caller synchronises the stream before reading it.
+    upload, quantise, linear from the tile blob ``qw_dev["rs"]`` and download are enqueued on ``stream``
+    (default: the current stream of the blob's device) by ONE native call.  Returns ``y_host``
+    (allocated pinned when not given); the caller synchronises the stream before reading it.
+    Independent requests issued round-robin on a few streams overlap their copies with each other's
+    kernels; every stream gets its own scratch and reduction workspace.
 
     The wrapper is on the per-layer critical path of a host-driven decode loop, so it caches what does
     not change between calls (buffer sizes per shape, the scratch per stream) and does no tensor work."""
@@ -638,7 +640,7 @@ def w4a8_linear_host(x_host: torch.Tensor, qw_dev: dict, y_host: torch.Tensor = 
         prev = torch.cuda.current_device()
         torch.cuda.set_device(dev)
     try:
-        stream = torch.cuda.current_stream().cuda_stream
+        stream = torch.cuda.current_stream().cuda_stream if stream is None else stream.cuda_stream
         key = (dev.index, stream)
         scratch = _HOST_SCRATCH.get(key)
         if scratch is None or scratch.numel() < need:
@@ -646,7 +648,10 @@ def w4a8_linear_host(x_host: torch.Tensor, qw_dev: dict, y_host: torch.Tensor = 
             _HOST_SCRATCH[key] = scratch
         ws = _WORKSPACES.get(key)
         if nws and (ws is None or ws.numel() < nws):
-            ws = _workspace(nws, dev)
+            if ws is not None:
+                _RETIRED.append(ws)
+            ws = _WORKSPACES[key] = torch.zeros((max(nws, 1 << 22),), dtype=torch.uint8, device=dev)
+            torch.cuda.current_stream().synchronize()   # zero-fill (current stream) before use on `stream`
         rc = lib.lq_w4a8_linear_host(x_host.data_ptr(), xc, blob.data_ptr(), s1.data_ptr(), y_host.data_ptr(), oc,
                                      M, N, K, scratch.data_ptr(), scratch.numel(),
                                      ws.data_ptr() if nws else None, ws.numel() if nws else 0, stream)
