@@ -106,6 +106,23 @@ def run_sweep(peaks, Ms=(1, 4, 8, 16, 32, 64, 128, 512, 2048, 8192)):
     return rows
 
 
+def run_quant(peaks, K=4096):
+    """The per-token activation quantiser alone (fp16 in): time and fraction of the HBM copy rate
+    for its algorithmic bytes (read 2 B, write 1 B per element + one scale per token)."""
+    rows = []
+    for M in (1, 16, 128, 2048, 8192):
+        C = max(3, -(-300_000_000 // (M * K * 3)))
+        C = min(C, 64)
+        xs = [torch.randn(M, K, device="cuda", dtype=torch.float16) for _ in range(C)]
+        t = graph_time_us(lambda i: torch.ops.liquidgemm.quant_per_token(xs[i % C]), C)
+        nbytes = M * K * 3 + 4 * M
+        rows.append({"M": M, "K": K, "us": round(t, 2), "GBps": round(nbytes / t / 1e3, 1),
+                     "hbm_frac": round(nbytes / t / 1e3 / peaks["hbm_gbs"], 3)})
+        del xs
+    torch.cuda.empty_cache()
+    return rows
+
+
 def run_splitk(peaks):
     rows = []
     for name in ("down", "gate_up"):
@@ -187,6 +204,7 @@ def run_extras(world, rank, local_rank, peaks):
     if world == 1:
         out["sweep"] = run_sweep(peaks)
         out["splitk"] = run_splitk(peaks)
+        out["quant_per_token"] = run_quant(peaks)
     out["tp70b"] = {"ranks": world, "layers": 80, "rows": run_tp70b(world, rank)}
     return out
 

@@ -125,6 +125,7 @@ w4a8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args) 
       Ring<NS> ring;
       int issued = 0;
       bool ok = true;
+      long long p_wait = 0;
       // Weight tiles do not depend on the previous kernel of the stream, the tokens do: the first NS
       // weight tiles are requested at once, then comes the wait for the previous kernel, then the
       // token boxes of those stages.
@@ -141,11 +142,13 @@ w4a8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args) 
         const uint8_t* src = args.blob + ((size_t)sg.tile * args.kt_total + sg.kb) * kTileBytes;
         for (int kt = sg.kb; kt < sg.ke; ++kt, src += kTileBytes) {
           if (issued == NS) meet_dependency();
+          const long long p0 = args.trace ? clock64() : 0;
           if (!ptx::mbar_wait_bounded(bar_empty + 8 * ring.s, ring.ph ^ 1u, kWaitLimitNs)) {
             atomicExch(args.status, 401);
             ok = false;
             break;
           }
+          if (args.trace) p_wait += clock64() - p0;
           const uint32_t full = bar_full + 8 * ring.s;
           ptx::mbar_expect_tx(full, kTx);
           ptx::bulk_load(ws + ring.s * kTileBytes, src, kTileBytes, full);
@@ -156,6 +159,7 @@ w4a8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args) 
         }
       }
       if (!dependency_met) meet_dependency();
+      if (args.trace) args.trace[blockIdx.x * 8 + 7] = p_wait;
       // Copies in flight write shared memory: they must have landed before the CTA may exit.
       const int pending = issued < NS ? issued : NS;
       for (int j = 0; j < pending; ++j) {
@@ -228,8 +232,9 @@ w4a8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args) 
     uint32_t seg = 0;
     bool waited_dependency = false;
     const bool tracing = args.trace != nullptr && d == 0;
+    long long e_wait = 0, e_load = 0, e_store = 0, d_wait = 0;
     bool first = true;
-    if (tracing) args.trace[blockIdx.x * 4 + 0] = (long long)ptx::globaltimer_ns();
+    if (tracing) args.trace[blockIdx.x * 8 + 0] = (long long)ptx::globaltimer_ns();
 
     while (walk.next(sg)) {
       // the channel scale is a weight: fetch it now, it is needed right after the last MMA
@@ -240,14 +245,16 @@ w4a8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args) 
 #pragma unroll 1
       for (int kt = sg.kb; kt < sg.ke; ++kt, ++step, ring.advance()) {
         if ((int)(step & 1u) != set) continue;
+        const long long w0 = tracing ? clock64() : 0;
         if (ok && !ptx::mbar_wait_bounded(bar_full + 8 * ring.s, ring.ph, kWaitLimitNs)) {
           atomicExch(args.status, 404);
           ok = false;
         }
+        if (tracing) d_wait += clock64() - w0;
         if (first) {
           // The stage holds tokens, so the producer is past its wait for the previous kernel: pull the
           // token scales (that kernel's output) into L1 now, the epilogue reads them under time pressure.
-          if (tracing) args.trace[blockIdx.x * 4 + 1] = (long long)ptx::globaltimer_ns();
+          if (tracing) args.trace[blockIdx.x * 8 + 1] = (long long)ptx::globaltimer_ns();
           first = false;
           dependency_wait();
           waited_dependency = true;
@@ -285,8 +292,9 @@ w4a8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args) 
         ptx::mbar_arrive(bar_aready + 8 * ring.s);
       }
 
-      if (tracing) args.trace[blockIdx.x * 4 + 2] = (long long)ptx::globaltimer_ns();   // last dequant done
+      if (tracing) args.trace[blockIdx.x * 8 + 2] = (long long)ptx::globaltimer_ns();   // last dequant done
       // ---- epilogue of the segment: set g takes the 16-column chunks g, g+2, ...
+      const long long e0 = tracing ? clock64() : 0;
       if (ok && !ptx::mbar_wait_bounded(bar_accfull, seg & 1u, kWaitLimitNs)) {
         atomicExch(args.status, 405);
         ok = false;
@@ -299,6 +307,8 @@ w4a8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args) 
       }
       unsigned long long* slot = args.slots + (size_t)sg.slot * (BN * 128);
       const long long nk = sg.ke - sg.kb;
+      const long long e1 = tracing ? clock64() : 0;
+      long long e2 = e1;
 #pragma unroll 1
       for (int c0 = set * 16; c0 < BN; c0 += 32) {
         if (c0 >= args.M) break;   // uniform over the warp
@@ -314,6 +324,10 @@ w4a8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args) 
         float sc[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) sc[j] = (scaled && c0 + j < args.M) ? __ldg(args.ascale + c0 + j) : 0.f;
+        if (tracing) {
+          if (sc[0] == 123.456f) atomicExch(args.status, 498);   // forces the loads to complete here
+          e2 = clock64();
+        }
         if (!sg.whole) {
           // One returning 64-bit atomic per element does the cross-CTA reduction: the word holds the
           // k-tiles added so far (bits 40..) and the sum of the contributions, each biased by 2^21 per
@@ -348,6 +362,12 @@ w4a8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args) 
           }
         }
       }
+      if (tracing) {
+        const long long e3 = clock64();
+        e_wait += e1 - e0;
+        e_load += e2 - e1;
+        e_store += e3 - e2;
+      }
       if (set * 16 >= BN || set * 16 >= args.M) {   // this set had no chunk: it still releases the accumulator
         __syncwarp();
         ptx::tc_fence_before();
@@ -355,7 +375,12 @@ w4a8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args) 
       }
       ++seg;
     }
-    if (tracing) args.trace[blockIdx.x * 4 + 3] = (long long)ptx::globaltimer_ns();
+    if (tracing) {
+      args.trace[blockIdx.x * 8 + 3] = (long long)ptx::globaltimer_ns();
+      args.trace[blockIdx.x * 8 + 4] = e_wait;
+      args.trace[blockIdx.x * 8 + 5] = e_load + e_store;
+      args.trace[blockIdx.x * 8 + 6] = d_wait;
+    }
   }
   ptx::tc_fence_before();
   __syncthreads();

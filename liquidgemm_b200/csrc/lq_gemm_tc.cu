@@ -794,9 +794,11 @@ struct Route {
 constexpr int kGemvBlobMaxM = 4;
 
 // Decode batches up to this size use the single-launch streaming kernel; its one-atomic-per-element
-// reduction is the cheapest way to join split tiles while a CTA holds few tokens, but from about 64
-// tokens on the int32 planes + finish pass of the tile kernel are faster (measured on B200).
-constexpr int kSkinnyMaxM = 32;
+// reduction is the cheapest way to join split tiles while a CTA holds few tokens.  From 17 tokens on
+// the int32 planes + finish pass of the tile kernel are as fast or faster (measured on B200; the
+// 32-token configuration of the streaming kernel additionally measured 3x slower with parked barrier
+// waits, cause not found, so it is not used).
+constexpr int kSkinnyMaxM = 16;
 
 static Route route_for(int M, int N, int K, int splitk) {
   const int kt = K / 128;
