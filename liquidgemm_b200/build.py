@@ -22,8 +22,7 @@ LIB_PATH = os.path.join(HERE, "_lq_b200.so")
 NVCC_FLAGS = [
     "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr",
-] + (["-DLQ_SPIN_WAITS"] if os.environ.get("LQ_SPIN_WAITS") == "1" else []) \
-  + (["-DLQ_PARK_NS=%su" % os.environ["LQ_PARK_NS"]] if os.environ.get("LQ_PARK_NS") else [])   # experiment switches
+]
 
 
 def _nvcc() -> str:

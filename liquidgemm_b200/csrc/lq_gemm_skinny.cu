@@ -29,6 +29,10 @@
 #include <cstdlib>
 #include <mutex>
 
+#ifndef LQ_SKINNY_SETS
+#define LQ_SKINNY_SETS 2
+#endif
+
 #include "lq_common.cuh"
 #include "lq_sched.cuh"
 #include "lq_tc_ptx.cuh"
@@ -41,7 +45,8 @@ int make_byte_matrix_map(CUtensorMap* map, const void* ptr, long rows, long row_
 namespace skinny {
 
 constexpr int kTileBytes = 8704;
-constexpr int kDequant = 256;              // two sets of 128
+constexpr int kSets = LQ_SKINNY_SETS;       // dequant sets of 128 threads, taking k-tiles round-robin
+constexpr int kDequant = 128 * kSets;
 constexpr int kThreads = 64 + kDequant;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 constexpr int kOutI32 = 3;
@@ -78,7 +83,6 @@ struct Cfg {
   static_assert(kSmemBytes <= 113 * 1024, "two CTAs per SM share the shared memory");
 };
 
-__device__ __forceinline__ void dequant_barrier() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 template <int BN, int NS>
 __global__ void __launch_bounds__(kThreads, 2)
@@ -172,7 +176,7 @@ w4a8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args) 
     ptx::tmem_alloc(tmem_slot, C::kTmemCols);
     ptx::tmem_relinquish();
     ptx::tc_fence_before();
-    asm volatile("bar.sync 2, 288;" ::: "memory");   // publishes the allocation to the dequant warps
+    asm volatile("bar.sync 2, %0;" ::"n"(32 + kDequant) : "memory");   // publishes the allocation to the dequant warps
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_p;
     const uint32_t tmem_acc = tmem_base;
@@ -217,11 +221,11 @@ w4a8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args) 
   } else {
     // ------------------------------------------------------------------ dequant sets, then epilogue
     const int d = threadIdx.x - 64;
-    const int set = d >> 7;                   // takes the k-tiles whose running index is set (mod 2)
+    const int set = d >> 7;                   // takes the k-tiles whose running index is set (mod kSets)
     const int quad = warp & 3;                // tensor-memory lane quadrant this warp may access
     const int row = quad * 32 + lane;         // weight row inside the tile == tensor-memory lane
     const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
-    asm volatile("bar.sync 2, 288;" ::: "memory");
+    asm volatile("bar.sync 2, %0;" ::"n"(32 + kDequant) : "memory");
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_p;
     const uint32_t tmem_acc = tmem_base + lane_addr;
@@ -244,7 +248,7 @@ w4a8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args) 
       const float w_scale = (n_ok && scaled) ? __ldg(args.s1 + n) : 0.f;
 #pragma unroll 1
       for (int kt = sg.kb; kt < sg.ke; ++kt, ++step, ring.advance()) {
-        if ((int)(step & 1u) != set) continue;
+        if ((int)(step % (uint32_t)kSets) != set) continue;
         const long long w0 = tracing ? clock64() : 0;
         if (ok && !ptx::mbar_wait_bounded(bar_full + 8 * ring.s, ring.ph, kWaitLimitNs)) {
           atomicExch(args.status, 404);
@@ -310,12 +314,12 @@ w4a8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args) 
       const long long e1 = tracing ? clock64() : 0;
       long long e2 = e1;
 #pragma unroll 1
-      for (int c0 = set * 16; c0 < BN; c0 += 32) {
+      for (int c0 = set * 16; c0 < BN; c0 += 16 * kSets) {
         if (c0 >= args.M) break;   // uniform over the warp
         int v[16];
         ptx::tmem_ld16(tmem_acc + c0, v);
         ptx::tc_wait_ld();
-        if (c0 + 32 >= BN || c0 + 32 >= args.M) {   // last chunk of this set: the accumulator may be reused
+        if (c0 + 16 * kSets >= BN || c0 + 16 * kSets >= args.M) {   // last chunk of this set: the accumulator may be reused
           __syncwarp();
           ptx::tc_fence_before();
           ptx::mbar_arrive(bar_accfree);
