@@ -129,6 +129,19 @@ LQ_API int lq_w4a8_gemv_blob_static(const void* x_i8, const void* blob, const vo
                                     const void* s1, void* out, int out_dtype, int M, int N, int K,
                                     void* stream);
 
+/* lq_w4a8_gemm_fused for a decode batch (M <= 16) whose output block [M, N] is written into n_outs
+ * (1..8) row-major matrices with row stride ld_out elements at column col0: with the full-width
+ * outputs of this GPU and of its peers as destinations (peer memory mapped into this process), the
+ * epilogue performs the all-gather of an N-sharded layer with plain stores over NVLink.  `outs` is
+ * a HOST array of device pointers.  Ordering towards the peers' consumers is the caller's job (a
+ * stream-ordered barrier between the ranks after the call).  Workspace as lq_w4a8_gemm_fused with
+ * splitk 0.  Replaces GEMM + all-gather of the reference's tensor-parallel use
+ * (liquidgemm/vllm_plugin.py:174-206 under vLLM's column-parallel linear). */
+LQ_API int lq_w4a8_gemm_fused_scatter(const int8_t* x_i8, const uint8_t* blob, const float* ascale,
+                                      const float* s1, void* const* outs, int n_outs, long ld_out,
+                                      long col0, int out_dtype, int M, int N, int K, void* workspace,
+                                      size_t workspace_bytes, void* stream);
+
 /* One whole linear layer for HOST activations and a HOST output: upload, per-token quantise, fused
  * W4A8 linear from the tile blob (automatic kernel choice by M), download, all enqueued on `stream`
  * by this one call; nothing is synchronised.  x_host [M,K] in x_dtype and y_host [M,N] in out_dtype

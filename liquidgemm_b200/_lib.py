@@ -37,6 +37,8 @@ _SIGNATURES = {
     "lq_gemv_blob_workspace_bytes": (c_size_t, []),
     "lq_w4a8_gemv_blob": (c_int, [P, P, P, P, P, c_int, c_int, c_int, c_int, P, c_size_t, P]),
     "lq_w4a8_gemv_blob_static": (c_int, [P, P, P, P, P, c_int, c_int, c_int, c_int, P]),
+    "lq_w4a8_gemm_fused_scatter": (c_int, [P, P, P, P, P, c_int, ctypes.c_long, ctypes.c_long, c_int, c_int, c_int,
+                                           c_int, P, c_size_t, P]),
     "lq_linear_host_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "lq_w4a8_linear_host": (c_int, [P, c_int, P, P, P, c_int, c_int, c_int, c_int, P, c_size_t, P, c_size_t, P]),
     "lq_gemm_v1_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),

@@ -68,6 +68,30 @@ __device__ __forceinline__ void store_out(void* y, size_t idx, float v, int out_
   }
 }
 
+// Where a kernel's outputs go: the same [M, N] block is written into up to 8 row-major matrices with
+// row stride `ld` elements at column offset `col0`.  One destination with ld = N, col0 = 0 is the
+// ordinary output; several destinations (this GPU's and its peers' full-width output, mapped into this
+// process) make the epilogue do the all-gather of an N-sharded layer with plain stores.
+struct OutSpec {
+  void* ptr[8];
+  int n;
+  long ld, col0;
+};
+inline OutSpec single_out(void* out, long N) {
+  OutSpec o = {};
+  o.ptr[0] = out;
+  o.n = 1;
+  o.ld = N;
+  o.col0 = 0;
+  return o;
+}
+__device__ __forceinline__ void store_out_all(const OutSpec& o, long m, long n, float v, int out_dtype) {
+  const size_t idx = (size_t)(m * o.ld + o.col0 + n);
+  store_out(o.ptr[0], idx, v, out_dtype);
+#pragma unroll 1
+  for (int r = 1; r < o.n; ++r) store_out(o.ptr[r], idx, v, out_dtype);
+}
+
 // ---------------------------------------------------------------------------------------------
 // memory
 // ---------------------------------------------------------------------------------------------

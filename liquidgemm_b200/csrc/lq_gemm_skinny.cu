@@ -55,7 +55,7 @@ struct Args {
   const uint8_t* blob;
   const float* ascale;   // [M]
   const float* s1;       // [N]
-  void* out;             // [M, N]
+  OutSpec out;           // [M, N] block, one or several destinations (int32 mode: the first only)
   unsigned long long* slots;   // [grid][BN][128] packed (k-tile count, biased partial sum), zero between launches
   int* status;
   int out_mode;          // LQ_DT_* or kOutI32
@@ -360,9 +360,8 @@ w4a8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args) 
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           if (c0 + j < args.M && (sg.whole || sc[j] == sc[j])) {
-            const size_t idx = (size_t)(c0 + j) * args.N + n;
-            if (scaled) store_out(args.out, idx, lqq_scale(v[j], sc[j], w_scale), args.out_mode);
-            else reinterpret_cast<int32_t*>(args.out)[idx] = v[j];
+            if (scaled) store_out_all(args.out, c0 + j, n, lqq_scale(v[j], sc[j], w_scale), args.out_mode);
+            else reinterpret_cast<int32_t*>(args.out.ptr[0])[(size_t)(c0 + j) * args.out.ld + args.out.col0 + n] = v[j];
           }
         }
       }
@@ -425,7 +424,7 @@ size_t skinny_workspace_bytes(int M, int N, int K) {
 }
 
 // out_mode: LQ_DT_* or 3 (raw int32).  M <= 128.  `ws`: skinny_workspace_bytes(), all zero, left all zero.
-int run_skinny_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, void* out,
+int run_skinny_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, const OutSpec& out,
                     int out_mode, int M, int N, int K, void* ws, size_t ws_bytes, cudaStream_t st) {
   using namespace skinny;
   if (!ws || ws_bytes < skinny_workspace_bytes(M, N, K)) return LQ_ERR_WORKSPACE;

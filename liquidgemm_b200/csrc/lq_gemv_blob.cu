@@ -38,7 +38,7 @@ struct Args {
   const int8_t* x;       // [M, K]
   const float* ascale;   // [M]
   const float* s1;       // [N]
-  void* out;             // [M, N]
+  OutSpec out;           // [M, N] block, one or several destinations
   unsigned long long* slots;   // [grid][MT][128] packed (k-tile count, biased partial sum), zero between launches
   int* status;
   int out_dtype;
@@ -244,8 +244,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_blob_kernel(const Args args)
         if (mine) {
 #pragma unroll
           for (int m = 0; m < MT; ++m)
-            if (m < M) store_out(args.out, (size_t)m * args.N + n, lqq_scale(acc[m], a_scale[m], w_scale),
-                                 args.out_dtype);
+            if (m < M) store_out_all(args.out, m, n, lqq_scale(acc[m], a_scale[m], w_scale), args.out_dtype);
         }
         consumer_barrier();   // `red` may be rewritten by the next segment
       } else {
@@ -270,7 +269,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_blob_kernel(const Args args)
               const long long total = (long long)(old[m] & ((1ull << 40) - 1)) + (long long)acc[m] + (nk << 21) -
                                       ((long long)args.kt_total << 21);
               __stcg(slot + m * 128 + row, 0ull);
-              store_out(args.out, (size_t)m * args.N + n, lqq_scale((int)total, a_scale[m], w_scale), args.out_dtype);
+              store_out_all(args.out, m, n, lqq_scale((int)total, a_scale[m], w_scale), args.out_dtype);
             }
           }
         }
@@ -322,10 +321,11 @@ size_t gemv_blob_workspace_bytes(int N, int K) {
 }
 
 // Same call with a size-checked workspace, for the GEMM entry points.
-int run_gemv_blob_ws(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, void* out,
-                     int out_dtype, int M, int N, int K, void* ws, size_t ws_bytes, cudaStream_t st);
+int run_gemv_blob_ws(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1,
+                     const OutSpec& out, int out_dtype, int M, int N, int K, void* ws, size_t ws_bytes,
+                     cudaStream_t st);
 
-int run_gemv_blob(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, void* out,
+int run_gemv_blob(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, const OutSpec& out,
                   int out_dtype, int M, int N, int K, unsigned long long* slots, cudaStream_t st) {
   using namespace gblob;
   Args a;
@@ -352,8 +352,9 @@ int run_gemv_blob(const int8_t* x, const uint8_t* blob, const float* ascale, con
   return launch<8, 7>(a, grid, st);
 }
 
-int run_gemv_blob_ws(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, void* out,
-                     int out_dtype, int M, int N, int K, void* ws, size_t ws_bytes, cudaStream_t st) {
+int run_gemv_blob_ws(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1,
+                     const OutSpec& out, int out_dtype, int M, int N, int K, void* ws, size_t ws_bytes,
+                     cudaStream_t st) {
   const int grid = gblob::grid_for(N, K);
   if (!ws || ws_bytes < gemv_blob_ws_bytes(grid)) return LQ_ERR_WORKSPACE;
   return run_gemv_blob(x, blob, ascale, s1, out, out_dtype, M, N, K, static_cast<unsigned long long*>(ws), st);
@@ -382,8 +383,8 @@ LQ_API int lq_w4a8_gemv_blob(const void* x_i8, const void* blob, const void* asc
   const int grid = gblob::grid_for(N, K);
   if (!workspace || workspace_bytes < gemv_blob_ws_bytes(grid)) return LQ_ERR_WORKSPACE;
   return run_gemv_blob(static_cast<const int8_t*>(x_i8), static_cast<const uint8_t*>(blob),
-                       static_cast<const float*>(ascale), static_cast<const float*>(s1), out, out_dtype, M, N, K,
-                       static_cast<unsigned long long*>(workspace), as_stream(stream));
+                       static_cast<const float*>(ascale), static_cast<const float*>(s1), single_out(out, N), out_dtype, M,
+                       N, K, static_cast<unsigned long long*>(workspace), as_stream(stream));
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -440,8 +441,8 @@ LQ_API int lq_w4a8_gemv_blob_static(const void* x_i8, const void* blob, const vo
   void* p = gblob::static_scratch_for_current_device();
   if (!p) return LQ_ERR_CUDA;
   return run_gemv_blob(static_cast<const int8_t*>(x_i8), static_cast<const uint8_t*>(blob),
-                       static_cast<const float*>(ascale), static_cast<const float*>(s1), out, out_dtype, M, N, K,
-                       static_cast<unsigned long long*>(p), as_stream(stream));
+                       static_cast<const float*>(ascale), static_cast<const float*>(s1), single_out(out, N), out_dtype, M,
+                       N, K, static_cast<unsigned long long*>(p), as_stream(stream));
 }
 
 }  // extern "C"

@@ -16,6 +16,8 @@ from __future__ import annotations
 
 import os
 
+import ctypes
+
 import torch
 
 from . import _lib
@@ -357,6 +359,30 @@ def gemv_blob(x_i8, blob, ascale, s1, N, K, out_dtype):
                 ws.zero_()
             check(rc, "gemv_blob")
     return y
+
+
+def gemm_fused_scatter(x_i8, blob, ascale, s1, out_ptrs, ld_out, col0, N, K, out_dtype):
+    """Decode linear (M <= 16) whose [M, N] output block is stored at column ``col0`` of every matrix in
+    ``out_ptrs`` (device addresses of row-major [M, ld_out] buffers of the output dtype: this GPU's and
+    its peers' full-width outputs).  The epilogue thereby does the all-gather of an N-sharded layer;
+    the caller orders the ranks afterwards (e.g. a symmetric-memory barrier on the same stream)."""
+    x_i8 = _i8(x_i8, "x_i8")
+    _req(K % 128 == 0 and x_i8.shape[1] == K, "K%128==0 required and x_i8 must be [M,K]")
+    _req(int(out_dtype) in _OUT_DTYPES, "out_dtype must be 0 (bf16), 1 (fp16) or 2 (fp32)")
+    blob = _check_blob(blob, N, K)
+    ascale, s1 = _f32(ascale, "ascale"), _f32(s1, "s1")
+    M = x_i8.shape[0]
+    _req(1 <= M <= 16, "gemm_fused_scatter is a decode path (1 <= M <= 16)")
+    _req(1 <= len(out_ptrs) <= 8 and ld_out >= N and 0 <= col0 <= ld_out - N, "bad destinations")
+    arr = (ctypes.c_void_p * len(out_ptrs))(*[int(p) for p in out_ptrs])
+    with _dev_ctx(x_i8):
+        ws = _workspace(lib.lq_gemm_workspace_bytes(M, N, K, 0), x_i8.device)
+        rc = lib.lq_w4a8_gemm_fused_scatter(_ptr(x_i8), _ptr(blob), _ptr(ascale), _ptr(s1), arr, len(out_ptrs),
+                                            int(ld_out), int(col0), int(out_dtype), M, N, K, _ptr(ws), ws.numel(),
+                                            _stream())
+        if rc != 0:
+            ws.zero_()
+        check(rc, "gemm_fused_scatter")
 
 
 def gemm_rowmajor(x_i8, gpack, s_u8, off_a, ascale, s1, N, K, out_dtype, splitk=None):

@@ -252,3 +252,22 @@ def test_prefill_scheduling_modes_are_exact(ops, M, S):
     assert np.array_equal(ops.gemm_i32(xt, w, N, K, splitk=S).cpu().numpy(), _acc(x, qw))
     y = ops.gemm_fused(xt, w, at, tq.s1, N, K, 1, splitk=S)
     assert_bits_equal(y, O.w4a8_matmul(x, ascale, qw), 1, f"M={M} S={S}")
+
+
+@pytest.mark.parametrize("M", [1, 4, 9, 16])
+def test_scatter_epilogue_writes_every_destination(ops, M):
+    """The gather-by-stores epilogue: the [M, N] block lands at the right columns of several wider
+    matrices (here two local buffers stand for this GPU's and a peer's output) and nowhere else."""
+    N, K, LD, COL0 = 384, 2048, 1000, 256
+    qw = random_lqq(N, K, 64, seed=40 + M)
+    tq = to_torch_qw(qw)
+    blob = ops.repack_rs_weight(tq).reshape(-1)
+    x, ascale = random_tokens(M, K, seed=M)
+    outs = [torch.full((M, LD), -7.0, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    ops.gemm_fused_scatter(torch.from_numpy(x).cuda(), blob, torch.from_numpy(ascale).cuda(), tq.s1,
+                           [o.data_ptr() for o in outs], LD, COL0, N, K, 0)
+    torch.cuda.synchronize()
+    want = O.w4a8_matmul(x, ascale, qw)
+    for o in outs:
+        assert_bits_equal(o[:, COL0:COL0 + N].contiguous(), want, 0, f"scatter M={M}")
+        assert bool((o[:, :COL0] == -7.0).all()) and bool((o[:, COL0 + N:] == -7.0).all())
