@@ -252,6 +252,8 @@ def main():
         run_reference_arm(args)
         return
 
+    # peer stores only: symmetric memory is used without NVLink multicast objects
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
     import torch
     import torch.distributed as dist
 

@@ -142,6 +142,22 @@ LQ_API int lq_w4a8_gemm_fused_scatter(const int8_t* x_i8, const uint8_t* blob, c
                                       long col0, int out_dtype, int M, int N, int K, void* workspace,
                                       size_t workspace_bytes, void* stream);
 
+/* The same with cross-GPU ordering done by the kernels themselves instead of a barrier launch:
+ * every CTA, after its last output store, adds 1 (release, system scope) to word `flag_index` of
+ * each destination rank's flag array `peer_flags[r]` (null: no signalling); and before it reads the
+ * tokens the kernel waits (at most 2 s, then a status code) until `*wait_flag >= wait_value`
+ * (null: no wait).  A consumer of the gathered output therefore passes the flag word its producers
+ * signalled and, as value, the sum over the ranks of lq_decode_grid() of the producing launch.
+ * Flags are zeroed by the host, with the ranks ordered once before the first kernel of a sequence. */
+LQ_API int lq_w4a8_gemm_fused_scatter_sync(const int8_t* x_i8, const uint8_t* blob, const float* ascale,
+                                           const float* s1, void* const* outs, int n_outs, long ld_out,
+                                           long col0, int out_dtype, int M, int N, int K,
+                                           unsigned* const* peer_flags, int flag_index,
+                                           const unsigned* wait_flag, unsigned wait_value,
+                                           void* workspace, size_t workspace_bytes, void* stream);
+/* CTAs a decode launch (M <= 16) of this shape uses on the current device. */
+LQ_API int lq_decode_grid(int M, int N, int K);
+
 /* One whole linear layer for HOST activations and a HOST output: upload, per-token quantise, fused
  * W4A8 linear from the tile blob (automatic kernel choice by M), download, all enqueued on `stream`
  * by this one call; nothing is synchronised.  x_host [M,K] in x_dtype and y_host [M,N] in out_dtype

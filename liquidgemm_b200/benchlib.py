@@ -141,43 +141,100 @@ def run_splitk(peaks):
     return rows
 
 
-def run_tp70b(world, rank, Ms=(1, 64, 2048), layers_in_stack=80, distinct_layers=3):
-    """80-layer stack of the four 70B-shape linears, each column-sharded along N over `world` ranks."""
+def _symmetric_outputs(world, M, names):
+    """Full-width [M, N] bf16 outputs allocated as symmetric memory: every rank can store into every
+    rank's buffer.  Returns {name: (tensor, handle)} or None where symmetric memory is unavailable."""
+    import torch.distributed as dist
+    try:
+        import torch.distributed._symmetric_memory as symm_mem
+        out = {}
+        for n in names:
+            t = symm_mem.empty((M, SHAPES_70B[n][0]), dtype=torch.bfloat16, device=torch.device("cuda", torch.cuda.current_device()))
+            out[n] = (t, symm_mem.rendezvous(t, dist.group.WORLD.group_name))
+        return out
+    except Exception:
+        return None
+
+
+def run_tp70b(world, rank, Ms=(1, 16, 64, 2048), layers_in_stack=80, distinct_layers=3):
+    """80-layer stack of the four 70B-shape linears, each column-sharded along N over `world` ranks:
+    without any exchange, with an NCCL all-gather of every output, and (decode batches) with the
+    gather done by the linear's own epilogue, which stores its slice into every rank's full-width
+    output over NVLink, followed by a symmetric-memory barrier on the stream."""
     import torch.distributed as dist
     rows = []
     names = list(SHAPES_70B)
     stack = []
     for l in range(distinct_layers):
-        stack.append({n: device_lqq(SHAPES_70B[n][0] // world, SHAPES_70B[n][1], seed=1000 * rank + 10 * l + i)
+        stack.append({n: device_lqq(SHAPES_70B[n][0] // world, SHAPES_70B[n][1], seed=1000 * rank + 10 * l + i,
+                                    want_gp=False)
                       for i, n in enumerate(names)})
     for M in Ms:
         toks = {n: device_tokens(M, SHAPES_70B[n][1], seed=M + i) for i, n in enumerate(names)}
         gathered = {n: torch.empty((world * M, SHAPES_70B[n][0] // world), dtype=torch.bfloat16, device="cuda")
                     for n in names}
+        symm = _symmetric_outputs(world, M, names) if (world > 1 and M <= 16) else None
+        flags = None
+        if symm is not None:
+            try:
+                import torch.distributed._symmetric_memory as symm_mem
+                ft = symm_mem.empty(1024, dtype=torch.int32, device=torch.device("cuda", torch.cuda.current_device()))
+                flags = (ft, symm_mem.rendezvous(ft, dist.group.WORLD.group_name))
+            except Exception:
+                flags = None
 
-        def one_stack(gather):
+        def one_stack(mode):
+            if mode == "fused_sync":
+                # kernels order themselves: launch k signals flag word k on every rank and waits for word
+                # k-1 (all ranks' CTAs of the previous linear) before it reads its tokens
+                ft, fh = flags
+                ft.zero_()
+                fh.barrier(channel=1)
+                k, prev_grid = 0, 0
+                for l in range(layers_in_stack):
+                    lay = stack[l % distinct_layers]
+                    for n in names:
+                        L = lay[n]
+                        full, hdl = symm[n]
+                        ops.gemm_fused_scatter(toks[n][0], L["rs"], toks[n][1], L["s1"], hdl.buffer_ptrs, full.shape[1],
+                                               rank * L["N"], L["N"], L["K"], 0, flag_ptrs=fh.buffer_ptrs, flag_index=k,
+                                               wait_ptr=(ft.data_ptr() + 4 * (k - 1)) if k else None,
+                                               wait_value=world * prev_grid)
+                        prev_grid = ops.decode_grid(M, L["N"], L["K"])
+                        k += 1
+                fh.barrier(channel=1)
+                return
             for l in range(layers_in_stack):
                 lay = stack[l % distinct_layers]
                 for n in names:
-                    y = linear_call(lay[n], toks[n][0], toks[n][1], M)
-                    if gather and world > 1:
-                        dist.all_gather_into_tensor(gathered[n], y)
+                    L = lay[n]
+                    if mode == "fused":
+                        full, hdl = symm[n]
+                        ops.gemm_fused_scatter(toks[n][0], L["rs"], toks[n][1], L["s1"], hdl.buffer_ptrs, full.shape[1],
+                                               rank * L["N"], L["N"], L["K"], 0)
+                        hdl.barrier(channel=0)
+                    else:
+                        y = linear_call(L, toks[n][0], toks[n][1], M)
+                        if mode == "nccl":
+                            dist.all_gather_into_tensor(gathered[n], y)
 
         res = {"M": M}
-        for gather in ((False, True) if world > 1 else (False,)):
+        modes = ["none"] + (["nccl"] if world > 1 else []) + (["fused"] if symm is not None else []) + \
+                (["fused_sync"] if flags is not None else [])
+        for mode in modes:
             s = torch.cuda.Stream()
             with torch.cuda.stream(s):
-                one_stack(gather)
+                one_stack(mode)
                 torch.cuda.synchronize()
                 use_graph = True
                 try:
                     g = torch.cuda.CUDAGraph()
                     with torch.cuda.graph(g, stream=s):
-                        one_stack(gather)
+                        one_stack(mode)
                     run = g.replay
                 except Exception:
                     use_graph = False
-                    run = lambda: one_stack(gather)
+                    run = lambda: one_stack(mode)
                 run()
                 if world > 1:
                     dist.barrier()
@@ -193,9 +250,22 @@ def run_tp70b(world, rank, Ms=(1, 64, 2048), layers_in_stack=80, distinct_layers
             t = torch.tensor([ms], dtype=torch.float64, device="cuda")
             if world > 1:
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            res["stack_ms_gather" if gather else "stack_ms_no_gather"] = round(float(t[0]), 3)
-            res["graph"] = use_graph
+            key = {"none": "stack_ms_no_gather", "nccl": "stack_ms_gather", "fused": "stack_ms_fused_gather",
+                   "fused_sync": "stack_ms_fused_gather_kernel_sync"}[mode]
+            res[key] = round(float(t[0]), 3)
+            res["graph_" + mode] = use_graph
+        if symm is not None:
+            # the stores really arrived: the last layer's full-width output equals the NCCL gather of the slices
+            lay = stack[(layers_in_stack - 1) % distinct_layers]
+            ok = True
+            for n in names:
+                y = linear_call(lay[n], toks[n][0], toks[n][1], M)
+                parts = [torch.empty_like(y) for _ in range(world)]
+                dist.all_gather(parts, y)
+                ok = ok and torch.equal(torch.cat(parts, dim=1), symm[n][0])
+            res["fused_gather_matches_nccl"] = bool(ok)
         rows.append(res)
+        del symm, flags
     return rows
 
 

@@ -85,6 +85,38 @@ inline OutSpec single_out(void* out, long N) {
   o.col0 = 0;
   return o;
 }
+// Cross-GPU ordering for the gather-by-stores epilogue.  Every CTA, after its last output store, adds 1
+// to word `index` of each destination rank's flag array (release, system scope); a consumer kernel
+// on rank r waits until its own word reached the number of CTAs of all ranks before it reads the
+// gathered data.  The flags live in memory every rank can write (symmetric memory); the host zeroes
+// them, and orders the ranks once, before the first kernel of a sequence.
+struct PeerSync {
+  unsigned* signal[8];     // per destination rank: its flag array (null array entries = no signalling)
+  int n_signal;
+  int signal_index;
+  const unsigned* wait;    // this rank's flag word to wait on before reading the tokens, or null
+  unsigned wait_value;
+};
+__device__ __forceinline__ void peer_signal(const PeerSync& p) {
+  for (int r = 0; r < p.n_signal; ++r)
+    asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.signal[r] + p.signal_index) : "memory");
+}
+// Bounded: gives up after `limit_ns` and returns false (the caller records a status code and goes on).
+__device__ __forceinline__ bool peer_wait(const PeerSync& p, unsigned long long limit_ns) {
+  if (!p.wait) return true;
+  unsigned long long t0 = 0;
+  for (unsigned spins = 0;; ++spins) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.wait) : "memory");
+    if (v >= p.wait_value) return true;
+    unsigned long long now;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+    if (spins == 0) t0 = now;
+    else if (now - t0 > limit_ns) return false;
+    __nanosleep(100);
+  }
+}
+
 __device__ __forceinline__ void store_out_all(const OutSpec& o, long m, long n, float v, int out_dtype) {
   const size_t idx = (size_t)(m * o.ld + o.col0 + n);
   store_out(o.ptr[0], idx, v, out_dtype);

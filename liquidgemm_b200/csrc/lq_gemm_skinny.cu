@@ -56,6 +56,7 @@ struct Args {
   const float* ascale;   // [M]
   const float* s1;       // [N]
   OutSpec out;           // [M, N] block, one or several destinations (int32 mode: the first only)
+  PeerSync sync;         // optional cross-GPU ordering around the gather-by-stores epilogue
   unsigned long long* slots;   // [grid][BN][128] packed (k-tile count, biased partial sum), zero between launches
   int* status;
   int out_mode;          // LQ_DT_* or kOutI32
@@ -137,6 +138,7 @@ w4a8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args) 
       bool dependency_met = false;
       auto meet_dependency = [&]() {
         dependency_wait();
+        if (!peer_wait(args.sync, kWaitLimitNs)) atomicExch(args.status, 409);   // tokens gathered from peers
         dependency_met = true;
         const int n = issued < NS ? issued : NS;
         for (int j = 0; j < n; ++j)
@@ -378,6 +380,12 @@ w4a8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args) 
       }
       ++seg;
     }
+    if (args.sync.n_signal > 0) {
+      // every output store of this CTA, including those into peer memory, is ordered before the flags
+      __threadfence_system();
+      asm volatile("bar.sync 1, %0;" ::"n"(kDequant) : "memory");
+      if (d == 0) peer_signal(args.sync);
+    }
     if (tracing) {
       args.trace[blockIdx.x * 8 + 3] = (long long)ptx::globaltimer_ns();
       args.trace[blockIdx.x * 8 + 4] = e_wait;
@@ -417,6 +425,10 @@ static DecodePlan plan_for(int N, int K) { return decode_plan((N + 127) / 128, K
 
 }  // namespace skinny
 
+// CTAs a launch of this shape uses: what a consumer of the gather-by-stores epilogue must see arrive
+// from every rank.
+int skinny_grid(int N, int K) { return skinny::plan_for(N, K).grid; }
+
 size_t skinny_workspace_bytes(int M, int N, int K) {
   (void)N;
   (void)K;
@@ -425,7 +437,7 @@ size_t skinny_workspace_bytes(int M, int N, int K) {
 
 // out_mode: LQ_DT_* or 3 (raw int32).  M <= 128.  `ws`: skinny_workspace_bytes(), all zero, left all zero.
 int run_skinny_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, const OutSpec& out,
-                    int out_mode, int M, int N, int K, void* ws, size_t ws_bytes, cudaStream_t st) {
+                    const PeerSync* sync, int out_mode, int M, int N, int K, void* ws, size_t ws_bytes, cudaStream_t st) {
   using namespace skinny;
   if (!ws || ws_bytes < skinny_workspace_bytes(M, N, K)) return LQ_ERR_WORKSPACE;
   const int bn = bn_for(M);
@@ -439,6 +451,7 @@ int run_skinny_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, c
   a.ascale = ascale;
   a.s1 = s1;
   a.out = out;
+  a.sync = sync ? *sync : PeerSync{};
   a.slots = static_cast<unsigned long long*>(ws);
   a.status = status_word();
   a.out_mode = out_mode;

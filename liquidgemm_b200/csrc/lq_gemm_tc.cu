@@ -56,11 +56,14 @@ int run_tile_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, con
                   int M, int N, int K, int splits, void* ws, size_t ws_bytes, cudaStream_t st);  // lq_gemm_tile.cu
 size_t skinny_workspace_bytes(int M, int N, int K);                          // lq_gemm_skinny.cu
 int run_skinny_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, const OutSpec& out,
-                    int out_mode, int M, int N, int K, void* ws, size_t ws_bytes, cudaStream_t st);  // lq_gemm_skinny.cu
+                    const PeerSync* sync, int out_mode, int M, int N, int K, void* ws, size_t ws_bytes,
+                    cudaStream_t st);  // lq_gemm_skinny.cu
 size_t gemv_blob_workspace_bytes(int N, int K);                              // lq_gemv_blob.cu
 int run_gemv_blob_ws(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1,
-                     const OutSpec& out, int out_dtype, int M, int N, int K, void* ws, size_t ws_bytes,
-                     cudaStream_t st);  // lq_gemv_blob.cu
+                     const OutSpec& out, const PeerSync* sync, int out_dtype, int M, int N, int K, void* ws,
+                     size_t ws_bytes, cudaStream_t st);  // lq_gemv_blob.cu
+int skinny_grid(int N, int K);                                               // lq_gemm_skinny.cu
+int gemv_blob_grid(int N, int K);                                            // lq_gemv_blob.cu
 int launch_gemv_plain_f32(const int8_t* x, const uint8_t* nibbles, const uint8_t* s_u8,
                           const uint8_t* off_a, const float* ascale, const float* s1, float* y, int M,
                           int N, int K, int G, cudaStream_t st);  // lq_gemv.cu
@@ -838,8 +841,8 @@ static int blob_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, 
   if (r.skinny) {
     if (int rc = lq_check_device()) return rc;
     if (M <= kGemvBlobMaxM && out_mode != kOutI32)
-      return run_gemv_blob_ws(x, blob, ascale, s1, single_out(out, N), out_mode, M, N, K, ws, ws_bytes, st);
-    return run_skinny_gemm(x, blob, ascale, s1, single_out(out, N), out_mode, M, N, K, ws, ws_bytes, st);
+      return run_gemv_blob_ws(x, blob, ascale, s1, single_out(out, N), nullptr, out_mode, M, N, K, ws, ws_bytes, st);
+    return run_skinny_gemm(x, blob, ascale, s1, single_out(out, N), nullptr, out_mode, M, N, K, ws, ws_bytes, st);
   }
   if (r.tile) {
     if (int rc = lq_check_device()) return rc;
@@ -862,25 +865,48 @@ int lq_w4a8_gemm_fused(const int8_t* x_i8, const uint8_t* blob, const float* asc
                    as_stream(stream));
 }
 
-int lq_w4a8_gemm_fused_scatter(const int8_t* x_i8, const uint8_t* blob, const float* ascale, const float* s1,
-                               void* const* outs, int n_outs, long ld_out, long col0, int out_dtype, int M, int N,
-                               int K, void* workspace, size_t workspace_bytes, void* stream) {
+int lq_w4a8_gemm_fused_scatter_sync(const int8_t* x_i8, const uint8_t* blob, const float* ascale, const float* s1,
+                                    void* const* outs, int n_outs, long ld_out, long col0, int out_dtype, int M,
+                                    int N, int K, unsigned* const* peer_flags, int flag_index,
+                                    const unsigned* wait_flag, unsigned wait_value, void* workspace,
+                                    size_t workspace_bytes, void* stream) {
   if (!x_i8 || !blob || !ascale || !s1 || !outs || n_outs < 1 || n_outs > 8) return LQ_ERR_BAD_ARG;
   if (out_dtype < 0 || out_dtype > 2 || ld_out < N || col0 < 0 || col0 + N > ld_out) return LQ_ERR_BAD_ARG;
   if (M < 1 || M > kSkinnyMaxM || N <= 0 || K < 128 || K % 128) return LQ_ERR_SHAPE;
   if ((reinterpret_cast<uintptr_t>(x_i8) | reinterpret_cast<uintptr_t>(blob)) % 16) return LQ_ERR_BAD_ARG;
+  if (flag_index < 0) return LQ_ERR_BAD_ARG;
   OutSpec o = {};
+  PeerSync ps = {};
   for (int r = 0; r < n_outs; ++r) {
-    if (!outs[r]) return LQ_ERR_BAD_ARG;
+    if (!outs[r] || (peer_flags && !peer_flags[r])) return LQ_ERR_BAD_ARG;
     o.ptr[r] = outs[r];
+    if (peer_flags) ps.signal[r] = peer_flags[r];
   }
   o.n = n_outs;
   o.ld = ld_out;
   o.col0 = col0;
+  ps.n_signal = peer_flags ? n_outs : 0;
+  ps.signal_index = flag_index;
+  ps.wait = wait_flag;
+  ps.wait_value = wait_value;
   if (int rc = lq_check_device()) return rc;
   if (M <= kGemvBlobMaxM)
-    return run_gemv_blob_ws(x_i8, blob, ascale, s1, o, out_dtype, M, N, K, workspace, workspace_bytes, as_stream(stream));
-  return run_skinny_gemm(x_i8, blob, ascale, s1, o, out_dtype, M, N, K, workspace, workspace_bytes, as_stream(stream));
+    return run_gemv_blob_ws(x_i8, blob, ascale, s1, o, &ps, out_dtype, M, N, K, workspace, workspace_bytes,
+                            as_stream(stream));
+  return run_skinny_gemm(x_i8, blob, ascale, s1, o, &ps, out_dtype, M, N, K, workspace, workspace_bytes,
+                         as_stream(stream));
+}
+
+int lq_w4a8_gemm_fused_scatter(const int8_t* x_i8, const uint8_t* blob, const float* ascale, const float* s1,
+                               void* const* outs, int n_outs, long ld_out, long col0, int out_dtype, int M, int N,
+                               int K, void* workspace, size_t workspace_bytes, void* stream) {
+  return lq_w4a8_gemm_fused_scatter_sync(x_i8, blob, ascale, s1, outs, n_outs, ld_out, col0, out_dtype, M, N, K,
+                                         nullptr, 0, nullptr, 0u, workspace, workspace_bytes, stream);
+}
+
+int lq_decode_grid(int M, int N, int K) {
+  if (M < 1 || M > kSkinnyMaxM || N <= 0 || K < 128 || K % 128) return 0;
+  return M <= kGemvBlobMaxM ? gemv_blob_grid(N, K) : skinny_grid(N, K);
 }
 
 int lq_w4a8_gemm_rowmajor(const int8_t* x_i8, const uint8_t* gpack, const uint8_t* s_u8, const uint8_t* offset_a,

@@ -39,6 +39,7 @@ struct Args {
   const float* ascale;   // [M]
   const float* s1;       // [N]
   OutSpec out;           // [M, N] block, one or several destinations
+  PeerSync sync;         // optional cross-GPU ordering around the gather-by-stores epilogue
   unsigned long long* slots;   // [grid][MT][128] packed (k-tile count, biased partial sum), zero between launches
   int* status;
   int out_dtype;
@@ -117,6 +118,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_blob_kernel(const Args args)
       bool dependency_met = false;
       auto meet_dependency = [&]() {
         dependency_wait();
+        if (!peer_wait(args.sync, kWaitLimitNs)) atomicExch(args.status, 303);   // tokens gathered from peers
         dependency_met = true;
         const int n = issued < NS ? issued : NS;
         for (int j = 0; j < n; ++j) {
@@ -276,6 +278,12 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_blob_kernel(const Args args)
         consumer_barrier();   // `red` may be rewritten by the next segment
       }
     }
+    if (args.sync.n_signal > 0) {
+      // every output store of this CTA, including those into peer memory, is ordered before the flags
+      __threadfence_system();
+      consumer_barrier();
+      if (c == 0) peer_signal(args.sync);
+    }
     if (tracing) args.trace[blockIdx.x * 4 + 3] = (long long)ptx::globaltimer_ns();
   }
   __syncthreads();
@@ -314,6 +322,8 @@ static int grid_for(int N, int K) { return plan_for(N, K).grid; }
 // Workspace bytes for a launch grid of `grid` CTAs: one 64-bit word per (token <= 8, row) of a slot.
 static size_t gemv_blob_ws_bytes(int grid) { return (size_t)grid * (8 * 128 * 8); }
 
+int gemv_blob_grid(int N, int K) { return gblob::grid_for(N, K); }   // CTAs a launch of this shape uses
+
 size_t gemv_blob_workspace_bytes(int N, int K) {
   (void)N;
   (void)K;
@@ -322,11 +332,12 @@ size_t gemv_blob_workspace_bytes(int N, int K) {
 
 // Same call with a size-checked workspace, for the GEMM entry points.
 int run_gemv_blob_ws(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1,
-                     const OutSpec& out, int out_dtype, int M, int N, int K, void* ws, size_t ws_bytes,
-                     cudaStream_t st);
+                     const OutSpec& out, const PeerSync* sync, int out_dtype, int M, int N, int K, void* ws,
+                     size_t ws_bytes, cudaStream_t st);
 
 int run_gemv_blob(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, const OutSpec& out,
-                  int out_dtype, int M, int N, int K, unsigned long long* slots, cudaStream_t st) {
+                  const PeerSync* sync, int out_dtype, int M, int N, int K, unsigned long long* slots,
+                  cudaStream_t st) {
   using namespace gblob;
   Args a;
   a.blob = blob;
@@ -334,6 +345,7 @@ int run_gemv_blob(const int8_t* x, const uint8_t* blob, const float* ascale, con
   a.ascale = ascale;
   a.s1 = s1;
   a.out = out;
+  a.sync = sync ? *sync : PeerSync{};
   a.slots = slots;
   a.status = status_word();
   a.out_dtype = out_dtype;
@@ -353,11 +365,11 @@ int run_gemv_blob(const int8_t* x, const uint8_t* blob, const float* ascale, con
 }
 
 int run_gemv_blob_ws(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1,
-                     const OutSpec& out, int out_dtype, int M, int N, int K, void* ws, size_t ws_bytes,
-                     cudaStream_t st) {
+                     const OutSpec& out, const PeerSync* sync, int out_dtype, int M, int N, int K, void* ws,
+                     size_t ws_bytes, cudaStream_t st) {
   const int grid = gblob::grid_for(N, K);
   if (!ws || ws_bytes < gemv_blob_ws_bytes(grid)) return LQ_ERR_WORKSPACE;
-  return run_gemv_blob(x, blob, ascale, s1, out, out_dtype, M, N, K, static_cast<unsigned long long*>(ws), st);
+  return run_gemv_blob(x, blob, ascale, s1, out, sync, out_dtype, M, N, K, static_cast<unsigned long long*>(ws), st);
 }
 
 }  // namespace lq
@@ -383,8 +395,8 @@ LQ_API int lq_w4a8_gemv_blob(const void* x_i8, const void* blob, const void* asc
   const int grid = gblob::grid_for(N, K);
   if (!workspace || workspace_bytes < gemv_blob_ws_bytes(grid)) return LQ_ERR_WORKSPACE;
   return run_gemv_blob(static_cast<const int8_t*>(x_i8), static_cast<const uint8_t*>(blob),
-                       static_cast<const float*>(ascale), static_cast<const float*>(s1), single_out(out, N), out_dtype, M,
-                       N, K, static_cast<unsigned long long*>(workspace), as_stream(stream));
+                       static_cast<const float*>(ascale), static_cast<const float*>(s1), single_out(out, N), nullptr,
+                       out_dtype, M, N, K, static_cast<unsigned long long*>(workspace), as_stream(stream));
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -441,8 +453,8 @@ LQ_API int lq_w4a8_gemv_blob_static(const void* x_i8, const void* blob, const vo
   void* p = gblob::static_scratch_for_current_device();
   if (!p) return LQ_ERR_CUDA;
   return run_gemv_blob(static_cast<const int8_t*>(x_i8), static_cast<const uint8_t*>(blob),
-                       static_cast<const float*>(ascale), static_cast<const float*>(s1), single_out(out, N), out_dtype, M,
-                       N, K, static_cast<unsigned long long*>(p), as_stream(stream));
+                       static_cast<const float*>(ascale), static_cast<const float*>(s1), single_out(out, N), nullptr,
+                       out_dtype, M, N, K, static_cast<unsigned long long*>(p), as_stream(stream));
 }
 
 }  // extern "C"

@@ -361,11 +361,16 @@ def gemv_blob(x_i8, blob, ascale, s1, N, K, out_dtype):
     return y
 
 
-def gemm_fused_scatter(x_i8, blob, ascale, s1, out_ptrs, ld_out, col0, N, K, out_dtype):
+def gemm_fused_scatter(x_i8, blob, ascale, s1, out_ptrs, ld_out, col0, N, K, out_dtype, flag_ptrs=None,
+                       flag_index=0, wait_ptr=None, wait_value=0):
     """Decode linear (M <= 16) whose [M, N] output block is stored at column ``col0`` of every matrix in
     ``out_ptrs`` (device addresses of row-major [M, ld_out] buffers of the output dtype: this GPU's and
     its peers' full-width outputs).  The epilogue thereby does the all-gather of an N-sharded layer;
-    the caller orders the ranks afterwards (e.g. a symmetric-memory barrier on the same stream)."""
+    the caller orders the ranks afterwards (e.g. a symmetric-memory barrier on the same stream), or lets
+    the kernels do it: with ``flag_ptrs`` (one uint32 flag array per destination rank) every CTA adds 1 to
+    word ``flag_index`` of each array after its last store, and with ``wait_ptr`` the kernel waits for
+    ``*wait_ptr >= wait_value`` before it reads the tokens (``wait_value`` = ranks x decode_grid() of the
+    launch that produced them)."""
     x_i8 = _i8(x_i8, "x_i8")
     _req(K % 128 == 0 and x_i8.shape[1] == K, "K%128==0 required and x_i8 must be [M,K]")
     _req(int(out_dtype) in _OUT_DTYPES, "out_dtype must be 0 (bf16), 1 (fp16) or 2 (fp32)")
@@ -375,14 +380,24 @@ def gemm_fused_scatter(x_i8, blob, ascale, s1, out_ptrs, ld_out, col0, N, K, out
     _req(1 <= M <= 16, "gemm_fused_scatter is a decode path (1 <= M <= 16)")
     _req(1 <= len(out_ptrs) <= 8 and ld_out >= N and 0 <= col0 <= ld_out - N, "bad destinations")
     arr = (ctypes.c_void_p * len(out_ptrs))(*[int(p) for p in out_ptrs])
+    flags = None
+    if flag_ptrs is not None:
+        _req(len(flag_ptrs) == len(out_ptrs), "one flag array per destination")
+        flags = (ctypes.c_void_p * len(flag_ptrs))(*[int(p) for p in flag_ptrs])
     with _dev_ctx(x_i8):
         ws = _workspace(lib.lq_gemm_workspace_bytes(M, N, K, 0), x_i8.device)
-        rc = lib.lq_w4a8_gemm_fused_scatter(_ptr(x_i8), _ptr(blob), _ptr(ascale), _ptr(s1), arr, len(out_ptrs),
-                                            int(ld_out), int(col0), int(out_dtype), M, N, K, _ptr(ws), ws.numel(),
-                                            _stream())
+        rc = lib.lq_w4a8_gemm_fused_scatter_sync(_ptr(x_i8), _ptr(blob), _ptr(ascale), _ptr(s1), arr, len(out_ptrs),
+                                                 int(ld_out), int(col0), int(out_dtype), M, N, K, flags,
+                                                 int(flag_index), wait_ptr, int(wait_value), _ptr(ws), ws.numel(),
+                                                 _stream())
         if rc != 0:
             ws.zero_()
         check(rc, "gemm_fused_scatter")
+
+
+def decode_grid(M, N, K):
+    """CTAs a decode launch (M <= 16) of this shape uses on the current device."""
+    return lib.lq_decode_grid(int(M), int(N), int(K))
 
 
 def gemm_rowmajor(x_i8, gpack, s_u8, off_a, ascale, s1, N, K, out_dtype, splitk=None):

@@ -271,3 +271,54 @@ def test_scatter_epilogue_writes_every_destination(ops, M):
     for o in outs:
         assert_bits_equal(o[:, COL0:COL0 + N].contiguous(), want, 0, f"scatter M={M}")
         assert bool((o[:, :COL0] == -7.0).all()) and bool((o[:, COL0 + N:] == -7.0).all())
+
+
+@pytest.mark.parametrize("M", [2, 12])
+def test_scatter_epilogue_signals_and_waits(ops, M):
+    """Kernel-side ordering of the gather-by-stores epilogue on one GPU: launch k adds its CTA count to
+    flag word k, launch k+1 waits for that count before it reads its tokens."""
+    from liquidgemm_b200._lib import lib
+    N, K = 640, 2048
+    qw = random_lqq(N, K, 64, seed=60 + M)
+    tq = to_torch_qw(qw)
+    blob = ops.repack_rs_weight(tq).reshape(-1)
+    x, ascale = random_tokens(M, K, seed=M)
+    xd, sd = torch.from_numpy(x).cuda(), torch.from_numpy(ascale).cuda()
+    flags = torch.zeros(8, dtype=torch.int32, device="cuda")
+    grid = ops.decode_grid(M, N, K)
+    assert grid > 0
+    outs = [torch.zeros((M, N), dtype=torch.float16, device="cuda") for _ in range(3)]
+    for k, o in enumerate(outs):
+        ops.gemm_fused_scatter(xd, blob, sd, tq.s1, [o.data_ptr()], N, 0, N, K, 1, flag_ptrs=[flags.data_ptr()],
+                               flag_index=k, wait_ptr=(flags.data_ptr() + 4 * (k - 1)) if k else None,
+                               wait_value=grid if k else 0)
+    torch.cuda.synchronize()
+    want = O.w4a8_matmul(x, ascale, qw)
+    for o in outs:
+        assert_bits_equal(o, want, 1, f"scatter+sync M={M}")
+    assert flags[:3].tolist() == [grid] * 3 and int(flags[3:].abs().sum()) == 0
+    assert lib.lq_poll_status(None) == 0
+
+
+def test_peer_wait_gives_up_and_reports(ops):
+    """A flag that nothing sets: the kernel stops waiting after its limit, records status 303 and still
+    finishes, and the context stays usable (LQ_ERR_TIMEOUT from lq_poll_status, site in the error text)."""
+    from liquidgemm_b200._lib import lib
+    N, K, M = 128, 256, 1
+    qw = random_lqq(N, K, 64, seed=77)
+    tq = to_torch_qw(qw)
+    blob = ops.repack_rs_weight(tq).reshape(-1)
+    x, ascale = random_tokens(M, K, seed=3)
+    xd, sd = torch.from_numpy(x).cuda(), torch.from_numpy(ascale).cuda()
+    flags = torch.zeros(2, dtype=torch.int32, device="cuda")
+    out = torch.zeros((M, N), dtype=torch.float16, device="cuda")
+    ops.gemm_fused_scatter(xd, blob, sd, tq.s1, [out.data_ptr()], N, 0, N, K, 1, wait_ptr=flags.data_ptr(),
+                           wait_value=5)
+    torch.cuda.synchronize()
+    assert lib.lq_poll_status(None) == -6                    # LQ_ERR_TIMEOUT
+    assert b"site 303" in lib.lq_last_cuda_error()
+    assert lib.lq_poll_status(None) == 0                     # reading clears it
+    # the launch itself completed (it went on after the limit), and the next call works normally
+    assert_bits_equal(out, O.w4a8_matmul(x, ascale, qw), 1, "after timeout")
+    got = ops.gemm_fused(xd, blob, sd, tq.s1, N, K, 1)
+    assert_bits_equal(got, O.w4a8_matmul(x, ascale, qw), 1, "next call")
