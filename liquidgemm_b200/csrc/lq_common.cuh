@@ -102,19 +102,26 @@ __device__ __forceinline__ void peer_signal(const PeerSync& p) {
     asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.signal[r] + p.signal_index) : "memory");
 }
 // Bounded: gives up after `limit_ns` and returns false (the caller records a status code and goes on).
+// Polls with relaxed loads and orders the following reads with one acquire fence at the end.
 __device__ __forceinline__ bool peer_wait(const PeerSync& p, unsigned long long limit_ns) {
   if (!p.wait) return true;
   unsigned long long t0 = 0;
+  bool ok = true;
   for (unsigned spins = 0;; ++spins) {
     unsigned v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.wait) : "memory");
-    if (v >= p.wait_value) return true;
+    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.wait) : "memory");
+    if (v >= p.wait_value) break;
     unsigned long long now;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
     if (spins == 0) t0 = now;
-    else if (now - t0 > limit_ns) return false;
-    __nanosleep(100);
+    else if (now - t0 > limit_ns) {
+      ok = false;
+      break;
+    }
+    __nanosleep(200);
   }
+  asm volatile("fence.acquire.sys;" ::: "memory");
+  return ok;
 }
 
 __device__ __forceinline__ void store_out_all(const OutSpec& o, long m, long n, float v, int out_dtype) {

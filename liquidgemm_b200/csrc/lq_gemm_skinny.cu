@@ -381,10 +381,13 @@ w4a8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args) 
       ++seg;
     }
     if (args.sync.n_signal > 0) {
-      // every output store of this CTA, including those into peer memory, is ordered before the flags
-      __threadfence_system();
+      // Every output store of this CTA, including those into peer memory, is ordered before the flags:
+      // the barrier makes the other threads' stores visible to thread 0 (CTA scope), and the release of
+      // its system-scope reduction is cumulative over them.
       asm volatile("bar.sync 1, %0;" ::"n"(kDequant) : "memory");
-      if (d == 0) peer_signal(args.sync);
+      if (d == 0) {
+        peer_signal(args.sync);   // red.release.sys: ordered after everything the barrier made visible
+      }
     }
     if (tracing) {
       args.trace[blockIdx.x * 8 + 3] = (long long)ptx::globaltimer_ns();

@@ -279,10 +279,13 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_blob_kernel(const Args args)
       }
     }
     if (args.sync.n_signal > 0) {
-      // every output store of this CTA, including those into peer memory, is ordered before the flags
-      __threadfence_system();
+      // Every output store of this CTA, including those into peer memory, is ordered before the flags:
+      // the barrier makes the other threads' stores visible to thread 0 (CTA scope), and the release of
+      // its system-scope reduction is cumulative over them.
       consumer_barrier();
-      if (c == 0) peer_signal(args.sync);
+      if (c == 0) {
+        peer_signal(args.sync);   // red.release.sys: ordered after everything the barrier made visible
+      }
     }
     if (tracing) args.trace[blockIdx.x * 4 + 3] = (long long)ptx::globaltimer_ns();
   }
