@@ -468,7 +468,12 @@ int run_skinny_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, c
   a.trace = g_trace;
   if (!a.status) return LQ_ERR_CUDA;
   switch (bn) {
-    case 16: return launch<16, 6>(tx, a, grid, st);
+    case 16: {
+      static const int ns = []() { const char* e = getenv("LQ_SKINNY_NS"); return e ? atoi(e) : 6; }();
+      if (ns == 7) return launch<16, 7>(tx, a, grid, st);
+      if (ns == 4) return launch<16, 4>(tx, a, grid, st);
+      return launch<16, 6>(tx, a, grid, st);
+    }
     case 32: return launch<32, 6>(tx, a, grid, st);
     case 64: return launch<64, 5>(tx, a, grid, st);
     default: return launch<128, 4>(tx, a, grid, st);

@@ -96,6 +96,22 @@ def prepare_layer(layer: torch.nn.Module, group_size: int, w4: bool, gemv: bool)
     del layer.weight
 
 
+def attach_prepacked(layer: torch.nn.Module, entry: dict, device=None) -> None:
+    """Give ``layer`` the buffers of :func:`prepare_layer` (W4 mode) from one entry of a prepacked
+    checkpoint directory (:func:`liquidgemm_b200.checkpoint.load_prepacked`) instead of quantising its
+    bf16 weight: same buffer names, nothing recomputed."""
+    dev = device if device is not None else entry["rs"].device
+    layer.lq_enabled = True
+    layer.lq_N, layer.lq_K = int(entry["N"]), int(entry["K"])
+    layer.register_buffer("lq_s1", entry["s1"].to(dev))
+    layer.register_buffer("lq_rs", entry["rs"].to(dev))
+    layer.register_buffer("lq_s_u8", entry["s_u8"].to(dev))
+    layer.register_buffer("lq_offset_a", entry["offset_a"].to(dev))
+    layer.lq_gemv = layer.lq_K % 128 == 0
+    if hasattr(layer, "weight"):
+        del layer.weight
+
+
 def apply_layer(layer: torch.nn.Module, x: torch.Tensor, bias: Optional[torch.Tensor], group_size: int,
                 w4: bool) -> torch.Tensor:
     """Forward of one linear (reference liquidgemm/vllm_plugin.py:174-206)."""
@@ -159,7 +175,8 @@ if _HAVE_VLLM:
 
         @classmethod
         def get_config_filenames(cls) -> list:
-            return []
+            from .checkpoint import CONFIG_NAME
+            return [CONFIG_NAME]   # written by liquidgemm_b200.checkpoint.save_prepacked
 
         @classmethod
         def from_config(cls, config: dict) -> "LiquidGemmConfig":
