@@ -98,8 +98,10 @@ struct PeerSync {
   unsigned wait_value;
 };
 __device__ __forceinline__ void peer_signal(const PeerSync& p) {
-  for (int r = 0; r < p.n_signal; ++r)
-    asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.signal[r] + p.signal_index) : "memory");
+#pragma unroll
+  for (int r = 0; r < 8; ++r)   // constant indices: see store_out_all
+    if (r < p.n_signal)
+      asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.signal[r] + p.signal_index) : "memory");
 }
 // Bounded: gives up after `limit_ns` and returns false (the caller records a status code and goes on).
 // Polls with relaxed loads and orders the following reads with one acquire fence at the end.
@@ -124,11 +126,25 @@ __device__ __forceinline__ bool peer_wait(const PeerSync& p, unsigned long long 
   return ok;
 }
 
+// Kernel parameters of the gather-by-stores variants.  They travel as a separate kernel parameter that
+// only the multi-destination instantiations have: measured on B200, a launch whose parameters exceed
+// 256 bytes costs about 0.5-1 us more, so the ordinary single-output kernels keep theirs below that.
+struct MultiOut {
+  OutSpec out;
+  PeerSync sync;
+};
+struct NoMultiOut {};
+
 __device__ __forceinline__ void store_out_all(const OutSpec& o, long m, long n, float v, int out_dtype) {
   const size_t idx = (size_t)(m * o.ld + o.col0 + n);
+  // Constant indices only: a run-time index into a kernel parameter makes the compiler copy the whole
+  // parameter block to local memory and read every field from there (measured: +1 us per launch).
   store_out(o.ptr[0], idx, v, out_dtype);
-#pragma unroll 1
-  for (int r = 1; r < o.n; ++r) store_out(o.ptr[r], idx, v, out_dtype);
+  if (o.n > 1) {
+#pragma unroll
+    for (int r = 1; r < 8; ++r)
+      if (r < o.n) store_out(o.ptr[r], idx, v, out_dtype);
+  }
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -28,6 +28,7 @@
 
 #include <cstdlib>
 #include <mutex>
+#include <type_traits>
 
 #ifndef LQ_SKINNY_SETS
 #define LQ_SKINNY_SETS 2
@@ -55,12 +56,11 @@ struct Args {
   const uint8_t* blob;
   const float* ascale;   // [M]
   const float* s1;       // [N]
-  OutSpec out;           // [M, N] block, one or several destinations (int32 mode: the first only)
-  PeerSync sync;         // optional cross-GPU ordering around the gather-by-stores epilogue
+  void* out;             // [M, N] (single-destination kernels; the others get a MultiOut parameter)
   unsigned long long* slots;   // [grid][BN][128] packed (k-tile count, biased partial sum), zero between launches
   int* status;
   int out_mode;          // LQ_DT_* or kOutI32
-  int M, N, K, kt_total, n_tiles, fixed_split;
+  int M, N, K, fixed_split;
   long long* trace;      // pipeline studies: [grid][4] globaltimer stamps, or null
   int debug_skip;        // pipeline studies only (results become wrong): 1 no tcgen05.st, 2 no MMA, 4 no dequant ALU
 };
@@ -85,9 +85,11 @@ struct Cfg {
 };
 
 
-template <int BN, int NS>
+template <int BN, int NS, bool MULTI>
 __global__ void __launch_bounds__(kThreads, 2)
-w4a8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args) {
+w4a8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args,
+                   const std::conditional_t<MULTI, MultiOut, NoMultiOut> multi) {
+  const int kt_total = args.K >> 7;
   using C = Cfg<BN, NS>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -120,7 +122,7 @@ w4a8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args) 
   __syncthreads();
   allow_dependents();   // the next kernel of the stream may start prefetching its weights
 
-  SegmentWalk walk(SchedArgs{args.kt_total, args.n_tiles, 1, args.fixed_split}, blockIdx.x, gridDim.x);
+  SegmentWalk walk(SchedArgs{kt_total, (args.N + 127) >> 7, 1, args.fixed_split}, blockIdx.x, gridDim.x);
   Segment sg;
 
   if (warp == 0) {
@@ -138,14 +140,16 @@ w4a8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args) 
       bool dependency_met = false;
       auto meet_dependency = [&]() {
         dependency_wait();
-        if (!peer_wait(args.sync, kWaitLimitNs)) atomicExch(args.status, 409);   // tokens gathered from peers
+        if constexpr (MULTI) {
+          if (!peer_wait(multi.sync, kWaitLimitNs)) atomicExch(args.status, 409);   // tokens gathered from peers
+        }
         dependency_met = true;
         const int n = issued < NS ? issued : NS;
         for (int j = 0; j < n; ++j)
           ptx::tensor_load_2d(xs + j * C::kXStage, &tmap_x, early_kt[j] * 128, 0, bar_full + 8 * j);
       };
       while (ok && walk.next(sg)) {
-        const uint8_t* src = args.blob + ((size_t)sg.tile * args.kt_total + sg.kb) * kTileBytes;
+        const uint8_t* src = args.blob + ((size_t)sg.tile * kt_total + sg.kb) * kTileBytes;
         for (int kt = sg.kb; kt < sg.ke; ++kt, src += kTileBytes) {
           if (issued == NS) meet_dependency();
           const long long p0 = args.trace ? clock64() : 0;
@@ -349,11 +353,11 @@ w4a8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args) 
           }
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            const bool done = (c0 + j < args.M) && ((long long)(old[j] >> 40) + nk == (long long)args.kt_total);
+            const bool done = (c0 + j < args.M) && ((long long)(old[j] >> 40) + nk == (long long)kt_total);
             if (done) {
               __stcg(slot + (c0 + j) * 128 + row, 0ull);
               v[j] = (int)((long long)(old[j] & ((1ull << 40) - 1)) + (long long)v[j] + (nk << 21) -
-                           ((long long)args.kt_total << 21));
+                           ((long long)kt_total << 21));
             } else {
               sc[j] = __int_as_float(0x7fc00000);   // marks "not finished here"
             }
@@ -362,8 +366,13 @@ w4a8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args) 
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           if (c0 + j < args.M && (sg.whole || sc[j] == sc[j])) {
-            if (scaled) store_out_all(args.out, c0 + j, n, lqq_scale(v[j], sc[j], w_scale), args.out_mode);
-            else reinterpret_cast<int32_t*>(args.out.ptr[0])[(size_t)(c0 + j) * args.out.ld + args.out.col0 + n] = v[j];
+            if (!scaled) {
+              reinterpret_cast<int32_t*>(args.out)[(size_t)(c0 + j) * args.N + n] = v[j];
+            } else {
+              const float y = lqq_scale(v[j], sc[j], w_scale);
+              if constexpr (MULTI) store_out_all(multi.out, c0 + j, n, y, args.out_mode);
+              else store_out(args.out, (size_t)(c0 + j) * args.N + n, y, args.out_mode);
+            }
           }
         }
       }
@@ -380,13 +389,13 @@ w4a8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args) 
       }
       ++seg;
     }
-    if (args.sync.n_signal > 0) {
+    if constexpr (MULTI) {
       // Every output store of this CTA, including those into peer memory, is ordered before the flags:
       // the barrier makes the other threads' stores visible to thread 0 (CTA scope), and the release of
       // its system-scope reduction is cumulative over them.
       asm volatile("bar.sync 1, %0;" ::"n"(kDequant) : "memory");
       if (d == 0) {
-        peer_signal(args.sync);   // red.release.sys: ordered after everything the barrier made visible
+        peer_signal(multi.sync);   // red.release.sys: ordered after everything the barrier made visible
       }
     }
     if (tracing) {
@@ -400,10 +409,10 @@ w4a8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args) 
   __syncthreads();
 }
 
-template <int BN, int NS>
-static int launch(const CUtensorMap& tx, const Args& a, int grid, cudaStream_t st) {
+template <int BN, int NS, bool MULTI>
+static int launch(const CUtensorMap& tx, const Args& a, const MultiOut* multi, int grid, cudaStream_t st) {
   using C = Cfg<BN, NS>;
-  auto kern = &w4a8_skinny_kernel<BN, NS>;
+  auto kern = &w4a8_skinny_kernel<BN, NS, MULTI>;
   static std::once_flag once[64];
   int dev = 0;
   cudaGetDevice(&dev);
@@ -411,7 +420,10 @@ static int launch(const CUtensorMap& tx, const Args& a, int grid, cudaStream_t s
   std::call_once(once[dev & 63], [&]() {
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
   });
-  if (e == cudaSuccess) e = launch_overlapped(kern, dim3(grid), dim3(kThreads), (size_t)C::kSmemBytes, st, tx, a);
+  if (e == cudaSuccess) {
+    if constexpr (MULTI) e = launch_overlapped(kern, dim3(grid), dim3(kThreads), (size_t)C::kSmemBytes, st, tx, a, *multi);
+    else e = launch_overlapped(kern, dim3(grid), dim3(kThreads), (size_t)C::kSmemBytes, st, tx, a, NoMultiOut{});
+  }
   if (e != cudaSuccess) {
     record_cuda_error(e, "w4a8_skinny_kernel launch");
     return LQ_ERR_CUDA;
@@ -453,31 +465,33 @@ int run_skinny_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, c
   a.blob = blob;
   a.ascale = ascale;
   a.s1 = s1;
-  a.out = out;
-  a.sync = sync ? *sync : PeerSync{};
+  // one plain destination with nothing to signal or wait for: the small-parameter kernels
+  const bool multi = out.n != 1 || out.ld != N || out.col0 != 0 || (sync && (sync->n_signal > 0 || sync->wait));
+  if (multi && out_mode == kOutI32) return LQ_ERR_BAD_ARG;
+  a.out = out.ptr[0];
   a.slots = static_cast<unsigned long long*>(ws);
   a.status = status_word();
   a.out_mode = out_mode;
   a.M = M;
   a.N = N;
   a.K = K;
-  a.kt_total = K / 128;
-  a.n_tiles = (N + 127) / 128;
   a.fixed_split = plan.fixed_split;
   a.debug_skip = g_debug_skip;
   a.trace = g_trace;
   if (!a.status) return LQ_ERR_CUDA;
-  switch (bn) {
-    case 16: {
-      static const int ns = []() { const char* e = getenv("LQ_SKINNY_NS"); return e ? atoi(e) : 6; }();
-      if (ns == 7) return launch<16, 7>(tx, a, grid, st);
-      if (ns == 4) return launch<16, 4>(tx, a, grid, st);
-      return launch<16, 6>(tx, a, grid, st);
+  if (!multi) {
+    switch (bn) {
+      case 16: return launch<16, 6, false>(tx, a, nullptr, grid, st);
+      case 32: return launch<32, 6, false>(tx, a, nullptr, grid, st);
+      case 64: return launch<64, 5, false>(tx, a, nullptr, grid, st);
+      default: return launch<128, 4, false>(tx, a, nullptr, grid, st);
     }
-    case 32: return launch<32, 6>(tx, a, grid, st);
-    case 64: return launch<64, 5>(tx, a, grid, st);
-    default: return launch<128, 4>(tx, a, grid, st);
   }
+  MultiOut mo;
+  mo.out = out;
+  mo.sync = sync ? *sync : PeerSync{};
+  if (bn != 16) return LQ_ERR_SHAPE;   // the gather-by-stores variant is a decode path (M <= 16)
+  return launch<16, 6, true>(tx, a, &mo, grid, st);
 }
 
 }  // namespace lq

@@ -19,7 +19,9 @@
 
 #include <stdint.h>
 
+#include <cstdlib>
 #include <mutex>
+#include <type_traits>
 
 #include "lq_common.cuh"
 #include "lq_sched.cuh"
@@ -38,12 +40,11 @@ struct Args {
   const int8_t* x;       // [M, K]
   const float* ascale;   // [M]
   const float* s1;       // [N]
-  OutSpec out;           // [M, N] block, one or several destinations
-  PeerSync sync;         // optional cross-GPU ordering around the gather-by-stores epilogue
+  void* out;             // [M, N] (single-destination kernels; the others get a MultiOut parameter)
   unsigned long long* slots;   // [grid][MT][128] packed (k-tile count, biased partial sum), zero between launches
   int* status;
   int out_dtype;
-  int M, N, K, kt_total, n_tiles, fixed_split;
+  int M, N, K, fixed_split;
   long long* trace;      // pipeline studies: [grid][4] globaltimer stamps, or null
 };
 
@@ -68,8 +69,10 @@ __device__ __forceinline__ int dp4a_s8(uint32_t w, uint32_t x, int acc) {
   return d;
 }
 
-template <int MT, int NS>
-__global__ void __launch_bounds__(kThreads, 2) gemv_blob_kernel(const Args args) {
+template <int MT, int NS, bool MULTI>
+__global__ void __launch_bounds__(kThreads, 2)
+gemv_blob_kernel(const Args args, const std::conditional_t<MULTI, MultiOut, NoMultiOut> multi) {
+  const int kt_total = args.K >> 7;
   using C = Cfg<MT, NS>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -97,8 +100,8 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_blob_kernel(const Args args)
   allow_dependents();   // the next kernel of the stream may start prefetching its weights
 
   SchedArgs sa;
-  sa.kt_total = args.kt_total;
-  sa.n_tiles = args.n_tiles;
+  sa.kt_total = kt_total;
+  sa.n_tiles = (args.N + 127) >> 7;
   sa.m_tiles = 1;
   sa.fixed_split = args.fixed_split;
   SegmentWalk walk(sa, blockIdx.x, gridDim.x);
@@ -118,7 +121,9 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_blob_kernel(const Args args)
       bool dependency_met = false;
       auto meet_dependency = [&]() {
         dependency_wait();
-        if (!peer_wait(args.sync, kWaitLimitNs)) atomicExch(args.status, 303);   // tokens gathered from peers
+        if constexpr (MULTI) {
+          if (!peer_wait(multi.sync, kWaitLimitNs)) atomicExch(args.status, 303);   // tokens gathered from peers
+        }
         dependency_met = true;
         const int n = issued < NS ? issued : NS;
         for (int j = 0; j < n; ++j) {
@@ -128,7 +133,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_blob_kernel(const Args args)
         }
       };
       while (ok && walk.next(sg)) {
-        const uint8_t* src = args.blob + ((size_t)sg.tile * args.kt_total + sg.kb) * kTileBytes;
+        const uint8_t* src = args.blob + ((size_t)sg.tile * kt_total + sg.kb) * kTileBytes;
         for (int kt = sg.kb; kt < sg.ke; ++kt, src += kTileBytes) {
           if (issued == NS) meet_dependency();
           if (!ptx::mbar_wait_bounded(bar_empty + 8 * ring.s, ring.ph ^ 1u, kWaitLimitNs)) {
@@ -177,6 +182,10 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_blob_kernel(const Args args)
       args.trace[(size_t)gridDim.x * 4 + blockIdx.x] = smid;   // SM ids behind the stamps
     }
     bool first = true;
+    auto emit = [&](long m, long n, float v) {
+      if constexpr (MULTI) store_out_all(multi.out, m, n, v, args.out_dtype);
+      else store_out(args.out, (size_t)m * args.N + n, v, args.out_dtype);
+    };
     float a_scale[MT];   // token scales: read once, they are needed right after the last tile
 #pragma unroll
     for (int m = 0; m < MT; ++m) a_scale[m] = (m < M) ? __ldg(args.ascale + m) : 0.f;
@@ -246,7 +255,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_blob_kernel(const Args args)
         if (mine) {
 #pragma unroll
           for (int m = 0; m < MT; ++m)
-            if (m < M) store_out_all(args.out, m, n, lqq_scale(acc[m], a_scale[m], w_scale), args.out_dtype);
+            if (m < M) emit(m, n, lqq_scale(acc[m], a_scale[m], w_scale));
         }
         consumer_barrier();   // `red` may be rewritten by the next segment
       } else {
@@ -267,24 +276,24 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_blob_kernel(const Args args)
           }
 #pragma unroll
           for (int m = 0; m < MT; ++m) {
-            if (m < M && (long long)(old[m] >> 40) + nk == (long long)args.kt_total) {
+            if (m < M && (long long)(old[m] >> 40) + nk == (long long)kt_total) {
               const long long total = (long long)(old[m] & ((1ull << 40) - 1)) + (long long)acc[m] + (nk << 21) -
-                                      ((long long)args.kt_total << 21);
+                                      ((long long)kt_total << 21);
               __stcg(slot + m * 128 + row, 0ull);
-              store_out_all(args.out, m, n, lqq_scale((int)total, a_scale[m], w_scale), args.out_dtype);
+              emit(m, n, lqq_scale((int)total, a_scale[m], w_scale));
             }
           }
         }
         consumer_barrier();   // `red` may be rewritten by the next segment
       }
     }
-    if (args.sync.n_signal > 0) {
+    if constexpr (MULTI) {
       // Every output store of this CTA, including those into peer memory, is ordered before the flags:
       // the barrier makes the other threads' stores visible to thread 0 (CTA scope), and the release of
       // its system-scope reduction is cumulative over them.
       consumer_barrier();
       if (c == 0) {
-        peer_signal(args.sync);   // red.release.sys: ordered after everything the barrier made visible
+        peer_signal(multi.sync);   // red.release.sys: ordered after everything the barrier made visible
       }
     }
     if (tracing) args.trace[blockIdx.x * 4 + 3] = (long long)ptx::globaltimer_ns();
@@ -292,10 +301,10 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_blob_kernel(const Args args)
   __syncthreads();
 }
 
-template <int MT, int NS>
-static int launch(const Args& a, int grid, cudaStream_t st) {
+template <int MT, int NS, bool MULTI>
+static int launch(const Args& a, const MultiOut* multi, int grid, cudaStream_t st) {
   using C = Cfg<MT, NS>;
-  auto kern = &gemv_blob_kernel<MT, NS>;
+  auto kern = &gemv_blob_kernel<MT, NS, MULTI>;
   static std::once_flag once[64];
   int dev = 0;
   cudaGetDevice(&dev);
@@ -307,7 +316,8 @@ static int launch(const Args& a, int grid, cudaStream_t st) {
     record_cuda_error(e, "cudaFuncSetAttribute(gemv_blob_kernel)");
     return LQ_ERR_CUDA;
   }
-  e = launch_overlapped(kern, dim3(grid), dim3(kThreads), (size_t)C::kSmemBytes, st, a);
+  if constexpr (MULTI) e = launch_overlapped(kern, dim3(grid), dim3(kThreads), (size_t)C::kSmemBytes, st, a, *multi);
+  else e = launch_overlapped(kern, dim3(grid), dim3(kThreads), (size_t)C::kSmemBytes, st, a, NoMultiOut{});
   if (e != cudaSuccess) {
     record_cuda_error(e, "gemv_blob_kernel launch");
     return LQ_ERR_CUDA;
@@ -347,24 +357,32 @@ int run_gemv_blob(const int8_t* x, const uint8_t* blob, const float* ascale, con
   a.x = x;
   a.ascale = ascale;
   a.s1 = s1;
-  a.out = out;
-  a.sync = sync ? *sync : PeerSync{};
+  // one plain destination with nothing to signal or wait for: the small-parameter kernels
+  const bool multi = out.n != 1 || out.ld != N || out.col0 != 0 || (sync && (sync->n_signal > 0 || sync->wait));
+  a.out = out.ptr[0];
   a.slots = slots;
   a.status = status_word();
   a.out_dtype = out_dtype;
   a.M = M;
   a.N = N;
   a.K = K;
-  a.kt_total = K / 128;
-  a.n_tiles = (N + 127) / 128;
   a.fixed_split = plan_for(N, K).fixed_split;
   a.trace = g_trace;
   if (!a.status) return LQ_ERR_CUDA;
   const int grid = grid_for(N, K);
-  if (M <= 1) return launch<1, 8>(a, grid, st);
-  if (M <= 2) return launch<2, 8>(a, grid, st);
-  if (M <= 4) return launch<4, 8>(a, grid, st);
-  return launch<8, 7>(a, grid, st);
+  if (!multi) {
+    if (M <= 1) return launch<1, 8, false>(a, nullptr, grid, st);
+    if (M <= 2) return launch<2, 8, false>(a, nullptr, grid, st);
+    if (M <= 4) return launch<4, 8, false>(a, nullptr, grid, st);
+    return launch<8, 7, false>(a, nullptr, grid, st);
+  }
+  MultiOut mo;
+  mo.out = out;
+  mo.sync = sync ? *sync : PeerSync{};
+  if (M <= 1) return launch<1, 8, true>(a, &mo, grid, st);
+  if (M <= 2) return launch<2, 8, true>(a, &mo, grid, st);
+  if (M <= 4) return launch<4, 8, true>(a, &mo, grid, st);
+  return launch<8, 7, true>(a, &mo, grid, st);
 }
 
 int run_gemv_blob_ws(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1,
