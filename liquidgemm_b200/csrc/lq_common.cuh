@@ -127,8 +127,9 @@ __device__ __forceinline__ bool peer_wait(const PeerSync& p, unsigned long long 
 }
 
 // Kernel parameters of the gather-by-stores variants.  They travel as a separate kernel parameter that
-// only the multi-destination instantiations have: measured on B200, a launch whose parameters exceed
-// 256 bytes costs about 0.5-1 us more, so the ordinary single-output kernels keep theirs below that.
+// only the multi-destination instantiations have: measured on B200, the programmatically serialised
+// decode launches cost 0.5-1 us more once their parameters exceed 256 bytes, so the ordinary
+// single-output kernels keep theirs below that.
 struct MultiOut {
   OutSpec out;
   PeerSync sync;

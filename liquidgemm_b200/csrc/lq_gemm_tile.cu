@@ -61,8 +61,9 @@ struct TcCfg {
 
 template <int BN, int NS, int NT, bool W4>
 __global__ void __launch_bounds__(kThreads, 1)
-w4a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
-               const GemmArgs args) {
+w4a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs args) {
+  // Only the blob-fed form exists, so the kernel takes one tensor map (the tokens).
+  static_assert(W4, "the tile kernel reads its weights from the tile blob");
   using Cfg = TcCfg<BN, NS, NT, W4>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -101,7 +102,6 @@ w4a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     ptx::mbar_init(bar_acc, 1);
     ptx::fence_mbar_init();
     ptx::prefetch_tensormap(&tmap_x);
-    if (!W4) ptx::prefetch_tensormap(&tmap_w);
   }
   if (warp == 1) {
     ptx::tmem_alloc(tmem_slot, Cfg::kTmemCols);
@@ -133,12 +133,8 @@ w4a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         }
         ptx::mbar_expect_tx(bar_full + 8 * s, kTx);
         const int kt = kt_begin + i;
-        if (W4) {
-          const uint8_t* src = args.blob + ((size_t)nt * args.kt_total + kt) * kTileBytes;
-          ptx::bulk_load(ws + s * Cfg::kWStage, src, kTileBytes, bar_full + 8 * s);
-        } else {
-          ptx::tensor_load_2d(ws + s * Cfg::kWStage, &tmap_w, kt * 128, nt * 128, bar_full + 8 * s);
-        }
+        const uint8_t* src = args.blob + ((size_t)nt * args.kt_total + kt) * kTileBytes;
+        ptx::bulk_load(ws + s * Cfg::kWStage, src, kTileBytes, bar_full + 8 * s);
         ptx::tensor_load_2d(xs + s * Cfg::kXStage, &tmap_x, kt * 128, m0, bar_full + 8 * s);
         ++issued;
       }
@@ -274,7 +270,7 @@ w4a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
 }
 
 template <int BN, int NS, int NT, bool W4>
-static int launch_cfg(const CUtensorMap& tx, const CUtensorMap& tw, const GemmArgs& a, int splits, cudaStream_t st) {
+static int launch_cfg(const CUtensorMap& tx, const GemmArgs& a, int splits, cudaStream_t st) {
   using Cfg = TcCfg<BN, NS, NT, W4>;
   auto kern = &w4a8_tile_kernel<BN, NS, NT, W4>;
   static std::once_flag once[64];
@@ -289,7 +285,7 @@ static int launch_cfg(const CUtensorMap& tx, const CUtensorMap& tw, const GemmAr
     return LQ_ERR_CUDA;
   }
   dim3 grid((a.N + 127) / 128, (a.M + BN - 1) / BN, splits);
-  kern<<<grid, kThreads, Cfg::kSmemBytes, st>>>(tx, tw, a);
+  kern<<<grid, kThreads, Cfg::kSmemBytes, st>>>(tx, a);
   return check_launch("w4a8_tile_kernel");
 }
 
@@ -338,10 +334,10 @@ int run_tile_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, con
   a.kt_total = K / 128;
   if (!a.status) return LQ_ERR_CUDA;
   switch (bn) {
-    case 16: rc = launch_cfg<16, 8, 4, true>(tx, tx, a, splits, st); break;
-    case 32: rc = launch_cfg<32, 8, 4, true>(tx, tx, a, splits, st); break;
-    case 64: rc = launch_cfg<64, 6, 4, true>(tx, tx, a, splits, st); break;
-    default: rc = launch_cfg<128, 4, 4, true>(tx, tx, a, splits, st); break;
+    case 16: rc = launch_cfg<16, 8, 4, true>(tx, a, splits, st); break;
+    case 32: rc = launch_cfg<32, 8, 4, true>(tx, a, splits, st); break;
+    case 64: rc = launch_cfg<64, 6, 4, true>(tx, a, splits, st); break;
+    default: rc = launch_cfg<128, 4, 4, true>(tx, a, splits, st); break;
   }
   if (rc || splits <= 1) return rc;
   return launch_finish(static_cast<const int32_t*>(ws), ascale, s1, out, out_mode, splits, M, N, st);
