@@ -195,20 +195,24 @@ LQ_API int lq_repack_tiles(const uint8_t* src, int src_layout, const uint8_t* s_
                     void* stream);
 
 /* Scheduling of the tensor-core GEMM, selected by the `splitk` argument of the calls below.
- *   M <= 128 (decode tiles): one tile per CTA, two CTAs per SM; every tile is cut into S k-ranges
- *            whose int32 partial planes one finish kernel reduces, scales and casts -- the split-K
- *            design of the reference (csrc/liquid_gemm/w4a8_wgmma.cu:39-56, 523-534).
- *            splitk = 0 picks S from the SM count, splitk = S >= 1 forces it (clamped to K/128).
- *   M  > 128 (prefill): one persistent CTA per SM.  splitk = 0: stream-K, the k-steps of all tiles
- *            are dealt out in equal contiguous ranges and tiles cut by a range boundary are
- *            reduced with int32 atomics; splitk = 1: whole tiles only; S > 1: fixed split.
+ *   splitk = 0 (automatic):
+ *     M <= 4   streaming dp4a GEMV over the tile blob (scaled outputs; int32 output uses the next);
+ *     M <= 16  single-launch streaming tensor-core kernel, stream-K over two CTAs per SM, tiles cut
+ *              between CTAs joined with one 64-bit atomic per output element;
+ *     larger   tile kernel: one 128-channel x up-to-128-token tile per CTA, two CTAs per SM, every
+ *              tile cut into S k-ranges (S from the SM count) whose int32 partial planes one finish
+ *              kernel reduces, scales and casts -- the split-K design of the reference
+ *              (csrc/liquid_gemm/w4a8_wgmma.cu:39-56, 523-534); S = 1 fuses the epilogue;
+ *     problems of 4096 or more 128 x 128 output tiles: the persistent stream-K kernel.
+ *   splitk = S >= 1: M <= 128: the tile kernel with exactly S k-ranges (clamped to K/128);
+ *              M > 128: the persistent kernel with whole tiles (1) or a fixed split (S > 1).
  *   splitk = -1 forces the persistent stream-K kernel for any M.
- * Partial sums are int32, so every setting gives bit-identical results.
+ * Partial sums are integers, so every setting gives bit-identical results.
  * lq_gemm_pick_splitk maps LIQUIDGEMM_SPLITK (`env_override`, 0 = unset) to that argument: like
  * the reference the override only applies to M <= 128 and is clamped to K/128; otherwise 0. */
 LQ_API int lq_gemm_pick_splitk(int M, int N, int K, int env_override);
 /* Workspace bytes for (M,N,K,splitk) and its kind: 0 = none, 1 = scratch (any contents; the
- * decode-tile planes), 2 = reduction buffer of the persistent kernel, which must be ALL ZERO when
+ * tile kernel's planes), 2 = reduction buffer of the streaming and persistent kernels, which must be ALL ZERO when
  * a call starts and is all zero again when its kernel ends (the kernel cleans up after itself), so
  * one zero-filled buffer serves any number of successive calls on a stream; calls that overlap on
  * the GPU need separate buffers, and after a LQ_ERR_TIMEOUT the caller must clear it. */

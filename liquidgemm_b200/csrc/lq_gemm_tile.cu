@@ -1,4 +1,4 @@
-// Decode-tile W4A8 GEMM (17 <= M <= 128): one 128-channel x BN-token tile per CTA, two CTAs per SM.
+// Tile W4A8 GEMM (M >= 17; up to 128 tokens per tile): one 128-channel x BN-token tile per CTA, two CTAs per SM.
 //
 // The persistent stream-K kernel keeps one CTA per SM; for a handful of k-steps per CTA its
 // single MMA-issuing thread and the cross-CTA reduction tail dominate.  With small token tiles the
@@ -312,7 +312,7 @@ size_t tile_workspace_bytes(int M, int N, int splits) {
   return splits <= 1 ? 0 : (size_t)splits * (size_t)M * (size_t)N * sizeof(int32_t);
 }
 
-// out_mode: LQ_DT_* or 3 (raw int32).  M <= 128.  `ws` holds `splits` int32 planes (need not be zeroed).
+// out_mode: LQ_DT_* or 3 (raw int32).  Any M.  `ws` holds `splits` int32 planes (need not be zeroed).
 int run_tile_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, void* out, int out_mode,
                   int M, int N, int K, int splits, void* ws, size_t ws_bytes, cudaStream_t st) {
   using namespace tile;
