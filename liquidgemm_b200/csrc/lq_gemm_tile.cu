@@ -11,7 +11,9 @@
 //
 // Per CTA: warp 0 = TMA producer (8704-byte bulk copy of the weight tile + BN x 128 token box per
 // k-step), warp 1 = TMEM allocation and tcgen05.mma issue (A operand from tensor memory), warps
-// 2..5 = dequant (thread r owns weight row r -> TMEM lane r) and epilogue.  All waits are bounded.
+// 2..5 and 6..9 = two dequant sets taking alternate k-steps (thread r of a set owns weight row r ->
+// TMEM lane r; one set alone needs ~800 cycles per k-step, more than the MMAs of two CTAs), then
+// epilogue, the sets sharing the accumulator's columns.  All waits are bounded.
 #include <cuda.h>
 
 #include <mutex>
@@ -30,7 +32,8 @@ namespace tile {
 
 constexpr int kTileBytes = 8704;
 constexpr int kI8TileBytes = 16384;
-constexpr int kThreads = 192;
+constexpr int kSets = 2;                  // dequant sets of 128 threads, taking k-tiles alternately
+constexpr int kThreads = 64 + 128 * kSets;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 constexpr int kOutI32 = 3;
 
@@ -108,7 +111,7 @@ w4a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs args
     ptx::tmem_relinquish();
   }
   if (warp >= 2 && args.out_mode != kOutI32) {
-    for (int j = threadIdx.x - 64; j < BN; j += 128) ascale_s[j] = (m0 + j < args.M) ? args.ascale[m0 + j] : 0.f;
+    for (int j = threadIdx.x - 64; j < BN; j += 128 * kSets) ascale_s[j] = (m0 + j < args.M) ? args.ascale[m0 + j] : 0.f;
   }
   ptx::tc_fence_before();
   __syncthreads();
@@ -182,9 +185,10 @@ w4a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs args
     const int quad = warp & 3;               // TMEM lane quadrant this warp may access
     const int row = quad * 32 + lane;        // weight row inside the tile == TMEM lane
     const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
+    const int set = (threadIdx.x - 64) >> 7;
     bool ok = true;
     if (W4) {
-      for (int i = 0; i < nk; ++i) {
+      for (int i = set; i < nk; i += kSets) {
         const int s = i % NS;
         const uint32_t ph = (uint32_t)(i / NS) & 1u;
         const int t = i % NT;
@@ -240,8 +244,8 @@ w4a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs args
       const float w_scale = (n_ok && args.out_mode != kOutI32) ? args.s1[n] : 0.f;
       int32_t* plane = reinterpret_cast<int32_t*>(args.out) + (size_t)z * args.M * args.N;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 16) {
-        if (m0 + c0 >= args.M) break;  // uniform over the CTA
+      for (int c0 = 16 * set; c0 < BN; c0 += 16 * kSets) {   // the sets share the accumulator's columns
+        if (m0 + c0 >= args.M) break;  // uniform over the warp
         int v[16];
         ptx::tmem_ld16(tmem_acc + lane_addr + c0, v);
         ptx::tc_wait_ld();
