@@ -202,8 +202,7 @@ LQ_API int lq_repack_tiles(const uint8_t* src, int src_layout, const uint8_t* s_
  *     larger   tile kernel: one 128-channel x up-to-128-token tile per CTA, two CTAs per SM, every
  *              tile cut into S k-ranges (S from the SM count) whose int32 partial planes one finish
  *              kernel reduces, scales and casts -- the split-K design of the reference
- *              (csrc/liquid_gemm/w4a8_wgmma.cu:39-56, 523-534); S = 1 fuses the epilogue;
- *     problems of 4096 or more 128 x 128 output tiles: the persistent stream-K kernel.
+ *              (csrc/liquid_gemm/w4a8_wgmma.cu:39-56, 523-534); S = 1 fuses the epilogue.
  *   splitk = S >= 1: M <= 128: the tile kernel with exactly S k-ranges (clamped to K/128);
  *              M > 128: the persistent kernel with whole tiles (1) or a fixed split (S > 1).
  *   splitk = -1 forces the persistent stream-K kernel for any M.

@@ -43,7 +43,6 @@ def test_size_helpers_without_gpu():
     assert lib.lq_gemm_workspace_bytes(64, 4096, 14336, 4) == 4 * 64 * 4096 * 4
     assert lib.lq_gemm_workspace_kind(64, 4096, 14336, 4) == 1
     assert lib.lq_gemm_workspace_kind(2048, 4096, 14336, 0) == 0     # tile kernel, one k-range: no workspace
-    assert lib.lq_gemm_workspace_kind(8192, 28672, 4096, 0) == 2     # 4096+ tiles: persistent stream-K
     assert lib.lq_gemm_workspace_kind(2048, 4096, 14336, -1) == 2
     assert lib.lq_gemm_workspace_kind(8, 4096, 14336, 0) == 2        # streaming decode kernel
     assert lib.lq_gemm_workspace_kind(2048, 4096, 14336, 1) == 0
