@@ -279,10 +279,25 @@ def run_extras(world, rank, local_rank, peaks):
     return out
 
 
+def run_one(name, M, reps=3):
+    """One (shape, M) point of the sweep: microseconds, TOPS, algorithmic GB/s (for profiling a single kernel)."""
+    N, K = SHAPES[name]
+    C = max(3, -(-400_000_000 // (N * K // 2)))
+    layers = [device_lqq(N, K, seed=31 * c + 1, want_gp=False) for c in range(C)]
+    x, sc = device_tokens(M, K, seed=M)
+    t = graph_time_us(lambda i: linear_call(layers[i % C], x, sc, M), C, reps)
+    return {"shape": name, "M": M, "us": round(t, 2), "TOPS": round(2.0 * M * N * K / t / 1e6, 1),
+            "alg_GBps": round(algorithmic_bytes(M, N, K) / t / 1e3, 1)}
+
+
 if __name__ == "__main__":
-    # ``python -m liquidgemm_b200.benchlib <hbm_gbs>``: single-GPU extras as one JSON object on stdout.
-    # bench.py runs this in a child process so that the headline numbers never depend on it.
+    # ``python -m liquidgemm_b200.benchlib <hbm_gbs>``: single-GPU extras as one JSON object on stdout
+    # (bench.py runs this in a child process so that the headline numbers never depend on it);
+    # ``python -m liquidgemm_b200.benchlib one <qkv|gate_up|down> <M>``: a single point of the sweep.
     import json
     import sys
     torch.cuda.set_device(0)
+    if len(sys.argv) > 1 and sys.argv[1] == "one":
+        print(json.dumps(run_one(sys.argv[2], int(sys.argv[3]))))
+        sys.exit(0)
     print(json.dumps(run_extras(1, 0, 0, {"hbm_gbs": float(sys.argv[1]) if len(sys.argv) > 1 else 6451.8})))
