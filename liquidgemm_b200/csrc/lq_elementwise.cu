@@ -128,6 +128,11 @@ __global__ void __launch_bounds__(256)
 finish_kernel(const int32_t* __restrict__ acc, const float* __restrict__ ascale,
               const float* __restrict__ s1, void* __restrict__ y, int out_dtype, int planes, int M,
               int N, bool vec) {
+  // Launched with programmatic stream serialisation behind the kernel that writes the planes: let the
+  // kernel after this one start (it prefetches weights, and waits for this grid before it touches
+  // tokens, planes or outputs), then wait for the planes to be complete.
+  allow_dependents();
+  dependency_wait();
   const long total = (long)M * N;
   const long quads = total >> 2;
   if (vec) {
@@ -261,7 +266,12 @@ int launch_finish(const int32_t* acc, const float* ascale, const float* s1, void
                                reinterpret_cast<uintptr_t>(s1);
   const bool vec = (N % 4 == 0) && (align_bits % 16 == 0);
   const long items = vec ? (total >> 2) : total;
-  finish_kernel<<<grid_for(items, 256, 8), 256, 0, st>>>(acc, ascale, s1, y, out_dtype, planes, M, N, vec);
+  cudaError_t e = launch_overlapped(finish_kernel, dim3(grid_for(items, 256, 8)), dim3(256), (size_t)0, st, acc, ascale,
+                                    s1, y, out_dtype, planes, M, N, vec);
+  if (e != cudaSuccess) {
+    record_cuda_error(e, "finish_kernel launch");
+    return LQ_ERR_CUDA;
+  }
   return check_launch("finish_kernel");
 }
 

@@ -88,7 +88,6 @@ w4a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs args
   const uint32_t tmem_slot = bar_acc + 8;
   uint8_t* gen = smem + (bars - base);
   volatile uint32_t* tmem_slot_p = reinterpret_cast<volatile uint32_t*>(gen + (2 * NS + 2 * NT + 1) * 8);
-  float* ascale_s = reinterpret_cast<float*>(gen + Cfg::kBarBytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nt = blockIdx.x, mt = blockIdx.y, z = blockIdx.z, splits = gridDim.z;
@@ -114,12 +113,10 @@ w4a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs args
     ptx::tmem_alloc(tmem_slot, Cfg::kTmemCols);
     ptx::tmem_relinquish();
   }
-  if (warp >= 2 && args.out_mode != kOutI32) {
-    for (int j = threadIdx.x - 64; j < BN; j += 128 * kSets) ascale_s[j] = (m0 + j < args.M) ? args.ascale[m0 + j] : 0.f;
-  }
   ptx::tc_fence_before();
   __syncthreads();
   ptx::tc_fence_after();
+  allow_dependents();   // the next kernel of the stream may start prefetching its weights
   const uint32_t tmem_base = *tmem_slot_p;
   const uint32_t tmem_acc = tmem_base;             // columns [0, BN)
   const uint32_t tmem_a = tmem_base + BN;          // NT operand stages of 32 columns
@@ -130,7 +127,19 @@ w4a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs args
       constexpr uint32_t kTx = Cfg::kXStage + Cfg::kWStage;
       int issued = 0;
       bool ok = true;
-      for (int i = 0; i < nk; ++i) {
+      // Weight tiles never depend on the previous kernel of the stream, the tokens do: the first NS
+      // weight tiles are requested at once, then comes the wait for that kernel, then the token boxes.
+      const int early = nk < NS ? nk : NS;
+      for (int i = 0; i < early; ++i) {
+        ptx::mbar_expect_tx(bar_full + 8 * i, kTx);
+        const uint8_t* src = args.blob + ((size_t)nt * args.kt_total + kt_begin + i) * kTileBytes;
+        ptx::bulk_load(ws + i * Cfg::kWStage, src, kTileBytes, bar_full + 8 * i);
+      }
+      dependency_wait();
+      for (int i = 0; i < early; ++i)
+        ptx::tensor_load_2d(xs + i * Cfg::kXStage, &tmap_x, (kt_begin + i) * 128, m0, bar_full + 8 * i);
+      issued = early;
+      for (int i = early; i < nk; ++i) {
         const int s = i % NS;
         const uint32_t ph = (uint32_t)(i / NS) & 1u;
         if (!ptx::mbar_wait_bounded(bar_empty + 8 * s, ph ^ 1u, kWaitLimitNs)) {
@@ -241,6 +250,7 @@ w4a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs args
       ok = false;
     }
     __syncwarp();
+    dependency_wait();   // outputs, planes and token scales belong to earlier kernels until here
     if (ok) {
       ptx::tc_fence_after();
       const long n = (long)nt * 128 + row;
@@ -254,13 +264,17 @@ w4a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs args
         ptx::tmem_ld16(tmem_acc + lane_addr + c0, v);
         ptx::tc_wait_ld();
         if (n_ok) {
+          float sc[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j)   // all loads of the chunk first: one round trip
+            sc[j] = (args.out_mode != kOutI32 && m0 + c0 + j < args.M) ? __ldg(args.ascale + m0 + c0 + j) : 0.f;
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int m = m0 + c0 + j;
             if (m < args.M) {
               const size_t idx = (size_t)m * args.N + n;
               if (args.out_mode == kOutI32) plane[idx] = v[j];
-              else store_out(args.out, idx, lqq_scale(v[j], ascale_s[c0 + j], w_scale), args.out_mode);
+              else store_out(args.out, idx, lqq_scale(v[j], sc[j], w_scale), args.out_mode);
             }
           }
         }
@@ -293,7 +307,11 @@ static int launch_cfg(const CUtensorMap& tx, const GemmArgs& a, int splits, cuda
     return LQ_ERR_CUDA;
   }
   dim3 grid((a.N + 127) / 128, (a.M + BN - 1) / BN, splits);
-  kern<<<grid, kThreads, Cfg::kSmemBytes, st>>>(tx, a);
+  cudaError_t le = launch_overlapped(kern, grid, dim3(kThreads), (size_t)Cfg::kSmemBytes, st, tx, a);
+  if (le != cudaSuccess) {
+    record_cuda_error(le, "w4a8_tile_kernel launch");
+    return LQ_ERR_CUDA;
+  }
   return check_launch("w4a8_tile_kernel");
 }
 
