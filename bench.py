@@ -358,7 +358,11 @@ def main():
     ms, e2e_ms = float(t_ms[0]), float(t_ms[1])
     status = lib.lq_poll_status(torch.cuda.current_stream().cuda_stream)
 
-    launches_per_step = len(launches)   # every linear of the sweep is one kernel launch
+    def kernels_of(name, M):
+        """Kernel launches of one linear: 2 when the tile kernel splits K (planes + finish pass), else 1."""
+        N, K = SHAPES[name]
+        return 2 if lib.lq_gemm_workspace_kind(M, N, K, 0) == 1 else 1
+    launches_per_step = sum(kernels_of(n, M) for n, M in launches)
     wbytes = sweep_weight_bytes()
     abytes = sum(algorithmic_bytes(M, *SHAPES[n]) for n, M in launches)
     step_s = ms / 1e3 / args.steps
@@ -404,7 +408,7 @@ def main():
                        "sharding": "each rank owns a full set of output channels (N-sharded, no collective)"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_RATIO * abytes,
-                         "of": peaks["source"], "kernel": "w4a8_skinny_kernel (M = 8, 16) + gemv_blob_kernel (M = 1, 4): the 12-op sweep",
+                         "of": peaks["source"], "kernel": "w4a8_tile_kernel [+ finish_kernel] (M = 8, 16) + gemv_blob_kernel (M = 1, 4): the 12-op sweep",
                          "algorithmic_bytes_per_step": abytes},
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": UNIT,

@@ -134,8 +134,8 @@ LQ_API int lq_w4a8_gemv_blob_static(const void* x_i8, const void* blob, const vo
  * outputs of this GPU and of its peers as destinations (peer memory mapped into this process), the
  * epilogue performs the all-gather of an N-sharded layer with plain stores over NVLink.  `outs` is
  * a HOST array of device pointers.  Ordering towards the peers' consumers is the caller's job (a
- * stream-ordered barrier between the ranks after the call).  Workspace as lq_w4a8_gemm_fused with
- * splitk 0.  Replaces GEMM + all-gather of the reference's tensor-parallel use
+ * stream-ordered barrier between the ranks after the call).  Workspace: lq_scatter_workspace_bytes().
+ * Replaces GEMM + all-gather of the reference's tensor-parallel use
  * (liquidgemm/vllm_plugin.py:174-206 under vLLM's column-parallel linear). */
 LQ_API int lq_w4a8_gemm_fused_scatter(const int8_t* x_i8, const uint8_t* blob, const float* ascale,
                                       const float* s1, void* const* outs, int n_outs, long ld_out,
@@ -155,8 +155,10 @@ LQ_API int lq_w4a8_gemm_fused_scatter_sync(const int8_t* x_i8, const uint8_t* bl
                                            unsigned* const* peer_flags, int flag_index,
                                            const unsigned* wait_flag, unsigned wait_value,
                                            void* workspace, size_t workspace_bytes, void* stream);
-/* CTAs a decode launch (M <= 16) of this shape uses on the current device. */
+/* CTAs a gather-by-stores launch (M <= 16) of this shape uses on the current device, and the bytes of
+ * its workspace (ALL ZERO on entry, left all zero; may be shared with the other zeroed workspaces). */
 LQ_API int lq_decode_grid(int M, int N, int K);
+LQ_API size_t lq_scatter_workspace_bytes(int M, int N, int K);
 
 /* One whole linear layer for HOST activations and a HOST output: upload, per-token quantise, fused
  * W4A8 linear from the tile blob (automatic kernel choice by M), download, all enqueued on `stream`
@@ -196,9 +198,8 @@ LQ_API int lq_repack_tiles(const uint8_t* src, int src_layout, const uint8_t* s_
 
 /* Scheduling of the tensor-core GEMM, selected by the `splitk` argument of the calls below.
  *   splitk = 0 (automatic):
- *     M <= 4   streaming dp4a GEMV over the tile blob (scaled outputs; int32 output uses the next);
- *     M <= 16  single-launch streaming tensor-core kernel, stream-K over two CTAs per SM, tiles cut
- *              between CTAs joined with one 64-bit atomic per output element;
+ *     M <= 4   streaming dp4a GEMV over the tile blob (scaled outputs; int32 output: the streaming
+ *              tensor-core kernel, stream-K with one 64-bit atomic per element to join cut tiles);
  *     larger   tile kernel: one 128-channel x up-to-128-token tile per CTA, two CTAs per SM, every
  *              tile cut into S k-ranges (S from the SM count) whose int32 partial planes one finish
  *              kernel reduces, scales and casts -- the split-K design of the reference

@@ -798,18 +798,19 @@ struct Route {
 // the Llama-3.1-8B shapes); it only produces scaled outputs, the int32 entry point always uses tensor cores.
 constexpr int kGemvBlobMaxM = 4;
 
-// Decode batches up to this size use the single-launch streaming kernel; its one-atomic-per-element
-// reduction is the cheapest way to join split tiles while a CTA holds few tokens.  From 17 tokens on
-// the int32 planes + finish pass of the tile kernel are as fast or faster (measured on B200; the
-// 32-token configuration of the streaming kernel additionally measured 3x slower with parked barrier
-// waits, cause not found, so it is not used).
+// Largest decode batch the single-launch streaming tensor-core kernel serves (its one-atomic-per-element
+// join is cheap only while a CTA holds few tokens; the 32-token configuration additionally measured 3x
+// slower with parked barrier waits, cause not found).  Since the tile kernel got a second dequant set
+// and programmatic dependent launch it is as fast or faster from 5 tokens on (8 tokens, 28672 x 4096:
+// 18.3 vs 20.0 us), so the automatic routing uses the streaming kernels up to kGemvBlobMaxM tokens only;
+// the streaming tensor-core kernel remains the engine of the gather-by-stores entry points.
 constexpr int kSkinnyMaxM = 16;
 
 static Route route_for(int M, int N, int K, int splitk) {
   const int kt = K / 128;
   if (splitk == -1) return {false, false, 0};
   if (M <= 128) {
-    if (splitk == 0 && M <= kSkinnyMaxM) return {false, true, 0};
+    if (splitk == 0 && M <= kGemvBlobMaxM) return {false, true, 0};
     int S = splitk > 0 ? splitk : tile_pick_splits(M, N, K);
     if (S > kt) S = kt;
     return {true, false, S < 1 ? 1 : S};
@@ -907,6 +908,12 @@ int lq_w4a8_gemm_fused_scatter(const int8_t* x_i8, const uint8_t* blob, const fl
                                int K, void* workspace, size_t workspace_bytes, void* stream) {
   return lq_w4a8_gemm_fused_scatter_sync(x_i8, blob, ascale, s1, outs, n_outs, ld_out, col0, out_dtype, M, N, K,
                                          nullptr, 0, nullptr, 0u, workspace, workspace_bytes, stream);
+}
+
+size_t lq_scatter_workspace_bytes(int M, int N, int K) {
+  if (M < 1 || M > kSkinnyMaxM || N <= 0 || K < 128 || K % 128) return 0;
+  const size_t a = skinny_workspace_bytes(M, N, K), b = M <= kGemvBlobMaxM ? gemv_blob_workspace_bytes(N, K) : 0;
+  return a > b ? a : b;
 }
 
 int lq_decode_grid(int M, int N, int K) {

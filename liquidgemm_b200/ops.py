@@ -385,7 +385,7 @@ def gemm_fused_scatter(x_i8, blob, ascale, s1, out_ptrs, ld_out, col0, N, K, out
         _req(len(flag_ptrs) == len(out_ptrs), "one flag array per destination")
         flags = (ctypes.c_void_p * len(flag_ptrs))(*[int(p) for p in flag_ptrs])
     with _dev_ctx(x_i8):
-        ws = _workspace(lib.lq_gemm_workspace_bytes(M, N, K, 0), x_i8.device)
+        ws = _workspace(lib.lq_scatter_workspace_bytes(M, N, K), x_i8.device)
         rc = lib.lq_w4a8_gemm_fused_scatter_sync(_ptr(x_i8), _ptr(blob), _ptr(ascale), _ptr(s1), arr, len(out_ptrs),
                                                  int(ld_out), int(col0), int(out_dtype), M, N, K, flags,
                                                  int(flag_index), wait_ptr, int(wait_value), _ptr(ws), ws.numel(),
@@ -640,6 +640,7 @@ def w4a8_linear(x: torch.Tensor, qw_dev: dict, out_dtype: torch.dtype = None) ->
 
 
 _HOST_SCRATCH: dict = {}
+_HOST_PLANES: dict = {}
 _HOST_SIZES: dict = {}
 
 
@@ -674,8 +675,9 @@ def w4a8_linear_host(x_host: torch.Tensor, qw_dev: dict, y_host: torch.Tensor = 
     sizes = _HOST_SIZES.get((M, N, K, xc, oc))
     if sizes is None:
         sizes = _HOST_SIZES[(M, N, K, xc, oc)] = (lib.lq_linear_host_scratch_bytes(M, N, K, xc, oc),
-                                                  lib.lq_gemm_workspace_bytes(M, N, K, 0))
-    need, nws = sizes
+                                                  lib.lq_gemm_workspace_bytes(M, N, K, 0),
+                                                  lib.lq_gemm_workspace_kind(M, N, K, 0))
+    need, nws, kind = sizes
     switch = torch.cuda.current_device() != dev.index
     if switch:
         prev = torch.cuda.current_device()
@@ -687,17 +689,20 @@ def w4a8_linear_host(x_host: torch.Tensor, qw_dev: dict, y_host: torch.Tensor = 
         if scratch is None or scratch.numel() < need:
             scratch = torch.empty((max(need, 1 << 22),), dtype=torch.uint8, device=dev)
             _HOST_SCRATCH[key] = scratch
-        ws = _WORKSPACES.get(key)
+        # kind 2: the shared all-zero reduction buffer (kernels leave it zero); kind 1: split-K planes,
+        # plain scratch that must NOT be the zero buffer, because nothing cleans it afterwards
+        pool = _WORKSPACES if kind == 2 else _HOST_PLANES
+        ws = pool.get(key)
         if nws and (ws is None or ws.numel() < nws):
             if ws is not None:
                 _RETIRED.append(ws)
-            ws = _WORKSPACES[key] = torch.zeros((max(nws, 1 << 22),), dtype=torch.uint8, device=dev)
+            ws = pool[key] = torch.zeros((max(nws, 1 << 22),), dtype=torch.uint8, device=dev)
             torch.cuda.current_stream().synchronize()   # zero-fill (current stream) before use on `stream`
         rc = lib.lq_w4a8_linear_host(x_host.data_ptr(), xc, blob.data_ptr(), s1.data_ptr(), y_host.data_ptr(), oc,
                                      M, N, K, scratch.data_ptr(), scratch.numel(),
                                      ws.data_ptr() if nws else None, ws.numel() if nws else 0, stream)
         if rc != 0:
-            if nws:
+            if nws and kind == 2:
                 ws.zero_()
             check(rc, "w4a8_linear_host")
     finally:

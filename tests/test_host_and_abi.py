@@ -44,7 +44,9 @@ def test_size_helpers_without_gpu():
     assert lib.lq_gemm_workspace_kind(64, 4096, 14336, 4) == 1
     assert lib.lq_gemm_workspace_kind(2048, 4096, 14336, 0) == 0     # tile kernel, one k-range: no workspace
     assert lib.lq_gemm_workspace_kind(2048, 4096, 14336, -1) == 2
-    assert lib.lq_gemm_workspace_kind(8, 4096, 14336, 0) == 2        # streaming decode kernel
+    assert lib.lq_gemm_workspace_kind(2, 4096, 14336, 0) == 2        # streaming decode kernels
+    assert lib.lq_gemm_workspace_kind(8, 4096, 14336, 0) == 1        # tile kernel with split-K planes
+    assert lib.lq_scatter_workspace_bytes(8, 4096, 14336) > 0
     assert lib.lq_gemm_workspace_kind(2048, 4096, 14336, 1) == 0
 
 
