@@ -234,8 +234,8 @@ def build_device_sets(torch, ops, n_sets, seed_base):
 
 
 # DRAM read+write bytes per launch / algorithmic bytes per launch, mean of six ncu captures of the decode
-# kernels (three shapes each of gemv_blob_kernel and w4a8_skinny_kernel); summary under profiles/.
-NCU_TRAFFIC_RATIO = 1.012
+# kernels (three launches each of gemv_blob_kernel and w4a8_tile_kernel); summary under profiles/.
+NCU_TRAFFIC_RATIO = 1.002
 
 
 def main():
