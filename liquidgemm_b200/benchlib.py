@@ -14,6 +14,8 @@ does not depend on the values; parity is the test-suite's job).
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import ops
@@ -173,7 +175,9 @@ def run_tp70b(world, rank, Ms=(1, 16, 64, 2048), layers_in_stack=80, distinct_la
         toks = {n: device_tokens(M, SHAPES_70B[n][1], seed=M + i) for i, n in enumerate(names)}
         gathered = {n: torch.empty((world * M, SHAPES_70B[n][0] // world), dtype=torch.bfloat16, device="cuda")
                     for n in names}
-        symm = _symmetric_outputs(world, M, names) if (world > 1 and M <= 16) else None
+        # gather by stores: measured and verified on two ranks; larger groups only on request
+        fused_ok = world == 2 or (world > 2 and os.environ.get("LQ_BENCH_FUSED_GATHER") == "1")
+        symm = _symmetric_outputs(world, M, names) if (fused_ok and M <= 16) else None
         flags = None
         if symm is not None:
             try:
