@@ -5,9 +5,13 @@
 
 One *step* is one pass of the decode sweep: M in {1, 4, 8, 16} over the three Llama-3.1-8B linear
 shapes (qkv 6144x4096, gate_up 28672x4096, down 4096x14336) = 12 linears through the decode
-dispatch of the plugin (``w4a8_gemv2`` for one or two tokens, the fused tensor-core op above).  Weights are seeded synthetic LQQ data of those
-shapes (no checkpoint is read); every launch uses the next of several weight copies so that the
-bytes it streams were evicted from L2 long before (working set > 2 x 126 MB).
+dispatch of the plugin (``torch.ops.liquidgemm.w4a8_wgmma_rs_fused`` on the tile blob, which picks the
+streaming GEMV or a tensor-core kernel by M).  Weights are seeded synthetic LQQ data of those shapes
+(no checkpoint is read).  Four weight copies rotate per launch: the linear of shape s at the i-th M
+of step t reads copy (t + i) mod 4, so a copy is read again only after three other copies of the
+same shape plus the rest of the sweep (more than 300 MB, over twice the 126 MB L2) went by.
+Before anything is timed, every (shape, M) of the sweep runs once and a 16-channel slice of its
+output, and its quantised tokens, are compared bit for bit with the CPU oracle (``parity`` in the line).
 
 The JSON line printed by rank 0 carries
   value     weight GB/s (packed weight bytes N*K/2 per launch / device time), whole job
@@ -161,10 +165,19 @@ class ClockSampler:
 # reference arm / CPU baseline
 # ----------------------------------------------------------------------------------------------
 
+def host_threads():
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
 def cpu_sweep(reps):
-    """Time the C oracle on the decode sweep.  Returns (seconds per sweep [best], threads, sample)."""
+    """Time the C oracle on the decode sweep.  Returns (seconds per sweep, threads used)."""
     from oracle import build_oracle
     lib = build_oracle.load()
+    # all host cores whatever the launcher exported (torchrun sets OMP_NUM_THREADS=1 for its children)
+    lib.lqo_set_num_threads(host_threads())
     threads = lib.lqo_num_threads()
     p = lambda a: a.ctypes.data_as(ctypes.c_void_p)
     data = {}
@@ -216,8 +229,13 @@ def run_reference_arm(args):
 # GPU arm
 # ----------------------------------------------------------------------------------------------
 
+PARITY_ROWS = 16
+
+
 def build_device_sets(torch, ops, n_sets, seed_base):
-    """n_sets independent copies of the three quantised layers on the device."""
+    """n_sets independent copies of the three quantised layers on the device (tile blob only: the one
+    weight format the dispatch reads).  Of every layer a 16-channel slice stays on the host for the
+    parity gate."""
     from liquidgemm_b200.quant import LiquidQuantWeight
     sets = []
     for c in range(n_sets):
@@ -226,15 +244,39 @@ def build_device_sets(torch, ops, n_sets, seed_base):
             codes, step, off, s1 = synth_lqq_codes(N, K, seed=seed_base + 17 * c + len(name))
             qw = LiquidQuantWeight(torch.from_numpy(codes).cuda(), torch.from_numpy(step).cuda(),
                                    torch.from_numpy(off).cuda(), torch.from_numpy(s1).cuda(), 64)
-            layer[name] = {"gp": ops.pack_gemv_interleaved(qw), "rs": ops.repack_rs_weight(qw).reshape(-1),
-                           "s_u8": qw.s_u8, "offset_a": qw.offset_a, "s1": qw.s1, "N": N, "K": K}
+            rows = np.sort(np.random.default_rng(c).choice(N, PARITY_ROWS, replace=False))
+            layer[name] = {"rs": ops.repack_rs_weight(qw).reshape(-1),
+                           "s_u8": qw.s_u8, "offset_a": qw.offset_a, "s1": qw.s1, "N": N, "K": K,
+                           "check": (rows, codes[rows].copy(), step[rows].copy(), off[rows].copy(), s1[rows].copy())}
             del qw, codes
         sets.append(layer)
     return sets
 
 
-# DRAM read+write bytes per launch / algorithmic bytes per launch, mean of six ncu captures of the decode
-# kernels (three launches each of gemv_blob_kernel and w4a8_tile_kernel); summary under profiles/.
+def parity_gate(torch, sets, acts, launches, run_linear):
+    """Every (shape, M) of the sweep once on every weight copy: quantised tokens and a 16-channel slice of
+    the bf16 output against the numpy oracle, bit for bit.  Returns (ok, cases checked)."""
+    from oracle import lqq_oracle as O
+    ok, n = True, 0
+    for name, M in launches:
+        a = acts[(name, M)]
+        xq_want, sc_want = O.quantize_activation(a["host"].float().numpy())
+        ok &= bool(np.array_equal(a["xq"].cpu().numpy(), xq_want))
+        ok &= bool(np.array_equal(a["sc"].cpu().numpy().view(np.uint32), sc_want.view(np.uint32)))
+        for layer_set in sets:
+            L = layer_set[name]
+            rows, codes, step, off, s1 = L["check"]
+            y = run_linear(L, a["xq"], a["sc"], M, OUT_BF16)
+            got = y[:, torch.from_numpy(rows).cuda()].cpu().view(torch.int16).numpy().view(np.uint16)
+            want = O.w4a8_linear(xq_want, sc_want, O.LQQWeight(codes, step, off, s1, 64), O.OUT_BF16)
+            ok &= bool(np.array_equal(got, want))
+            n += 1
+    return ok, n
+
+
+# DRAM read+write bytes per launch / algorithmic bytes per launch, mean over the ncu captures of the decode
+# kernels summarised under profiles/ (taken on single launches of the same shapes; the benchmark itself
+# never runs under a profiler, so `roofline.traffic` is that measured ratio times the step's algorithmic bytes).
 NCU_TRAFFIC_RATIO = 1.002
 
 
@@ -273,7 +315,7 @@ def main():
     if rank == 0:
         sampler.start()
     peaks = measured_peaks()
-    n_sets = 3
+    n_sets = 4
     sets = build_device_sets(torch, ops, n_sets, seed_base=1000 * rank)
 
     gen = torch.Generator().manual_seed(rank)
@@ -287,18 +329,20 @@ def main():
     launches = [(name, M) for M in SWEEP_M for name in SHAPES]
 
     def decode_linear(L, xq, sc, M, out_dtype):
-        """The decode dispatch of the plugin (liquidgemm_b200.ops.use_gemv): everything is served from
-        the tile blob; the row-major GEMV pack is only a fallback for layers without a blob."""
-        if ops.use_gemv(M, L["N"], L["K"], True, True):
-            return torch.ops.liquidgemm.w4a8_gemv2(xq, L["gp"], L["s_u8"], L["offset_a"], sc, L["s1"], L["N"], L["K"],
-                                                   64, out_dtype)
+        """The op the plugin's forward calls (liquidgemm_b200.vllm_plugin.apply_layer): the fused linear on
+        the tile blob, which dispatches on M inside the library."""
         return torch.ops.liquidgemm.w4a8_wgmma_rs_fused(xq, L["rs"], L["s_u8"], L["offset_a"], sc, L["s1"], L["N"],
                                                         L["K"], 64, out_dtype)
 
+    def copy_for(step, name, M):
+        return sets[(step + SWEEP_M.index(M)) % n_sets][name]
+
     def enqueue_sweep(c):
         for name, M in launches:
-            L, a = sets[c][name], acts[(name, M)]
-            decode_linear(L, a["xq"], a["sc"], M, OUT_BF16)
+            a = acts[(name, M)]
+            decode_linear(copy_for(c, name, M), a["xq"], a["sc"], M, OUT_BF16)
+
+    parity_ok, parity_cases = parity_gate(torch, sets, acts, launches, decode_linear)
 
     stream = torch.cuda.Stream()
     graphs = []
@@ -339,8 +383,8 @@ def main():
 
     def e2e_step(c):
         for i, (name, M) in enumerate(launches):
-            L, a = sets[c][name], acts[(name, M)]
-            ops.w4a8_linear_host(a["host"], L, a["out_host"], stream=e2e_streams[i % 3])
+            a = acts[(name, M)]
+            ops.w4a8_linear_host(a["host"], copy_for(c, name, M), a["out_host"], stream=e2e_streams[i % 3])
 
     e2e_steps = max(3, min(args.steps, 50))
     for i in range(3):
@@ -404,7 +448,8 @@ def main():
             "vs_baseline": None, "dtype": "int8 x uint4 -> int32", "data": "synthetic",
             "config": {"workload": "decode GEMV sweep M in {1,4,8,16} x Llama-3.1-8B qkv/gate_up/down (configs[1])",
                        "group_size": 64, "out": "bf16", "launches_per_step": len(launches),
-                       "l2": f"{n_sets} weight copies rotate (302 MB working set > 2 x L2); step captured in a CUDA graph",
+                       "l2": f"{n_sets} weight copies rotate per launch (a copy is re-read after > 300 MB of other "
+                             "weights, over 2 x L2); step captured in a CUDA graph",
                        "sharding": "each rank owns a full set of output channels (N-sharded, no collective)"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_RATIO * abytes,
@@ -416,6 +461,7 @@ def main():
                     "d2h_bytes_per_step": sum(M * SHAPES[n][0] * 2 for n, M in launches),
                     "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
             "gpu_launches": launches_per_step * args.steps,
+            "parity": bool(parity_ok and status == 0), "parity_cases": parity_cases,
             "clocks": clocks, "device_status": status, "extras": extras,
         }
         print(json.dumps(line), flush=True)

@@ -80,15 +80,10 @@ LQ_API int lq_scale_epilogue(const int32_t* acc, const float* ascale, const floa
 
 /* Decode GEMV, M <= 16: y = scale_epilogue(x_i8 @ q_hat^T) straight from the row-major
  * interleaved pack of liquidgemm/ops.py:68-75.  Requires K % 128 == 0 and group_size == 64.
- * Replaces torch.ops.liquidgemm.w4a8_gemv2 (reference csrc/liquid_gemm/gemv2.cu:82-120).
- * lq_w4a8_gemv_variant is the same call with the kernel forced (1 = dp4a, 2 = mma.sync): a
- * tuning hook for the dispatch table, without a reference counterpart. */
+ * Replaces torch.ops.liquidgemm.w4a8_gemv2 (reference csrc/liquid_gemm/gemv2.cu:82-120). */
 LQ_API int lq_w4a8_gemv(const int8_t* x_i8, const uint8_t* gpack, const uint8_t* s_u8,
                  const uint8_t* offset_a, const float* ascale, const float* s1, void* y,
                  int out_dtype, int M, int N, int K, int group_size, void* stream);
-LQ_API int lq_w4a8_gemv_variant(const int8_t* x_i8, const uint8_t* gpack, const uint8_t* s_u8,
-                         const uint8_t* offset_a, const float* ascale, const float* s1, void* y,
-                         int out_dtype, int M, int N, int K, int variant, void* stream);
 
 /* The same GEMV as a persistent stream-K kernel (TMA ring + mma.sync): the fast path behind
  * torch.ops.liquidgemm.w4a8_gemv2.  It needs a reduction workspace of lq_gemv_workspace_bytes(N, K)
@@ -115,19 +110,28 @@ LQ_API int lq_w4a8_gemv_blob(const void* x_i8, const void* blob, const void* asc
 
 /* lq_w4a8_gemv_blob without a workspace argument: the reduction scratch is an array inside the
  * library's device image (4 194 304 bytes, enough for 512 CTAs = devices of up to 256 SMs), so the
- * call needs no buffer from any allocator.  This entry point has no counterpart in the reference.
+ * call needs no buffer from any allocator.  It is meant for callers that cannot obtain device memory
+ * where the call is made: a serving process whose memory plan has already handed every byte of the GPU
+ * to its own pools, or code running where entering an allocator is not allowed.  This entry point has
+ * no counterpart in the reference.
  *  - Limits: M <= 8, K % 128 == 0, x_i8 and blob 16-byte aligned as for lq_w4a8_gemv_blob; a device
  *    whose 2 x SM count exceeds 512 is refused with LQ_ERR_WORKSPACE (text in lq_last_cuda_error()).
- *  - The FIRST call on each device (with that device current) looks the array up and clears it with
- *    a synchronous cudaMemset: make that first call outside any stream capture and outside
+ *  - The FIRST call on each device (with that device current) looks the array's device address up,
+ *    clears the array and then synchronises the whole device, so that the cleared array is seen by a
+ *    kernel on any stream.  Make that first call before any stream capture and outside
  *    latency-critical sections; later calls only enqueue the kernel.
- *  - The array must be all zero when a call starts and every successful call leaves it all zero.
- *    There is one array per device: two calls that overlap in time on the same device (different
- *    streams or threads) race on it and give wrong sums; serialise them.  Between calls the array
- *    simply keeps what the last call left (zeros after a successful one). */
+ *  - The array must be all zero when a call starts, and every call whose kernel runs to completion
+ *    leaves it all zero.  There is one array per device and every call shares it: two calls that
+ *    overlap in time on the same device (different streams or threads) race on it and give wrong
+ *    sums; serialise them.
+ *  - If lq_poll_status() reports LQ_ERR_TIMEOUT after such a call (a bounded device-side wait gave up),
+ *    the array may hold partial sums: enqueue lq_w4a8_gemv_blob_static_reset(stream) before the next
+ *    call, otherwise every later result on that device is wrong.  The reset is a cudaMemsetAsync on
+ *    `stream`; it allocates and synchronises nothing. */
 LQ_API int lq_w4a8_gemv_blob_static(const void* x_i8, const void* blob, const void* ascale,
                                     const void* s1, void* out, int out_dtype, int M, int N, int K,
                                     void* stream);
+LQ_API int lq_w4a8_gemv_blob_static_reset(void* stream);
 
 /* lq_w4a8_gemm_fused for a decode batch (M <= 16) whose output block [M, N] is written into n_outs
  * (1..8) row-major matrices with row stride ld_out elements at column col0: with the full-width
@@ -196,10 +200,22 @@ LQ_API int lq_repack_tiles(const uint8_t* src, int src_layout, const uint8_t* s_
                     const uint8_t* offset_a, uint8_t* blob, int N, int K, int group_size,
                     void* stream);
 
+/* LiquidQuant weight quantiser on the device: w [N, K] (w_dtype: LQ_DT_*) -> s1 [N] float32, s_u8 and
+ * offset_a [N, K/group_size], and optionally codes [N, K] (one 4-bit code per byte) and / or the tile blob
+ * of lq_tile_blob_bytes(N, K) bytes (either may be null).  Two kernels, no host read: the overflow
+ * invariants are checked on the device (lq_poll_status reports site 501).  Bit-identical to the
+ * reference's quantize_weight on the CPU followed by its prepack
+ * (liquidgemm/quant.py:61-100, liquidgemm/ops.py:118-150).  K % 128 == 0, group_size 64 or 128;
+ * codes and blob 16-byte aligned. */
+LQ_API int lq_quantize_weight(const void* w, int w_dtype, int N, int K, int group_size, float* s1,
+                              uint8_t* s_u8, uint8_t* offset_a, uint8_t* codes, uint8_t* blob,
+                              void* stream);
+
 /* Scheduling of the tensor-core GEMM, selected by the `splitk` argument of the calls below.
  *   splitk = 0 (automatic):
- *     M <= 4   streaming dp4a GEMV over the tile blob (scaled outputs; int32 output: the streaming
- *              tensor-core kernel, stream-K with one 64-bit atomic per element to join cut tiles);
+ *     M <= 2, and M <= 4 on matrices up to 64 M weights: streaming dp4a GEMV over the tile blob;
+ *     M <= 16  (and int32 output at any small M): the streaming tensor-core kernel, ONE launch:
+ *              stream-K over two CTAs per SM, one 64-bit atomic per element joins cut tiles;
  *     larger   tile kernel: one 128-channel x up-to-128-token tile per CTA, two CTAs per SM, every
  *              tile cut into S k-ranges (S from the SM count) whose int32 partial planes one finish
  *              kernel reduces, scales and casts -- the split-K design of the reference
@@ -218,6 +234,8 @@ LQ_API int lq_gemm_pick_splitk(int M, int N, int K, int env_override);
  * the GPU need separate buffers, and after a LQ_ERR_TIMEOUT the caller must clear it. */
 LQ_API size_t lq_gemm_workspace_bytes(int M, int N, int K, int splitk);
 LQ_API int lq_gemm_workspace_kind(int M, int N, int K, int splitk);
+/* Kernel launches one fused call with these arguments makes (2 when the tile kernel splits K). */
+LQ_API int lq_gemm_launches(int M, int N, int K, int splitk);
 
 /* W4A8 tensor-core GEMM, exact int32 accumulators acc[M,N] = x_i8 @ q_hat^T.
  * Replaces torch.ops.liquidgemm.w4a8_wgmma_rs (reference csrc/liquid_gemm/w4a8_wgmma.cu:505-570).
@@ -231,6 +249,14 @@ LQ_API int lq_w4a8_gemm_i32(const int8_t* x_i8, const uint8_t* blob, int32_t* ac
 LQ_API int lq_w4a8_gemm_fused(const int8_t* x_i8, const uint8_t* blob, const float* ascale,
                        const float* s1, void* y, int out_dtype, int M, int N, int K, int splitk,
                        void* workspace, size_t workspace_bytes, void* stream);
+
+/* lq_w4a8_gemm_fused (automatic scheduling) with the layer's bias added inside the kernel's epilogue:
+ * y = (T)((T)((float)acc * ascale[m] * s1[n]) + bias[n]), i.e. the bias joins the value already rounded to
+ * the output type T, exactly what the reference's plugin computes with a separate PyTorch add after its
+ * operator (liquidgemm/vllm_plugin.py:205-206).  `bias`: [N] in the output dtype, or null. */
+LQ_API int lq_w4a8_linear_bias(const int8_t* x_i8, const uint8_t* blob, const float* ascale,
+                        const float* s1, const void* bias, void* y, int out_dtype, int M, int N, int K,
+                        void* workspace, size_t workspace_bytes, void* stream);
 
 /* The same fused GEMM reading the weights in the row-major interleaved GEMV pack
  * (liquidgemm/ops.py:68-75: [N, K/2]) with the standard [N, K/64] step / offset arrays, i.e. one

@@ -11,6 +11,8 @@ from ctypes import c_char_p, c_int, c_size_t, c_void_p
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "_lq_b200.so")
+if os.environ.get("LIQUIDGEMM_B200_TRACE") == "1":   # pipeline studies: `python -m liquidgemm_b200.build --trace`
+    LIB_PATH = os.path.join(_HERE, "_lq_b200_trace.so")
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(
@@ -30,13 +32,13 @@ _SIGNATURES = {
     "lq_quant_per_token": (c_int, [P, c_int, P, P, c_int, c_int, P]),
     "lq_scale_epilogue": (c_int, [P, P, P, P, c_int, c_int, c_int, P]),
     "lq_w4a8_gemv": (c_int, [P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P]),
-    "lq_w4a8_gemv_variant": (c_int, [P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P]),
     "lq_w4a8_gemm_rowmajor": (c_int, [P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, c_size_t, P]),
     "lq_gemv_workspace_bytes": (c_size_t, [c_int, c_int]),
     "lq_w4a8_gemv_stream": (c_int, [P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, P, c_size_t, P]),
     "lq_gemv_blob_workspace_bytes": (c_size_t, []),
     "lq_w4a8_gemv_blob": (c_int, [P, P, P, P, P, c_int, c_int, c_int, c_int, P, c_size_t, P]),
     "lq_w4a8_gemv_blob_static": (c_int, [P, P, P, P, P, c_int, c_int, c_int, c_int, P]),
+    "lq_w4a8_gemv_blob_static_reset": (c_int, [P]),
     "lq_w4a8_gemm_fused_scatter": (c_int, [P, P, P, P, P, c_int, ctypes.c_long, ctypes.c_long, c_int, c_int, c_int,
                                            c_int, P, c_size_t, P]),
     "lq_w4a8_gemm_fused_scatter_sync": (c_int, [P, P, P, P, P, c_int, ctypes.c_long, ctypes.c_long, c_int, c_int, c_int,
@@ -52,6 +54,9 @@ _SIGNATURES = {
     "lq_gemm_pick_splitk": (c_int, [c_int, c_int, c_int, c_int]),
     "lq_gemm_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "lq_gemm_workspace_kind": (c_int, [c_int, c_int, c_int, c_int]),
+    "lq_gemm_launches": (c_int, [c_int, c_int, c_int, c_int]),
+    "lq_w4a8_linear_bias": (c_int, [P, P, P, P, P, P, c_int, c_int, c_int, c_int, P, c_size_t, P]),
+    "lq_quantize_weight": (c_int, [P, c_int, c_int, c_int, c_int, P, P, P, P, P, P]),
     "lq_w4a8_gemm_i32": (c_int, [P, P, P, c_int, c_int, c_int, c_int, P, c_size_t, P]),
     "lq_w4a8_gemm_fused": (c_int, [P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, c_size_t, P]),
     "lq_i8_gemm_i32": (c_int, [P, P, P, c_int, c_int, c_int, P]),

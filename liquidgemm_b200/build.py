@@ -14,10 +14,14 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
-SOURCES = ["lq_api.cu", "lq_elementwise.cu", "lq_gemv.cu", "lq_gemm_tc.cu", "lq_gemm_tile.cu", "lq_gemv_stream.cu", "lq_gemv_blob.cu", "lq_gemm_skinny.cu", "lq_host.cu",
-           "lq_debug.cu"]
+SOURCES = ["lq_api.cu", "lq_elementwise.cu", "lq_gemv.cu", "lq_gemm_tc.cu", "lq_gemm_tile.cu", "lq_gemv_stream.cu",
+           "lq_gemv_blob.cu", "lq_decode_tc.cu", "lq_quantize.cu", "lq_host.cu"]
 HEADERS = ["lq_common.cuh", "lq_tc_ptx.cuh", "lq_sched.cuh", os.path.join("..", "..", "include", "liquidgemm_b200.h")]
 LIB_PATH = os.path.join(HERE, "_lq_b200.so")
+# Measurement-only kernels (building-block rates; nothing in the product calls them): a library of their own,
+# built on request with ``python -m liquidgemm_b200.build --debug`` and loaded by liquidgemm_b200.microbench.
+DEBUG_SOURCES = ["lq_api.cu", os.path.join("dbg", "lq_debug.cu")]
+DEBUG_LIB_PATH = os.path.join(HERE, "_lq_b200_dbg.so")
 
 NVCC_FLAGS = [
     "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
@@ -32,24 +36,35 @@ def _nvcc() -> str:
     raise RuntimeError("nvcc not found")
 
 
-def _stale() -> bool:
-    if not os.path.exists(LIB_PATH):
+def _stale(lib_path, sources) -> bool:
+    if not os.path.exists(lib_path):
         return True
-    t = os.path.getmtime(LIB_PATH)
-    deps = [os.path.join(CSRC, s) for s in SOURCES + HEADERS] + [os.path.abspath(__file__)]
+    t = os.path.getmtime(lib_path)
+    deps = [os.path.join(CSRC, s) for s in sources + HEADERS] + [os.path.abspath(__file__)]
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    """Compile every .cu into one shared library; returns its path."""
-    if not force and not _stale():
-        return LIB_PATH
+TRACE_LIB_PATH = os.path.join(HERE, "_lq_b200_trace.so")
+
+
+def build(force: bool = False, verbose: bool = False, debug: bool = False, trace: bool = False) -> str:
+    """Compile every .cu of the product (or, with ``debug``, the measurement kernels) into one shared
+    library; returns its path.  ``trace`` builds the product sources with -DLQ_PIPELINE_TRACE (per-CTA cycle
+    counters in the decode kernel) into a library of its own, which ``LIQUIDGEMM_B200_TRACE=1`` makes
+    :mod:`liquidgemm_b200._lib` load instead."""
+    lib_path, sources = (DEBUG_LIB_PATH, DEBUG_SOURCES) if debug else (LIB_PATH, SOURCES)
+    if trace:
+        lib_path = TRACE_LIB_PATH
+    if not force and not _stale(lib_path, sources):
+        return lib_path
     nvcc = _nvcc()
     objs = []
     procs = []
-    for src in SOURCES:
-        obj = os.path.join(CSRC, src.replace(".cu", ".o"))
+    for src in sources:
+        obj = os.path.join(CSRC, src.replace(".cu", ".dbg.o" if debug else ".trace.o" if trace else ".o"))
         cmd = [nvcc, *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
+        if trace:
+            cmd.insert(1, "-DLQ_PIPELINE_TRACE")
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
@@ -62,11 +77,12 @@ def build(force: bool = False, verbose: bool = False) -> str:
         failed |= p.returncode != 0
     if failed:
         raise RuntimeError("nvcc failed")
-    tmp = LIB_PATH + ".tmp"
+    tmp = lib_path + ".tmp"
     subprocess.check_call([nvcc, "-shared", "-o", tmp, *objs, "-gencode", "arch=compute_100a,code=sm_100a"])
-    os.replace(tmp, LIB_PATH)
-    return LIB_PATH
+    os.replace(tmp, lib_path)
+    return lib_path
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, debug="--debug" in sys.argv,
+                trace="--trace" in sys.argv))

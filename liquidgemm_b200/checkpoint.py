@@ -4,7 +4,8 @@ The reference has no on-disk format: every start-up re-quantises the bf16 checkp
 (liquidgemm/vllm_plugin.py:136-172) and its config hooks are stubs (``get_config_filenames`` returns
 ``[]``, liquidgemm/vllm_plugin.py:92-99).  This module defines one:
 
-``<dir>/liquidgemm_config.json``   format version, group size, the layer table (name, N, K, file, sha256)
+``<dir>/liquidgemm_config.json``   format version, blob layout version, group size, the layer table (name, N, K,
+                                   file, sha256)
 ``<dir>/<index>.lqq``              one file per layer: ``torch.save`` of ``{"rs", "s1", "s_u8", "offset_a"}``
                                    as CPU tensors (``rs`` is the tile blob the kernels read)
 
@@ -17,6 +18,7 @@ from __future__ import annotations
 import hashlib
 import json
 import os
+import re
 from typing import Dict, Iterable, Tuple
 
 import torch
@@ -25,6 +27,10 @@ FORMAT = "liquidgemm-b200-prepacked"
 VERSION = 1
 CONFIG_NAME = "liquidgemm_config.json"
 TILE_BYTES = 8704
+# Version of the tile blob itself (4 x [128 rows][16 B] interleaved nibbles + [128][step0, off0, step1, off1]
+# per 128 x 128 tile); a change of that layout must bump it so that old directories are refused.
+BLOB_LAYOUT = 1
+_FILE_RE = re.compile(r"^[0-9]{5}\.lqq$")
 
 
 def blob_bytes(N: int, K: int) -> int:
@@ -58,8 +64,8 @@ def save_prepacked(directory: str, layers: Iterable[Tuple[str, dict]], group_siz
         path = os.path.join(directory, fname)
         torch.save(payload, path)
         table.append({"name": name, "N": N, "K": K, "file": fname, "sha256": _sha256(path)})
-    cfg = {"format": FORMAT, "version": VERSION, "quant_method": "liquidgemm", "group_size": int(group_size),
-           "w4": True, "layers": table}
+    cfg = {"format": FORMAT, "version": VERSION, "blob_layout": BLOB_LAYOUT, "tile_bytes": TILE_BYTES,
+           "quant_method": "liquidgemm", "group_size": int(group_size), "w4": True, "layers": table}
     cfg_path = os.path.join(directory, CONFIG_NAME)
     with open(cfg_path, "w") as f:
         json.dump(cfg, f, indent=1)
@@ -73,6 +79,14 @@ def read_config(directory: str) -> dict:
         raise ValueError(f"{directory}: not a {FORMAT} directory")
     if int(cfg.get("version", -1)) != VERSION:
         raise ValueError(f"{directory}: format version {cfg.get('version')} is not supported (expected {VERSION})")
+    if int(cfg.get("blob_layout", -1)) != BLOB_LAYOUT or int(cfg.get("tile_bytes", -1)) != TILE_BYTES:
+        raise ValueError(f"{directory}: tile blob layout {cfg.get('blob_layout')} / {cfg.get('tile_bytes')} bytes per "
+                         f"tile is not the one this library reads ({BLOB_LAYOUT} / {TILE_BYTES})")
+    for ent in cfg.get("layers", []):
+        # the file name comes from the json: it must be a plain NNNNN.lqq inside the directory
+        if not isinstance(ent.get("file"), str) or not _FILE_RE.match(ent["file"]):
+            raise ValueError(f"{directory}: layer {ent.get('name')!r} names the file {ent.get('file')!r}; "
+                             "expected NNNNN.lqq inside the directory")
     return cfg
 
 

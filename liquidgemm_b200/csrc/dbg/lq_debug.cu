@@ -1,7 +1,7 @@
 // Measurement-only kernels (no product path calls them): the issue/execute rate of
 // tcgen05.mma kind::i8 for a given N, with the A operand in tensor memory or in shared memory.
-#include "lq_common.cuh"
-#include "lq_tc_ptx.cuh"
+#include "../lq_common.cuh"
+#include "../lq_tc_ptx.cuh"
 
 namespace lq {
 __device__ __forceinline__ bool dbg_test_wait(uint32_t bar, uint32_t parity) {
@@ -43,6 +43,9 @@ mma_rate_kernel(int n, int iters, int a_in_tmem, long long* out) {
   // a_in_tmem bit 1: allocate 256 columns (accumulator <= 128 wide) so two CTAs share an SM
   const uint32_t cols = (a_in_tmem & 2) ? 256u : 512u;
   const uint32_t a_col = cols / 2;
+  // bit 2: alternate between two accumulators (columns [0, n) and [n, 2n)) from one MMA to the next, to tell a
+  // dependent-accumulate latency from an issue limit
+  const uint32_t alt = (a_in_tmem & 4) ? (uint32_t)n : 0u;
   a_in_tmem &= 1;
   if (threadIdx.x < 32) {
     ptx::tmem_alloc(smem_u32(&tmem_slot), cols);
@@ -59,8 +62,9 @@ mma_rate_kernel(int n, int iters, int a_in_tmem, long long* out) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const uint64_t bdesc = ptx::smem_desc_sw128(base + j * 32);
-        if (a_in_tmem) ptx::mma_i8_ts(tmem_base, tmem_base + a_col + j * 8, bdesc, idesc, 1u);
-        else ptx::mma_i8_ss(tmem_base, ptx::smem_desc_sw128(base + 32768 + j * 32), bdesc, idesc, 1u);
+        const uint32_t acc = tmem_base + ((j & 1) ? alt : 0u);
+        if (a_in_tmem) ptx::mma_i8_ts(acc, tmem_base + a_col + j * 8, bdesc, idesc, 1u);
+        else ptx::mma_i8_ss(acc, ptx::smem_desc_sw128(base + 32768 + j * 32), bdesc, idesc, 1u);
       }
     }
     const long long t_issue = clock64();
@@ -84,6 +88,7 @@ mma_rate_kernel(int n, int iters, int a_in_tmem, long long* out) {
 extern "C" LQ_API int lq_debug_mma_rate(int n, int iters, int a_in_tmem, int ctas, long long* out, void* stream) {
   if (n < 16 || n > 256 || n % 16 || iters <= 0 || ctas <= 0 || !out) return LQ_ERR_BAD_ARG;
   if ((a_in_tmem & 2) && n > 128) return LQ_ERR_BAD_ARG;
+  if ((a_in_tmem & 4) && n > ((a_in_tmem & 2) ? 64 : 128)) return LQ_ERR_BAD_ARG;
   const int smem = 1024 + 32768 + 16384;
   static bool attr_done = false;
   if (!attr_done) {

@@ -68,6 +68,30 @@ __device__ __forceinline__ void store_out(void* y, size_t idx, float v, int out_
   }
 }
 
+// Bias element n of a vector stored in the output dtype, as float.
+__device__ __forceinline__ float load_bias(const void* b, long n, int out_dtype) {
+  if (out_dtype == LQ_DT_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(b)[n]);
+  if (out_dtype == LQ_DT_F16) return __half2float(reinterpret_cast<const __half*>(b)[n]);
+  return reinterpret_cast<const float*>(b)[n];
+}
+
+// Store with an optional bias.  The product is first rounded to the output type and the bias is added to
+// that rounded value in float32, then rounded again: exactly what PyTorch's `y + bias` computes on the
+// operator's output (the reference adds its bias that way, liquidgemm/vllm_plugin.py:205-206).
+__device__ __forceinline__ void store_out_bias(void* y, size_t idx, float v, float bias, bool has_bias, int out_dtype) {
+  if (out_dtype == LQ_DT_BF16) {
+    __nv_bfloat16 t = __float2bfloat16_rn(v);
+    if (has_bias) t = __float2bfloat16_rn(__fadd_rn(__bfloat162float(t), bias));
+    reinterpret_cast<__nv_bfloat16*>(y)[idx] = t;
+  } else if (out_dtype == LQ_DT_F16) {
+    __half t = __float2half_rn(v);
+    if (has_bias) t = __float2half_rn(__fadd_rn(__half2float(t), bias));
+    reinterpret_cast<__half*>(y)[idx] = t;
+  } else {
+    reinterpret_cast<float*>(y)[idx] = has_bias ? __fadd_rn(v, bias) : v;
+  }
+}
+
 // Where a kernel's outputs go: the same [M, N] block is written into up to 8 row-major matrices with
 // row stride `ld` elements at column offset `col0`.  One destination with ld = N, col0 = 0 is the
 // ordinary output; several destinations (this GPU's and its peers' full-width output, mapped into this
@@ -145,6 +169,17 @@ __device__ __forceinline__ void store_out_all(const OutSpec& o, long m, long n, 
 #pragma unroll
     for (int r = 1; r < 8; ++r)
       if (r < o.n) store_out(o.ptr[r], idx, v, out_dtype);
+  }
+}
+
+__device__ __forceinline__ void store_out_all(const OutSpec& o, long m, long n, float v, float bias, bool has_bias,
+                                              int out_dtype) {
+  const size_t idx = (size_t)(m * o.ld + o.col0 + n);
+  store_out_bias(o.ptr[0], idx, v, bias, has_bias, out_dtype);   // constant indices only, as above
+  if (o.n > 1) {
+#pragma unroll
+    for (int r = 1; r < 8; ++r)
+      if (r < o.n) store_out_bias(o.ptr[r], idx, v, bias, has_bias, out_dtype);
   }
 }
 

@@ -74,6 +74,9 @@ quant_per_token_kernel(const T* __restrict__ x, int8_t* __restrict__ xq, float* 
   // The linear that consumes these tokens is launched with programmatic stream serialisation: let it
   // start streaming its weights now; it waits for this grid before it reads the tokens.
   allow_dependents();
+  // This grid itself may have been started while the previous kernel of the stream was still running:
+  // that kernel may still write the activations or read the buffers written here.
+  dependency_wait();
   const long m = blockIdx.x;
   const T* xr = x + m * K;
   int8_t* qr = xq + m * K;
@@ -126,8 +129,8 @@ quant_per_token_kernel(const T* __restrict__ x, int8_t* __restrict__ xq, float* 
 // (reference csrc/liquid_gemm/w4a8_wgmma.cu:39-56).
 __global__ void __launch_bounds__(256)
 finish_kernel(const int32_t* __restrict__ acc, const float* __restrict__ ascale,
-              const float* __restrict__ s1, void* __restrict__ y, int out_dtype, int planes, int M,
-              int N, bool vec) {
+              const float* __restrict__ s1, const void* __restrict__ bias, void* __restrict__ y, int out_dtype,
+              int planes, int M, int N, bool vec) {
   // Launched with programmatic stream serialisation behind the kernel that writes the planes: let the
   // kernel after this one start (it prefetches weights, and waits for this grid before it touches
   // tokens, planes or outputs), then wait for the planes to be complete.
@@ -152,8 +155,22 @@ finish_kernel(const int32_t* __restrict__ acc, const float* __restrict__ ascale,
       }
       const float a = ascale[m];
       const float4 w1 = *reinterpret_cast<const float4*>(s1 + n);
-      const float r0 = lqq_scale(v.x, a, w1.x), r1 = lqq_scale(v.y, a, w1.y);
-      const float r2 = lqq_scale(v.z, a, w1.z), r3 = lqq_scale(v.w, a, w1.w);
+      float r0 = lqq_scale(v.x, a, w1.x), r1 = lqq_scale(v.y, a, w1.y);
+      float r2 = lqq_scale(v.z, a, w1.z), r3 = lqq_scale(v.w, a, w1.w);
+      if (bias) {
+        // bias joins the value already rounded to the output type (PyTorch's `y + bias`); the stores
+        // below round the sum once more
+        const float b0 = load_bias(bias, n, out_dtype), b1 = load_bias(bias, n + 1, out_dtype);
+        const float b2 = load_bias(bias, n + 2, out_dtype), b3 = load_bias(bias, n + 3, out_dtype);
+        if (out_dtype == LQ_DT_BF16) {
+          r0 = __bfloat162float(__float2bfloat16_rn(r0)); r1 = __bfloat162float(__float2bfloat16_rn(r1));
+          r2 = __bfloat162float(__float2bfloat16_rn(r2)); r3 = __bfloat162float(__float2bfloat16_rn(r3));
+        } else if (out_dtype == LQ_DT_F16) {
+          r0 = __half2float(__float2half_rn(r0)); r1 = __half2float(__float2half_rn(r1));
+          r2 = __half2float(__float2half_rn(r2)); r3 = __half2float(__float2half_rn(r3));
+        }
+        r0 = __fadd_rn(r0, b0); r1 = __fadd_rn(r1, b1); r2 = __fadd_rn(r2, b2); r3 = __fadd_rn(r3, b3);
+      }
       if (out_dtype == LQ_DT_F32) {
         *reinterpret_cast<float4*>(reinterpret_cast<float*>(y) + idx) = make_float4(r0, r1, r2, r3);
       } else if (out_dtype == LQ_DT_BF16) {
@@ -180,7 +197,8 @@ finish_kernel(const int32_t* __restrict__ acc, const float* __restrict__ ascale,
       int v = acc[idx];
       for (int p = 1; p < planes; ++p) v += acc[(long)p * total + idx];
       if (out_dtype == 3) reinterpret_cast<int32_t*>(y)[idx] = v;
-      else store_out(y, idx, lqq_scale(v, ascale[m], s1[n]), out_dtype);
+      else store_out_bias(y, idx, lqq_scale(v, ascale[m], s1[n]), bias ? load_bias(bias, n, out_dtype) : 0.f,
+                          bias != nullptr, out_dtype);
     }
   }
 }
@@ -258,16 +276,16 @@ static int grid_for(long work_items, int threads, int waves) {
   return (int)blocks;
 }
 
-int launch_finish(const int32_t* acc, const float* ascale, const float* s1, void* y, int out_dtype,
+int launch_finish(const int32_t* acc, const float* ascale, const float* s1, const void* bias, void* y, int out_dtype,
                   int planes, int M, int N, cudaStream_t st) {
   const long total = (long)M * N;
   // four outputs per thread when every row start stays 16-byte aligned
   const uintptr_t align_bits = reinterpret_cast<uintptr_t>(acc) | reinterpret_cast<uintptr_t>(y) |
-                               reinterpret_cast<uintptr_t>(s1);
+                               reinterpret_cast<uintptr_t>(s1) | reinterpret_cast<uintptr_t>(bias);
   const bool vec = (N % 4 == 0) && (align_bits % 16 == 0);
   const long items = vec ? (total >> 2) : total;
   cudaError_t e = launch_overlapped(finish_kernel, dim3(grid_for(items, 256, 8)), dim3(256), (size_t)0, st, acc, ascale,
-                                    s1, y, out_dtype, planes, M, N, vec);
+                                    s1, bias, y, out_dtype, planes, M, N, vec);
   if (e != cudaSuccess) {
     record_cuda_error(e, "finish_kernel launch");
     return LQ_ERR_CUDA;
@@ -307,18 +325,26 @@ int lq_quant_per_token(const void* x, int in_dtype, int8_t* xq, float* ascale, i
   if (!x || !xq || !ascale || M < 0 || K <= 0) return LQ_ERR_BAD_ARG;
   if (M == 0) return LQ_OK;
   cudaStream_t st = as_stream(stream);
+  cudaError_t e;
   switch (in_dtype) {
     case LQ_DT_BF16:
-      quant_per_token_kernel<__nv_bfloat16><<<M, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), xq, ascale, K);
+      e = launch_overlapped(quant_per_token_kernel<__nv_bfloat16>, dim3(M), dim3(256), (size_t)0, st,
+                            static_cast<const __nv_bfloat16*>(x), xq, ascale, K);
       break;
     case LQ_DT_F16:
-      quant_per_token_kernel<__half><<<M, 256, 0, st>>>(static_cast<const __half*>(x), xq, ascale, K);
+      e = launch_overlapped(quant_per_token_kernel<__half>, dim3(M), dim3(256), (size_t)0, st,
+                            static_cast<const __half*>(x), xq, ascale, K);
       break;
     case LQ_DT_F32:
-      quant_per_token_kernel<float><<<M, 256, 0, st>>>(static_cast<const float*>(x), xq, ascale, K);
+      e = launch_overlapped(quant_per_token_kernel<float>, dim3(M), dim3(256), (size_t)0, st,
+                            static_cast<const float*>(x), xq, ascale, K);
       break;
     default:
       return LQ_ERR_BAD_ARG;
+  }
+  if (e != cudaSuccess) {
+    record_cuda_error(e, "quant_per_token_kernel launch");
+    return LQ_ERR_CUDA;
   }
   return check_launch("quant_per_token_kernel");
 }
@@ -328,7 +354,7 @@ int lq_scale_epilogue(const int32_t* acc, const float* ascale, const float* s1, 
   if (!acc || !ascale || !s1 || !y || M < 0 || N <= 0) return LQ_ERR_BAD_ARG;
   if (out_dtype < 0 || out_dtype > 2) return LQ_ERR_BAD_ARG;
   if (M == 0) return LQ_OK;
-  return launch_finish(acc, ascale, s1, y, out_dtype, 1, M, N, as_stream(stream));
+  return launch_finish(acc, ascale, s1, nullptr, y, out_dtype, 1, M, N, as_stream(stream));
 }
 
 size_t lq_tile_blob_bytes(int N, int K) {

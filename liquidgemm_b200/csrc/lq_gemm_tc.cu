@@ -53,17 +53,18 @@ namespace lq {
 
 int tile_pick_splits(int M, int N, int K);                                   // lq_gemm_tile.cu
 size_t tile_workspace_bytes(int M, int N, int splits);                       // lq_gemm_tile.cu
-int run_tile_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, void* out, int out_mode,
-                  int M, int N, int K, int splits, void* ws, size_t ws_bytes, cudaStream_t st);  // lq_gemm_tile.cu
-size_t skinny_workspace_bytes(int M, int N, int K);                          // lq_gemm_skinny.cu
-int run_skinny_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, const OutSpec& out,
-                    const PeerSync* sync, int out_mode, int M, int N, int K, void* ws, size_t ws_bytes,
-                    cudaStream_t st);  // lq_gemm_skinny.cu
+int run_tile_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, const void* bias,
+                  void* out, int out_mode, int M, int N, int K, int splits, void* ws, size_t ws_bytes,
+                  cudaStream_t st);  // lq_gemm_tile.cu
+size_t decode_tc_workspace_bytes(int M, int N, int K);                       // lq_decode_tc.cu
+int run_decode_tc(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, const void* bias,
+                  const OutSpec& out, const PeerSync* sync, int out_mode, int M, int N, int K, void* ws,
+                  size_t ws_bytes, cudaStream_t st);  // lq_decode_tc.cu
 size_t gemv_blob_workspace_bytes(int N, int K);                              // lq_gemv_blob.cu
-int run_gemv_blob_ws(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1,
+int run_gemv_blob_ws(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, const void* bias,
                      const OutSpec& out, const PeerSync* sync, int out_dtype, int M, int N, int K, void* ws,
                      size_t ws_bytes, cudaStream_t st);  // lq_gemv_blob.cu
-int skinny_grid(int N, int K);                                               // lq_gemm_skinny.cu
+int decode_tc_grid(int N, int K);                                            // lq_decode_tc.cu
 int gemv_blob_grid(int N, int K);                                            // lq_gemv_blob.cu
 int launch_gemv_plain_f32(const int8_t* x, const uint8_t* nibbles, const uint8_t* s_u8,
                           const uint8_t* off_a, const float* ascale, const float* s1, float* y, int M,
@@ -787,81 +788,115 @@ int lq_gemm_pick_splitk(int M, int N, int K, int env_override) {
   return 0;
 }
 
-// Which kernel serves (M, splitk): the two-CTAs-per-SM decode-tile kernel with `splits` int32 planes
-// (M <= 128), or the persistent kernel (stream-K for splitk 0 / -1, fixed split otherwise).
+// Which kernel serves (M, splitk).
+enum RouteKind {
+  kRoutePersistent,   // one CTA per SM, stream-K or a fixed split (explicit requests above 128 tokens, splitk -1)
+  kRouteTile,         // two CTAs per SM, one tile each, `splits` int32 planes + finish pass when splits > 1
+  kRouteGemv,         // streaming dp4a GEMV over the blob (scaled outputs only)
+  kRouteDecodeTc,     // streaming tensor-core kernel, one launch, atomic join
+};
 struct Route {
-  bool tile;     // decode-tile kernel with `splits` int32 planes (explicit split-K request, M <= 128)
-  bool skinny;   // streaming stream-K kernel for M <= 128 (the default for decode batches)
+  RouteKind kind;
   int splits;
 };
-// Up to this many tokens the dp4a streaming GEMV over the blob beats the tensor-core kernel (measured on
-// the Llama-3.1-8B shapes); it only produces scaled outputs, the int32 entry point always uses tensor cores.
+// Up to this many tokens the dp4a streaming GEMV over the blob beats the tensor-core kernels (measured on
+// the Llama-3.1-8B shapes: its integer pipe is full at four tokens on the small matrices and at three on the
+// large one); it only produces scaled outputs, the int32 entry point always uses tensor cores.
 constexpr int kGemvBlobMaxM = 4;
 
-// Largest decode batch the single-launch streaming tensor-core kernel serves (its one-atomic-per-element
-// join is cheap only while a CTA holds few tokens; the 32-token configuration additionally measured 3x
-// slower with parked barrier waits, cause not found).  Since the tile kernel got a second dequant set
-// and programmatic dependent launch it is as fast or faster from 5 tokens on (8 tokens, 28672 x 4096:
-// 18.3 vs 20.0 us), so the automatic routing uses the streaming kernels up to kGemvBlobMaxM tokens only;
-// the streaming tensor-core kernel remains the engine of the gather-by-stores entry points.
-constexpr int kSkinnyMaxM = 16;
+// Largest decode batch of the single-launch streaming tensor-core kernel: its one-atomic-per-element
+// join is cheap only while a CTA holds few tokens.  LQ_DECODE_TC_MAX_M (16 or 32) moves the limit for
+// measurements.
+static int decode_tc_max_m() {
+  static const int v = []() {
+    const char* e = getenv("LQ_DECODE_TC_MAX_M");
+    const int n = e ? atoi(e) : 16;
+    return n <= 0 ? 0 : n >= 32 ? 32 : 16;
+  }();
+  return v;
+}
+constexpr int kScatterMaxM = 16;   // the gather-by-stores entry points are decode paths
 
-static Route route_for(int M, int N, int K, int splitk) {
+static bool gemv_serves(int M, int N, int K) {
+  return M <= 2 || (M <= kGemvBlobMaxM && (long)N * K <= (1L << 26));
+}
+
+static Route route_for(int M, int N, int K, int splitk, bool scaled) {
   const int kt = K / 128;
-  if (splitk == -1) return {false, false, 0};
+  if (splitk == -1) return {kRoutePersistent, 0};
   if (M <= 128) {
-    // 3-4 tokens on a large matrix are already integer-issue bound in the dp4a GEMV (28672 x 4096, 4 tokens:
-    // 20.7 us against 18.1 us on tensor cores); small matrices and 1-2 tokens stay on the GEMV
-    if (splitk == 0 && (M <= 2 || (M <= kGemvBlobMaxM && (long)N * K <= (1L << 26)))) return {false, true, 0};
+    if (splitk == 0) {
+      if (scaled && gemv_serves(M, N, K)) return {kRouteGemv, 0};
+      if (M <= decode_tc_max_m()) return {kRouteDecodeTc, 0};
+    }
     int S = splitk > 0 ? splitk : tile_pick_splits(M, N, K);
     if (S > kt) S = kt;
-    return {true, false, S < 1 ? 1 : S};
+    return {kRouteTile, S < 1 ? 1 : S};
   }
-  // Automatic choice: the two-CTAs-per-SM tile kernel.  With two dequant sets it is ahead of the
-  // persistent stream-K kernel at every size measured (M = 256: 2x, M = 2048: 1.1-1.3x, M = 16384 on
+  // Automatic choice above 128 tokens: the two-CTAs-per-SM tile kernel.  With two dequant sets it is ahead
+  // of the persistent stream-K kernel at every size measured (M = 256: 2x, M = 2048: 1.1-1.3x, M = 16384 on
   // 28672 x 4096: 1.13x); the persistent kernel stays reachable through an explicit split argument.
-  if (splitk == 0) return {true, false, tile_pick_splits(M, N, K)};
-  return {false, false, splitk};
+  if (splitk == 0) return {kRouteTile, tile_pick_splits(M, N, K)};
+  return {kRoutePersistent, splitk};
 }
 
+static size_t route_ws_bytes(const Route& r, int M, int N, int K) {
+  switch (r.kind) {
+    case kRouteGemv: return gemv_blob_workspace_bytes(N, K);
+    case kRouteDecodeTc: return decode_tc_workspace_bytes(M, N, K);
+    case kRouteTile: return tile_workspace_bytes(M, N, r.splits);
+    default: return make_plan(M, N, K, r.splits).ws_bytes;
+  }
+}
+
+// The size does not know whether the caller wants scaled or int32 outputs: the larger of the two routes.
 size_t lq_gemm_workspace_bytes(int M, int N, int K, int splitk) {
   if (M <= 0 || N <= 0 || K < 128) return 0;
-  const Route r = route_for(M, N, K, splitk);
-  if (r.skinny) {
-    const size_t a = skinny_workspace_bytes(M, N, K), b = M <= kGemvBlobMaxM ? gemv_blob_workspace_bytes(N, K) : 0;
-    return a > b ? a : b;
-  }
-  return r.tile ? tile_workspace_bytes(M, N, r.splits) : make_plan(M, N, K, r.splits).ws_bytes;
+  const size_t a = route_ws_bytes(route_for(M, N, K, splitk, true), M, N, K);
+  const size_t b = route_ws_bytes(route_for(M, N, K, splitk, false), M, N, K);
+  return a > b ? a : b;
 }
 
+// 0: none, 1: scratch (split-K planes; any content), 2: the shared buffer that is all zero between calls.
 int lq_gemm_workspace_kind(int M, int N, int K, int splitk) {
   if (lq_gemm_workspace_bytes(M, N, K, splitk) == 0) return 0;
-  return route_for(M, N, K, splitk).tile ? 1 : 2;
+  return route_for(M, N, K, splitk, true).kind == kRouteTile ? 1 : 2;
 }
 
-static int blob_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, void* out, int out_mode,
-                     int M, int N, int K, int splitk, void* ws, size_t ws_bytes, cudaStream_t st) {
+// Kernel launches one call makes (for callers that count them).
+int lq_gemm_launches(int M, int N, int K, int splitk) {
+  if (M <= 0 || N <= 0 || K < 128) return 0;
+  const Route r = route_for(M, N, K, splitk, true);
+  return (r.kind == kRouteTile && r.splits > 1) ? 2 : 1;
+}
+
+static int blob_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, const void* bias,
+                     void* out, int out_mode, int M, int N, int K, int splitk, void* ws, size_t ws_bytes,
+                     cudaStream_t st) {
   if (!x || !blob || !out || M < 0 || N <= 0 || K <= 0) return LQ_ERR_BAD_ARG;
   if (K % 128) return LQ_ERR_SHAPE;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(blob)) % 16) return LQ_ERR_BAD_ARG;
   if (M == 0) return LQ_OK;
-  const Route r = route_for(M, N, K, splitk);
-  if (r.skinny) {
+  const Route r = route_for(M, N, K, splitk, out_mode != kOutI32);
+  if (r.kind != kRoutePersistent) {
     if (int rc = lq_check_device()) return rc;
-    if (M <= kGemvBlobMaxM && out_mode != kOutI32)
-      return run_gemv_blob_ws(x, blob, ascale, s1, single_out(out, N), nullptr, out_mode, M, N, K, ws, ws_bytes, st);
-    return run_skinny_gemm(x, blob, ascale, s1, single_out(out, N), nullptr, out_mode, M, N, K, ws, ws_bytes, st);
   }
-  if (r.tile) {
-    if (int rc = lq_check_device()) return rc;
-    return run_tile_gemm(x, blob, ascale, s1, out, out_mode, M, N, K, r.splits, ws, ws_bytes, st);
+  switch (r.kind) {
+    case kRouteGemv:
+      return run_gemv_blob_ws(x, blob, ascale, s1, bias, single_out(out, N), nullptr, out_mode, M, N, K, ws, ws_bytes, st);
+    case kRouteDecodeTc:
+      return run_decode_tc(x, blob, ascale, s1, bias, single_out(out, N), nullptr, out_mode, M, N, K, ws, ws_bytes, st);
+    case kRouteTile:
+      return run_tile_gemm(x, blob, ascale, s1, bias, out, out_mode, M, N, K, r.splits, ws, ws_bytes, st);
+    default:
+      if (bias) return LQ_ERR_BAD_ARG;   // the persistent kernel has no bias epilogue
+      return run_gemm<kBlob>(x, blob, nullptr, nullptr, ascale, s1, out, out_mode, M, N, K, r.splits, ws, ws_bytes, st);
   }
-  return run_gemm<kBlob>(x, blob, nullptr, nullptr, ascale, s1, out, out_mode, M, N, K, r.splits, ws, ws_bytes, st);
 }
 
 int lq_w4a8_gemm_i32(const int8_t* x_i8, const uint8_t* blob, int32_t* acc, int M, int N, int K, int splitk,
                      void* workspace, size_t workspace_bytes, void* stream) {
-  return blob_gemm(x_i8, blob, nullptr, nullptr, acc, kOutI32, M, N, K, splitk, workspace, workspace_bytes,
+  return blob_gemm(x_i8, blob, nullptr, nullptr, nullptr, acc, kOutI32, M, N, K, splitk, workspace, workspace_bytes,
                    as_stream(stream));
 }
 
@@ -869,7 +904,16 @@ int lq_w4a8_gemm_fused(const int8_t* x_i8, const uint8_t* blob, const float* asc
                        int out_dtype, int M, int N, int K, int splitk, void* workspace, size_t workspace_bytes,
                        void* stream) {
   if (!ascale || !s1 || out_dtype < 0 || out_dtype > 2) return LQ_ERR_BAD_ARG;
-  return blob_gemm(x_i8, blob, ascale, s1, y, out_dtype, M, N, K, splitk, workspace, workspace_bytes,
+  return blob_gemm(x_i8, blob, ascale, s1, nullptr, y, out_dtype, M, N, K, splitk, workspace, workspace_bytes,
+                   as_stream(stream));
+}
+
+int lq_w4a8_linear_bias(const int8_t* x_i8, const uint8_t* blob, const float* ascale, const float* s1,
+                        const void* bias, void* y, int out_dtype, int M, int N, int K, void* workspace,
+                        size_t workspace_bytes, void* stream) {
+  if (!ascale || !s1 || out_dtype < 0 || out_dtype > 2) return LQ_ERR_BAD_ARG;
+  if (bias && (reinterpret_cast<uintptr_t>(bias) % (out_dtype == LQ_DT_F32 ? 4 : 2))) return LQ_ERR_BAD_ARG;
+  return blob_gemm(x_i8, blob, ascale, s1, bias, y, out_dtype, M, N, K, 0, workspace, workspace_bytes,
                    as_stream(stream));
 }
 
@@ -880,7 +924,7 @@ int lq_w4a8_gemm_fused_scatter_sync(const int8_t* x_i8, const uint8_t* blob, con
                                     size_t workspace_bytes, void* stream) {
   if (!x_i8 || !blob || !ascale || !s1 || !outs || n_outs < 1 || n_outs > 8) return LQ_ERR_BAD_ARG;
   if (out_dtype < 0 || out_dtype > 2 || ld_out < N || col0 < 0 || col0 + N > ld_out) return LQ_ERR_BAD_ARG;
-  if (M < 1 || M > kSkinnyMaxM || N <= 0 || K < 128 || K % 128) return LQ_ERR_SHAPE;
+  if (M < 1 || M > kScatterMaxM || N <= 0 || K < 128 || K % 128) return LQ_ERR_SHAPE;
   if ((reinterpret_cast<uintptr_t>(x_i8) | reinterpret_cast<uintptr_t>(blob)) % 16) return LQ_ERR_BAD_ARG;
   if (flag_index < 0) return LQ_ERR_BAD_ARG;
   OutSpec o = {};
@@ -898,11 +942,11 @@ int lq_w4a8_gemm_fused_scatter_sync(const int8_t* x_i8, const uint8_t* blob, con
   ps.wait = wait_flag;
   ps.wait_value = wait_value;
   if (int rc = lq_check_device()) return rc;
-  if (M <= kGemvBlobMaxM)
-    return run_gemv_blob_ws(x_i8, blob, ascale, s1, o, &ps, out_dtype, M, N, K, workspace, workspace_bytes,
+  if (gemv_serves(M, N, K))
+    return run_gemv_blob_ws(x_i8, blob, ascale, s1, nullptr, o, &ps, out_dtype, M, N, K, workspace, workspace_bytes,
                             as_stream(stream));
-  return run_skinny_gemm(x_i8, blob, ascale, s1, o, &ps, out_dtype, M, N, K, workspace, workspace_bytes,
-                         as_stream(stream));
+  return run_decode_tc(x_i8, blob, ascale, s1, nullptr, o, &ps, out_dtype, M, N, K, workspace, workspace_bytes,
+                       as_stream(stream));
 }
 
 int lq_w4a8_gemm_fused_scatter(const int8_t* x_i8, const uint8_t* blob, const float* ascale, const float* s1,
@@ -913,14 +957,13 @@ int lq_w4a8_gemm_fused_scatter(const int8_t* x_i8, const uint8_t* blob, const fl
 }
 
 size_t lq_scatter_workspace_bytes(int M, int N, int K) {
-  if (M < 1 || M > kSkinnyMaxM || N <= 0 || K < 128 || K % 128) return 0;
-  const size_t a = skinny_workspace_bytes(M, N, K), b = M <= kGemvBlobMaxM ? gemv_blob_workspace_bytes(N, K) : 0;
-  return a > b ? a : b;
+  if (M < 1 || M > kScatterMaxM || N <= 0 || K < 128 || K % 128) return 0;
+  return gemv_serves(M, N, K) ? gemv_blob_workspace_bytes(N, K) : decode_tc_workspace_bytes(M, N, K);
 }
 
 int lq_decode_grid(int M, int N, int K) {
-  if (M < 1 || M > kSkinnyMaxM || N <= 0 || K < 128 || K % 128) return 0;
-  return M <= kGemvBlobMaxM ? gemv_blob_grid(N, K) : skinny_grid(N, K);
+  if (M < 1 || M > kScatterMaxM || N <= 0 || K < 128 || K % 128) return 0;
+  return gemv_serves(M, N, K) ? gemv_blob_grid(N, K) : decode_tc_grid(N, K);
 }
 
 int lq_w4a8_gemm_rowmajor(const int8_t* x_i8, const uint8_t* gpack, const uint8_t* s_u8, const uint8_t* offset_a,

@@ -16,6 +16,7 @@
 // epilogue, the sets sharing the accumulator's columns.  All waits are bounded.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "lq_common.cuh"
@@ -23,7 +24,7 @@
 
 namespace lq {
 
-int launch_finish(const int32_t* acc, const float* ascale, const float* s1, void* y, int out_dtype,
+int launch_finish(const int32_t* acc, const float* ascale, const float* s1, const void* bias, void* y, int out_dtype,
                   int planes, int M, int N, cudaStream_t st);  // lq_elementwise.cu
 int make_byte_matrix_map(CUtensorMap* map, const void* ptr, long rows, long row_bytes, int box_rows,
                          int box_bytes);  // lq_gemm_tc.cu
@@ -45,6 +46,7 @@ struct GemmArgs {
   const uint8_t* blob;   // W4: tile blob
   const float* ascale;   // [M]
   const float* s1;       // [N]
+  const void* bias;      // [N] in the output dtype, or null (fused epilogue only)
   void* out;             // scaled output [M,N] or int32 planes [splits][M][N]
   int* status;
   int out_mode;          // LQ_DT_* or kOutI32
@@ -218,6 +220,22 @@ w4a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs args
         const uint32_t meta = *reinterpret_cast<const uint32_t*>(wst + 8192 + row * 4);
         ptx::mbar_arrive(bar_empty + 8 * s);
 
+        // Unpack into registers first, wait for the operand stage afterwards: the arithmetic of this k-step
+        // overlaps the MMAs that still read the stage.
+        const uint32_t step0 = meta & 0xffu, a0 = ((meta >> 8) & 0xffu) * 0x01010101u;
+        const uint32_t step1 = (meta >> 16) & 0xffu, a1 = (meta >> 24) * 0x01010101u;
+        uint32_t v[4][8];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const uint32_t step = c < 2 ? step0 : step1;
+          const uint32_t ab = c < 2 ? a0 : a1;
+          const uint32_t pk[4] = {ch[c].x, ch[c].y, ch[c].z, ch[c].w};
+#pragma unroll
+          for (int h = 0; h < 4; ++h) {
+            v[c][2 * h] = lqq_dequant4(pk[h] & 0x0F0F0F0Fu, step, ab);
+            v[c][2 * h + 1] = lqq_dequant4((pk[h] >> 4) & 0x0F0F0F0Fu, step, ab);
+          }
+        }
         if (!ptx::mbar_wait_bounded(bar_afree + 8 * t, pht ^ 1u, kWaitLimitNs)) {
           atomicExch(args.status, 104);
           ok = false;
@@ -225,21 +243,8 @@ w4a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs args
         }
         __syncwarp();   // lanes leave the poll loops one by one; tcgen05.st / wait::st need the warp converged
         ptx::tc_fence_after();
-        const uint32_t step0 = meta & 0xffu, a0 = ((meta >> 8) & 0xffu) * 0x01010101u;
-        const uint32_t step1 = (meta >> 16) & 0xffu, a1 = (meta >> 24) * 0x01010101u;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const uint32_t step = c < 2 ? step0 : step1;
-          const uint32_t ab = c < 2 ? a0 : a1;
-          const uint32_t pk[4] = {ch[c].x, ch[c].y, ch[c].z, ch[c].w};
-          uint32_t v[8];
-#pragma unroll
-          for (int h = 0; h < 4; ++h) {
-            v[2 * h] = lqq_dequant4(pk[h] & 0x0F0F0F0Fu, step, ab);
-            v[2 * h + 1] = lqq_dequant4((pk[h] >> 4) & 0x0F0F0F0Fu, step, ab);
-          }
-          ptx::tmem_st8(tmem_a + lane_addr + t * 32 + c * 8, v);
-        }
+        for (int c = 0; c < 4; ++c) ptx::tmem_st8(tmem_a + lane_addr + t * 32 + c * 8, v[c]);
         ptx::tc_wait_st();
         ptx::tc_fence_before();
         ptx::mbar_arrive(bar_aready + 8 * t);
@@ -256,6 +261,8 @@ w4a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs args
       const long n = (long)nt * 128 + row;
       const bool n_ok = n < args.N;
       const float w_scale = (n_ok && args.out_mode != kOutI32) ? args.s1[n] : 0.f;
+      const bool has_bias = args.out_mode != kOutI32 && args.bias != nullptr;
+      const float bias = (has_bias && n_ok) ? load_bias(args.bias, n, args.out_mode) : 0.f;
       int32_t* plane = reinterpret_cast<int32_t*>(args.out) + (size_t)z * args.M * args.N;
 #pragma unroll 1
       for (int c0 = 16 * set; c0 < BN; c0 += 16 * kSets) {   // the sets share the accumulator's columns
@@ -274,7 +281,7 @@ w4a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs args
             if (m < args.M) {
               const size_t idx = (size_t)m * args.N + n;
               if (args.out_mode == kOutI32) plane[idx] = v[j];
-              else store_out(args.out, idx, lqq_scale(v[j], sc[j], w_scale), args.out_mode);
+              else store_out_bias(args.out, idx, lqq_scale(v[j], sc[j], w_scale), bias, has_bias, args.out_mode);
             }
           }
         }
@@ -315,6 +322,37 @@ static int launch_cfg(const CUtensorMap& tx, const GemmArgs& a, int splits, cuda
   return check_launch("w4a8_tile_kernel");
 }
 
+// Token-tile widths: the smallest that holds a decode batch; for prefill 128 or 192 tokens.  A dequantised
+// weight tile costs the same whatever it is multiplied with, so wider token tiles do more tensor-core
+// work per unpacked byte (192 tokens: 1.5x); but tiles are not split further, so the width that leaves
+// the last wave of two CTAs per SM fullest wins.
+static int wide_tiles() {
+  static const int v = []() {
+    const char* e = getenv("LQ_TILE_WIDE");
+    return e ? atoi(e) : 0;
+  }();
+  return v;
+}
+static int tile_bn_for(int M, int N) {
+  if (M <= 128) return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
+  if (!wide_tiles()) return 128;
+  const long slots = 2L * sm_count();
+  const long nt = (N + 127) / 128;
+  double best = 0;
+  int best_bn = 128;
+  const int cand[2] = {128, 192};
+  for (int bn : cand) {
+    const long tiles = nt * ((M + bn - 1) / bn);
+    const long waves = (tiles + slots - 1) / slots;
+    // useful token columns per unit of time: a wave of 192-token tiles takes about 1.25x a wave of 128
+    const double rate = (double)M / ((double)waves * (bn == 192 ? 1.25 : 1.0));
+    if (rate > best * 1.0001) {
+      best = rate;
+      best_bn = bn;
+    }
+  }
+  return best_bn;
+}
 static int tile_bn(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128; }
 
 }  // namespace tile
@@ -340,11 +378,12 @@ size_t tile_workspace_bytes(int M, int N, int splits) {
 }
 
 // out_mode: LQ_DT_* or 3 (raw int32).  Any M.  `ws` holds `splits` int32 planes (need not be zeroed).
-int run_tile_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, void* out, int out_mode,
-                  int M, int N, int K, int splits, void* ws, size_t ws_bytes, cudaStream_t st) {
+int run_tile_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, const void* bias,
+                  void* out, int out_mode, int M, int N, int K, int splits, void* ws, size_t ws_bytes,
+                  cudaStream_t st) {
   using namespace tile;
   if (splits > 1 && (!ws || ws_bytes < tile_workspace_bytes(M, N, splits))) return LQ_ERR_WORKSPACE;
-  const int bn = tile_bn(M);
+  const int bn = splits > 1 ? tile_bn(M) : tile_bn_for(M, N);
   CUtensorMap tx;
   int rc = make_byte_matrix_map(&tx, x, M, K, bn, 128);
   if (rc) return rc;
@@ -352,6 +391,7 @@ int run_tile_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, con
   a.blob = blob;
   a.ascale = splits > 1 ? nullptr : ascale;
   a.s1 = splits > 1 ? nullptr : s1;
+  a.bias = splits > 1 ? nullptr : bias;
   a.out = splits > 1 ? ws : out;
   a.status = status_word();
   a.out_mode = splits > 1 ? kOutI32 : out_mode;
@@ -364,10 +404,11 @@ int run_tile_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, con
     case 16: rc = launch_cfg<16, 8, 4, true>(tx, a, splits, st); break;
     case 32: rc = launch_cfg<32, 8, 4, true>(tx, a, splits, st); break;
     case 64: rc = launch_cfg<64, 6, 4, true>(tx, a, splits, st); break;
+    case 192: rc = launch_cfg<192, 3, 2, true>(tx, a, splits, st); break;
     default: rc = launch_cfg<128, 4, 4, true>(tx, a, splits, st); break;
   }
   if (rc || splits <= 1) return rc;
-  return launch_finish(static_cast<const int32_t*>(ws), ascale, s1, out, out_mode, splits, M, N, st);
+  return launch_finish(static_cast<const int32_t*>(ws), ascale, s1, bias, out, out_mode, splits, M, N, st);
 }
 
 }  // namespace lq

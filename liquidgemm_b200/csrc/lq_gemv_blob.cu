@@ -13,7 +13,9 @@
 //  * the partial sums of an n-tile cut by a range boundary meet in a zeroed workspace word per
 //    output element through ONE returning 64-bit atomic add that carries the k-tile count along with
 //    the sum; whoever completes the count stores the output and re-zeroes the word.  Integer addition
-//    commutes, so the result is bit-identical for every grid size.
+//    commutes, so the result is bit-identical for every grid size.  A CTA whose range starts inside one
+//    tile and ends inside the next issues the atomics of the first tile and reads their results only
+//    after its last tile, so their round trip through L2 is hidden behind the stream.
 // Every wait is bounded: on expiry the thread records a site code in the status word, stops waiting
 // and runs the rest of its control flow (barriers included) so the CTA still exits.
 
@@ -34,6 +36,10 @@ constexpr int kTileBytes = 8704;   // 4 chunks x [128 rows][16 B] + [128 rows][s
 constexpr int kConsumers = 256;
 constexpr int kThreads = 32 + kConsumers;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
+// The wait for tokens gathered from peer GPUs gives up well before the barrier waits of the threads that
+// depend on it, so that one late peer is reported once (by the producer) and the rest of the CTA still
+// finishes its reduction and leaves the workspace clean.
+constexpr uint64_t kPeerWaitLimitNs = 1000000000ull;
 
 struct Args {
   const uint8_t* blob;
@@ -45,7 +51,7 @@ struct Args {
   int* status;
   int out_dtype;
   int M, N, K, fixed_split;
-  long long* trace;      // pipeline studies: [grid][4] globaltimer stamps, or null
+  const void* bias;      // [N] in the output dtype, or null
 };
 
 template <int MT, int NS>
@@ -57,7 +63,10 @@ struct Cfg {
   // Never three CTAs on one SM: with programmatic dependent launch the next kernel's CTAs fill whatever
   // fits, and an SM that holds three streams while its neighbour holds one makes the slowest CTA
   // (hence the kernel) much later than the average one.  Asking for more than a third of the SM's
-  // shared memory caps residency at two.
+  // shared memory caps residency at two.  (Sizing the CTAs so that four fit, in the hope that the next
+  // launch's two CTAs per SM would sit beside this launch's and have their first ring of tiles loaded
+  // early, measured 5-30 % slower on every shape: the grids are not all exactly two CTAs per SM, so some
+  // SMs end up with three streams of one launch.)
   static constexpr int kSmemBytes = kUsedBytes > 78 * 1024 ? kUsedBytes : 78 * 1024;
 };
 
@@ -122,7 +131,7 @@ gemv_blob_kernel(const Args args, const std::conditional_t<MULTI, MultiOut, NoMu
       auto meet_dependency = [&]() {
         dependency_wait();
         if constexpr (MULTI) {
-          if (!peer_wait(multi.sync, kWaitLimitNs)) atomicExch(args.status, 303);   // tokens gathered from peers
+          if (!peer_wait(multi.sync, kPeerWaitLimitNs)) atomicExch(args.status, 303);   // tokens gathered from peers
         }
         dependency_met = true;
         const int n = issued < NS ? issued : NS;
@@ -173,22 +182,39 @@ gemv_blob_kernel(const Args args, const std::conditional_t<MULTI, MultiOut, NoMu
     const uint32_t meta_off = 8192u + (uint32_t)row * 4 + 2 * h;
     Ring<NS> ring;
     bool ok = true;
-    const bool tracing = args.trace != nullptr && c == 0;
     dependency_wait();   // outputs, the reduction workspace and the tokens belong to earlier kernels until here
-    if (tracing) {
-      uint32_t smid;
-      asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-      args.trace[blockIdx.x * 4 + 0] = (long long)ptx::globaltimer_ns();
-      args.trace[(size_t)gridDim.x * 4 + blockIdx.x] = smid;   // SM ids behind the stamps
-    }
-    bool first = true;
-    auto emit = [&](long m, long n, float v) {
-      if constexpr (MULTI) store_out_all(multi.out, m, n, v, args.out_dtype);
-      else store_out(args.out, (size_t)m * args.N + n, v, args.out_dtype);
+    const bool has_bias = args.bias != nullptr;
+    auto emit = [&](long m, long n, float v, float bias) {
+      if constexpr (MULTI) store_out_all(multi.out, m, n, v, bias, has_bias, args.out_dtype);
+      else store_out_bias(args.out, (size_t)m * args.N + n, v, bias, has_bias, args.out_dtype);
     };
     float a_scale[MT];   // token scales: read once, they are needed right after the last tile
 #pragma unroll
     for (int m = 0; m < MT; ++m) a_scale[m] = (m < M) ? __ldg(args.ascale + m) : 0.f;
+
+    // A partial segment whose atomics are in flight while the CTA streams its next segment.
+    bool pend = false;
+    unsigned long long pend_old[MT];
+    int pend_acc[MT];
+    long pend_n = 0;
+    long long pend_nk = 0;
+    float pend_w = 0.f;
+    unsigned long long* pend_slot = nullptr;
+    // The thread whose add completed the tile's k-tile count holds the full sum in the value it got back:
+    // it re-zeroes the word and stores the output.
+    auto finish_partial = [&](const unsigned long long (&old)[MT], const int (&part)[MT], long n, long long nk,
+                              float w_scale, unsigned long long* slot) {
+      const float bias = has_bias ? load_bias(args.bias, n, args.out_dtype) : 0.f;
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        if (m < M && (long long)(old[m] >> 40) + nk == (long long)kt_total) {
+          const long long total = (long long)(old[m] & ((1ull << 40) - 1)) + (long long)part[m] + (nk << 21) -
+                                  ((long long)kt_total << 21);
+          __stcg(slot + m * 128 + row, 0ull);
+          emit(m, n, lqq_scale((int)total, a_scale[m], w_scale), bias);
+        }
+      }
+    };
 
     while (walk.next(sg)) {
       const long n = (long)sg.tile * 128 + row;
@@ -202,10 +228,6 @@ gemv_blob_kernel(const Args args, const std::conditional_t<MULTI, MultiOut, NoMu
         if (ok && !ptx::mbar_wait_bounded(bar_full + 8 * ring.s, ring.ph, kWaitLimitNs)) {
           atomicExch(args.status, 302);
           ok = false;
-        }
-        if (first) {
-          if (tracing) args.trace[blockIdx.x * 4 + 1] = (long long)ptx::globaltimer_ns();
-          first = false;
         }
         const uint8_t* wst = smem + (ws - base) + ring.s * kTileBytes;
         const uint4 c0 = *reinterpret_cast<const uint4*>(wst + w_off);
@@ -239,7 +261,6 @@ gemv_blob_kernel(const Args args, const std::conditional_t<MULTI, MultiOut, NoMu
         ring.advance();
       }
 
-      if (tracing) args.trace[blockIdx.x * 4 + 2] = (long long)ptx::globaltimer_ns();   // last main loop end
       // ---- reduce the two k-groups of every row, then finish or publish the partial sums
       if (h == 1) {
 #pragma unroll
@@ -253,40 +274,44 @@ gemv_blob_kernel(const Args args, const std::conditional_t<MULTI, MultiOut, NoMu
       }
       if (sg.whole) {
         if (mine) {
+          const float bias = has_bias ? load_bias(args.bias, n, args.out_dtype) : 0.f;
 #pragma unroll
           for (int m = 0; m < MT; ++m)
-            if (m < M) emit(m, n, lqq_scale(acc[m], a_scale[m], w_scale));
+            if (m < M) emit(m, n, lqq_scale(acc[m], a_scale[m], w_scale), bias);
         }
-        consumer_barrier();   // `red` may be rewritten by the next segment
-      } else {
+      } else if (mine) {
         // One returning 64-bit atomic per element does the whole cross-CTA reduction: the word holds
         // the number of k-tiles added so far (bits 40..) and the sum of the contributions, each
-        // biased by 2^21 per k-tile so that it is non-negative and never borrows from the count.
-        // The thread whose add completes the tile's k-tile count holds the full sum in the value it
-        // got back, stores the output and re-zeroes the word: no fence, no counter, no read-back.
+        // biased by 2^21 per k-tile so that it is non-negative and never borrows from the count:
+        // no fence, no counter, no read-back.
         unsigned long long* slot = args.slots + (size_t)sg.slot * (MT * 128);
-        if (mine) {
-          const long long nk = sg.ke - sg.kb;
-          unsigned long long old[MT];
+        const long long nk = sg.ke - sg.kb;
+        unsigned long long old[MT];
 #pragma unroll
-          for (int m = 0; m < MT; ++m) {
-            const unsigned long long add = (unsigned long long)((long long)acc[m] + (nk << 21)) |
-                                           ((unsigned long long)nk << 40);
-            old[m] = (m < M) ? atomicAdd(slot + m * 128 + row, add) : 0ull;
-          }
-#pragma unroll
-          for (int m = 0; m < MT; ++m) {
-            if (m < M && (long long)(old[m] >> 40) + nk == (long long)kt_total) {
-              const long long total = (long long)(old[m] & ((1ull << 40) - 1)) + (long long)acc[m] + (nk << 21) -
-                                      ((long long)kt_total << 21);
-              __stcg(slot + m * 128 + row, 0ull);
-              emit(m, n, lqq_scale((int)total, a_scale[m], w_scale));
-            }
-          }
+        for (int m = 0; m < MT; ++m) {
+          const unsigned long long add = (unsigned long long)((long long)acc[m] + (nk << 21)) |
+                                         ((unsigned long long)nk << 40);
+          old[m] = (m < M) ? atomicAdd(slot + m * 128 + row, add) : 0ull;
         }
-        consumer_barrier();   // `red` may be rewritten by the next segment
+        if (walk.has_more() && !pend) {
+          // more tiles follow: look at the returned values after them
+          pend = true;
+#pragma unroll
+          for (int m = 0; m < MT; ++m) {
+            pend_old[m] = old[m];
+            pend_acc[m] = acc[m];
+          }
+          pend_n = n;
+          pend_nk = nk;
+          pend_w = w_scale;
+          pend_slot = slot;
+        } else {
+          finish_partial(old, acc, n, nk, w_scale, slot);
+        }
       }
+      consumer_barrier();   // `red` may be rewritten by the next segment
     }
+    if (pend) finish_partial(pend_old, pend_acc, pend_n, pend_nk, pend_w, pend_slot);
     if constexpr (MULTI) {
       // Every output store of this CTA, including those into peer memory, is ordered before the flags:
       // the barrier makes the other threads' stores visible to thread 0 (CTA scope), and the release of
@@ -296,7 +321,6 @@ gemv_blob_kernel(const Args args, const std::conditional_t<MULTI, MultiOut, NoMu
         peer_signal(multi.sync);   // red.release.sys: ordered after everything the barrier made visible
       }
     }
-    if (tracing) args.trace[blockIdx.x * 4 + 3] = (long long)ptx::globaltimer_ns();
   }
   __syncthreads();
 }
@@ -325,8 +349,6 @@ static int launch(const Args& a, const MultiOut* multi, int grid, cudaStream_t s
   return check_launch("gemv_blob_kernel");
 }
 
-static long long* g_trace = nullptr;
-
 static DecodePlan plan_for(int N, int K) { return decode_plan((N + 127) / 128, K / 128, 2 * sm_count(), false); }
 static int grid_for(int N, int K) { return plan_for(N, K).grid; }
 
@@ -344,13 +366,13 @@ size_t gemv_blob_workspace_bytes(int N, int K) {
 }
 
 // Same call with a size-checked workspace, for the GEMM entry points.
-int run_gemv_blob_ws(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1,
+int run_gemv_blob_ws(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, const void* bias,
                      const OutSpec& out, const PeerSync* sync, int out_dtype, int M, int N, int K, void* ws,
                      size_t ws_bytes, cudaStream_t st);
 
-int run_gemv_blob(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, const OutSpec& out,
-                  const PeerSync* sync, int out_dtype, int M, int N, int K, unsigned long long* slots,
-                  cudaStream_t st) {
+int run_gemv_blob(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, const void* bias,
+                  const OutSpec& out, const PeerSync* sync, int out_dtype, int M, int N, int K,
+                  unsigned long long* slots, cudaStream_t st) {
   using namespace gblob;
   Args a;
   a.blob = blob;
@@ -367,7 +389,7 @@ int run_gemv_blob(const int8_t* x, const uint8_t* blob, const float* ascale, con
   a.N = N;
   a.K = K;
   a.fixed_split = plan_for(N, K).fixed_split;
-  a.trace = g_trace;
+  a.bias = bias;
   if (!a.status) return LQ_ERR_CUDA;
   const int grid = grid_for(N, K);
   if (!multi) {
@@ -385,12 +407,13 @@ int run_gemv_blob(const int8_t* x, const uint8_t* blob, const float* ascale, con
   return launch<8, 7, true>(a, &mo, grid, st);
 }
 
-int run_gemv_blob_ws(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1,
+int run_gemv_blob_ws(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, const void* bias,
                      const OutSpec& out, const PeerSync* sync, int out_dtype, int M, int N, int K, void* ws,
                      size_t ws_bytes, cudaStream_t st) {
   const int grid = gblob::grid_for(N, K);
   if (!ws || ws_bytes < gemv_blob_ws_bytes(grid)) return LQ_ERR_WORKSPACE;
-  return run_gemv_blob(x, blob, ascale, s1, out, sync, out_dtype, M, N, K, static_cast<unsigned long long*>(ws), st);
+  return run_gemv_blob(x, blob, ascale, s1, bias, out, sync, out_dtype, M, N, K,
+                       static_cast<unsigned long long*>(ws), st);
 }
 
 }  // namespace lq
@@ -398,11 +421,6 @@ int run_gemv_blob_ws(const int8_t* x, const uint8_t* blob, const float* ascale, 
 using namespace lq;
 
 extern "C" {
-
-// Pipeline-study hook: device buffer of 4 x int64 per CTA (2 x SM count CTAs) that receives
-// globaltimer stamps (start, first tile landed, last main loop done, exit), followed by one int64 SM id
-// per CTA; null switches it off.
-LQ_API void lq_debug_set_blob_trace(void* device_buffer) { gblob::g_trace = static_cast<long long*>(device_buffer); }
 
 LQ_API size_t lq_gemv_blob_workspace_bytes(void) { return gemv_blob_ws_bytes(2 * sm_count()); }
 
@@ -416,8 +434,8 @@ LQ_API int lq_w4a8_gemv_blob(const void* x_i8, const void* blob, const void* asc
   const int grid = gblob::grid_for(N, K);
   if (!workspace || workspace_bytes < gemv_blob_ws_bytes(grid)) return LQ_ERR_WORKSPACE;
   return run_gemv_blob(static_cast<const int8_t*>(x_i8), static_cast<const uint8_t*>(blob),
-                       static_cast<const float*>(ascale), static_cast<const float*>(s1), single_out(out, N), nullptr,
-                       out_dtype, M, N, K, static_cast<unsigned long long*>(workspace), as_stream(stream));
+                       static_cast<const float*>(ascale), static_cast<const float*>(s1), nullptr, single_out(out, N),
+                       nullptr, out_dtype, M, N, K, static_cast<unsigned long long*>(workspace), as_stream(stream));
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -430,7 +448,7 @@ namespace gblob {
 
 // Room for 512 CTAs (two per SM on up to 256 SMs): 512 x (8 tokens x 128 rows x 8 B) reduction
 // words, 4 194 304 bytes of device memory that exist as long as the library is loaded.  The loader
-// zero-fills it; the kernel leaves it zero-filled.
+// zero-fills it; every kernel that completes leaves it zero-filled.
 constexpr int kStaticMaxCtas = 512;
 constexpr size_t kStaticBytes = (size_t)kStaticMaxCtas * 8 * 128 * 8;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticBytes];
@@ -439,7 +457,11 @@ static void* g_static_ptr[64];
 static cudaError_t g_static_err[64];
 static std::once_flag g_static_once[64];
 
-// First use on a device (that device current): resolve the array's address and clear it once.
+// First use on a device (that device current): resolve the array's address and clear it once.  The host
+// name `g_static_scratch` is only a handle for the runtime; the kernel needs the device address that
+// cudaGetSymbolAddress returns for the current device.  cudaMemset on device memory returns before the
+// fill has run and is ordered only against the legacy default stream, so the set-up ends with a device-wide
+// synchronise: when it returns the array is zero for a kernel on ANY stream, blocking or not.
 static void* static_scratch_for_current_device() {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
@@ -447,6 +469,7 @@ static void* static_scratch_for_current_device() {
     void* p = nullptr;
     cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
     if (e == cudaSuccess) e = cudaMemset(p, 0, kStaticBytes);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
     g_static_err[dev] = e;
     g_static_ptr[dev] = e == cudaSuccess ? p : nullptr;
     if (e != cudaSuccess) record_cuda_error(e, "static GEMV scratch set-up");
@@ -474,8 +497,22 @@ LQ_API int lq_w4a8_gemv_blob_static(const void* x_i8, const void* blob, const vo
   void* p = gblob::static_scratch_for_current_device();
   if (!p) return LQ_ERR_CUDA;
   return run_gemv_blob(static_cast<const int8_t*>(x_i8), static_cast<const uint8_t*>(blob),
-                       static_cast<const float*>(ascale), static_cast<const float*>(s1), single_out(out, N), nullptr,
-                       out_dtype, M, N, K, static_cast<unsigned long long*>(p), as_stream(stream));
+                       static_cast<const float*>(ascale), static_cast<const float*>(s1), nullptr, single_out(out, N),
+                       nullptr, out_dtype, M, N, K, static_cast<unsigned long long*>(p), as_stream(stream));
+}
+
+// Clears the built-in scratch of the current device on `stream` (a cudaMemsetAsync: nothing is allocated,
+// nothing is synchronised).  Needed only after a call whose kernel gave up a bounded wait (lq_poll_status
+// returned LQ_ERR_TIMEOUT): such a kernel can leave partial sums behind, and every later call would add to them.
+LQ_API int lq_w4a8_gemv_blob_static_reset(void* stream) {
+  void* p = gblob::static_scratch_for_current_device();
+  if (!p) return LQ_ERR_CUDA;
+  cudaError_t e = cudaMemsetAsync(p, 0, gblob::kStaticBytes, as_stream(stream));
+  if (e != cudaSuccess) {
+    record_cuda_error(e, "lq_w4a8_gemv_blob_static_reset");
+    return LQ_ERR_CUDA;
+  }
+  return LQ_OK;
 }
 
 }  // extern "C"

@@ -46,6 +46,7 @@ struct SegmentWalk {
     const unsigned big = r * (q + 1);
     return unit < big ? (int)(unit / (q + 1)) : (int)(r + (unit - big) / q);
   }
+  __device__ bool has_more() const { return split == 0 ? u < u_end : w < w_end; }   // after next(): segments left
   __device__ bool next(Segment& s) {
     if (split == 0) {
       if (u >= u_end) return false;

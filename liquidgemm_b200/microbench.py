@@ -42,6 +42,14 @@ def mma_rate(iters: int = 2000) -> None:
                 issue = float(np.median(o[:, 1])) / (iters * 4)
                 print(f"ctas={ctas:3d} {'TS' if ts else 'SS'} N={n:3d}: {cyc:7.1f} cycles/MMA (issue {issue:6.1f})"
                       f"  -> {128 * n * 32 / cyc:7.0f} MAC/clk/SM", flush=True)
+    # two accumulators taken in turn: is the floor a dependent-accumulate latency?
+    for n in (16, 64, 128):
+        out = torch.zeros(148 * 2, dtype=torch.int64, device="cuda")
+        for _ in range(2):
+            assert fn(n, iters, 5, 148, out.data_ptr(), _stream()) == 0
+        torch.cuda.synchronize()
+        cyc = float(np.median(out.cpu().numpy().reshape(148, 2)[:, 0])) / (iters * 4)
+        print(f"ctas=148 TS N={n:3d} two accumulators in turn: {cyc:7.1f} cycles/MMA", flush=True)
     # two CTAs per SM (256 tensor-memory columns each): do their MMA streams overlap?
     for n in (16, 128):
         out = torch.zeros(296 * 2, dtype=torch.int64, device="cuda")

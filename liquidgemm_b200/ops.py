@@ -50,8 +50,10 @@ _SCHEMAS = {
     "w4a8_wgmma_rs": "(Tensor x_i8, Tensor w, Tensor spack, Tensor s_u8, Tensor off_a, int N, int K, int group_size, bool packed) -> Tensor",
     "w4a8_wgmma_rs_fused": "(Tensor x_i8, Tensor w, Tensor s_u8, Tensor off_a, Tensor ascale, Tensor s1, int N, int K, int group_size, int out_dtype) -> Tensor",
     "w4a8_gemv2": "(Tensor x_i8, Tensor gpack, Tensor s_u8, Tensor off_a, Tensor ascale, Tensor s1, int N, int K, int group_size, int out_dtype) -> Tensor",
-    # additions of this library (no reference counterpart): INT8 GEMM with the fused scale epilogue
+    # additions of this library (no reference counterpart): INT8 GEMM with the fused scale epilogue, and the
+    # fused W4A8 linear with the bias added inside the kernel's epilogue
     "i8_gemm_scaled": "(Tensor a, Tensor b, Tensor a_scale, Tensor b_scale, int out_dtype) -> Tensor",
+    "w4a8_linear_bias": "(Tensor x_i8, Tensor w, Tensor ascale, Tensor s1, Tensor? bias, int N, int K, int out_dtype) -> Tensor",
 }
 
 _libdef = torch.library.Library("liquidgemm", "DEF")
@@ -106,6 +108,11 @@ def _f_i8(a, b):
 @torch.library.register_fake("liquidgemm::i8_gemm_scaled")
 def _f_i8s(a, b, a_scale, b_scale, out_dtype):
     return a.new_empty((a.shape[0], b.shape[0]), dtype=_OUT_DTYPES[int(out_dtype)])
+
+
+@torch.library.register_fake("liquidgemm::w4a8_linear_bias")
+def _f_lb(x_i8, w, ascale, s1, bias, N, K, out_dtype):
+    return x_i8.new_empty((x_i8.shape[0], N), dtype=_OUT_DTYPES[int(out_dtype)])
 
 
 @torch.library.register_fake("liquidgemm::w4a8_wgmma")
@@ -282,10 +289,29 @@ def _workspace(nbytes: int, device: torch.device):
     return ws
 
 
+def poll_status(device=None) -> None:
+    """Read (and clear) the device-side status word of ``device`` (default: the current one) after
+    synchronising its current stream.  Kernels never hang: a bounded wait that gives up records a site code
+    there and the kernel finishes, possibly with partial sums left in the shared reduction workspaces.  When
+    the word is set this function therefore clears every cached workspace of the device and raises
+    :class:`liquidgemm_b200._lib.LiquidGemmError`; call it wherever a wrong result must not go unnoticed
+    (after a benchmark, between serving batches, in tests)."""
+    dev = torch.cuda.current_device() if device is None else torch.device(device).index
+    with torch.cuda.device(dev):
+        rc = lib.lq_poll_status(_stream())
+        if rc != 0:
+            for (d, _), ws in list(_WORKSPACES.items()):
+                if d == dev:
+                    ws.zero_()
+            torch.cuda.synchronize()
+        check(rc, "poll_status")
+
+
 def _gemm_call(fn_name, x_i8, M, N, K, splitk, call):
     """Run one tensor-core GEMM entry point with the workspace its scheduling needs: fresh scratch for
-    the decode-tile planes, or the cached zero-filled reduction buffer of the persistent kernel (cleared
-    again if the call fails, since a failed kernel may leave partial sums behind)."""
+    the decode-tile planes, or the cached zero-filled reduction buffer of the streaming / persistent
+    kernels (cleared again if the enqueue fails; a device-side timeout is reported by
+    :func:`poll_status`, which clears it too)."""
     S = _splitk_for(M, N, K) if splitk is None else int(splitk)
     nbytes = lib.lq_gemm_workspace_bytes(M, N, K, S)
     kind = lib.lq_gemm_workspace_kind(M, N, K, S)
@@ -337,6 +363,54 @@ def gemm_fused(x_i8, blob, ascale, s1, N, K, out_dtype, splitk=None):
                    lambda S, ws, nb, st: lib.lq_w4a8_gemm_fused(_ptr(x_i8), _ptr(blob), _ptr(ascale), _ptr(s1), _ptr(y),
                                                                 int(out_dtype), M, N, K, S, ws, nb, st))
     return y
+
+
+def linear_bias(x_i8, blob, ascale, s1, bias, N, K, out_dtype):
+    """Fused W4A8 linear from a tile blob with the bias added in the kernel's epilogue (``bias`` may be
+    None): ``(T)((T)(acc * ascale[m] * s1[n]) + bias[n])``, bit-identical to the operator followed by
+    PyTorch's ``y + bias`` (reference liquidgemm/vllm_plugin.py:205-206)."""
+    x_i8 = _i8(x_i8, "x_i8")
+    _req(K % 128 == 0 and x_i8.shape[1] == K, "K%128==0 required and x_i8 must be [M,K]")
+    _req(int(out_dtype) in _OUT_DTYPES, "out_dtype must be 0 (bf16), 1 (fp16) or 2 (fp32)")
+    blob = _check_blob(blob.reshape(-1), N, K)
+    ascale, s1 = _f32(ascale, "ascale"), _f32(s1, "s1")
+    M = x_i8.shape[0]
+    _req(ascale.numel() == M and s1.numel() == N, "ascale must be [M] and s1 [N]")
+    if bias is not None:
+        _req(bias.is_cuda and bias.dtype == _OUT_DTYPES[int(out_dtype)] and bias.numel() == N,
+             "bias must be a CUDA [N] tensor of the output dtype")
+        bias = bias.contiguous()
+    y = torch.empty((M, N), dtype=_OUT_DTYPES[int(out_dtype)], device=x_i8.device)
+    if M:
+        _gemm_call("w4a8_linear_bias", x_i8, M, N, K, 0,
+                   lambda S, ws, nb, st: lib.lq_w4a8_linear_bias(_ptr(x_i8), _ptr(blob), _ptr(ascale), _ptr(s1),
+                                                                 _ptr(bias) if bias is not None else None, _ptr(y),
+                                                                 int(out_dtype), M, N, K, ws, nb, st))
+    return y
+
+
+def quantize_weight_cuda(W: torch.Tensor, group_size: int = 64, want_codes: bool = True, want_blob: bool = False):
+    """LiquidQuant quantiser as two CUDA kernels (``lq_quantize_weight``): bit-identical to
+    :func:`liquidgemm_b200.quant.quantize_weight` and to the reference's CPU result
+    (liquidgemm/quant.py:61-100) without its chain of elementwise launches and host reads.
+    Returns ``(LiquidQuantWeight, blob)``; ``qweight_u4`` is None without ``want_codes`` and ``blob`` is
+    None without ``want_blob``.  Needs K % 128 == 0 and a group size of 64 or 128."""
+    _req(W.is_cuda and W.dim() == 2 and W.dtype in _DTYPE_CODES, "W must be a 2-D CUDA tensor of bf16, fp16 or fp32")
+    N, K = W.shape
+    _req(K % 128 == 0 and group_size in (64, 128), "K % 128 == 0 and group_size 64 or 128 required")
+    W = W.detach().contiguous()
+    dev = W.device
+    G = K // group_size
+    s1 = torch.empty((N,), dtype=torch.float32, device=dev)
+    s_u8 = torch.empty((N, G), dtype=torch.uint8, device=dev)
+    off = torch.empty((N, G), dtype=torch.uint8, device=dev)
+    codes = torch.empty((N, K), dtype=torch.uint8, device=dev) if want_codes else None
+    blob = torch.empty(((N + 127) // 128, K // 128, TILE_BYTES), dtype=torch.uint8, device=dev) if want_blob else None
+    with _dev_ctx(W):
+        check(lib.lq_quantize_weight(_ptr(W), _DTYPE_CODES[W.dtype], N, K, group_size, _ptr(s1), _ptr(s_u8), _ptr(off),
+                                     _ptr(codes) if want_codes else None, _ptr(blob) if want_blob else None,
+                                     _stream()), "quantize_weight")
+    return LiquidQuantWeight(codes, s_u8, off, s1, group_size), blob
 
 
 def gemv_blob(x_i8, blob, ascale, s1, N, K, out_dtype):
@@ -536,6 +610,7 @@ _impl.impl("w4a8_wgmma_rs_fused", _wgmma_rs_fused)
 _impl.impl("w4a8_wgmma", _wgmma_ss)
 _impl.impl("wgmma_i8_gemm", _wgmma_i8)
 _impl.impl("i8_gemm_scaled", _i8_gemm_scaled)
+_impl.impl("w4a8_linear_bias", linear_bias)
 _impl.impl("w4a8_gemm", _gemm_v1)
 _libdef.impl("wgmma_rs_a_coords", _coords, "CompositeExplicitAutograd")
 
@@ -687,6 +762,8 @@ def w4a8_linear_host(x_host: torch.Tensor, qw_dev: dict, y_host: torch.Tensor = 
         key = (dev.index, stream)
         scratch = _HOST_SCRATCH.get(key)
         if scratch is None or scratch.numel() < need:
+            if scratch is not None:
+                _RETIRED.append(scratch)   # kernels already enqueued on `stream` may still use it
             scratch = torch.empty((max(need, 1 << 22),), dtype=torch.uint8, device=dev)
             _HOST_SCRATCH[key] = scratch
         # kind 2: the shared all-zero reduction buffer (kernels leave it zero); kind 1: split-K planes,

@@ -40,18 +40,22 @@ class LiquidQuantWeight:
     s1: torch.Tensor
     group_size: int
 
+    # ``qweight_u4`` may be None when the codes were packed straight into a tile blob and never stored one
+    # per byte (liquidgemm_b200.ops.quantize_weight_cuda(..., want_codes=False)); the sizes then come from
+    # the group arrays.
     @property
     def N(self) -> int:
-        return self.qweight_u4.shape[0]
+        return self.s_u8.shape[0]
 
     @property
     def K(self) -> int:
-        return self.qweight_u4.shape[1]
+        return self.s_u8.shape[1] * self.group_size
 
     def to(self, device) -> "LiquidQuantWeight":
         """Copy of the container with every tensor on ``device``."""
-        return LiquidQuantWeight(self.qweight_u4.to(device), self.s_u8.to(device),
-                                 self.offset_a.to(device), self.s1.to(device), self.group_size)
+        codes = None if self.qweight_u4 is None else self.qweight_u4.to(device)
+        return LiquidQuantWeight(codes, self.s_u8.to(device), self.offset_a.to(device), self.s1.to(device),
+                                 self.group_size)
 
 
 def _const(like: torch.Tensor, value: float) -> torch.Tensor:
@@ -67,6 +71,11 @@ def quantize_weight(W: torch.Tensor, group_size: int = 64) -> LiquidQuantWeight:
     if n_cols % group_size:
         raise AssertionError(f"K={n_cols} not divisible by group_size={group_size}")
     n_groups = n_cols // group_size
+    if W.is_cuda and n_cols % 128 == 0 and group_size in (64, 128) and \
+            W.dtype in (torch.float32, torch.float16, torch.bfloat16):
+        # on the device the whole quantiser is two kernels of the native library (same bits as below)
+        from . import ops
+        return ops.quantize_weight_cuda(W, group_size, want_codes=True, want_blob=False)[0]
     w32 = W.detach().to(torch.float32)
 
     # level 1: one symmetric scale per output channel.  The divisor is a tensor on purpose: torch's

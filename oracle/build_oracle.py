@@ -54,6 +54,8 @@ def load() -> ctypes.CDLL:
     lib = ctypes.CDLL(lib_path(variant))
     P, I = ctypes.c_void_p, ctypes.c_int
     lib.lqo_num_threads.restype = I
+    lib.lqo_set_num_threads.argtypes = [I]
+    lib.lqo_set_num_threads.restype = None
     lib.lqo_dequant_i8.argtypes = [P, P, P, P, I, I, I]
     lib.lqo_dequant_i8_simd.argtypes = [P, P, P, P, I, I, I]
     lib.lqo_int_gemm.argtypes = [P, P, P, I, I, I]

@@ -21,6 +21,15 @@
 #include <omp.h>
 #endif
 
+/* Pin the team size (a launcher such as torchrun exports OMP_NUM_THREADS=1; the baseline should use the host). */
+void lqo_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 int lqo_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

@@ -61,3 +61,20 @@ def assert_bits_equal(got: torch.Tensor, y_f32: np.ndarray, out_dtype: int, what
         bad = np.argwhere(g != e)
         raise AssertionError(f"{what}: {len(bad)} of {g.size} elements differ; first at {bad[0].tolist()}: "
                              f"got 0x{int(g[tuple(bad[0])]):x} want 0x{int(e[tuple(bad[0])]):x}")
+
+
+def bits_to_f32(b: np.ndarray, out_dtype: int) -> np.ndarray:
+    """Exact float32 value of bf16 / fp16 / fp32 bit patterns."""
+    if out_dtype == O.OUT_BF16:
+        return (b.astype(np.uint32) << np.uint32(16)).view(np.float32)
+    if out_dtype == O.OUT_F16:
+        return b.view(np.float16).astype(np.float32)
+    return b.view(np.float32)
+
+
+def with_bias_f32(y_f32: np.ndarray, bias_bits: np.ndarray, out_dtype: int) -> np.ndarray:
+    """What ``y.to(T) + bias`` gives in PyTorch for T = bf16 / fp16 / fp32 (the reference adds the bias to
+    the already cast output, liquidgemm/vllm_plugin.py:205-206): round the product to T, add the bias in
+    float32, round again (the caller casts the returned float32 to T)."""
+    y_t = bits_to_f32(expected_bits(y_f32, out_dtype), out_dtype)
+    return (y_t + bits_to_f32(bias_bits, out_dtype)[None, :]).astype(np.float32)

@@ -64,3 +64,25 @@ def test_attach_prepacked_gives_the_layer_its_buffers(tmp_path):
     names = dict(layer.named_buffers())
     assert set(names) == {"lq_s1", "lq_rs", "lq_s_u8", "lq_offset_a"}
     assert torch.equal(names["lq_rs"], entry["rs"])
+
+
+def test_file_names_from_the_json_cannot_leave_the_directory(tmp_path):
+    C.save_prepacked(str(tmp_path), [("a", _layer(128, 128, 6))])
+    cfgp = os.path.join(str(tmp_path), C.CONFIG_NAME)
+    cfg = json.load(open(cfgp))
+    for bad in ("../00000.lqq", "/etc/passwd", "sub/00000.lqq", "00000.bin"):
+        cfg["layers"][0]["file"] = bad
+        json.dump(cfg, open(cfgp, "w"))
+        with pytest.raises(ValueError):
+            C.load_prepacked(str(tmp_path))
+
+
+def test_blob_layout_version_is_checked(tmp_path):
+    C.save_prepacked(str(tmp_path), [("a", _layer(128, 128, 7))])
+    cfgp = os.path.join(str(tmp_path), C.CONFIG_NAME)
+    cfg = json.load(open(cfgp))
+    assert cfg["blob_layout"] == C.BLOB_LAYOUT and cfg["tile_bytes"] == C.TILE_BYTES
+    cfg["blob_layout"] = C.BLOB_LAYOUT + 1
+    json.dump(cfg, open(cfgp, "w"))
+    with pytest.raises(ValueError):
+        C.read_config(str(tmp_path))

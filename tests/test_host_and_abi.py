@@ -45,7 +45,9 @@ def test_size_helpers_without_gpu():
     assert lib.lq_gemm_workspace_kind(2048, 4096, 14336, 0) == 0     # tile kernel, one k-range: no workspace
     assert lib.lq_gemm_workspace_kind(2048, 4096, 14336, -1) == 2
     assert lib.lq_gemm_workspace_kind(2, 4096, 14336, 0) == 2        # streaming decode kernels
-    assert lib.lq_gemm_workspace_kind(8, 4096, 14336, 0) == 1        # tile kernel with split-K planes
+    assert lib.lq_gemm_workspace_kind(8, 4096, 14336, 0) == 2        # streaming tensor-core kernel, atomic join
+    assert lib.lq_gemm_workspace_kind(64, 4096, 14336, 0) == 1       # tile kernel with split-K planes
+    assert lib.lq_gemm_launches(8, 4096, 14336, 0) == 1 and lib.lq_gemm_launches(64, 4096, 14336, 0) == 2
     assert lib.lq_scatter_workspace_bytes(8, 4096, 14336) > 0
     assert lib.lq_gemm_workspace_kind(2048, 4096, 14336, 1) == 0
 
@@ -76,7 +78,7 @@ def test_operator_schemas_match_the_reference():
         src = open(os.path.join(REFERENCE_ROOT, "csrc", "liquid_gemm", "torch_bindings.cpp")).read()
         joined = re.sub(r'"\s*\n\s*"', "", src)
         for name, sig in ops._SCHEMAS.items():
-            if name in ("i8_gemm_scaled", "wgmma_rs_a_coords"):
+            if name in ("i8_gemm_scaled", "w4a8_linear_bias", "wgmma_rs_a_coords"):
                 continue
             assert (name + sig) in joined, f"schema of {name} differs from the reference's torch_bindings.cpp"
 
