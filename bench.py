@@ -15,8 +15,8 @@ output, and its quantised tokens, are compared bit for bit with the CPU oracle (
 
 The JSON line printed by rank 0 carries
   value     weight GB/s (packed weight bytes N*K/2 per launch / device time), whole job
-  e2e       the same metric through the host-buffer C entry point (lq_w4a8_linear_host): per launch a pinned fp16
-            activation copy to the device, quant_per_token + GEMV, and the result copied back
+  e2e       the same metric from host buffers (ops.HostStepPlan over lq_w4a8_linear_host): per linear a pinned
+            fp16 activation copy to the device, quant_per_token + linear, and the result copied back
   roofline  algorithmic bytes of the sweep / device time, against the measured HBM copy rate
   cpu_baseline  the CPU oracle (C, OpenMP) on the same sweep, timed on this host
   extras    the other benchmark configurations (split-K decode tiles, prefill TOPS, cuBLAS bf16
@@ -376,25 +376,36 @@ def main():
         ms = e0.elapsed_time(e1)
     clocks = sampler.summary(wall0, wall1) if rank == 0 else None
 
-    # ---- e2e: host buffers in, host buffers out, through the public ops
-    # Independent requests: issued round-robin on three streams so that the copies of one linear overlap
-    # the kernels of another (each stream has its own scratch and workspace inside the library).
-    e2e_streams = [torch.cuda.Stream() for _ in range(3)]
+    # ---- e2e: host buffers in, host buffers out, through the public API
+    # One step = the same 12 linears as host-buffer requests (liquidgemm_b200.ops.HostStepPlan): per linear
+    # a pinned fp16 activation copy to the device, quant_per_token, the linear, and the output copied back
+    # to pinned host memory -- recorded once per weight rotation and replayed with one call per step.  The
+    # requests of a step are independent and spread over three streams inside the plan.
+    def requests_for(c):
+        return [(acts[(name, M)]["host"], copy_for(c, name, M), acts[(name, M)]["out_host"]) for name, M in launches]
 
-    def e2e_step(c):
-        for i, (name, M) in enumerate(launches):
-            a = acts[(name, M)]
-            ops.w4a8_linear_host(a["host"], copy_for(c, name, M), a["out_host"], stream=e2e_streams[i % 3])
-
-    e2e_steps = max(3, min(args.steps, 50))
+    e2e_stream = torch.cuda.Stream()          # one stream: the steps run strictly one after the other
+    plans = [ops.HostStepPlan(requests_for(c), stream=e2e_stream) for c in range(n_sets)]
+    e2e_steps = max(3, min(args.steps, 100))
     for i in range(3):
-        e2e_step(i % n_sets)
+        plans[i % n_sets].run()
+    for p in plans:
+        p.synchronize()
     barrier()
     t0 = time.perf_counter()
     for i in range(e2e_steps):
-        e2e_step(i % n_sets)
+        plans[i % n_sets].run()
+    for p in plans:
+        p.synchronize()
     barrier()                                  # device-wide synchronise: every stream has drained
     e2e_ms = (time.perf_counter() - t0) * 1e3
+    # the outputs that came back are the right ones (last replay of every plan)
+    e2e_ok = True
+    for name, M in launches:
+        a = acts[(name, M)]
+        c_last = (e2e_steps - 1) % n_sets
+        want = decode_linear(copy_for(c_last, name, M), a["xq"], a["sc"], M, 1)
+        e2e_ok &= bool(torch.equal(want.cpu(), a["out_host"]))
 
     t_ms = torch.tensor([ms, e2e_ms], dtype=torch.float64, device="cuda")
     if world > 1:
@@ -405,7 +416,7 @@ def main():
     def kernels_of(name, M):
         """Kernel launches of one linear: 2 when the tile kernel splits K (planes + finish pass), else 1."""
         N, K = SHAPES[name]
-        return 2 if lib.lq_gemm_workspace_kind(M, N, K, 0) == 1 else 1
+        return lib.lq_gemm_launches(M, N, K, 0)
     launches_per_step = sum(kernels_of(n, M) for n, M in launches)
     wbytes = sweep_weight_bytes()
     abytes = sum(algorithmic_bytes(M, *SHAPES[n]) for n, M in launches)
@@ -421,7 +432,8 @@ def main():
             # numbers measured above
             try:
                 env = dict(os.environ, CUDA_VISIBLE_DEVICES=os.environ.get("CUDA_VISIBLE_DEVICES", str(local_rank)))
-                out = subprocess.run([sys.executable, "-m", "liquidgemm_b200.benchlib", str(peaks["hbm_gbs"])], cwd=ROOT,
+                out = subprocess.run([sys.executable, "-m", "liquidgemm_b200.benchlib", str(peaks["hbm_gbs"]),
+                                      str(peaks["bf16_tflops"])], cwd=ROOT,
                                      env=env, capture_output=True, text=True, timeout=900)
                 extras = json.loads(out.stdout.strip().splitlines()[-1]) if out.returncode == 0 else {
                     "error": (out.stderr or "")[-400:]}
@@ -433,6 +445,22 @@ def main():
                 extras = benchlib.run_extras(world, rank, local_rank, peaks)
             except Exception as exc:
                 extras = {"error": repr(exc)}
+
+    # A compact copy of the secondary results inside `config` (the full tables stay under `extras`).
+    summary = {}
+    try:
+        if "sweep" in extras:
+            summary["prefill"] = [
+                {"shape": r["shape"], "M": r["M"], "TOPS": r["TOPS"], "of_4500": r["int8_frac_of_4500"],
+                 "of_2x_measured_bf16": r.get("int8_frac_of_2x_bf16"), "x_cublas_bf16": r["speedup_vs_cublas_bf16"]}
+                for r in extras["sweep"] if r["M"] in (2048, 8192)]
+            summary["decode_us"] = {f'{r["shape"]}:{r["M"]}': [r["us"], r["hbm_frac"], r["speedup_vs_cublas_bf16"]]
+                                    for r in extras["sweep"] if r["M"] <= 128}
+            summary["decode_us_columns"] = ["us per launch", "fraction of measured HBM rate", "x cuBLAS bf16"]
+        if "tp70b" in extras:
+            summary["tp70b_stack_ms"] = extras["tp70b"]["rows"]
+    except Exception as exc:
+        summary["error"] = repr(exc)
 
     cpu = None
     if rank == 0 and world == 1:
@@ -450,16 +478,19 @@ def main():
                        "group_size": 64, "out": "bf16", "launches_per_step": len(launches),
                        "l2": f"{n_sets} weight copies rotate per launch (a copy is re-read after > 300 MB of other "
                              "weights, over 2 x L2); step captured in a CUDA graph",
-                       "sharding": "each rank owns a full set of output channels (N-sharded, no collective)"},
+                       "sharding": "each rank owns a full set of output channels (N-sharded, no collective)",
+                       "summary": summary},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_RATIO * abytes,
-                         "of": peaks["source"], "kernel": "w4a8_tile_kernel [+ finish_kernel] (M = 8, 16) + gemv_blob_kernel (M = 1, 4): the 12-op sweep",
+                         "of": peaks["source"], "kernel": "w4a8_decode_tc_kernel (M = 8, 16; gate_up at M = 4) + gemv_blob_kernel (M = 1, 4): the 12-op sweep, one launch per linear",
                          "algorithmic_bytes_per_step": abytes},
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": UNIT,
                     "h2d_bytes_per_step": sum(M * SHAPES[n][1] * 2 for n, M in launches),
                     "d2h_bytes_per_step": sum(M * SHAPES[n][0] * 2 for n, M in launches),
-                    "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
+                    "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps, "outputs_match_device_path": bool(e2e_ok),
+                    "api": "liquidgemm_b200.ops.HostStepPlan.run(): pinned fp16 tokens -> H2D -> quant_per_token -> "
+                           "linear -> D2H of every output, one recorded step per call"},
             "gpu_launches": launches_per_step * args.steps,
             "parity": bool(parity_ok and status == 0), "parity_cases": parity_cases,
             "clocks": clocks, "device_status": status, "extras": extras,

@@ -80,21 +80,12 @@ LQ_API int lq_scale_epilogue(const int32_t* acc, const float* ascale, const floa
 
 /* Decode GEMV, M <= 16: y = scale_epilogue(x_i8 @ q_hat^T) straight from the row-major
  * interleaved pack of liquidgemm/ops.py:68-75.  Requires K % 128 == 0 and group_size == 64.
- * Replaces torch.ops.liquidgemm.w4a8_gemv2 (reference csrc/liquid_gemm/gemv2.cu:82-120). */
+ * Replaces torch.ops.liquidgemm.w4a8_gemv2 (reference csrc/liquid_gemm/gemv2.cu:82-120) for callers that
+ * hold that pack; layers prepared by this library keep the tile blob only and are served by
+ * lq_w4a8_gemm_fused. */
 LQ_API int lq_w4a8_gemv(const int8_t* x_i8, const uint8_t* gpack, const uint8_t* s_u8,
                  const uint8_t* offset_a, const float* ascale, const float* s1, void* y,
                  int out_dtype, int M, int N, int K, int group_size, void* stream);
-
-/* The same GEMV as a persistent stream-K kernel (TMA ring + mma.sync): the fast path behind
- * torch.ops.liquidgemm.w4a8_gemv2.  It needs a reduction workspace of lq_gemv_workspace_bytes(N, K)
- * bytes that is ALL ZERO on entry and is left all zero (same contract as lq_gemm_workspace_bytes).
- * No reference counterpart beyond the op itself (the reference GEMV is one warp per row,
- * csrc/liquid_gemm/gemv2.cu:21-80). */
-LQ_API size_t lq_gemv_workspace_bytes(int N, int K);
-LQ_API int lq_w4a8_gemv_stream(const int8_t* x_i8, const uint8_t* gpack, const uint8_t* s_u8,
-                        const uint8_t* offset_a, const float* ascale, const float* s1, void* y,
-                        int out_dtype, int M, int N, int K, void* workspace, size_t workspace_bytes,
-                        void* stream);
 
 /* The decode GEMV (1..8 tokens) fed from the GEMM's tile blob instead of a GEMV-specific pack, so a
  * layer keeps ONE copy of its 4-bit weights for every batch size (the reference's GEMV mode stores
@@ -257,17 +248,6 @@ LQ_API int lq_w4a8_gemm_fused(const int8_t* x_i8, const uint8_t* blob, const flo
 LQ_API int lq_w4a8_linear_bias(const int8_t* x_i8, const uint8_t* blob, const float* ascale,
                         const float* s1, const void* bias, void* y, int out_dtype, int M, int N, int K,
                         void* workspace, size_t workspace_bytes, void* stream);
-
-/* The same fused GEMM reading the weights in the row-major interleaved GEMV pack
- * (liquidgemm/ops.py:68-75: [N, K/2]) with the standard [N, K/64] step / offset arrays, i.e. one
- * weight format for every M.  No direct reference counterpart (the reference keeps two packs,
- * liquidgemm/vllm_plugin.py:153-164); it backs torch.ops.liquidgemm.w4a8_gemv2 for the token counts
- * where tensor cores beat dp4a.  K % 128 == 0, group_size 64.  Always the persistent stream-K
- * kernel (`splitk` is ignored): the workspace is lq_gemm_workspace_bytes(M, N, K, -1), kind 2. */
-LQ_API int lq_w4a8_gemm_rowmajor(const int8_t* x_i8, const uint8_t* gpack, const uint8_t* s_u8,
-                          const uint8_t* offset_a, const float* ascale, const float* s1, void* y,
-                          int out_dtype, int M, int N, int K, int splitk, void* workspace,
-                          size_t workspace_bytes, void* stream);
 
 /* Plain INT8 x INT8 -> INT32 tensor-core GEMM c[M,N] = a[M,K] @ b[N,K]^T.
  * Replaces torch.ops.liquidgemm.wgmma_i8_gemm (reference csrc/liquid_gemm/w4a8_wgmma.cu:648-694).

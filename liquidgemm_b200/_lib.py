@@ -32,9 +32,6 @@ _SIGNATURES = {
     "lq_quant_per_token": (c_int, [P, c_int, P, P, c_int, c_int, P]),
     "lq_scale_epilogue": (c_int, [P, P, P, P, c_int, c_int, c_int, P]),
     "lq_w4a8_gemv": (c_int, [P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P]),
-    "lq_w4a8_gemm_rowmajor": (c_int, [P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, c_size_t, P]),
-    "lq_gemv_workspace_bytes": (c_size_t, [c_int, c_int]),
-    "lq_w4a8_gemv_stream": (c_int, [P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, P, c_size_t, P]),
     "lq_gemv_blob_workspace_bytes": (c_size_t, []),
     "lq_w4a8_gemv_blob": (c_int, [P, P, P, P, P, c_int, c_int, c_int, c_int, P, c_size_t, P]),
     "lq_w4a8_gemv_blob_static": (c_int, [P, P, P, P, P, c_int, c_int, c_int, c_int, P]),

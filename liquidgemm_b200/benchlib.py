@@ -9,7 +9,8 @@ does not depend on the values; parity is the test-suite's job).
                 (bench/rs_bench.py:44, bench/RESULTS.md:218-224).
 * ``splitk``  : decode-tile GEMM M in {32, 64, 128} on down / gate_up for split-K 1, 2, 4, 8.
 * ``tp70b``   : Llama-3-70B-shape linears column-sharded along N over the ranks, 80 layers x 4
-                linears, with and without an NCCL all-gather of every output.
+                linears: without exchange, with an NCCL all-gather of every output (on the compute stream and
+                overlapped on a second stream), and with the gather done by the linears' own store epilogues.
 """
 
 from __future__ import annotations
@@ -20,7 +21,7 @@ import torch
 
 from . import ops
 
-SHAPES = {"qkv": (6144, 4096), "gate_up": (28672, 4096), "down": (4096, 14336)}
+SHAPES = {"qkv": (6144, 4096), "o": (4096, 4096), "gate_up": (28672, 4096), "down": (4096, 14336)}
 SHAPES_70B = {"qkv": (10240, 8192), "o": (8192, 8192), "gate_up": (57344, 8192), "down": (8192, 28672)}
 INT8_DENSE_TOPS = 4500.0   # B200 datasheet, dense
 
@@ -102,7 +103,7 @@ def run_sweep(peaks, Ms=(1, 4, 8, 16, 32, 64, 128, 512, 2048, 8192)):
                          "alg_GBps": round(gbs, 1), "hbm_frac": round(gbs / peaks["hbm_gbs"], 3),
                          "TOPS": round(tops, 1), "int8_frac_of_4500": round(tops / INT8_DENSE_TOPS, 3),
                          "cublas_bf16_us": round(tb, 2), "speedup_vs_cublas_bf16": round(tb / t, 2),
-                         "kernel": "dp4a stream" if M <= 4 else "tcgen05"})
+                         "int8_frac_of_2x_bf16": round(tops / (2.0 * peaks.get("bf16_tflops", 1685.0)), 3)})
         del layers, wbf
         torch.cuda.empty_cache()
     return rows
@@ -158,11 +159,22 @@ def _symmetric_outputs(world, M, names):
         return None
 
 
-def run_tp70b(world, rank, Ms=(1, 16, 64, 2048), layers_in_stack=80, distinct_layers=3):
-    """80-layer stack of the four 70B-shape linears, each column-sharded along N over `world` ranks:
-    without any exchange, with an NCCL all-gather of every output, and (decode batches) with the
-    gather done by the linear's own epilogue, which stores its slice into every rank's full-width
-    output over NVLink, followed by a symmetric-memory barrier on the stream."""
+def run_tp70b(world, rank, Ms=(1, 64, 2048), layers_in_stack=80, distinct_layers=3):
+    """80-layer stack of the four 70B-shape linears, each column-sharded along N over `world` ranks, timed
+    (CUDA events around graph replays, max over ranks) in up to four ways:
+
+    * ``no_gather``     sharded linears only;
+    * ``nccl``          an NCCL all-gather of every output on the compute stream (the stated baseline);
+    * ``nccl_overlap``  the same collective on a second stream, so that the gather of linear i runs under the
+                        GEMM of linear i + 1 (each output has its own buffer; joined at the end of the stack);
+    * ``stores``        gather by stores: the linear's own epilogue writes its slice into every rank's
+                        full-width output over NVLink (plain peer stores into symmetric memory), and the
+                        ranks are ordered ONCE PER LAYER by a symmetric-memory barrier on the stream, i.e.
+                        the four outputs of a layer are complete on every rank when the next layer starts.
+
+    On one rank the unsharded stack is ``single_gpu_ms``; with more ranks every rank also times that
+    unsharded stack on its own GPU, so that the strong-scaling efficiency t1 / (N * tN) of each mode comes
+    from one run."""
     import torch.distributed as dist
     rows = []
     names = list(SHAPES_70B)
@@ -171,79 +183,73 @@ def run_tp70b(world, rank, Ms=(1, 16, 64, 2048), layers_in_stack=80, distinct_la
         stack.append({n: device_lqq(SHAPES_70B[n][0] // world, SHAPES_70B[n][1], seed=1000 * rank + 10 * l + i,
                                     want_gp=False)
                       for i, n in enumerate(names)})
+    full_stack = stack
+    if world > 1:
+        full_stack = [{n: device_lqq(SHAPES_70B[n][0], SHAPES_70B[n][1], seed=10 * l + i, want_gp=False)
+                       for i, n in enumerate(names)} for l in range(distinct_layers)]
     for M in Ms:
         toks = {n: device_tokens(M, SHAPES_70B[n][1], seed=M + i) for i, n in enumerate(names)}
         gathered = {n: torch.empty((world * M, SHAPES_70B[n][0] // world), dtype=torch.bfloat16, device="cuda")
-                    for n in names}
-        # gather by stores: measured and verified on two ranks; larger groups only on request
-        fused_ok = world == 2 or (world > 2 and os.environ.get("LQ_BENCH_FUSED_GATHER") == "1")
-        symm = _symmetric_outputs(world, M, names) if (fused_ok and M <= 16) else None
-        flags = None
-        if symm is not None:
-            try:
-                import torch.distributed._symmetric_memory as symm_mem
-                ft = symm_mem.empty(1024, dtype=torch.int32, device=torch.device("cuda", torch.cuda.current_device()))
-                flags = (ft, symm_mem.rendezvous(ft, dist.group.WORLD.group_name))
-            except Exception:
-                flags = None
+                    for n in names} if world > 1 else None
+        symm = _symmetric_outputs(world, M, names) if world > 1 else None
+        comm = torch.cuda.Stream() if world > 1 else None
 
         def one_stack(mode):
-            if mode == "fused_sync":
-                # kernels order themselves: launch k signals flag word k on every rank and waits for word
-                # k-1 (all ranks' CTAs of the previous linear) before it reads its tokens
-                ft, fh = flags
-                ft.zero_()
-                fh.barrier(channel=1)
-                k, prev_grid = 0, 0
-                for l in range(layers_in_stack):
-                    lay = stack[l % distinct_layers]
-                    for n in names:
-                        L = lay[n]
-                        full, hdl = symm[n]
-                        ops.gemm_fused_scatter(toks[n][0], L["rs"], toks[n][1], L["s1"], hdl.buffer_ptrs, full.shape[1],
-                                               rank * L["N"], L["N"], L["K"], 0, flag_ptrs=fh.buffer_ptrs, flag_index=k,
-                                               wait_ptr=(ft.data_ptr() + 4 * (k - 1)) if k else None,
-                                               wait_value=world * prev_grid)
-                        prev_grid = ops.decode_grid(M, L["N"], L["K"])
-                        k += 1
-                fh.barrier(channel=1)
-                return
+            lays = full_stack if mode == "single" else stack
+            done = []
             for l in range(layers_in_stack):
-                lay = stack[l % distinct_layers]
+                lay = lays[l % distinct_layers]
                 for n in names:
                     L = lay[n]
-                    if mode == "fused":
+                    if mode == "stores":
                         full, hdl = symm[n]
                         ops.gemm_fused_scatter(toks[n][0], L["rs"], toks[n][1], L["s1"], hdl.buffer_ptrs, full.shape[1],
                                                rank * L["N"], L["N"], L["K"], 0)
-                        hdl.barrier(channel=0)
                     else:
                         y = linear_call(L, toks[n][0], toks[n][1], M)
                         if mode == "nccl":
                             dist.all_gather_into_tensor(gathered[n], y)
+                        elif mode == "nccl_overlap":
+                            cur = torch.cuda.current_stream()
+                            comm.wait_stream(cur)
+                            with torch.cuda.stream(comm):
+                                out = torch.empty_like(gathered[n])
+                                dist.all_gather_into_tensor(out, y)
+                                y.record_stream(comm)
+                            done.append(out)
+                            if len(done) > 8:
+                                done.pop(0)
+                if mode == "stores":
+                    symm[names[0]][1].barrier(channel=0)   # one ordering point per layer
+            if mode == "nccl_overlap":
+                torch.cuda.current_stream().wait_stream(comm)
 
         res = {"M": M}
-        modes = ["none"] + (["nccl"] if world > 1 else []) + (["fused"] if symm is not None else []) + \
-                (["fused_sync"] if flags is not None else [])
+        modes = (["no_gather"] if world > 1 else ["single"]) + \
+                (["nccl"] if world > 1 else []) + (["nccl_overlap"] if world > 1 and M >= 512 else []) + \
+                (["stores"] if symm is not None else []) + \
+                (["single"] if world > 1 else [])
         for mode in modes:
             s = torch.cuda.Stream()
             with torch.cuda.stream(s):
                 one_stack(mode)
                 torch.cuda.synchronize()
-                use_graph = True
-                try:
-                    g = torch.cuda.CUDAGraph()
-                    with torch.cuda.graph(g, stream=s):
-                        one_stack(mode)
-                    run = g.replay
-                except Exception:
-                    use_graph = False
-                    run = lambda: one_stack(mode)
+                use_graph = mode != "nccl_overlap"
+                run = lambda: one_stack(mode)
+                if use_graph:
+                    try:
+                        g = torch.cuda.CUDAGraph()
+                        with torch.cuda.graph(g, stream=s):
+                            one_stack(mode)
+                        run = g.replay
+                    except Exception:
+                        use_graph = False
+                        torch.cuda.synchronize()
                 run()
                 if world > 1:
                     dist.barrier()
                 torch.cuda.synchronize()
-                reps = 3
+                reps = 3 if M <= 64 else 2
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record(s)
                 for _ in range(reps):
@@ -254,10 +260,14 @@ def run_tp70b(world, rank, Ms=(1, 16, 64, 2048), layers_in_stack=80, distinct_la
             t = torch.tensor([ms], dtype=torch.float64, device="cuda")
             if world > 1:
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            key = {"none": "stack_ms_no_gather", "nccl": "stack_ms_gather", "fused": "stack_ms_fused_gather",
-                   "fused_sync": "stack_ms_fused_gather_kernel_sync"}[mode]
-            res[key] = round(float(t[0]), 3)
-            res["graph_" + mode] = use_graph
+            res[mode + "_ms"] = round(float(t[0]), 3)
+            if not use_graph:
+                res[mode + "_graph"] = False
+        if world > 1:
+            t1 = res["single_ms"]
+            for mode in ("no_gather", "nccl", "nccl_overlap", "stores"):
+                if mode + "_ms" in res:
+                    res[mode + "_eff"] = round(t1 / (world * res[mode + "_ms"]), 3)
         if symm is not None:
             # the stores really arrived: the last layer's full-width output equals the NCCL gather of the slices
             lay = stack[(layers_in_stack - 1) % distinct_layers]
@@ -267,9 +277,10 @@ def run_tp70b(world, rank, Ms=(1, 16, 64, 2048), layers_in_stack=80, distinct_la
                 parts = [torch.empty_like(y) for _ in range(world)]
                 dist.all_gather(parts, y)
                 ok = ok and torch.equal(torch.cat(parts, dim=1), symm[n][0])
-            res["fused_gather_matches_nccl"] = bool(ok)
+            res["stores_match_nccl"] = bool(ok)
         rows.append(res)
-        del symm, flags
+        del symm, gathered
+        torch.cuda.empty_cache()
     return rows
 
 
@@ -304,4 +315,5 @@ if __name__ == "__main__":
     if len(sys.argv) > 1 and sys.argv[1] == "one":
         print(json.dumps(run_one(sys.argv[2], int(sys.argv[3]))))
         sys.exit(0)
-    print(json.dumps(run_extras(1, 0, 0, {"hbm_gbs": float(sys.argv[1]) if len(sys.argv) > 1 else 6451.8})))
+    print(json.dumps(run_extras(1, 0, 0, {"hbm_gbs": float(sys.argv[1]) if len(sys.argv) > 1 else 6451.8,
+                                          "bf16_tflops": float(sys.argv[2]) if len(sys.argv) > 2 else 1685.0})))

@@ -5,19 +5,21 @@
 //  * Work = the (n-tile, k-tile) grid of 8704-byte blob tiles, cut into equal contiguous ranges, one
 //    per CTA, two CTAs per SM (stream-K; layers with few n-tiles are cut into equal k-ranges per tile):
 //    every SM streams the same number of weight bytes whatever N and K are.
-//  * warp 0  producer: one thread feeds two rings.  The weight ring (NW stages, one contiguous bulk copy
-//            of a tile each) is released by the dequant threads as soon as they hold the tile in
-//            registers, so its depth only has to cover the memory latency.  The operand ring (NT stages:
-//            a 128-byte-swizzled tensor-map box of the BN x 128 token slice in shared memory plus 32
-//            columns of tensor memory for the dequantised weights) is released by the MMAs.  Tying the
-//            weight tile to the MMA's completion, as one ring would, puts unpack, operand store, four MMAs
-//            and the commit inside the window the ring has to cover: measured, the stream then ran at
-//            two thirds of the rate of the dp4a GEMV, whose ring holds a tile only until it is read.
+//  * warp 0  producer: one thread keeps a ring of NW weight tiles in flight, one contiguous bulk copy
+//            each.  The dequant threads release a stage as soon as they hold the tile in registers, so
+//            the ring only has to cover the memory latency.  The tokens do NOT come through the copy
+//            engine: measured on B200, a second (tensor-map) copy per k-tile made the copy engine the
+//            bottleneck -- the producer was never idle, its copy instructions blocked on a full queue, the
+//            MMAs waited for token boxes a third of the time and the stream ran at 60 % of the dp4a GEMV's
+//            rate.  The 128 threads of the dequant set that owns a k-tile fetch its BN x 128-byte token
+//            slice themselves (16 bytes each, an L2 hit issued before the wait for the weights) and store
+//            it into the operand stage in the 128-byte-swizzled layout the MMA's descriptor expects.
 //  * warps 2..9  two dequant sets taking alternate k-tiles; thread r of a set owns weight row r:
 //            64 bytes of nibbles -> 128 INT8 (AND / SHR+AND / IMAD / XOR on 4-lane words) ->
 //            tcgen05.st into tensor-memory lane r (the MMA's A operand, 4 consecutive k per column).
 //  * warp 1  MMA: one thread issues four 128 x BN x 32 tcgen05.mma kind::i8 per k-tile (A from tensor
-//            memory, B = tokens through a shared-memory descriptor); its commit recycles the stage.
+//            memory, B = tokens through a shared-memory descriptor); its commit recycles the operand
+//            stage (NT stages: 32 tensor-memory columns + the token slice in shared memory).
 //  * Two accumulators in tensor memory, taken in turn by the segments (tile, k-range) of the CTA's
 //    range.  Set p owns accumulator p and runs the epilogue of a segment only when that accumulator is
 //    needed again, or at the very end -- where the two sets finish the CTA's (at most two) partial
@@ -36,7 +38,6 @@
 // Every wait is bounded; a thread whose wait expires records a site code, stops waiting and still
 // runs the rest of its control flow, so the CTA reaches the exit where tensor memory is released.
 
-#include <cuda.h>
 #include <stdint.h>
 
 #include <cstdlib>
@@ -48,9 +49,6 @@
 #include "lq_tc_ptx.cuh"
 
 namespace lq {
-
-int make_byte_matrix_map(CUtensorMap* map, const void* ptr, long rows, long row_bytes, int box_rows,
-                         int box_bytes);   // lq_gemm_tc.cu
 
 namespace dtc {
 
@@ -64,9 +62,9 @@ __device__ long long g_trace[1024 * 16];
 #define TR_VAR(name) long long name = 0
 #else
 #define TR_NOW() 0ll
-#define TR_ADD(acc, t0) ((void)0)
-#define TR_SET(slot, v) ((void)0)
-#define TR_VAR(name) ((void)0)
+#define TR_ADD(acc, t0) ((void)(t0))
+#define TR_SET(slot, v) ((void)(v))
+#define TR_VAR(name) const long long name = 0
 #endif
 
 constexpr int kTileBytes = 8704;
@@ -82,6 +80,7 @@ constexpr int kOutI32 = 3;
 
 struct Args {
   const uint8_t* blob;
+  const int8_t* x;       // [M, K]
   const float* ascale;   // [M]
   const float* s1;       // [N]
   const void* bias;      // [N] in the output dtype, or null
@@ -90,6 +89,7 @@ struct Args {
   int* status;
   int out_mode;          // LQ_DT_* or kOutI32
   int M, N, K, fixed_split;
+  int prefetch;          // tiles per CTA requested into L2 ahead of the first ring
 };
 
 template <int BN, int NW, int NT>
@@ -99,8 +99,8 @@ struct Cfg {
   static constexpr int kACols = 32 * NT;    // one tensor-memory operand stage per token box
   static constexpr int kColsNeeded = kAccCols + kACols;
   static constexpr int kTmemCols = kColsNeeded <= 128 ? 128 : 256;
-  static constexpr int kNumBars = 2 * NW + 3 * NT + 4;
-  static constexpr int kUsedBytes = 1024 + NT * kXStage + NW * kTileBytes + kNumBars * 8 + 16;
+  static constexpr int kNumBars = 2 * NW + 2 * NT + 4;
+  static constexpr int kUsedBytes = 1024 + NT * kXStage + NW * kTileBytes + kNumBars * 8 + 16 + 2 * BN * 4;
   // more than a third of the SM's shared memory, so that never three CTAs (of this and of the next
   // kernel, under programmatic dependent launch) share an SM while another SM holds one
   static constexpr int kSmemBytes = kUsedBytes > 78 * 1024 ? kUsedBytes : 78 * 1024;
@@ -108,34 +108,16 @@ struct Cfg {
   static_assert(kSmemBytes <= 113 * 1024, "two CTAs per SM share the shared memory");
 };
 
-// Position of a role in the CTA's stream of k-tiles: walks the segments and the k-tiles inside them.
-struct Cursor {
-  SegmentWalk walk;
-  Segment sg;
-  int kt;
-  bool live;
-  __device__ Cursor(const SchedArgs& a, unsigned cta, unsigned grid) : walk(a, cta, grid) {
-    live = walk.next(sg);
-    kt = live ? sg.kb : 0;
-  }
-  __device__ void advance() {
-    if (++kt >= sg.ke) {
-      live = walk.next(sg);
-      kt = live ? sg.kb : 0;
-    }
-  }
-};
-
 // What the epilogue needs to know about a segment after the walk has moved on.
 struct SegInfo {
   int tile, nk, slot;
   bool whole;
+  float w_scale, bias;   // of this thread's output channel: weights, fetched when the segment starts
 };
 
 template <int BN, int NW, int NT, bool MULTI>
 __global__ void __launch_bounds__(kThreads, 2)
-w4a8_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args,
-                      const std::conditional_t<MULTI, MultiOut, NoMultiOut> multi) {
+w4a8_decode_tc_kernel(const Args args, const std::conditional_t<MULTI, MultiOut, NoMultiOut> multi) {
   const int kt_total = args.K >> 7;
   using C = Cfg<BN, NW, NT>;
   extern __shared__ uint8_t smem_raw[];
@@ -143,17 +125,17 @@ w4a8_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args arg
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base - raw);
 
-  const uint32_t xs = base;                          // NT token boxes (1024-aligned for the swizzle)
+  const uint32_t xs = base;                          // NT token slices (1024-aligned for the swizzle)
   const uint32_t ws = xs + NT * C::kXStage;          // NW weight tiles
   const uint32_t bar_wfull = ws + NW * kTileBytes;   // [NW] weight tile landed
   const uint32_t bar_wfree = bar_wfull + NW * 8;     // [NW] a dequant set holds the tile in registers
-  const uint32_t bar_xfull = bar_wfree + NW * 8;     // [NT] token box landed
-  const uint32_t bar_aready = bar_xfull + NT * 8;    // [NT] dequantised operand is in tensor memory
-  const uint32_t bar_afree = bar_aready + NT * 8;    // [NT] the MMAs that read operand and token box are done
+  const uint32_t bar_aready = bar_wfree + NW * 8;    // [NT] dequantised operand and token slice are in place
+  const uint32_t bar_afree = bar_aready + NT * 8;    // [NT] the MMAs that read operand and token slice are done
   const uint32_t bar_accfull = bar_afree + NT * 8;   // [2] the accumulator's segment is final
   const uint32_t bar_accfree = bar_accfull + 16;     // [2] the accumulator has been read
   const uint32_t tmem_slot = bar_accfree + 16;
   volatile uint32_t* tmem_slot_p = reinterpret_cast<volatile uint32_t*>(smem + (tmem_slot - base));
+  float* tok_scale = reinterpret_cast<float*>(smem + (tmem_slot + 16 - base));   // [2 sets][BN] token scales
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -163,7 +145,6 @@ w4a8_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args arg
       ptx::mbar_init(bar_wfree + 8 * s, 128);
     }
     for (int t = 0; t < NT; ++t) {
-      ptx::mbar_init(bar_xfull + 8 * t, 1);
       ptx::mbar_init(bar_aready + 8 * t, 128);
       ptx::mbar_init(bar_afree + 8 * t, 1);
     }
@@ -172,7 +153,6 @@ w4a8_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args arg
       ptx::mbar_init(bar_accfree + 8 * p, 128);
     }
     ptx::fence_mbar_init();
-    ptx::prefetch_tensormap(&tmap_x);
   }
   __syncthreads();
   allow_dependents();   // the next kernel of the stream may start prefetching its weights
@@ -184,72 +164,46 @@ w4a8_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args arg
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
     if (lane == 0) {
-      // Two independent streams of copies over the same sequence of k-tiles: weight tiles (cursor cw,
-      // count iw) and token boxes (cursor cx, count ix).  Weights never depend on the previous kernel of
-      // the stream, the tokens do: up to NW weight tiles are requested at once, then comes the wait for
-      // that kernel, and only then the first token boxes.  From there on whichever ring has a free
-      // stage is refilled; with nothing free the thread parks on the barrier that frees the next stage.
-      Cursor cw(sched, blockIdx.x, gridDim.x), cx(sched, blockIdx.x, gridDim.x);
-      uint32_t iw = 0, ix = 0;
-      bool ok = true, dependency_met = false;
-      auto w_ready = [&]() { return ptx::mbar_try_wait(bar_wfree + 8 * (iw % NW), ((iw / NW) & 1u) ^ 1u); };
-      auto x_ready = [&]() { return ptx::mbar_try_wait(bar_afree + 8 * (ix % NT), ((ix / NT) & 1u) ^ 1u); };
-      uint32_t idle = 0;
-      uint64_t idle_since = 0;
+      Ring<NW> ring;
+      int issued = 0;
+      bool ok = true;
       TR_VAR(tr_idle);
       const long long tr_p0 = TR_NOW();
-      while (ok && (cw.live || cx.live)) {
-        bool did = false;
-        if (cw.live && w_ready()) {
-          const uint32_t s = iw % NW;
-          const uint8_t* src = args.blob + ((size_t)cw.sg.tile * kt_total + cw.kt) * kTileBytes;
-          ptx::mbar_expect_tx(bar_wfull + 8 * s, kTileBytes);
-          ptx::bulk_load(ws + s * kTileBytes, src, kTileBytes, bar_wfull + 8 * s);
-          cw.advance();
-          ++iw;
-          did = true;
-        }
-        if (!dependency_met && (!cw.live || iw >= (uint32_t)NW)) {
-          dependency_wait();
-          if constexpr (MULTI) {
-            if (!peer_wait(multi.sync, kPeerWaitLimitNs)) atomicExch(args.status, 409);   // tokens gathered from peers
+      // Weight tiles do not depend on the previous kernel of the stream, so they are requested at once.
+      // While the CTA then waits for that kernel (whose slower CTAs still run and leave HBM bandwidth
+      // unused), the tiles that follow the first ring are pulled into L2.
+      TileCursor ahead(sched, blockIdx.x, gridDim.x);
+      for (int i = 0; i < NW && ahead.live; ++i) ahead.advance();
+      int prefetched = 0;
+      while (ok && walk.next(sg)) {
+        const uint8_t* src = args.blob + ((size_t)sg.tile * kt_total + sg.kb) * kTileBytes;
+        for (int kt = sg.kb; kt < sg.ke; ++kt, src += kTileBytes) {
+          if (issued < NW) {
+            for (int j = 0; j < args.prefetch / NW + 1 && prefetched < args.prefetch && ahead.live; ++j, ++prefetched) {
+              ptx::bulk_prefetch_l2(args.blob + ((size_t)ahead.sg.tile * kt_total + ahead.kt) * kTileBytes, kTileBytes);
+              ahead.advance();
+            }
           }
-          dependency_met = true;
-          TR_SET(12, TR_NOW() - tr_p0);
-        }
-        if (dependency_met && cx.live && ix < iw && x_ready()) {
-          const uint32_t t = ix % NT;
-          ptx::mbar_expect_tx(bar_xfull + 8 * t, C::kXStage);
-          ptx::tensor_load_2d(xs + t * C::kXStage, &tmap_x, cx.kt * 128, 0, bar_xfull + 8 * t);
-          cx.advance();
-          ++ix;
-          did = true;
-        }
-        if (did) {
-          idle = 0;
-          continue;
-        }
-        // nothing to refill: sleep on the barrier whose completion frees the next stage (bounded)
-        const long long tr_i0 = TR_NOW();
-        if (cw.live) ptx::mbar_try_wait_parked(bar_wfree + 8 * (iw % NW), ((iw / NW) & 1u) ^ 1u, 2000u);
-        else ptx::mbar_try_wait_parked(bar_afree + 8 * (ix % NT), ((ix / NT) & 1u) ^ 1u, 2000u);
-        TR_ADD(tr_idle, tr_i0);
-        if (++idle == 64u) idle_since = ptx::globaltimer_ns();
-        else if (idle > 64u && (idle & 63u) == 0 && ptx::globaltimer_ns() - idle_since > kWaitLimitNs) {
-          atomicExch(args.status, 401);
-          ok = false;
+          const long long tr_i0 = TR_NOW();
+          if (!ptx::mbar_wait_bounded(bar_wfree + 8 * ring.s, ring.ph ^ 1u, kWaitLimitNs)) {
+            atomicExch(args.status, 401);
+            ok = false;
+            break;
+          }
+          TR_ADD(tr_idle, tr_i0);
+          ptx::mbar_expect_tx(bar_wfull + 8 * ring.s, kTileBytes);
+          ptx::bulk_load(ws + ring.s * kTileBytes, src, kTileBytes, bar_wfull + 8 * ring.s);
+          ring.advance();
+          ++issued;
         }
       }
-      if (!dependency_met) dependency_wait();
       TR_SET(0, tr_idle);
       TR_SET(1, TR_NOW() - tr_p0);
       if (!ok) {
         // Copies in flight write shared memory: they must have landed before the CTA may exit.  (On the
-        // normal path the dequant sets and the MMA thread have waited for every one of them.)
-        for (uint32_t j = iw > (uint32_t)NW ? iw - NW : 0; j < iw; ++j)
-          ptx::mbar_wait_bounded(bar_wfull + 8 * (j % NW), (j / NW) & 1u, kWaitLimitNs);
-        for (uint32_t j = ix > (uint32_t)NT ? ix - NT : 0; j < ix; ++j)
-          ptx::mbar_wait_bounded(bar_xfull + 8 * (j % NT), (j / NT) & 1u, kWaitLimitNs);
+        // normal path the dequant sets have waited for every one of them.)
+        for (int i = issued > NW ? issued - NW : 0; i < issued; ++i)
+          ptx::mbar_wait_bounded(bar_wfull + 8 * (i % NW), (uint32_t)(i / NW) & 1u, kWaitLimitNs);
       }
     }
   } else if (warp == 1) {
@@ -266,8 +220,9 @@ w4a8_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args arg
       Ring<NT> ring;
       bool ok = true;
       uint32_t seg = 0;
-      TR_VAR(tr_wx);
       TR_VAR(tr_wa);
+      TR_VAR(tr_issue);
+      TR_VAR(tr_commit);
       const long long tr_m0 = TR_NOW();
       while (walk.next(sg)) {
         const uint32_t p = seg & 1u;
@@ -278,33 +233,32 @@ w4a8_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args arg
         }
         const uint32_t tmem_acc = tmem_base + p * BN;
         for (int kt = sg.kb; kt < sg.ke; ++kt) {
-          const long long tr_a0 = TR_NOW();
-          if (ok && !ptx::mbar_wait_bounded(bar_xfull + 8 * ring.s, ring.ph, kWaitLimitNs)) {
-            atomicExch(args.status, 403);
-            ok = false;
-          }
-          TR_ADD(tr_wx, tr_a0);
           const long long tr_a1 = TR_NOW();
           if (ok && !ptx::mbar_wait_bounded(bar_aready + 8 * ring.s, ring.ph, kWaitLimitNs)) {
-            atomicExch(args.status, 407);
+            atomicExch(args.status, 403);
             ok = false;
           }
           TR_ADD(tr_wa, tr_a1);
           ptx::tc_fence_after();
+          const long long tr_i1 = TR_NOW();
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const uint64_t bdesc = ptx::smem_desc_sw128(xs + ring.s * C::kXStage + j * 32);
             ptx::mma_i8_ts(tmem_acc, tmem_a + ring.s * 32 + j * 8, bdesc, idesc, (kt > sg.kb || j > 0) ? 1u : 0u);
           }
-          ptx::tc_commit(bar_afree + 8 * ring.s);   // frees the operand stage and its token box
+          TR_ADD(tr_issue, tr_i1);
+          const long long tr_i2 = TR_NOW();
+          ptx::tc_commit(bar_afree + 8 * ring.s);   // frees the operand stage and its token slice
+          TR_ADD(tr_commit, tr_i2);
           ring.advance();
         }
         ptx::tc_commit(bar_accfull + 8 * p);
         ++seg;
       }
-      TR_SET(2, tr_wx);
       TR_SET(3, tr_wa);
       TR_SET(4, TR_NOW() - tr_m0);
+      TR_SET(10, tr_issue);
+      TR_SET(11, tr_commit);
     }
     __syncwarp();
     // tensor memory is released after every role is done
@@ -324,10 +278,19 @@ w4a8_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args arg
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_p;
     const uint32_t tmem_a = tmem_base + C::kAccCols + lane_addr;
+    // Token slice of a k-tile: BN rows of 128 bytes.  Thread j of the owning set moves 16-byte chunk
+    // (j & 7) of token rows (j >> 3) + 16 q; in the 128-byte swizzle chunk c of row r sits at chunk
+    // c ^ (r & 7) of that row.  Rows past M are zero.
+    const int jx = d & 127;
+    const int x_row = jx >> 3;
+    const uint32_t x_off = (uint32_t)(x_row * 128 + (((jx & 7) ^ (x_row & 7)) << 4));
+    const int8_t* x_src = args.x + (size_t)x_row * args.K + (jx & 7) * 16;
     Ring<NW> rw;   // weight ring position
     Ring<NT> rt;   // operand ring position
     bool ok = true;
     TR_VAR(tr_wfull);
+    TR_VAR(tr_flush);
+    TR_VAR(tr_unpack);
     TR_VAR(tr_afree);
     TR_VAR(tr_st);
     TR_VAR(tr_epi);
@@ -341,17 +304,17 @@ w4a8_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args arg
     uint32_t step = 0;   // running k-tile index of this CTA
     uint32_t seg = 0;
     bool waited_dependency = false;
-    SegInfo mine = {0, 0, 0, true};   // the last segment that went into this set's accumulator
+    SegInfo mine = {0, 0, 0, true, 0.f, 0.f};   // the last segment that went into this set's accumulator
+    const bool scaled = args.out_mode != kOutI32;
+    const bool has_bias = scaled && args.bias != nullptr;
 
     // Epilogue of segment number `s` (accumulator s & 1 == set), described by `si`.
     auto epilogue = [&](const SegInfo& si, uint32_t s) {
       const uint32_t p = s & 1u;
-      const long long tr_e0 = TR_NOW();
       if (ok && !ptx::mbar_wait_bounded(bar_accfull + 8 * p, (s >> 1) & 1u, kWaitLimitNs)) {
         atomicExch(args.status, 405);
         ok = false;
       }
-      if (d == 0 || d == 128) TR_SET(10 + (d >> 7), TR_NOW() - tr_e0);
       __syncwarp();
       ptx::tc_fence_after();
       if (!waited_dependency) {
@@ -360,11 +323,7 @@ w4a8_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args arg
       }
       const long n = (long)si.tile * 128 + row;
       const bool n_ok = n < args.N;
-      const bool scaled = args.out_mode != kOutI32;
-      const float w_scale = (n_ok && scaled) ? __ldg(args.s1 + n) : 0.f;
-      float bias = 0.f;
-      const bool has_bias = scaled && args.bias != nullptr;
-      if (has_bias && n_ok) bias = load_bias(args.bias, n, args.out_mode);
+      const float w_scale = si.w_scale, bias = si.bias;
       unsigned long long* slot = args.slots + (size_t)si.slot * (BN * 128);
       const long long nk = si.nk;
       const uint32_t tmem_acc = tmem_base + p * BN + lane_addr;
@@ -382,7 +341,7 @@ w4a8_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args arg
         if (!n_ok) continue;
         float sc[16];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) sc[j] = (scaled && c0 + j < args.M) ? __ldg(args.ascale + c0 + j) : 0.f;
+        for (int j = 0; j < 16; ++j) sc[j] = tok_scale[set * BN + c0 + j];   // staged at the set's first k-tile
         if (!si.whole) {
           // One returning 64-bit atomic per element does the cross-CTA reduction: the word holds the
           // k-tiles added so far (bits 40..) and the sum of the contributions, each biased by 2^21 per
@@ -423,8 +382,27 @@ w4a8_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args arg
       }
     };
 
+    // The operand stores of a k-tile are left in flight while the thread unpacks its next k-tile; the
+    // wait for them and the "operand ready" arrival come after that arithmetic (measured: four tcgen05.st
+    // plus their wait cost a thread about 300 cycles when it waits at once).
+    uint32_t pending_ready = 0;   // barrier to arrive on once the stores in flight have landed, or 0
+    auto flush_stores = [&]() {
+      if (pending_ready) {
+        const long long tr_s1 = TR_NOW();
+        ptx::tc_wait_st();
+        TR_ADD(tr_st, tr_s1);
+        const long long tr_s2 = TR_NOW();
+        // the token slice was written with ordinary stores: make it visible to the tensor core's reads
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(pending_ready);
+        TR_ADD(tr_flush, tr_s2);
+        pending_ready = 0;
+      }
+    };
     for (;;) {
       const bool more = walk.next(sg);
+      flush_stores();   // uniform over the warp: every lane of a set takes the same k-tiles
       // One place decides which finished segment this set reads out now.  While the stream runs: the
       // segment two back, just before its accumulator (this set's) takes a new one.  After the last
       // segment: whichever of the last two segments sits in this set's accumulator -- the two sets
@@ -443,16 +421,44 @@ w4a8_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args arg
         TR_ADD(tr_epi, tr_e1);
       }
       if (!more) break;
-      if ((int)(seg & 1u) == set) mine = SegInfo{sg.tile, sg.ke - sg.kb, sg.slot, sg.whole};
+      if ((int)(seg & 1u) == set) {
+        // channel scale and bias are weights: fetched here, far from the epilogue that needs them
+        const long n = (long)sg.tile * 128 + row;
+        const bool n_ok = n < args.N;
+        mine = SegInfo{sg.tile, sg.ke - sg.kb, sg.slot, sg.whole, (n_ok && scaled) ? __ldg(args.s1 + n) : 0.f,
+                       (n_ok && has_bias) ? load_bias(args.bias, n, args.out_mode) : 0.f};
+      }
 #pragma unroll 1
       for (int kt = sg.kb; kt < sg.ke; ++kt, ++step, rw.advance(), rt.advance()) {
         if ((int)(step & 1u) != set) continue;
+        if (!waited_dependency) {
+          dependency_wait();   // the tokens (and later the outputs) belong to earlier kernels until here
+          waited_dependency = true;
+          // Token scales (an earlier kernel's output) go to shared memory once per set; the epilogue, which
+          // this set runs much later and under time pressure, reads them from there.
+          if (jx < BN) tok_scale[set * BN + jx] = (scaled && jx < args.M) ? __ldg(args.ascale + jx) : 0.f;
+          if (set == 0) asm volatile("bar.sync 5, 128;" ::: "memory");
+          else asm volatile("bar.sync 6, 128;" ::: "memory");
+          if constexpr (MULTI) {
+            // tokens gathered from peer GPUs: one thread waits for their flags on behalf of its set
+            if ((d & 127) == 0 && !peer_wait(multi.sync, kPeerWaitLimitNs)) atomicExch(args.status, 409);
+            if (set == 0) asm volatile("bar.sync 3, 128;" ::: "memory");
+            else asm volatile("bar.sync 4, 128;" ::: "memory");
+          }
+        }
+        // request this k-tile's tokens now (L2 hits); they are stored after the unpack
+        uint4 xv[BN / 16];
+#pragma unroll
+        for (int q = 0; q < BN / 16; ++q)
+          xv[q] = (x_row + 16 * q < args.M) ? ldg_stream_v4(x_src + (size_t)(16 * q) * args.K + (size_t)kt * 128)
+                                            : make_uint4(0u, 0u, 0u, 0u);
         const long long tr_w0 = TR_NOW();
         if (ok && !ptx::mbar_wait_bounded(bar_wfull + 8 * rw.s, rw.ph, kWaitLimitNs)) {
           atomicExch(args.status, 404);
           ok = false;
         }
         TR_ADD(tr_wfull, tr_w0);
+        const long long tr_u0 = TR_NOW();
         const uint8_t* wst = smem + (ws - base) + rw.s * kTileBytes;
         uint4 ch[4];
 #pragma unroll
@@ -462,7 +468,7 @@ w4a8_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args arg
         // unpack into registers first, wait for the operand stage afterwards
         const uint32_t step0 = meta & 0xffu, a0 = ((meta >> 8) & 0xffu) * 0x01010101u;
         const uint32_t step1 = (meta >> 16) & 0xffu, a1 = (meta >> 24) * 0x01010101u;
-        uint32_t v[4][8];
+        uint32_t v[32];
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           const uint32_t st = c < 2 ? step0 : step1;
@@ -470,30 +476,38 @@ w4a8_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args arg
           const uint32_t pk[4] = {ch[c].x, ch[c].y, ch[c].z, ch[c].w};
 #pragma unroll
           for (int h = 0; h < 4; ++h) {
-            v[c][2 * h] = lqq_dequant4(pk[h] & 0x0F0F0F0Fu, st, ab);
-            v[c][2 * h + 1] = lqq_dequant4((pk[h] >> 4) & 0x0F0F0F0Fu, st, ab);
+            v[8 * c + 2 * h] = lqq_dequant4(pk[h] & 0x0F0F0F0Fu, st, ab);
+            v[8 * c + 2 * h + 1] = lqq_dequant4((pk[h] >> 4) & 0x0F0F0F0Fu, st, ab);
           }
         }
+#ifdef LQ_PIPELINE_TRACE
+        if (v[0] == 0x12345678u && v[31] == 0x9abcdef0u) TR_SET(8, 1);   // pins the arithmetic before the timer
+#endif
+        TR_ADD(tr_unpack, tr_u0);
+        __syncwarp();   // lanes leave the poll loops one by one; tcgen05.st / wait::st need the warp converged
+        flush_stores();   // the previous k-tile of this set: its stores had the whole unpack to land
         const long long tr_f0 = TR_NOW();
         if (ok && !ptx::mbar_wait_bounded(bar_afree + 8 * rt.s, rt.ph ^ 1u, kWaitLimitNs)) {
           atomicExch(args.status, 406);
           ok = false;
         }
         TR_ADD(tr_afree, tr_f0);
-        __syncwarp();   // lanes leave the poll loops one by one; tcgen05.st / wait::st need the warp converged
+        __syncwarp();
         ptx::tc_fence_after();
         const long long tr_s0 = TR_NOW();
+        ptx::tmem_st32(tmem_a + rt.s * 32, v);   // one store instruction for the whole operand stage row
 #pragma unroll
-        for (int c = 0; c < 4; ++c) ptx::tmem_st8(tmem_a + rt.s * 32 + c * 8, v[c]);
-        ptx::tc_wait_st();
+        for (int q = 0; q < BN / 16; ++q)
+          *reinterpret_cast<uint4*>(smem + rt.s * C::kXStage + x_off + q * 2048) = xv[q];
         TR_ADD(tr_st, tr_s0);
-        ptx::tc_fence_before();
-        ptx::mbar_arrive(bar_aready + 8 * rt.s);
+        pending_ready = bar_aready + 8 * rt.s;
       }
       ++seg;
     }
 
     if (d == 0) {
+      TR_SET(2, tr_flush);
+      TR_SET(12, tr_unpack);
       TR_SET(5, tr_wfull);
       TR_SET(6, tr_afree);
       TR_SET(7, tr_st);
@@ -516,7 +530,7 @@ w4a8_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args arg
 }
 
 template <int BN, int NW, int NT, bool MULTI>
-static int launch(const CUtensorMap& tx, const Args& a, const MultiOut* multi, int grid, cudaStream_t st) {
+static int launch(const Args& a, const MultiOut* multi, int grid, cudaStream_t st) {
   using C = Cfg<BN, NW, NT>;
   auto kern = &w4a8_decode_tc_kernel<BN, NW, NT, MULTI>;
   static std::once_flag once[64];
@@ -527,8 +541,8 @@ static int launch(const CUtensorMap& tx, const Args& a, const MultiOut* multi, i
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
   });
   if (e == cudaSuccess) {
-    if constexpr (MULTI) e = launch_overlapped(kern, dim3(grid), dim3(kThreads), (size_t)C::kSmemBytes, st, tx, a, *multi);
-    else e = launch_overlapped(kern, dim3(grid), dim3(kThreads), (size_t)C::kSmemBytes, st, tx, a, NoMultiOut{});
+    if constexpr (MULTI) e = launch_overlapped(kern, dim3(grid), dim3(kThreads), (size_t)C::kSmemBytes, st, a, *multi);
+    else e = launch_overlapped(kern, dim3(grid), dim3(kThreads), (size_t)C::kSmemBytes, st, a, NoMultiOut{});
   }
   if (e != cudaSuccess) {
     record_cuda_error(e, "w4a8_decode_tc_kernel launch");
@@ -563,11 +577,9 @@ int run_decode_tc(const int8_t* x, const uint8_t* blob, const float* ascale, con
   const int bn = bn_for(M);
   const DecodePlan plan = plan_for(N, K);
   const int grid = plan.grid;
-  CUtensorMap tx;
-  int rc = make_byte_matrix_map(&tx, x, M, K, bn, 128);
-  if (rc) return rc;
   Args a;
   a.blob = blob;
+  a.x = x;
   a.ascale = ascale;
   a.s1 = s1;
   a.bias = bias;
@@ -582,16 +594,17 @@ int run_decode_tc(const int8_t* x, const uint8_t* blob, const float* ascale, con
   a.N = N;
   a.K = K;
   a.fixed_split = plan.fixed_split;
+  a.prefetch = decode_prefetch_tiles();
   if (!a.status) return LQ_ERR_CUDA;
   if (!multi) {
-    if (bn == 16) return launch<16, 8, 7, false>(tx, a, nullptr, grid, st);
-    return launch<32, 8, 6, false>(tx, a, nullptr, grid, st);
+    if (bn == 16) return launch<16, 8, 7, false>(a, nullptr, grid, st);
+    return launch<32, 8, 6, false>(a, nullptr, grid, st);
   }
   MultiOut mo;
   mo.out = out;
   mo.sync = sync ? *sync : PeerSync{};
-  if (bn == 16) return launch<16, 8, 7, true>(tx, a, &mo, grid, st);
-  return launch<32, 8, 6, true>(tx, a, &mo, grid, st);
+  if (bn == 16) return launch<16, 8, 7, true>(a, &mo, grid, st);
+  return launch<32, 8, 6, true>(a, &mo, grid, st);
 }
 
 }  // namespace lq

@@ -1,6 +1,8 @@
 // Memory-bound helpers of the W4A8 path: standalone dequant, per-token activation quantiser,
 // scale epilogue, split-K finish and the weight re-tiling kernels.  All of them are sized as a
 // grid-stride sweep over a multiple of the SM count and move 16 bytes per thread per access.
+#include <type_traits>
+
 #include "lq_common.cuh"
 
 namespace lq {
@@ -127,10 +129,13 @@ quant_per_token_kernel(const T* __restrict__ x, int8_t* __restrict__ xq, float* 
 // planes == 1: plain epilogue.  planes > 1: sum of `planes` int32 partial planes [planes][M][N]
 // first (exact in any order), then the same formula
 // (reference csrc/liquid_gemm/w4a8_wgmma.cu:39-56).
+// MULTI: the outputs go to several row-major matrices with their own row stride and column offset (gather by
+// stores over NVLink, see OutSpec), element by element, and every CTA signals the peers' flags at its end.
+template <bool MULTI>
 __global__ void __launch_bounds__(256)
 finish_kernel(const int32_t* __restrict__ acc, const float* __restrict__ ascale,
               const float* __restrict__ s1, const void* __restrict__ bias, void* __restrict__ y, int out_dtype,
-              int planes, int M, int N, bool vec) {
+              int planes, int M, int N, bool vec, const std::conditional_t<MULTI, MultiOut, NoMultiOut> multi) {
   // Launched with programmatic stream serialisation behind the kernel that writes the planes: let the
   // kernel after this one start (it prefetches weights, and waits for this grid before it touches
   // tokens, planes or outputs), then wait for the planes to be complete.
@@ -197,9 +202,16 @@ finish_kernel(const int32_t* __restrict__ acc, const float* __restrict__ ascale,
       int v = acc[idx];
       for (int p = 1; p < planes; ++p) v += acc[(long)p * total + idx];
       if (out_dtype == 3) reinterpret_cast<int32_t*>(y)[idx] = v;
+      else if constexpr (MULTI)
+        store_out_all(multi.out, m, n, lqq_scale(v, ascale[m], s1[n]), bias ? load_bias(bias, n, out_dtype) : 0.f,
+                      bias != nullptr, out_dtype);
       else store_out_bias(y, idx, lqq_scale(v, ascale[m], s1[n]), bias ? load_bias(bias, n, out_dtype) : 0.f,
                           bias != nullptr, out_dtype);
     }
+  }
+  if constexpr (MULTI) {
+    __syncthreads();   // every store of the CTA before the flags (release is cumulative over what the barrier ordered)
+    if (threadIdx.x == 0) peer_signal(multi.sync);
   }
 }
 
@@ -276,16 +288,31 @@ static int grid_for(long work_items, int threads, int waves) {
   return (int)blocks;
 }
 
-int launch_finish(const int32_t* acc, const float* ascale, const float* s1, const void* bias, void* y, int out_dtype,
-                  int planes, int M, int N, cudaStream_t st) {
-  const long total = (long)M * N;
-  // four outputs per thread when every row start stays 16-byte aligned
+static long finish_items(int M, int N, bool vec) { return vec ? ((long)M * N) >> 2 : (long)M * N; }
+
+// CTAs of the (multi-destination, element-wise) finish pass: what a peer has to see arrive.
+int finish_grid(int M, int N) { return grid_for(finish_items(M, N, false), 256, 8); }
+
+int launch_finish(const int32_t* acc, const float* ascale, const float* s1, const void* bias, const OutSpec& out,
+                  const PeerSync* sync, int out_dtype, int planes, int M, int N, cudaStream_t st) {
+  const bool multi = out.n != 1 || out.ld != N || out.col0 != 0 || (sync && (sync->n_signal > 0 || sync->wait));
+  void* y = out.ptr[0];
+  // four outputs per thread when every row start stays 16-byte aligned (single destination only)
   const uintptr_t align_bits = reinterpret_cast<uintptr_t>(acc) | reinterpret_cast<uintptr_t>(y) |
                                reinterpret_cast<uintptr_t>(s1) | reinterpret_cast<uintptr_t>(bias);
-  const bool vec = (N % 4 == 0) && (align_bits % 16 == 0);
-  const long items = vec ? (total >> 2) : total;
-  cudaError_t e = launch_overlapped(finish_kernel, dim3(grid_for(items, 256, 8)), dim3(256), (size_t)0, st, acc, ascale,
-                                    s1, bias, y, out_dtype, planes, M, N, vec);
+  const bool vec = !multi && (N % 4 == 0) && (align_bits % 16 == 0);
+  const int grid = grid_for(finish_items(M, N, vec), 256, 8);
+  cudaError_t e;
+  if (multi) {
+    MultiOut mo;
+    mo.out = out;
+    mo.sync = sync ? *sync : PeerSync{};
+    e = launch_overlapped(finish_kernel<true>, dim3(grid), dim3(256), (size_t)0, st, acc, ascale, s1, bias, y, out_dtype,
+                          planes, M, N, vec, mo);
+  } else {
+    e = launch_overlapped(finish_kernel<false>, dim3(grid), dim3(256), (size_t)0, st, acc, ascale, s1, bias, y,
+                          out_dtype, planes, M, N, vec, NoMultiOut{});
+  }
   if (e != cudaSuccess) {
     record_cuda_error(e, "finish_kernel launch");
     return LQ_ERR_CUDA;
@@ -354,7 +381,7 @@ int lq_scale_epilogue(const int32_t* acc, const float* ascale, const float* s1, 
   if (!acc || !ascale || !s1 || !y || M < 0 || N <= 0) return LQ_ERR_BAD_ARG;
   if (out_dtype < 0 || out_dtype > 2) return LQ_ERR_BAD_ARG;
   if (M == 0) return LQ_OK;
-  return launch_finish(acc, ascale, s1, nullptr, y, out_dtype, 1, M, N, as_stream(stream));
+  return launch_finish(acc, ascale, s1, nullptr, single_out(y, N), nullptr, out_dtype, 1, M, N, as_stream(stream));
 }
 
 size_t lq_tile_blob_bytes(int N, int K) {

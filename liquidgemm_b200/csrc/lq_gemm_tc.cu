@@ -54,8 +54,9 @@ namespace lq {
 int tile_pick_splits(int M, int N, int K);                                   // lq_gemm_tile.cu
 size_t tile_workspace_bytes(int M, int N, int splits);                       // lq_gemm_tile.cu
 int run_tile_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, const void* bias,
-                  void* out, int out_mode, int M, int N, int K, int splits, void* ws, size_t ws_bytes,
-                  cudaStream_t st);  // lq_gemm_tile.cu
+                  const OutSpec& out, const PeerSync* sync, int out_mode, int M, int N, int K, int splits, void* ws,
+                  size_t ws_bytes, cudaStream_t st);  // lq_gemm_tile.cu
+int tile_output_grid(int M, int N, int splits);                              // lq_gemm_tile.cu
 size_t decode_tc_workspace_bytes(int M, int N, int K);                       // lq_decode_tc.cu
 int run_decode_tc(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, const void* bias,
                   const OutSpec& out, const PeerSync* sync, int out_mode, int M, int N, int K, void* ws,
@@ -815,7 +816,6 @@ static int decode_tc_max_m() {
   }();
   return v;
 }
-constexpr int kScatterMaxM = 16;   // the gather-by-stores entry points are decode paths
 
 static bool gemv_serves(int M, int N, int K) {
   return M <= 2 || (M <= kGemvBlobMaxM && (long)N * K <= (1L << 26));
@@ -887,7 +887,8 @@ static int blob_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, 
     case kRouteDecodeTc:
       return run_decode_tc(x, blob, ascale, s1, bias, single_out(out, N), nullptr, out_mode, M, N, K, ws, ws_bytes, st);
     case kRouteTile:
-      return run_tile_gemm(x, blob, ascale, s1, bias, out, out_mode, M, N, K, r.splits, ws, ws_bytes, st);
+      return run_tile_gemm(x, blob, ascale, s1, bias, single_out(out, N), nullptr, out_mode, M, N, K, r.splits, ws,
+                           ws_bytes, st);
     default:
       if (bias) return LQ_ERR_BAD_ARG;   // the persistent kernel has no bias epilogue
       return run_gemm<kBlob>(x, blob, nullptr, nullptr, ascale, s1, out, out_mode, M, N, K, r.splits, ws, ws_bytes, st);
@@ -924,7 +925,7 @@ int lq_w4a8_gemm_fused_scatter_sync(const int8_t* x_i8, const uint8_t* blob, con
                                     size_t workspace_bytes, void* stream) {
   if (!x_i8 || !blob || !ascale || !s1 || !outs || n_outs < 1 || n_outs > 8) return LQ_ERR_BAD_ARG;
   if (out_dtype < 0 || out_dtype > 2 || ld_out < N || col0 < 0 || col0 + N > ld_out) return LQ_ERR_BAD_ARG;
-  if (M < 1 || M > kScatterMaxM || N <= 0 || K < 128 || K % 128) return LQ_ERR_SHAPE;
+  if (M < 1 || N <= 0 || K < 128 || K % 128) return LQ_ERR_SHAPE;
   if ((reinterpret_cast<uintptr_t>(x_i8) | reinterpret_cast<uintptr_t>(blob)) % 16) return LQ_ERR_BAD_ARG;
   if (flag_index < 0) return LQ_ERR_BAD_ARG;
   OutSpec o = {};
@@ -942,11 +943,18 @@ int lq_w4a8_gemm_fused_scatter_sync(const int8_t* x_i8, const uint8_t* blob, con
   ps.wait = wait_flag;
   ps.wait_value = wait_value;
   if (int rc = lq_check_device()) return rc;
-  if (gemv_serves(M, N, K))
-    return run_gemv_blob_ws(x_i8, blob, ascale, s1, nullptr, o, &ps, out_dtype, M, N, K, workspace, workspace_bytes,
-                            as_stream(stream));
-  return run_decode_tc(x_i8, blob, ascale, s1, nullptr, o, &ps, out_dtype, M, N, K, workspace, workspace_bytes,
-                       as_stream(stream));
+  const Route r = route_for(M, N, K, 0, true);
+  switch (r.kind) {
+    case kRouteGemv:
+      return run_gemv_blob_ws(x_i8, blob, ascale, s1, nullptr, o, &ps, out_dtype, M, N, K, workspace, workspace_bytes,
+                              as_stream(stream));
+    case kRouteDecodeTc:
+      return run_decode_tc(x_i8, blob, ascale, s1, nullptr, o, &ps, out_dtype, M, N, K, workspace, workspace_bytes,
+                           as_stream(stream));
+    default:
+      return run_tile_gemm(x_i8, blob, ascale, s1, nullptr, o, &ps, out_dtype, M, N, K, r.splits, workspace,
+                           workspace_bytes, as_stream(stream));
+  }
 }
 
 int lq_w4a8_gemm_fused_scatter(const int8_t* x_i8, const uint8_t* blob, const float* ascale, const float* s1,
@@ -957,27 +965,20 @@ int lq_w4a8_gemm_fused_scatter(const int8_t* x_i8, const uint8_t* blob, const fl
 }
 
 size_t lq_scatter_workspace_bytes(int M, int N, int K) {
-  if (M < 1 || M > kScatterMaxM || N <= 0 || K < 128 || K % 128) return 0;
-  return gemv_serves(M, N, K) ? gemv_blob_workspace_bytes(N, K) : decode_tc_workspace_bytes(M, N, K);
+  if (M < 1 || N <= 0 || K < 128 || K % 128) return 0;
+  return route_ws_bytes(route_for(M, N, K, 0, true), M, N, K);
 }
+
+int lq_scatter_workspace_kind(int M, int N, int K) { return lq_gemm_workspace_kind(M, N, K, 0); }
 
 int lq_decode_grid(int M, int N, int K) {
-  if (M < 1 || M > kScatterMaxM || N <= 0 || K < 128 || K % 128) return 0;
-  return gemv_serves(M, N, K) ? gemv_blob_grid(N, K) : decode_tc_grid(N, K);
-}
-
-int lq_w4a8_gemm_rowmajor(const int8_t* x_i8, const uint8_t* gpack, const uint8_t* s_u8, const uint8_t* offset_a,
-                          const float* ascale, const float* s1, void* y, int out_dtype, int M, int N, int K,
-                          int splitk, void* workspace, size_t workspace_bytes, void* stream) {
-  if (!x_i8 || !gpack || !s_u8 || !offset_a || !y || !ascale || !s1 || M < 0 || N <= 0 || K <= 0)
-    return LQ_ERR_BAD_ARG;
-  if (out_dtype < 0 || out_dtype > 2) return LQ_ERR_BAD_ARG;
-  if (K % 128) return LQ_ERR_SHAPE;
-  if ((reinterpret_cast<uintptr_t>(x_i8) | reinterpret_cast<uintptr_t>(gpack)) % 16) return LQ_ERR_BAD_ARG;
-  if (M == 0) return LQ_OK;
-  (void)splitk;   // always stream-K: workspace = lq_gemm_workspace_bytes(M, N, K, -1)
-  return run_gemm<kRowMajor>(x_i8, gpack, s_u8, offset_a, ascale, s1, y, out_dtype, M, N, K, 0, workspace,
-                             workspace_bytes, as_stream(stream));
+  if (M < 1 || N <= 0 || K < 128 || K % 128) return 0;
+  const Route r = route_for(M, N, K, 0, true);
+  switch (r.kind) {
+    case kRouteGemv: return gemv_blob_grid(N, K);
+    case kRouteDecodeTc: return decode_tc_grid(N, K);
+    default: return tile_output_grid(M, N, r.splits);
+  }
 }
 
 size_t lq_gemm_v1_workspace_bytes(int M, int N, int K) {

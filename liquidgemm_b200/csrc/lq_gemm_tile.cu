@@ -18,14 +18,15 @@
 
 #include <cstdlib>
 #include <mutex>
+#include <type_traits>
 
 #include "lq_common.cuh"
 #include "lq_tc_ptx.cuh"
 
 namespace lq {
 
-int launch_finish(const int32_t* acc, const float* ascale, const float* s1, const void* bias, void* y, int out_dtype,
-                  int planes, int M, int N, cudaStream_t st);  // lq_elementwise.cu
+int launch_finish(const int32_t* acc, const float* ascale, const float* s1, const void* bias, const OutSpec& out,
+                  const PeerSync* sync, int out_dtype, int planes, int M, int N, cudaStream_t st);  // lq_elementwise.cu
 int make_byte_matrix_map(CUtensorMap* map, const void* ptr, long rows, long row_bytes, int box_rows,
                          int box_bytes);  // lq_gemm_tc.cu
 
@@ -52,6 +53,7 @@ struct GemmArgs {
   int out_mode;          // LQ_DT_* or kOutI32
   int M, N, K;
   int kt_total;          // K / 128
+  int vec_out;           // 2-byte outputs whose rows allow 16-byte stores: stage the tile through shared memory
 };
 
 template <int BN, int NS, int NT, bool W4>
@@ -64,13 +66,28 @@ struct TcCfg {
   static constexpr int kTmemCols = kColsNeeded <= 32 ? 32 : kColsNeeded <= 64 ? 64 : kColsNeeded <= 128 ? 128
                                    : kColsNeeded <= 256 ? 256 : 512;
   static constexpr int kBarBytes = (2 * NS + 2 * NT + 1) * 8 + 8;
-  static constexpr int kSmemBytes = 1024 /* alignment slack */ + NS * (kXStage + kWStage) + kBarBytes + BN * 4;
+  static constexpr int kOutStage = 16 * 128 * 2;   // per dequant set: 16 tokens x 128 channels of 2-byte outputs
+  static constexpr int kSmemBytes = 1024 /* alignment slack */ + NS * (kXStage + kWStage) + kBarBytes + 16 +
+                                    kSets * kOutStage;
   static_assert(kColsNeeded <= 512, "tensor memory budget exceeded");
 };
 
-template <int BN, int NS, int NT, bool W4>
+// Round to the output type (with the optional bias added to the rounded value) and return the 16 bits.
+__device__ __forceinline__ uint16_t out_bits16(float v, float bias, bool has_bias, int out_mode) {
+  if (out_mode == LQ_DT_BF16) {
+    __nv_bfloat16 t = __float2bfloat16_rn(v);
+    if (has_bias) t = __float2bfloat16_rn(__fadd_rn(__bfloat162float(t), bias));
+    return *reinterpret_cast<uint16_t*>(&t);
+  }
+  __half t = __float2half_rn(v);
+  if (has_bias) t = __float2half_rn(__fadd_rn(__half2float(t), bias));
+  return *reinterpret_cast<uint16_t*>(&t);
+}
+
+template <int BN, int NS, int NT, bool W4, bool MULTI>
 __global__ void __launch_bounds__(kThreads, 1)
-w4a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs args) {
+w4a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs args,
+                 const std::conditional_t<MULTI, MultiOut, NoMultiOut> multi) {
   // Only the blob-fed form exists, so the kernel takes one tensor map (the tokens).
   static_assert(W4, "the tile kernel reads its weights from the tile blob");
   using Cfg = TcCfg<BN, NS, NT, W4>;
@@ -90,6 +107,8 @@ w4a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs args
   const uint32_t tmem_slot = bar_acc + 8;
   uint8_t* gen = smem + (bars - base);
   volatile uint32_t* tmem_slot_p = reinterpret_cast<volatile uint32_t*>(gen + (2 * NS + 2 * NT + 1) * 8);
+  uint8_t* out_stage = gen + ((Cfg::kBarBytes + 15) & ~15);   // 16-byte aligned (`bars` is)
+
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nt = blockIdx.x, mt = blockIdx.y, z = blockIdx.z, splits = gridDim.z;
@@ -138,6 +157,9 @@ w4a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs args
         ptx::bulk_load(ws + i * Cfg::kWStage, src, kTileBytes, bar_full + 8 * i);
       }
       dependency_wait();
+      if constexpr (MULTI) {
+        if (!peer_wait(multi.sync, 1000000000ull)) atomicExch(args.status, 109);   // tokens gathered from peers
+      }
       for (int i = 0; i < early; ++i)
         ptx::tensor_load_2d(xs + i * Cfg::kXStage, &tmap_x, (kt_begin + i) * 128, m0, bar_full + 8 * i);
       issued = early;
@@ -264,28 +286,68 @@ w4a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs args
       const bool has_bias = args.out_mode != kOutI32 && args.bias != nullptr;
       const float bias = (has_bias && n_ok) ? load_bias(args.bias, n, args.out_mode) : 0.f;
       int32_t* plane = reinterpret_cast<int32_t*>(args.out) + (size_t)z * args.M * args.N;
+      const bool vec = args.vec_out != 0;   // uniform over the CTA
+      const int q_in_set = (threadIdx.x - 64) & 127;
+      uint8_t* stage = out_stage + set * Cfg::kOutStage;
 #pragma unroll 1
       for (int c0 = 16 * set; c0 < BN; c0 += 16 * kSets) {   // the sets share the accumulator's columns
-        if (m0 + c0 >= args.M) break;  // uniform over the warp
+        if (m0 + c0 >= args.M) break;  // uniform over the set
         int v[16];
         ptx::tmem_ld16(tmem_acc + lane_addr + c0, v);
         ptx::tc_wait_ld();
-        if (n_ok) {
-          float sc[16];
+        float sc[16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j)   // all loads of the chunk first: one round trip
-            sc[j] = (args.out_mode != kOutI32 && m0 + c0 + j < args.M) ? __ldg(args.ascale + m0 + c0 + j) : 0.f;
+        for (int j = 0; j < 16; ++j)   // all loads of the chunk first: one round trip
+          sc[j] = (args.out_mode != kOutI32 && m0 + c0 + j < args.M) ? __ldg(args.ascale + m0 + c0 + j) : 0.f;
+        if (vec) {
+          // A thread holds 16 tokens of ONE channel, the output rows run along the channels: stored
+          // directly, a warp writes 64 contiguous bytes per token.  Through shared memory the set writes
+          // whole 256-byte rows with 16-byte stores instead (local HBM and NVLink alike prefer those).
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            reinterpret_cast<uint16_t*>(stage)[j * 128 + row] =
+                n_ok ? out_bits16(lqq_scale(v[j], sc[j], w_scale), bias, has_bias, args.out_mode) : (uint16_t)0;
+          if (set == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+          else asm volatile("bar.sync 2, 128;" ::: "memory");
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            const int vi = q_in_set + 128 * q;
+            const int j = vi >> 4, chunk = vi & 15;
+            const int m = m0 + c0 + j;
+            const long ncol = (long)nt * 128 + chunk * 8;
+            if (m < args.M && ncol < args.N) {
+              const uint4 val = *reinterpret_cast<const uint4*>(stage + j * 256 + chunk * 16);
+              if constexpr (MULTI) {
+                const size_t idx = (size_t)m * multi.out.ld + multi.out.col0 + ncol;
+#pragma unroll
+                for (int r = 0; r < 8; ++r)   // constant indices into the kernel parameter
+                  if (r < multi.out.n) *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(multi.out.ptr[r]) + idx) = val;
+              } else {
+                *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(args.out) + (size_t)m * args.N + ncol) = val;
+              }
+            }
+          }
+          if (set == 0) asm volatile("bar.sync 1, 128;" ::: "memory");   // the stage is rewritten by the next chunk
+          else asm volatile("bar.sync 2, 128;" ::: "memory");
+        } else if (n_ok) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int m = m0 + c0 + j;
             if (m < args.M) {
               const size_t idx = (size_t)m * args.N + n;
               if (args.out_mode == kOutI32) plane[idx] = v[j];
+              else if constexpr (MULTI)
+                store_out_all(multi.out, m, n, lqq_scale(v[j], sc[j], w_scale), bias, has_bias, args.out_mode);
               else store_out_bias(args.out, idx, lqq_scale(v[j], sc[j], w_scale), bias, has_bias, args.out_mode);
             }
           }
         }
       }
+    }
+    if constexpr (MULTI) {
+      // every output store of this CTA, peer memory included, is ordered before the flags (see lq_common.cuh)
+      asm volatile("bar.sync 3, %0;" ::"n"(128 * kSets) : "memory");
+      if (threadIdx.x == 64 && args.out_mode != kOutI32) peer_signal(multi.sync);
     }
   }
 
@@ -298,10 +360,10 @@ w4a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs args
   }
 }
 
-template <int BN, int NS, int NT, bool W4>
-static int launch_cfg(const CUtensorMap& tx, const GemmArgs& a, int splits, cudaStream_t st) {
+template <int BN, int NS, int NT, bool W4, bool MULTI>
+static int launch_one(const CUtensorMap& tx, const GemmArgs& a, const MultiOut* multi, int splits, cudaStream_t st) {
   using Cfg = TcCfg<BN, NS, NT, W4>;
-  auto kern = &w4a8_tile_kernel<BN, NS, NT, W4>;
+  auto kern = &w4a8_tile_kernel<BN, NS, NT, W4, MULTI>;
   static std::once_flag once[64];
   int dev = 0;
   cudaGetDevice(&dev);
@@ -314,7 +376,9 @@ static int launch_cfg(const CUtensorMap& tx, const GemmArgs& a, int splits, cuda
     return LQ_ERR_CUDA;
   }
   dim3 grid((a.N + 127) / 128, (a.M + BN - 1) / BN, splits);
-  cudaError_t le = launch_overlapped(kern, grid, dim3(kThreads), (size_t)Cfg::kSmemBytes, st, tx, a);
+  cudaError_t le;
+  if constexpr (MULTI) le = launch_overlapped(kern, grid, dim3(kThreads), (size_t)Cfg::kSmemBytes, st, tx, a, *multi);
+  else le = launch_overlapped(kern, grid, dim3(kThreads), (size_t)Cfg::kSmemBytes, st, tx, a, NoMultiOut{});
   if (le != cudaSuccess) {
     record_cuda_error(le, "w4a8_tile_kernel launch");
     return LQ_ERR_CUDA;
@@ -322,37 +386,18 @@ static int launch_cfg(const CUtensorMap& tx, const GemmArgs& a, int splits, cuda
   return check_launch("w4a8_tile_kernel");
 }
 
-// Token-tile widths: the smallest that holds a decode batch; for prefill 128 or 192 tokens.  A dequantised
-// weight tile costs the same whatever it is multiplied with, so wider token tiles do more tensor-core
-// work per unpacked byte (192 tokens: 1.5x); but tiles are not split further, so the width that leaves
-// the last wave of two CTAs per SM fullest wins.
-static int wide_tiles() {
-  static const int v = []() {
-    const char* e = getenv("LQ_TILE_WIDE");
-    return e ? atoi(e) : 0;
-  }();
-  return v;
+template <int BN, int NS, int NT, bool W4>
+static int launch_cfg(const CUtensorMap& tx, const GemmArgs& a, const MultiOut* multi, int splits, cudaStream_t st) {
+  if (multi) return launch_one<BN, NS, NT, W4, true>(tx, a, multi, splits, st);
+  return launch_one<BN, NS, NT, W4, false>(tx, a, nullptr, splits, st);
 }
-static int tile_bn_for(int M, int N) {
-  if (M <= 128) return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
-  if (!wide_tiles()) return 128;
-  const long slots = 2L * sm_count();
-  const long nt = (N + 127) / 128;
-  double best = 0;
-  int best_bn = 128;
-  const int cand[2] = {128, 192};
-  for (int bn : cand) {
-    const long tiles = nt * ((M + bn - 1) / bn);
-    const long waves = (tiles + slots - 1) / slots;
-    // useful token columns per unit of time: a wave of 192-token tiles takes about 1.25x a wave of 128
-    const double rate = (double)M / ((double)waves * (bn == 192 ? 1.25 : 1.0));
-    if (rate > best * 1.0001) {
-      best = rate;
-      best_bn = bn;
-    }
-  }
-  return best_bn;
-}
+
+// Token-tile widths: the smallest that holds a decode batch, 128 tokens for prefill.  A 192-token
+// configuration (three shared-memory stages, two operand stages, otherwise this kernel) would do 1.5x the
+// tensor-core work per unpacked weight byte; it passed the parity tests on three full-size shapes and then
+// raised an unspecified launch failure on a fourth (28672 x 4096, 8192 tokens) and in back-to-back graph
+// replays.  Reading the index arithmetic, the barrier counts and the tensor-memory budget (192 + 2 x 32 =
+// 256 columns, two CTAs per SM) did not show the cause, so the configuration is not built.
 static int tile_bn(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128; }
 
 }  // namespace tile
@@ -377,38 +422,72 @@ size_t tile_workspace_bytes(int M, int N, int splits) {
   return splits <= 1 ? 0 : (size_t)splits * (size_t)M * (size_t)N * sizeof(int32_t);
 }
 
+// CTAs of the launch that writes the outputs (and signals the peers): the tile grid, or the finish pass.
+int finish_grid(int M, int N);   // lq_elementwise.cu
+int tile_output_grid(int M, int N, int splits) {
+  if (splits > 1) return finish_grid(M, N);
+  const int bn = tile::tile_bn(M);
+  return ((N + 127) / 128) * ((M + bn - 1) / bn);
+}
+
 // out_mode: LQ_DT_* or 3 (raw int32).  Any M.  `ws` holds `splits` int32 planes (need not be zeroed).
+// `out`: one or several destinations (gather by stores); `sync`: optional cross-GPU flags.
 int run_tile_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, const void* bias,
-                  void* out, int out_mode, int M, int N, int K, int splits, void* ws, size_t ws_bytes,
-                  cudaStream_t st) {
+                  const OutSpec& out, const PeerSync* sync, int out_mode, int M, int N, int K, int splits, void* ws,
+                  size_t ws_bytes, cudaStream_t st) {
   using namespace tile;
   if (splits > 1 && (!ws || ws_bytes < tile_workspace_bytes(M, N, splits))) return LQ_ERR_WORKSPACE;
-  const int bn = splits > 1 ? tile_bn(M) : tile_bn_for(M, N);
+  const int bn = tile_bn(M);
   CUtensorMap tx;
   int rc = make_byte_matrix_map(&tx, x, M, K, bn, 128);
   if (rc) return rc;
+  const bool multi = out.n != 1 || out.ld != N || out.col0 != 0 || (sync && (sync->n_signal > 0 || sync->wait));
+  if (multi && out_mode == kOutI32) return LQ_ERR_BAD_ARG;
   GemmArgs a;
   a.blob = blob;
   a.ascale = splits > 1 ? nullptr : ascale;
   a.s1 = splits > 1 ? nullptr : s1;
   a.bias = splits > 1 ? nullptr : bias;
-  a.out = splits > 1 ? ws : out;
+  a.out = splits > 1 ? ws : out.ptr[0];
   a.status = status_word();
   a.out_mode = splits > 1 ? kOutI32 : out_mode;
   a.M = M;
   a.N = N;
   a.K = K;
   a.kt_total = K / 128;
+  bool vec = splits <= 1 && (out_mode == LQ_DT_BF16 || out_mode == LQ_DT_F16) && N % 8 == 0 && out.ld % 8 == 0 &&
+             out.col0 % 8 == 0;
+  for (int r = 0; r < out.n; ++r) vec = vec && (reinterpret_cast<uintptr_t>(out.ptr[r]) % 16 == 0);
+  a.vec_out = vec ? 1 : 0;
   if (!a.status) return LQ_ERR_CUDA;
+  MultiOut mo;
+  const MultiOut* mop = nullptr;
+  if (multi && splits <= 1) {
+    mo.out = out;
+    mo.sync = sync ? *sync : PeerSync{};
+    mop = &mo;
+  } else if (multi && sync && sync->wait) {
+    // the planes kernel only waits for the tokens; the finish pass writes and signals
+    mo.out = single_out(ws, N);
+    mo.sync = PeerSync{};
+    mo.sync.wait = sync->wait;
+    mo.sync.wait_value = sync->wait_value;
+    mop = &mo;
+  }
   switch (bn) {
-    case 16: rc = launch_cfg<16, 8, 4, true>(tx, a, splits, st); break;
-    case 32: rc = launch_cfg<32, 8, 4, true>(tx, a, splits, st); break;
-    case 64: rc = launch_cfg<64, 6, 4, true>(tx, a, splits, st); break;
-    case 192: rc = launch_cfg<192, 3, 2, true>(tx, a, splits, st); break;
-    default: rc = launch_cfg<128, 4, 4, true>(tx, a, splits, st); break;
+    case 16: rc = launch_cfg<16, 8, 4, true>(tx, a, mop, splits, st); break;
+    case 32: rc = launch_cfg<32, 8, 4, true>(tx, a, mop, splits, st); break;
+    case 64: rc = launch_cfg<64, 6, 4, true>(tx, a, mop, splits, st); break;
+    default: rc = launch_cfg<128, 4, 4, true>(tx, a, mop, splits, st); break;
   }
   if (rc || splits <= 1) return rc;
-  return launch_finish(static_cast<const int32_t*>(ws), ascale, s1, bias, out, out_mode, splits, M, N, st);
+  PeerSync fsync = {};
+  if (sync) {
+    fsync = *sync;
+    fsync.wait = nullptr;   // the planes kernel already waited
+  }
+  return launch_finish(static_cast<const int32_t*>(ws), ascale, s1, bias, out, sync ? &fsync : nullptr, out_mode, splits,
+                       M, N, st);
 }
 
 }  // namespace lq

@@ -267,13 +267,13 @@ gemv_mma_kernel(const int8_t* __restrict__ X, const uint8_t* __restrict__ Wp,
   }
 }
 
-// variant: 0 = pick by M, 1 = dp4a kernel, 2 = mma.sync kernel (M > 1 only)
+// dp4a kernel up to four tokens, warp-MMA kernel above (measured crossover on B200)
 template <bool PLAIN>
 static int launch_gemv(const int8_t* x, const uint8_t* wp, const uint8_t* s_u8, const uint8_t* off_a,
                        const float* ascale, const float* s1, void* y, int out_dtype, int M, int N,
-                       int K, int G, cudaStream_t st, int variant = 0) {
+                       int K, int G, cudaStream_t st) {
   const int warps_per_block = 8;
-  const bool use_mma = !PLAIN && (variant == 2 || (variant == 0 && M > 4));
+  const bool use_mma = !PLAIN && M > 4;
   if (use_mma) {
     const long warps = ((long)N + 15) / 16;
     const int blocks = (int)((warps + warps_per_block - 1) / warps_per_block);
@@ -319,16 +319,4 @@ extern "C" int lq_w4a8_gemv(const int8_t* x_i8, const uint8_t* gpack, const uint
   if (M == 0) return LQ_OK;
   return launch_gemv<false>(x_i8, gpack, s_u8, offset_a, ascale, s1, y, out_dtype, M, N, K, K / 64,
                             as_stream(stream));
-}
-
-// Tuning hook: same contract as lq_w4a8_gemv with the kernel chosen by the caller
-// (1 = dp4a, 2 = mma.sync).  Used by the benchmark sweeps that decide the dispatch table.
-extern "C" int lq_w4a8_gemv_variant(const int8_t* x_i8, const uint8_t* gpack, const uint8_t* s_u8,
-                                           const uint8_t* offset_a, const float* ascale, const float* s1,
-                                           void* y, int out_dtype, int M, int N, int K, int variant,
-                                           void* stream) {
-  if (!x_i8 || !gpack || !s_u8 || !offset_a || !ascale || !s1 || !y) return LQ_ERR_BAD_ARG;
-  if (M <= 0 || M > 16 || N <= 0 || K <= 0 || K % 128 || out_dtype < 0 || out_dtype > 2) return LQ_ERR_SHAPE;
-  return launch_gemv<false>(x_i8, gpack, s_u8, offset_a, ascale, s1, y, out_dtype, M, N, K, K / 64,
-                            as_stream(stream), variant);
 }

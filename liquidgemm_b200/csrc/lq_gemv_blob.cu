@@ -52,6 +52,7 @@ struct Args {
   int out_dtype;
   int M, N, K, fixed_split;
   const void* bias;      // [N] in the output dtype, or null
+  int prefetch;          // tiles per CTA requested into L2 ahead of the first ring
 };
 
 template <int MT, int NS>
@@ -141,9 +142,21 @@ gemv_blob_kernel(const Args args, const std::conditional_t<MULTI, MultiOut, NoMu
             ptx::bulk_load(xs + j * C::kXStage + m * 128, xsrc + (size_t)m * args.K, 128, bar_full + 8 * j);
         }
       };
+      // While this CTA waits for the previous kernel of the stream (whose slower CTAs are still running and
+      // leave HBM bandwidth unused), the tiles that follow the first ring are pulled into L2: kPrefetch
+      // tiles, requested one by one beside the ring's own copies.
+      TileCursor ahead(sa, blockIdx.x, gridDim.x);
+      for (int i = 0; i < NS && ahead.live; ++i) ahead.advance();
+      int prefetched = 0;
       while (ok && walk.next(sg)) {
         const uint8_t* src = args.blob + ((size_t)sg.tile * kt_total + sg.kb) * kTileBytes;
         for (int kt = sg.kb; kt < sg.ke; ++kt, src += kTileBytes) {
+          if (issued < NS) {
+            for (int j = 0; j < args.prefetch / NS + 1 && prefetched < args.prefetch && ahead.live; ++j, ++prefetched) {
+              ptx::bulk_prefetch_l2(args.blob + ((size_t)ahead.sg.tile * kt_total + ahead.kt) * kTileBytes, kTileBytes);
+              ahead.advance();
+            }
+          }
           if (issued == NS) meet_dependency();
           if (!ptx::mbar_wait_bounded(bar_empty + 8 * ring.s, ring.ph ^ 1u, kWaitLimitNs)) {
             atomicExch(args.status, 301);
@@ -390,6 +403,7 @@ int run_gemv_blob(const int8_t* x, const uint8_t* blob, const float* ascale, con
   a.K = K;
   a.fixed_split = plan_for(N, K).fixed_split;
   a.bias = bias;
+  a.prefetch = decode_prefetch_tiles();
   if (!a.status) return LQ_ERR_CUDA;
   const int grid = grid_for(N, K);
   if (!multi) {

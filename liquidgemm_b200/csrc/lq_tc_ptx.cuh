@@ -33,6 +33,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Non-blocking probe of the phase (try_wait may itself suspend the thread for an implementation-defined
+// time when the phase is still pending; test_wait never does).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 // try_wait that lets the hardware park the thread for up to `hint_ns` while the phase is pending (it
 // is resumed when the phase completes), instead of returning at once for the caller to spin.
 __device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
@@ -89,6 +104,10 @@ __device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, ui
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
                "l"(src), "r"(bytes), "r"(bar)
                : "memory");
+}
+// Asks the memory system to bring a contiguous range into L2 (no completion to wait for; 16-byte granules).
+__device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
 }
 // 2-D tiled load through a tensor map; x is the innermost (contiguous) coordinate in elements.
 __device__ __forceinline__ void tensor_load_2d(uint32_t dst_smem, const void* tmap, int x, int y, uint32_t bar) {

@@ -214,52 +214,11 @@ def _gemv2(x_i8, gpack, s_u8, off_a, ascale, s1, N, K, group_size, out_dtype):
     y = torch.empty((M, N), dtype=_OUT_DTYPES[int(out_dtype)], device=x_i8.device)
     if M == 0:
         return y
-    # Kernel choice by measurement on B200 (weights in the row-major pack):
-    #   M <= 2, or M <= 4 with short K : warp-per-row-pair dp4a kernel straight from global memory
-    #   M <= 4 with long K             : persistent TMA-ring dp4a kernel (stream-K)
-    #   larger M                       : dp4a runs out of issue slots; big matrices use the warp-MMA
-    #                                    kernel, the others the tensor-core kernel on the same pack
+    # One kernel family reads the row-major pack: dp4a up to four tokens, warp-level MMA above.  Layers
+    # prepared by this package hold the tile blob instead, which the faster kernels read.
     with _dev_ctx(x_i8):
-        if M <= 2 or (M <= 4 and K < 8192):
-            check(lib.lq_w4a8_gemv(_ptr(x_i8), _ptr(gpack), _ptr(s_u8), _ptr(off_a), _ptr(ascale), _ptr(s1), _ptr(y),
-                                   int(out_dtype), M, N, K, group_size, _stream()), "w4a8_gemv2")
-        elif M <= 4:
-            ws = _workspace(lib.lq_gemv_workspace_bytes(N, K), x_i8.device)
-            rc = lib.lq_w4a8_gemv_stream(_ptr(x_i8), _ptr(gpack), _ptr(s_u8), _ptr(off_a), _ptr(ascale), _ptr(s1),
-                                         _ptr(y), int(out_dtype), M, N, K, _ptr(ws), ws.numel(), _stream())
-            if rc != 0:
-                ws.zero_()
-            check(rc, "w4a8_gemv2")
-        elif N * K >= (1 << 26):
-            check(lib.lq_w4a8_gemv(_ptr(x_i8), _ptr(gpack), _ptr(s_u8), _ptr(off_a), _ptr(ascale), _ptr(s1), _ptr(y),
-                                   int(out_dtype), M, N, K, group_size, _stream()), "w4a8_gemv2")
-        else:
-            nbytes = lib.lq_gemm_workspace_bytes(M, N, K, -1)
-            ws = _workspace(nbytes, x_i8.device)
-            rc = lib.lq_w4a8_gemm_rowmajor(_ptr(x_i8), _ptr(gpack), _ptr(s_u8), _ptr(off_a), _ptr(ascale), _ptr(s1),
-                                           _ptr(y), int(out_dtype), M, N, K, 0, _ptr(ws), ws.numel(), _stream())
-            if rc != 0:
-                ws.zero_()
-            check(rc, "w4a8_gemv2")
-    return y
-
-
-def gemv_stream(x_i8, gpack, s_u8, off_a, ascale, s1, N, K, out_dtype):
-    """The persistent TMA-ring GEMV kernel for any M <= 16 (tuning / test entry point)."""
-    x_i8 = _i8(x_i8, "x_i8")
-    M = x_i8.shape[0]
-    _req(M <= 16 and K % 128 == 0, "M <= 16 and K % 128 == 0 required")
-    gpack, s_u8, off_a = _u8(gpack, "gpack"), _u8(s_u8, "s_u8"), _u8(off_a, "off_a")
-    ascale, s1 = _f32(ascale, "ascale"), _f32(s1, "s1")
-    y = torch.empty((M, N), dtype=_OUT_DTYPES[int(out_dtype)], device=x_i8.device)
-    if M:
-        with _dev_ctx(x_i8):
-            ws = _workspace(lib.lq_gemv_workspace_bytes(N, K), x_i8.device)
-            rc = lib.lq_w4a8_gemv_stream(_ptr(x_i8), _ptr(gpack), _ptr(s_u8), _ptr(off_a), _ptr(ascale), _ptr(s1),
-                                         _ptr(y), int(out_dtype), M, N, K, _ptr(ws), ws.numel(), _stream())
-            if rc != 0:
-                ws.zero_()
-            check(rc, "gemv_stream")
+        check(lib.lq_w4a8_gemv(_ptr(x_i8), _ptr(gpack), _ptr(s_u8), _ptr(off_a), _ptr(ascale), _ptr(s1), _ptr(y),
+                               int(out_dtype), M, N, K, group_size, _stream()), "w4a8_gemv2")
     return y
 
 
@@ -437,21 +396,22 @@ def gemv_blob(x_i8, blob, ascale, s1, N, K, out_dtype):
 
 def gemm_fused_scatter(x_i8, blob, ascale, s1, out_ptrs, ld_out, col0, N, K, out_dtype, flag_ptrs=None,
                        flag_index=0, wait_ptr=None, wait_value=0):
-    """Decode linear (M <= 16) whose [M, N] output block is stored at column ``col0`` of every matrix in
+    """Fused linear (any M) whose [M, N] output block is stored at column ``col0`` of every matrix in
     ``out_ptrs`` (device addresses of row-major [M, ld_out] buffers of the output dtype: this GPU's and
     its peers' full-width outputs).  The epilogue thereby does the all-gather of an N-sharded layer;
-    the caller orders the ranks afterwards (e.g. a symmetric-memory barrier on the same stream), or lets
-    the kernels do it: with ``flag_ptrs`` (one uint32 flag array per destination rank) every CTA adds 1 to
-    word ``flag_index`` of each array after its last store, and with ``wait_ptr`` the kernel waits for
-    ``*wait_ptr >= wait_value`` before it reads the tokens (``wait_value`` = ranks x decode_grid() of the
-    launch that produced them)."""
+    the caller orders the ranks afterwards (e.g. a symmetric-memory barrier on the same stream, once per
+    group of linears whose outputs are consumed together), or lets the kernels do it: with ``flag_ptrs``
+    (one uint32 flag array per destination rank) every CTA of the launch that writes the outputs adds 1
+    to word ``flag_index`` of each array after its last store, and with ``wait_ptr`` the kernel waits for
+    ``*wait_ptr >= wait_value`` before it reads the tokens (``wait_value`` = sum over the ranks of
+    decode_grid() of the launch that produced them)."""
     x_i8 = _i8(x_i8, "x_i8")
     _req(K % 128 == 0 and x_i8.shape[1] == K, "K%128==0 required and x_i8 must be [M,K]")
     _req(int(out_dtype) in _OUT_DTYPES, "out_dtype must be 0 (bf16), 1 (fp16) or 2 (fp32)")
     blob = _check_blob(blob, N, K)
     ascale, s1 = _f32(ascale, "ascale"), _f32(s1, "s1")
     M = x_i8.shape[0]
-    _req(1 <= M <= 16, "gemm_fused_scatter is a decode path (1 <= M <= 16)")
+    _req(M >= 1, "gemm_fused_scatter needs at least one token")
     _req(1 <= len(out_ptrs) <= 8 and ld_out >= N and 0 <= col0 <= ld_out - N, "bad destinations")
     arr = (ctypes.c_void_p * len(out_ptrs))(*[int(p) for p in out_ptrs])
     flags = None
@@ -459,39 +419,26 @@ def gemm_fused_scatter(x_i8, blob, ascale, s1, out_ptrs, ld_out, col0, N, K, out
         _req(len(flag_ptrs) == len(out_ptrs), "one flag array per destination")
         flags = (ctypes.c_void_p * len(flag_ptrs))(*[int(p) for p in flag_ptrs])
     with _dev_ctx(x_i8):
-        ws = _workspace(lib.lq_scatter_workspace_bytes(M, N, K), x_i8.device)
+        nbytes = lib.lq_scatter_workspace_bytes(M, N, K)
+        kind = lib.lq_gemm_workspace_kind(M, N, K, 0)
+        if kind == 1:
+            ws = torch.empty((nbytes,), dtype=torch.uint8, device=x_i8.device)   # split-K planes: plain scratch
+        else:
+            ws = _workspace(nbytes, x_i8.device)
         rc = lib.lq_w4a8_gemm_fused_scatter_sync(_ptr(x_i8), _ptr(blob), _ptr(ascale), _ptr(s1), arr, len(out_ptrs),
                                                  int(ld_out), int(col0), int(out_dtype), M, N, K, flags,
-                                                 int(flag_index), wait_ptr, int(wait_value), _ptr(ws), ws.numel(),
-                                                 _stream())
-        if rc != 0:
+                                                 int(flag_index), wait_ptr, int(wait_value),
+                                                 _ptr(ws) if ws is not None else None,
+                                                 ws.numel() if ws is not None else 0, _stream())
+        if rc != 0 and ws is not None and kind == 2:
             ws.zero_()
         check(rc, "gemm_fused_scatter")
 
 
 def decode_grid(M, N, K):
-    """CTAs a decode launch (M <= 16) of this shape uses on the current device."""
+    """CTAs of the launch that writes (and signals) the outputs of a fused linear of this shape on the current
+    device: what a consumer of the gather-by-stores epilogue has to see arrive from every rank."""
     return lib.lq_decode_grid(int(M), int(N), int(K))
-
-
-def gemm_rowmajor(x_i8, gpack, s_u8, off_a, ascale, s1, N, K, out_dtype, splitk=None):
-    """Fused W4A8 linear on tensor cores straight from the row-major GEMV pack (any M)."""
-    x_i8 = _i8(x_i8, "x_i8")
-    _req(K % 128 == 0 and x_i8.shape[1] == K, "K%128==0 required and x_i8 must be [M,K]")
-    _req(int(out_dtype) in _OUT_DTYPES, "out_dtype must be 0 (bf16), 1 (fp16) or 2 (fp32)")
-    gpack, s_u8, off_a = _u8(gpack, "gpack"), _u8(s_u8, "s_u8"), _u8(off_a, "off_a")
-    ascale, s1 = _f32(ascale, "ascale"), _f32(s1, "s1")
-    M = x_i8.shape[0]
-    _req(gpack.numel() == N * K // 2, "gpack must be [N,K/2]")
-    _req(s_u8.numel() == N * (K // 64) and off_a.numel() == N * (K // 64), "s_u8/off_a must be [N, K/64]")
-    _req(ascale.numel() == M and s1.numel() == N, "ascale must be [M] and s1 [N]")
-    y = torch.empty((M, N), dtype=_OUT_DTYPES[int(out_dtype)], device=x_i8.device)
-    if M:
-        _gemm_call("w4a8_gemm_rowmajor", x_i8, M, N, K, -1,
-                   lambda S, ws, nb, st: lib.lq_w4a8_gemm_rowmajor(_ptr(x_i8), _ptr(gpack), _ptr(s_u8), _ptr(off_a),
-                                                                   _ptr(ascale), _ptr(s1), _ptr(y), int(out_dtype),
-                                                                   M, N, K, S, ws, nb, st))
-    return y
 
 
 def _repack_device(src, layout, s_u8, off_a, N, K, group_size):
@@ -786,6 +733,53 @@ def w4a8_linear_host(x_host: torch.Tensor, qw_dev: dict, y_host: torch.Tensor = 
         if switch:
             torch.cuda.set_device(prev)
     return y_host
+
+
+class HostStepPlan:
+    """A fixed set of host-buffer linears (one decode step of a host-driven loop) recorded once and replayed
+    with a single call.
+
+    ``requests`` is a list of ``(x_host, layer, y_host)`` as for :func:`w4a8_linear_host`: pinned host
+    activations, a layer dict with the tile blob, a pinned host output.  Construction runs every request
+    once (which also sizes the per-stream scratch) and then records the same calls -- host-to-device copy,
+    token quantiser, linear, device-to-host copy, spread round-robin over ``n_streams`` streams so that the
+    copies of one request overlap the kernels of another -- into a CUDA graph.  :meth:`run` replays it: the
+    host pays for one launch instead of four to five driver calls per linear, which is what a step of 5-20 us
+    kernels is otherwise dominated by.  The buffers are read and written in place on every replay; call
+    :meth:`synchronize` before reading the outputs.  Plans built on the same ``stream`` replay in order.  (The reference drives every linear from Python, one
+    operator call at a time: liquidgemm/vllm_plugin.py:174-206.)"""
+
+    def __init__(self, requests, n_streams: int = 3, device=None, stream: "torch.cuda.Stream" = None):
+        if not requests:
+            raise RuntimeError("liquidgemm_b200: HostStepPlan needs at least one request")
+        self.requests = list(requests)
+        dev = torch.device(device) if device is not None else self.requests[0][1]["rs"].device
+        self.device = dev
+        with torch.cuda.device(dev):
+            # replays are ordered on `stream`: plans that share it run one after the other, like the steps
+            # of a decode loop
+            self.main = stream if stream is not None else torch.cuda.Stream()
+            self.side = [torch.cuda.Stream() for _ in range(max(1, int(n_streams)))]
+            # eager pass: allocates scratch and workspaces of every stream outside the capture
+            for i, (x, L, y) in enumerate(self.requests):
+                w4a8_linear_host(x, L, y, stream=self.side[i % len(self.side)])
+            torch.cuda.synchronize()
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph, stream=self.main):
+                for st in self.side:
+                    st.wait_stream(self.main)
+                for i, (x, L, y) in enumerate(self.requests):
+                    w4a8_linear_host(x, L, y, stream=self.side[i % len(self.side)])
+                for st in self.side:
+                    self.main.wait_stream(st)
+
+    def run(self) -> None:
+        """Enqueue the whole step (on the plan's own stream)."""
+        with torch.cuda.stream(self.main):
+            self.graph.replay()
+
+    def synchronize(self) -> None:
+        self.main.synchronize()
 
 
 def use_gemv(M: int, N: int, K: int, have_gp: bool, have_rs: bool) -> bool:

@@ -212,18 +212,6 @@ def test_device_status_word_is_clean(ops):
     assert lib.lq_poll_status(torch.cuda.current_stream().cuda_stream) == 0
 
 
-@pytest.mark.parametrize("M", [1, 4, 8, 16, 40, 128, 200])
-@pytest.mark.parametrize("N,K", [(512, 4096), (320, 1152), (4096, 14336)])
-def test_rowmajor_tensor_core_path(ops, M, N, K):
-    """The tensor-core GEMM reading the row-major GEMV pack and the plain [N, K/64] step/offset arrays."""
-    qw = random_lqq(N, K, 64, seed=N + M)
-    tq = to_torch_qw(qw)
-    x, ascale = random_tokens(M, K, seed=M)
-    y = ops.gemm_rowmajor(torch.from_numpy(x).cuda(), ops.pack_gemv_interleaved(tq), tq.s_u8, tq.offset_a,
-                          torch.from_numpy(ascale).cuda(), tq.s1, N, K, 0)
-    assert_bits_equal(y, O.w4a8_matmul(x, ascale, qw), 0, f"rowmajor {M}x{N}x{K}")
-
-
 def test_workspace_is_left_clean(ops):
     """Stream-K leaves its reduction workspace all-zero, so back-to-back calls stay exact."""
     N, K, M = 384, 14336, 24

@@ -88,15 +88,3 @@ def test_v1_gemm_small_m_plain_nibbles(ops, M):
     x, ascale = random_tokens(M, 4096, seed=M)
     got = ops.w4a8_gemm(torch.from_numpy(x), torch.from_numpy(ascale), to_torch_qw(qw), out_dtype=torch.float32)
     assert_bits_equal(got, O.w4a8_matmul(x, ascale, qw), 2, f"v1 M={M}")
-
-
-@pytest.mark.parametrize("M", [1, 2, 4, 7, 8, 16])
-@pytest.mark.parametrize("N,K", [(512, 4096), (200, 1152), (4096, 14336)])
-def test_stream_gemv_kernel(ops, M, N, K):
-    """The persistent TMA-ring dp4a kernel on its own, every token bucket, ragged N and K % 256 != 0."""
-    qw = random_lqq(N, K, 64, seed=N + M)
-    tq = to_torch_qw(qw)
-    x, ascale = random_tokens(M, K, seed=M)
-    y = ops.gemv_stream(torch.from_numpy(x).cuda(), ops.pack_gemv_interleaved(tq), tq.s_u8, tq.offset_a,
-                        torch.from_numpy(ascale).cuda(), tq.s1, N, K, 0)
-    assert_bits_equal(y, O.w4a8_matmul(x, ascale, qw), 0, f"stream gemv {M}x{N}x{K}")
