@@ -58,17 +58,6 @@ bool pdl_enabled() {
   return on;
 }
 
-// Tiles per CTA that the streaming decode kernels ask into L2 beyond their first ring of copies
-// (LQ_L2_PREFETCH_TILES overrides it for measurements; 0 switches the prefetch off).
-int decode_prefetch_tiles() {
-  static const int v = []() {
-    const char* e = getenv("LQ_L2_PREFETCH_TILES");
-    const int n = e ? atoi(e) : 12;
-    return n < 0 ? 0 : n > 64 ? 64 : n;
-  }();
-  return v;
-}
-
 int* status_word() {
   int dev = current_device();
   return dev < 0 ? nullptr : g_status_ptr[dev];

@@ -16,7 +16,6 @@ namespace lq {
 void record_cuda_error(cudaError_t e, const char* where);   // lq_api.cu
 int check_launch(const char* where);                        // lq_api.cu: cudaGetLastError -> code
 int sm_count();                                             // lq_api.cu: cached per device
-int decode_prefetch_tiles();                                // lq_api.cu: L2 prefetch depth of the decode kernels
 int* status_word();                                         // lq_api.cu: device address of the status word
 
 inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }

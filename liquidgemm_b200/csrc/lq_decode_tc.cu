@@ -89,7 +89,6 @@ struct Args {
   int* status;
   int out_mode;          // LQ_DT_* or kOutI32
   int M, N, K, fixed_split;
-  int prefetch;          // tiles per CTA requested into L2 ahead of the first ring
 };
 
 template <int BN, int NW, int NT>
@@ -170,20 +169,9 @@ w4a8_decode_tc_kernel(const Args args, const std::conditional_t<MULTI, MultiOut,
       TR_VAR(tr_idle);
       const long long tr_p0 = TR_NOW();
       // Weight tiles do not depend on the previous kernel of the stream, so they are requested at once.
-      // While the CTA then waits for that kernel (whose slower CTAs still run and leave HBM bandwidth
-      // unused), the tiles that follow the first ring are pulled into L2.
-      TileCursor ahead(sched, blockIdx.x, gridDim.x);
-      for (int i = 0; i < NW && ahead.live; ++i) ahead.advance();
-      int prefetched = 0;
       while (ok && walk.next(sg)) {
         const uint8_t* src = args.blob + ((size_t)sg.tile * kt_total + sg.kb) * kTileBytes;
         for (int kt = sg.kb; kt < sg.ke; ++kt, src += kTileBytes) {
-          if (issued < NW) {
-            for (int j = 0; j < args.prefetch / NW + 1 && prefetched < args.prefetch && ahead.live; ++j, ++prefetched) {
-              ptx::bulk_prefetch_l2(args.blob + ((size_t)ahead.sg.tile * kt_total + ahead.kt) * kTileBytes, kTileBytes);
-              ahead.advance();
-            }
-          }
           const long long tr_i0 = TR_NOW();
           if (!ptx::mbar_wait_bounded(bar_wfree + 8 * ring.s, ring.ph ^ 1u, kWaitLimitNs)) {
             atomicExch(args.status, 401);
@@ -382,27 +370,8 @@ w4a8_decode_tc_kernel(const Args args, const std::conditional_t<MULTI, MultiOut,
       }
     };
 
-    // The operand stores of a k-tile are left in flight while the thread unpacks its next k-tile; the
-    // wait for them and the "operand ready" arrival come after that arithmetic (measured: four tcgen05.st
-    // plus their wait cost a thread about 300 cycles when it waits at once).
-    uint32_t pending_ready = 0;   // barrier to arrive on once the stores in flight have landed, or 0
-    auto flush_stores = [&]() {
-      if (pending_ready) {
-        const long long tr_s1 = TR_NOW();
-        ptx::tc_wait_st();
-        TR_ADD(tr_st, tr_s1);
-        const long long tr_s2 = TR_NOW();
-        // the token slice was written with ordinary stores: make it visible to the tensor core's reads
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        ptx::tc_fence_before();
-        ptx::mbar_arrive(pending_ready);
-        TR_ADD(tr_flush, tr_s2);
-        pending_ready = 0;
-      }
-    };
     for (;;) {
       const bool more = walk.next(sg);
-      flush_stores();   // uniform over the warp: every lane of a set takes the same k-tiles
       // One place decides which finished segment this set reads out now.  While the stream runs: the
       // segment two back, just before its accumulator (this set's) takes a new one.  After the last
       // segment: whichever of the last two segments sits in this set's accumulator -- the two sets
@@ -484,8 +453,6 @@ w4a8_decode_tc_kernel(const Args args, const std::conditional_t<MULTI, MultiOut,
         if (v[0] == 0x12345678u && v[31] == 0x9abcdef0u) TR_SET(8, 1);   // pins the arithmetic before the timer
 #endif
         TR_ADD(tr_unpack, tr_u0);
-        __syncwarp();   // lanes leave the poll loops one by one; tcgen05.st / wait::st need the warp converged
-        flush_stores();   // the previous k-tile of this set: its stores had the whole unpack to land
         const long long tr_f0 = TR_NOW();
         if (ok && !ptx::mbar_wait_bounded(bar_afree + 8 * rt.s, rt.ph ^ 1u, kWaitLimitNs)) {
           atomicExch(args.status, 406);
@@ -499,8 +466,17 @@ w4a8_decode_tc_kernel(const Args args, const std::conditional_t<MULTI, MultiOut,
 #pragma unroll
         for (int q = 0; q < BN / 16; ++q)
           *reinterpret_cast<uint4*>(smem + rt.s * C::kXStage + x_off + q * 2048) = xv[q];
+        // Wait for the operand store at once.  (Leaving it in flight during the next unpack and arriving
+        // afterwards was measured: 1-3 % slower here, 10-30 % slower in the prefill kernel -- "operand ready"
+        // one unpack later starves the MMAs more than the store's latency costs the thread.)
+        ptx::tc_wait_st();
         TR_ADD(tr_st, tr_s0);
-        pending_ready = bar_aready + 8 * rt.s;
+        const long long tr_s2 = TR_NOW();
+        // the token slice was written with ordinary stores: make it visible to the tensor core's reads
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(bar_aready + 8 * rt.s);
+        TR_ADD(tr_flush, tr_s2);
       }
       ++seg;
     }
@@ -594,7 +570,6 @@ int run_decode_tc(const int8_t* x, const uint8_t* blob, const float* ascale, con
   a.N = N;
   a.K = K;
   a.fixed_split = plan.fixed_split;
-  a.prefetch = decode_prefetch_tiles();
   if (!a.status) return LQ_ERR_CUDA;
   if (!multi) {
     if (bn == 16) return launch<16, 8, 7, false>(a, nullptr, grid, st);

@@ -243,7 +243,9 @@ w4a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs args
         ptx::mbar_arrive(bar_empty + 8 * s);
 
         // Unpack into registers first, wait for the operand stage afterwards: the arithmetic of this k-step
-        // overlaps the MMAs that still read the stage.
+        // overlaps the MMAs that still read the stage.  (Leaving the operand store in flight during the NEXT
+        // unpack, as the decode kernel does, was measured here and lost 10-30 % at prefill sizes: the MMAs of
+        // a 128-token tile are long enough to starve when "operand ready" comes one unpack later.)
         const uint32_t step0 = meta & 0xffu, a0 = ((meta >> 8) & 0xffu) * 0x01010101u;
         const uint32_t step1 = (meta >> 16) & 0xffu, a1 = (meta >> 24) * 0x01010101u;
         uint32_t v[4][8];
@@ -398,7 +400,14 @@ static int launch_cfg(const CUtensorMap& tx, const GemmArgs& a, const MultiOut* 
 // raised an unspecified launch failure on a fourth (28672 x 4096, 8192 tokens) and in back-to-back graph
 // replays.  Reading the index arithmetic, the barrier counts and the tensor-memory budget (192 + 2 x 32 =
 // 256 columns, two CTAs per SM) did not show the cause, so the configuration is not built.
-static int tile_bn(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128; }
+static int tile_bn(int M) {
+  static const int narrow = []() {
+    const char* e = getenv("LQ_TILE_NARROW");   // measurement switch: 64-token tiles for 65..128 tokens
+    return e ? atoi(e) : 0;
+  }();
+  if (narrow && M > 64 && M <= 128) return 64;
+  return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
+}
 
 }  // namespace tile
 

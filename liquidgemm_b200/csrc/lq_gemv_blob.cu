@@ -52,7 +52,6 @@ struct Args {
   int out_dtype;
   int M, N, K, fixed_split;
   const void* bias;      // [N] in the output dtype, or null
-  int prefetch;          // tiles per CTA requested into L2 ahead of the first ring
 };
 
 template <int MT, int NS>
@@ -120,6 +119,8 @@ gemv_blob_kernel(const Args args, const std::conditional_t<MULTI, MultiOut, NoMu
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
     if (lane == 0) {
+      // One plain 128-byte copy per token and k-tile.  (A single tensor-map box of MT rows x 128 bytes per
+      // k-tile instead was measured: equal at two tokens, 10-15 % slower at four.)
       const uint32_t tx = (uint32_t)(kTileBytes + M * 128);
       Ring<NS> ring;
       int issued = 0;
@@ -142,21 +143,12 @@ gemv_blob_kernel(const Args args, const std::conditional_t<MULTI, MultiOut, NoMu
             ptx::bulk_load(xs + j * C::kXStage + m * 128, xsrc + (size_t)m * args.K, 128, bar_full + 8 * j);
         }
       };
-      // While this CTA waits for the previous kernel of the stream (whose slower CTAs are still running and
-      // leave HBM bandwidth unused), the tiles that follow the first ring are pulled into L2: kPrefetch
-      // tiles, requested one by one beside the ring's own copies.
-      TileCursor ahead(sa, blockIdx.x, gridDim.x);
-      for (int i = 0; i < NS && ahead.live; ++i) ahead.advance();
-      int prefetched = 0;
+      // (Asking the tiles behind the first ring into L2 with cp.async.bulk.prefetch while the CTA waits for
+      // the previous kernel was measured and lost 5-25 %: the requests compete with the demand copies of
+      // this ring and of the previous kernel's last CTAs, which are the critical path.)
       while (ok && walk.next(sg)) {
         const uint8_t* src = args.blob + ((size_t)sg.tile * kt_total + sg.kb) * kTileBytes;
         for (int kt = sg.kb; kt < sg.ke; ++kt, src += kTileBytes) {
-          if (issued < NS) {
-            for (int j = 0; j < args.prefetch / NS + 1 && prefetched < args.prefetch && ahead.live; ++j, ++prefetched) {
-              ptx::bulk_prefetch_l2(args.blob + ((size_t)ahead.sg.tile * kt_total + ahead.kt) * kTileBytes, kTileBytes);
-              ahead.advance();
-            }
-          }
           if (issued == NS) meet_dependency();
           if (!ptx::mbar_wait_bounded(bar_empty + 8 * ring.s, ring.ph ^ 1u, kWaitLimitNs)) {
             atomicExch(args.status, 301);
@@ -403,7 +395,6 @@ int run_gemv_blob(const int8_t* x, const uint8_t* blob, const float* ascale, con
   a.K = K;
   a.fixed_split = plan_for(N, K).fixed_split;
   a.bias = bias;
-  a.prefetch = decode_prefetch_tiles();
   if (!a.status) return LQ_ERR_CUDA;
   const int grid = grid_for(N, K);
   if (!multi) {

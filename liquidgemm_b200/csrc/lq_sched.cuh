@@ -71,24 +71,6 @@ struct SegmentWalk {
   }
 };
 
-// Position in a CTA's stream of k-tiles: walks the segments and the k-tiles inside them.
-struct TileCursor {
-  SegmentWalk walk;
-  Segment sg;
-  int kt;
-  bool live;
-  __device__ TileCursor(const SchedArgs& a, unsigned cta, unsigned grid) : walk(a, cta, grid) {
-    live = walk.next(sg);
-    kt = live ? sg.kb : 0;
-  }
-  __device__ void advance() {
-    if (++kt >= sg.ke) {
-      live = walk.next(sg);
-      kt = live ? sg.kb : 0;
-    }
-  }
-};
-
 // Work split of the streaming decode kernels over `slots` resident CTAs.  With few output tiles every
 // tile is cut into S equal k-ranges, one CTA each: a CTA then has exactly one segment, so no CTA pays
 // the segment epilogue twice.  With many tiles the k-tiles of all tiles are laid end to end and cut

@@ -105,10 +105,6 @@ __device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, ui
                "l"(src), "r"(bytes), "r"(bar)
                : "memory");
 }
-// Asks the memory system to bring a contiguous range into L2 (no completion to wait for; 16-byte granules).
-__device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
-}
 // 2-D tiled load through a tensor map; x is the innermost (contiguous) coordinate in elements.
 __device__ __forceinline__ void tensor_load_2d(uint32_t dst_smem, const void* tmap, int x, int y, uint32_t bar) {
   asm volatile(

@@ -1,23 +1,46 @@
 """Pipeline microbenchmarks for the sm_100a building blocks of the W4A8 kernels.
 
+    python -m liquidgemm_b200.build --debug           # once: the measurement kernels, a library of their own
     python -m liquidgemm_b200.microbench mma_rate     # tcgen05.mma kind::i8 issue-to-issue cost
     python -m liquidgemm_b200.microbench sync_cost    # mbarrier / commit / bulk-copy instruction costs
     python -m liquidgemm_b200.microbench tma_stream   # HBM streaming rate of ring-buffered bulk copies
     python -m liquidgemm_b200.microbench tma_rows     # the same with one bulk copy per weight row
 
-Each one launches a measurement-only kernel exported by the native library (``lq_debug_*``); none of
-them is on a product path.  They need a B200; every device-side wait in them is bounded.
+    python -m liquidgemm_b200.build --trace           # once: the product sources with -DLQ_PIPELINE_TRACE
+    python -m liquidgemm_b200.microbench decode_trace gate_up 8   # per-CTA cycle counters of the decode kernel
+
+The first four launch measurement-only kernels (``lq_debug_*`` in ``csrc/dbg/lq_debug.cu``); none of them is
+in the product library.  ``decode_trace`` runs the real decode tensor-core kernel from the trace build and
+prints where each role's cycles go.  They need a B200; every device-side wait in them is bounded.
 """
 
 from __future__ import annotations
 
 import ctypes
+import os
 import sys
 
 import numpy as np
 import torch
 
-from ._lib import lib
+_HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+class _Lazy:
+    """The debug library, loaded on first use (it is not built by default)."""
+
+    _lib = None
+
+    def __getattr__(self, name):
+        if _Lazy._lib is None:
+            path = os.path.join(_HERE, "_lq_b200_dbg.so")
+            if not os.path.exists(path):
+                raise ImportError(f"{path} is missing: build it with `python -m liquidgemm_b200.build --debug`")
+            _Lazy._lib = ctypes.CDLL(path)
+        return getattr(_Lazy._lib, name)
+
+
+lib = _Lazy()
 
 _I, _P, _L = ctypes.c_int, ctypes.c_void_p, ctypes.c_long
 
@@ -119,9 +142,51 @@ def tma_rows(total_bytes: int = 400_000_000) -> None:
               f"cycles/stage {float(np.median(cyc.cpu().numpy())) / steps:7.1f}", flush=True)
 
 
+def decode_trace(shape: str = "gate_up", M: int = 8) -> None:
+    """Per-CTA cycle counters of ``w4a8_decode_tc_kernel`` on one Llama-3.1-8B shape (trace build of the
+    library): median / 10th / 90th percentile over the CTAs of the last launch of a graph of back-to-back
+    launches over rotating weight copies.  Counters are sums over the k-tiles a role handled."""
+    if os.environ.get("LIQUIDGEMM_B200_TRACE") != "1":
+        import subprocess
+        env = dict(os.environ, LIQUIDGEMM_B200_TRACE="1")
+        sys.exit(subprocess.call([sys.executable, "-m", "liquidgemm_b200.microbench", "decode_trace", shape, str(M)],
+                                 env=env))
+    from . import benchlib as B
+    from ._lib import lib as plib
+    N, K = B.SHAPES[shape]
+    C = 6
+    layers = [B.device_lqq(N, K, seed=31 * c + 1, want_gp=False) for c in range(C)]
+    x, sc = B.device_tokens(M, K, seed=M)
+    t = B.graph_time_us(lambda i: B.linear_call(layers[i % C], x, sc, M), C, 3)
+    buf = (ctypes.c_longlong * (1024 * 16))()
+    plib.lq_debug_read_decode_trace.argtypes = [ctypes.c_void_p]
+    assert plib.lq_debug_read_decode_trace(buf) == 0
+    a = np.frombuffer(buf, dtype=np.int64).reshape(1024, 16)[:plib.lq_decode_grid(M, N, K)]
+    names = {0: "producer: waiting for a free weight stage", 1: "producer: whole loop",
+             3: "MMA thread: waiting for operands", 4: "MMA thread: whole loop", 10: "MMA thread: issuing 4 MMAs",
+             11: "MMA thread: commit", 5: "dequant thread: waiting for the weight tile",
+             12: "dequant thread: shared loads + unpack", 7: "dequant thread: tcgen05.st + token store + wait::st",
+             2: "dequant thread: proxy fence + arrive", 6: "dequant thread: waiting for the operand stage",
+             9: "dequant thread: epilogues", 8: "dequant thread: whole role (incl. wait for the previous kernel)"}
+    print(f"{shape} {N}x{K}, M = {M}: {t:.2f} us per launch (trace build), {len(a)} CTAs; cycles per CTA")
+    for slot, label in names.items():
+        col = a[:, slot]
+        print(f"  {label:62s} median {int(np.median(col)):7d}   p10 {int(np.percentile(col, 10)):7d}   "
+              f"p90 {int(np.percentile(col, 90)):7d}")
+    t0 = a[:, 13].min()
+    for label, col in (("CTA start", a[:, 13]), ("CTA end", a[:, 14])):
+        c = col - t0
+        print(f"  {label:10s} ns after the first CTA's start: min {int(c.min())}  median {int(np.median(c))}  "
+              f"max {int(c.max())}")
+
+
 _CASES = {"mma_rate": mma_rate, "sync_cost": sync_cost, "tma_stream": tma_stream, "tma_rows": tma_rows}
 
 if __name__ == "__main__":
+    torch.cuda.set_device(0)
+    if len(sys.argv) > 1 and sys.argv[1] == "decode_trace":
+        decode_trace(*(sys.argv[2:3] or ["gate_up"]), *(int(v) for v in sys.argv[3:4]))
+        sys.exit(0)
     which = sys.argv[1:] or list(_CASES)
     for name in which:
         print(f"== {name}", flush=True)

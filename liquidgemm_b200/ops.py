@@ -760,16 +760,25 @@ class HostStepPlan:
             # of a decode loop
             self.main = stream if stream is not None else torch.cuda.Stream()
             self.side = [torch.cuda.Stream() for _ in range(max(1, int(n_streams)))]
+            # Requests go to the stream with the least work so far, largest first (bytes streamed and copied
+            # stand in for time): the chains of copy -> quantise -> linear -> copy then end together.
+            cost = [L["N"] * L["K"] // 2 + 3 * x.numel() + 2 * y.numel() * y.element_size() for x, L, y in self.requests]
+            load = [0] * len(self.side)
+            self.assignment = [0] * len(self.requests)
+            for i in sorted(range(len(self.requests)), key=lambda j: -cost[j]):
+                k = min(range(len(self.side)), key=lambda q: load[q])
+                self.assignment[i] = k
+                load[k] += cost[i]
             # eager pass: allocates scratch and workspaces of every stream outside the capture
             for i, (x, L, y) in enumerate(self.requests):
-                w4a8_linear_host(x, L, y, stream=self.side[i % len(self.side)])
+                w4a8_linear_host(x, L, y, stream=self.side[self.assignment[i]])
             torch.cuda.synchronize()
             self.graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(self.graph, stream=self.main):
                 for st in self.side:
                     st.wait_stream(self.main)
                 for i, (x, L, y) in enumerate(self.requests):
-                    w4a8_linear_host(x, L, y, stream=self.side[i % len(self.side)])
+                    w4a8_linear_host(x, L, y, stream=self.side[self.assignment[i]])
                 for st in self.side:
                     self.main.wait_stream(st)
 
