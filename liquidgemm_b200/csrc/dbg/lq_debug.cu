@@ -10,6 +10,14 @@ __device__ __forceinline__ bool dbg_test_wait(uint32_t bar, uint32_t parity) {
                : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
+// One lane of the (converged) warp, the same one every time.
+__device__ __forceinline__ bool dbg_elect_one() {
+  uint32_t pred = 0;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
 // Bounded: gives up after ~2^22 polls so that a wrong experiment ends instead of hanging.
 __device__ __forceinline__ void dbg_wait(uint32_t bar, uint32_t parity, int mode) {
   for (int i = 0; i < (1 << 22); ++i) {
@@ -37,7 +45,7 @@ mma_rate_kernel(int n, int iters, int a_in_tmem, long long* out) {
   }
   // operands: B tile (256 rows x 128 B) at base, A tile (128 x 128 B) behind it; contents are
   // whatever the memory holds after this fill (values do not change the timing)
-  for (int i = threadIdx.x; i < (32768 + 16384) / 4; i += blockDim.x)
+  for (int i = threadIdx.x; i < (1024 + 32768 + 16384) / 4; i += blockDim.x)
     reinterpret_cast<uint32_t*>(smem_raw + (base - raw_addr))[i] = 0x01020304u * (i + 1);
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   // a_in_tmem bit 1: allocate 256 columns (accumulator <= 128 wide) so two CTAs share an SM
@@ -46,6 +54,8 @@ mma_rate_kernel(int n, int iters, int a_in_tmem, long long* out) {
   // bit 2: alternate between two accumulators (columns [0, n) and [n, 2n)) from one MMA to the next, to tell a
   // dependent-accumulate latency from an issue limit
   const uint32_t alt = (a_in_tmem & 4) ? (uint32_t)n : 0u;
+  // bit 3: the whole warp walks the issue loop and one elected lane issues (instead of `if (thread 0) loop`)
+  const bool uniform_issue = (a_in_tmem & 8) != 0;
   a_in_tmem &= 1;
   if (threadIdx.x < 32) {
     ptx::tmem_alloc(smem_u32(&tmem_slot), cols);
@@ -55,16 +65,47 @@ mma_rate_kernel(int n, int iters, int a_in_tmem, long long* out) {
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
-  if (threadIdx.x == 0) {
+  if (uniform_issue) {
+    // The whole warp walks the loop (operands stay warp-uniform values); one elected lane issues.
+    if (threadIdx.x < 32) {
+      const uint32_t idesc = ptx::idesc_i8(n);
+      const bool leader = dbg_elect_one();
+      const long long t0 = clock64();
+      for (int i = 0; i < iters; ++i) {
+        // a stage-dependent operand address, as in a real main loop
+        const uint32_t sbase = base + (uint32_t)(i & 1) * 1024u;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint64_t bdesc = ptx::smem_desc_sw128(sbase + j * 32);
+          const uint32_t acc = tmem_base + ((j & 1) ? alt : 0u);
+          if (leader) {
+            if (a_in_tmem) ptx::mma_i8_ts(acc, tmem_base + a_col + j * 8, bdesc, idesc, 1u);
+            else ptx::mma_i8_ss(acc, ptx::smem_desc_sw128(sbase + 32768 + j * 32), bdesc, idesc, 1u);
+          }
+        }
+        __syncwarp();
+      }
+      if (leader) {
+        const long long t_issue = clock64();
+        ptx::tc_commit(bar_addr);
+        ptx::mbar_wait_bounded(bar_addr, 0u, 2000000000ull);
+        const long long t1 = clock64();
+        out[blockIdx.x * 2] = t1 - t0;
+        out[blockIdx.x * 2 + 1] = t_issue - t0;
+      }
+      __syncwarp();
+    }
+  } else if (threadIdx.x == 0) {
     const uint32_t idesc = ptx::idesc_i8(n);
     const long long t0 = clock64();
     for (int i = 0; i < iters; ++i) {
+      const uint32_t sbase = base + (uint32_t)(i & 1) * 1024u;   // a stage-dependent operand address
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const uint64_t bdesc = ptx::smem_desc_sw128(base + j * 32);
+        const uint64_t bdesc = ptx::smem_desc_sw128(sbase + j * 32);
         const uint32_t acc = tmem_base + ((j & 1) ? alt : 0u);
         if (a_in_tmem) ptx::mma_i8_ts(acc, tmem_base + a_col + j * 8, bdesc, idesc, 1u);
-        else ptx::mma_i8_ss(acc, ptx::smem_desc_sw128(base + 32768 + j * 32), bdesc, idesc, 1u);
+        else ptx::mma_i8_ss(acc, ptx::smem_desc_sw128(sbase + 32768 + j * 32), bdesc, idesc, 1u);
       }
     }
     const long long t_issue = clock64();
@@ -89,7 +130,7 @@ extern "C" LQ_API int lq_debug_mma_rate(int n, int iters, int a_in_tmem, int cta
   if (n < 16 || n > 256 || n % 16 || iters <= 0 || ctas <= 0 || !out) return LQ_ERR_BAD_ARG;
   if ((a_in_tmem & 2) && n > 128) return LQ_ERR_BAD_ARG;
   if ((a_in_tmem & 4) && n > ((a_in_tmem & 2) ? 64 : 128)) return LQ_ERR_BAD_ARG;
-  const int smem = 1024 + 32768 + 16384;
+  const int smem = 2048 + 32768 + 16384;
   static bool attr_done = false;
   if (!attr_done) {
     cudaFuncSetAttribute(lq::mma_rate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -177,7 +218,7 @@ namespace lq {
 // region of `src`) through a ring of `ns` shared-memory stages with bulk copies; one thread
 // produces, one thread consumes (wait full -> arrive empty).  Upper bound for any TMA-fed kernel.
 __global__ void __launch_bounds__(64, 1)
-tma_stream_kernel(const uint8_t* src, int stage_bytes, int ns, int steps, long long* cycles) {
+tma_stream_kernel(const uint8_t* src, int stage_bytes, int ns, int steps, int wrap, int share, long long* cycles) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 127u) & ~127u;
@@ -191,14 +232,18 @@ tma_stream_kernel(const uint8_t* src, int stage_bytes, int ns, int steps, long l
   }
   __syncthreads();
   const long long t0 = clock64();
-  const uint8_t* my = src + (size_t)blockIdx.x * steps * stage_bytes;
+  // wrap > 0: the CTA re-reads a region of `wrap` stages (an L2-resident stream when the regions of all CTAs
+  // fit there); share > 1: that many consecutive CTAs read the same region (tiles shared between CTAs).
+  const int span = wrap > 0 ? wrap : steps;
+  const uint8_t* my = src + (size_t)(blockIdx.x / share) * span * stage_bytes;
   if (threadIdx.x == 0) {
-    int s = 0;
+    int s = 0, w = 0;
     uint32_t ph = 0;
     for (int i = 0; i < steps; ++i) {
       dbg_wait(smem_u32(&bars[32 + s]), ph ^ 1u, 0);
       ptx::mbar_expect_tx(smem_u32(&bars[s]), stage_bytes);
-      ptx::bulk_load(base + s * stage_bytes, my + (size_t)i * stage_bytes, stage_bytes, smem_u32(&bars[s]));
+      ptx::bulk_load(base + s * stage_bytes, my + (size_t)w * stage_bytes, stage_bytes, smem_u32(&bars[s]));
+      if (++w == span) w = 0;
       if (++s == ns) { s = 0; ph ^= 1u; }
     }
   } else if (threadIdx.x == 32) {
@@ -215,14 +260,25 @@ tma_stream_kernel(const uint8_t* src, int stage_bytes, int ns, int steps, long l
 }
 }  // namespace lq
 
-extern "C" LQ_API int lq_debug_tma_stream(const void* src, int stage_bytes, int ns, int steps, int ctas,
-                                          long long* cycles, void* stream) {
-  if (ns < 1 || ns > 32 || stage_bytes % 16 || stage_bytes * ns > 200 * 1024) return LQ_ERR_BAD_ARG;
+static int launch_tma_stream(const void* src, int stage_bytes, int ns, int steps, int wrap, int share, int ctas,
+                             long long* cycles, void* stream) {
+  if (ns < 1 || ns > 32 || stage_bytes % 16 || stage_bytes * ns > 200 * 1024 || share < 1 || wrap < 0) return LQ_ERR_BAD_ARG;
   const int smem = stage_bytes * ns + 256;
   cudaFuncSetAttribute(lq::tma_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 201 * 1024);
   lq::tma_stream_kernel<<<ctas, 64, smem, lq::as_stream(stream)>>>(static_cast<const uint8_t*>(src), stage_bytes, ns,
-                                                                   steps, cycles);
+                                                                   steps, wrap, share, cycles);
   return lq::check_launch("tma_stream_kernel");
+}
+
+extern "C" LQ_API int lq_debug_tma_stream(const void* src, int stage_bytes, int ns, int steps, int ctas,
+                                          long long* cycles, void* stream) {
+  return launch_tma_stream(src, stage_bytes, ns, steps, 0, 1, ctas, cycles, stream);
+}
+
+// The same stream out of L2: every group of `share` CTAs re-reads its own region of `wrap` stages.
+extern "C" LQ_API int lq_debug_tma_stream_l2(const void* src, int stage_bytes, int ns, int steps, int wrap, int share,
+                                             int ctas, long long* cycles, void* stream) {
+  return launch_tma_stream(src, stage_bytes, ns, steps, wrap, share, ctas, cycles, stream);
 }
 
 namespace lq {
@@ -386,4 +442,154 @@ extern "C" LQ_API int lq_debug_tma_rows(const void* src, int rows, int row_bytes
   lq::tma_rows_kernel<<<ctas, 64, smem, lq::as_stream(stream)>>>(static_cast<const uint8_t*>(src), rows, row_bytes,
                                                                  row_stride, ns, steps, pieces_per_row, cycles);
   return lq::check_launch("tma_rows_kernel");
+}
+
+namespace lq {
+// Two independent bulk-copy rings inside one CTA (producers: threads 0 and 64, consumers: threads 32 and 96):
+// whether the fixed cost of a bulk copy is paid per issuing thread or per CTA.
+__global__ void __launch_bounds__(128, 1)
+tma_stream2_kernel(const uint8_t* src, int stage_bytes, int ns, int steps, int wrap, long long* cycles) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 127u) & ~127u;
+  __shared__ uint64_t bars[128];
+  const int ring = threadIdx.x >> 6;            // 0 or 1
+  const int role = (threadIdx.x >> 5) & 1;      // 0 producer warp, 1 consumer warp
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 2 * ns; ++i) {
+      ptx::mbar_init(smem_u32(&bars[i]), 1);
+      ptx::mbar_init(smem_u32(&bars[64 + i]), 1);
+    }
+    ptx::fence_mbar_init();
+  }
+  __syncthreads();
+  const long long t0 = clock64();
+  const int span = wrap > 0 ? wrap : steps;
+  const uint8_t* my = src + (size_t)(blockIdx.x * 2 + ring) * span * stage_bytes;
+  const uint32_t ring_smem = base + ring * ns * stage_bytes;
+  uint64_t* full = &bars[ring * ns];
+  uint64_t* empty = &bars[64 + ring * ns];
+  if ((threadIdx.x & 31) == 0) {
+    int s = 0, w = 0;
+    uint32_t ph = 0;
+    for (int i = 0; i < steps; ++i) {
+      if (role == 0) {
+        dbg_wait(smem_u32(&empty[s]), ph ^ 1u, 0);
+        ptx::mbar_expect_tx(smem_u32(&full[s]), stage_bytes);
+        ptx::bulk_load(ring_smem + s * stage_bytes, my + (size_t)w * stage_bytes, stage_bytes, smem_u32(&full[s]));
+        if (++w == span) w = 0;
+      } else {
+        dbg_wait(smem_u32(&full[s]), ph, 0);
+        ptx::mbar_arrive(smem_u32(&empty[s]));
+      }
+      if (++s == ns) { s = 0; ph ^= 1u; }
+    }
+    if (role == 1) cycles[blockIdx.x * 2 + ring] = clock64() - t0;
+  }
+  __syncthreads();
+}
+}  // namespace lq
+
+extern "C" LQ_API int lq_debug_tma_stream2(const void* src, int stage_bytes, int ns, int steps, int wrap, int ctas,
+                                           long long* cycles, void* stream) {
+  if (ns < 1 || ns > 32 || stage_bytes % 16 || 2 * stage_bytes * ns > 200 * 1024 || wrap < 0) return LQ_ERR_BAD_ARG;
+  const int smem = 2 * stage_bytes * ns + 256;
+  cudaFuncSetAttribute(lq::tma_stream2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 201 * 1024);
+  lq::tma_stream2_kernel<<<ctas, 128, smem, lq::as_stream(stream)>>>(static_cast<const uint8_t*>(src), stage_bytes, ns,
+                                                                     steps, wrap, cycles);
+  return lq::check_launch("tma_stream2_kernel");
+}
+
+namespace lq {
+// tcgen05.mma.cta_group::2 (a pair of CTAs on two SMs issues one 256 x N x 32 MMA; each CTA holds 128 rows of A
+// and of the accumulator in its own tensor memory and N / 2 rows of B in its own shared memory): the issue
+// rate seen by the leader CTA, like mma_rate_kernel.  out[2 * cta] = cycles to completion, [2 * cta + 1] = status
+// (0 ok, 1 the wait for the commit ran out).
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(128, 1)
+mma_rate2_kernel(int n, int iters, int a_in_tmem, int extra, long long* out) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  __shared__ uint64_t bar;
+  __shared__ uint64_t side_bar[3];   // extra & 1 / & 2: one / two more commits per group of four MMAs go here;
+                                     // [2] is a completed barrier for the extra & 4 wait
+  __shared__ uint32_t tmem_slot;
+  const uint32_t bar_addr = smem_u32(&bar);
+  uint32_t rank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(bar_addr, 1);
+    for (int i = 0; i < 3; ++i) ptx::mbar_init(smem_u32(&side_bar[i]), 1);
+    ptx::fence_mbar_init();
+    ptx::mbar_arrive(smem_u32(&side_bar[2]));   // phase 0 of [2] is complete
+  }
+  for (int i = threadIdx.x; i < (16384 + 16384) / 4; i += blockDim.x)
+    reinterpret_cast<uint32_t*>(smem_raw + (base - raw_addr))[i] = 0x01020304u * (i + 1);
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  if (threadIdx.x < 32) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(512u)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  ptx::tc_fence_before();
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  long long t0 = clock64();
+  if (rank == 0 && threadIdx.x == 0) {
+    const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((256u >> 4) << 24);
+    t0 = clock64();
+    for (int i = 0; i < iters; ++i) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint64_t bdesc = ptx::smem_desc_sw128(base + j * 32);
+        if (a_in_tmem) {
+          asm volatile(
+              "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+              "tcgen05.mma.cta_group::2.kind::i8 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_base),
+              "r"(tmem_base + 256u + j * 8), "l"(bdesc), "r"(idesc), "r"(1u)
+              : "memory");
+        } else {
+          const uint64_t adesc = ptx::smem_desc_sw128(base + 16384 + j * 32);
+          asm volatile(
+              "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+              "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_base),
+              "l"(adesc), "l"(bdesc), "r"(idesc), "r"(1u)
+              : "memory");
+        }
+      }
+      if (extra & 3) ptx::tc_commit_pair(smem_u32(&side_bar[0]));
+      if (extra & 2) ptx::tc_commit_pair(smem_u32(&side_bar[1]));
+      if (extra & 4) {
+        ptx::mbar_wait_bounded(smem_u32(&side_bar[2]), 0u, 1000000ull);
+        ptx::tc_fence_after();
+      }
+    }
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+                     bar_addr),
+                 "h"(mask)
+                 : "memory");
+  }
+  if (threadIdx.x == 0) {
+    const bool ok = ptx::mbar_wait_bounded(bar_addr, 0u, 2000000000ull);
+    out[blockIdx.x * 2] = clock64() - t0;
+    out[blockIdx.x * 2 + 1] = ok ? 0 : 1;
+  }
+  ptx::tc_fence_before();
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  if (threadIdx.x < 32) {
+    ptx::tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+}  // namespace lq
+
+extern "C" LQ_API int lq_debug_mma_rate2(int n, int iters, int a_in_tmem, int extra, int ctas, long long* out,
+                                         void* stream) {
+  if (n < 32 || n > 256 || n % 32 || iters <= 0 || ctas <= 0 || (ctas & 1) || !out) return LQ_ERR_BAD_ARG;
+  const int smem = 1024 + 16384 + 16384;
+  cudaFuncSetAttribute(lq::mma_rate2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  lq::mma_rate2_kernel<<<ctas, 128, smem, lq::as_stream(stream)>>>(n, iters, a_in_tmem, extra, out);
+  return lq::check_launch("mma_rate2_kernel");
 }

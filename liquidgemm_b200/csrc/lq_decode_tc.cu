@@ -203,7 +203,9 @@ w4a8_decode_tc_kernel(const Args args, const std::conditional_t<MULTI, MultiOut,
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_p;
     const uint32_t tmem_a = tmem_base + C::kAccCols;
-    if (lane == 0) {
+    {
+      // The whole warp walks the loop; one elected lane issues (see ptx::elect_one).
+      const bool leader = ptx::elect_one();
       constexpr uint32_t idesc = ptx::idesc_i8(BN);
       Ring<NT> ring;
       bool ok = true;
@@ -216,37 +218,42 @@ w4a8_decode_tc_kernel(const Args args, const std::conditional_t<MULTI, MultiOut,
         const uint32_t p = seg & 1u;
         // the accumulator's previous segment (two back) must have been read out by its set
         if (seg >= 2 && ok && !ptx::mbar_wait_bounded(bar_accfree + 8 * p, ((seg >> 1) - 1u) & 1u, kWaitLimitNs)) {
-          atomicExch(args.status, 402);
+          if (leader) atomicExch(args.status, 402);
           ok = false;
         }
         const uint32_t tmem_acc = tmem_base + p * BN;
         for (int kt = sg.kb; kt < sg.ke; ++kt) {
           const long long tr_a1 = TR_NOW();
           if (ok && !ptx::mbar_wait_bounded(bar_aready + 8 * ring.s, ring.ph, kWaitLimitNs)) {
-            atomicExch(args.status, 403);
+            if (leader) atomicExch(args.status, 403);
             ok = false;
           }
           TR_ADD(tr_wa, tr_a1);
+          __syncwarp();
           ptx::tc_fence_after();
           const long long tr_i1 = TR_NOW();
+          const uint32_t xb = xs + ring.s * C::kXStage;
+          const uint32_t ab = tmem_a + ring.s * 32;
+          if (leader) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const uint64_t bdesc = ptx::smem_desc_sw128(xs + ring.s * C::kXStage + j * 32);
-            ptx::mma_i8_ts(tmem_acc, tmem_a + ring.s * 32 + j * 8, bdesc, idesc, (kt > sg.kb || j > 0) ? 1u : 0u);
+            for (int j = 0; j < 4; ++j)
+              ptx::mma_i8_ts(tmem_acc, ab + j * 8, ptx::smem_desc_sw128(xb + j * 32), idesc, (kt > sg.kb || j > 0) ? 1u : 0u);
           }
           TR_ADD(tr_issue, tr_i1);
           const long long tr_i2 = TR_NOW();
-          ptx::tc_commit(bar_afree + 8 * ring.s);   // frees the operand stage and its token slice
+          if (leader) ptx::tc_commit(bar_afree + 8 * ring.s);   // frees the operand stage and its token slice
           TR_ADD(tr_commit, tr_i2);
           ring.advance();
         }
-        ptx::tc_commit(bar_accfull + 8 * p);
+        if (leader) ptx::tc_commit(bar_accfull + 8 * p);
         ++seg;
       }
-      TR_SET(3, tr_wa);
-      TR_SET(4, TR_NOW() - tr_m0);
-      TR_SET(10, tr_issue);
-      TR_SET(11, tr_commit);
+      if (leader) {
+        TR_SET(3, tr_wa);
+        TR_SET(4, TR_NOW() - tr_m0);
+        TR_SET(10, tr_issue);
+        TR_SET(11, tr_commit);
+      }
     }
     __syncwarp();
     // tensor memory is released after every role is done

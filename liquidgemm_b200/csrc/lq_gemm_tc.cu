@@ -18,10 +18,10 @@
 // the kernel ends.  A fixed split-K factor can be requested instead (tile = S equal k-ranges).
 //
 // Roles inside a CTA (16 warps), connected by mbarrier rings:
-//   warp 0       producer : one thread issues, per k-step, the weight tile (one 8704-byte bulk
-//                           copy from the tile blob, or a tensor-map box from the row-major
-//                           layouts) and the BN x 128 activation box (128-byte swizzle; token rows
-//                           past M are zero-filled by the TMA unit).
+//   warps 0, 2   producers: per k-step, warp 0 issues the weight tile (one 8704-byte bulk copy from
+//                           the tile blob, or a tensor-map box of INT8 weights) and warp 2 the
+//                           BN x 128 activation box (128-byte swizzle; token rows past M are
+//                           zero-filled by the TMA unit).
 //   warps 4..7,  dequant  : two sets take alternate k-steps; thread r owns weight row r of the tile:
 //   12..15                  64 bytes of nibbles (four
 //                           conflict-free 16-byte shared loads) + two (step, offset) pairs ->
@@ -35,7 +35,8 @@
 //                           accumulator while the MMAs of the next segment fill the other one;
 //                           (float)acc * ascale[m] * s1[n] + cast, int32 stores, or the partial
 //                           reduction described above.
-// The TMA ring runs NS k-steps ahead, the dequantised operand ring NT k-steps ahead of the MMAs.
+// The TMA ring runs NS k-steps ahead of the MMAs; operand stage s in tensor memory is tied to
+// shared-memory stage s.
 //
 // Every wait is bounded: when a barrier does not complete within kWaitLimitNs the thread writes
 // a site code to the status word, leaves its loop, and the CTA still reaches the common exit
@@ -56,7 +57,7 @@ size_t tile_workspace_bytes(int M, int N, int splits);                       // 
 int run_tile_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, const void* bias,
                   const OutSpec& out, const PeerSync* sync, int out_mode, int M, int N, int K, int splits, void* ws,
                   size_t ws_bytes, cudaStream_t st);  // lq_gemm_tile.cu
-int tile_output_grid(int M, int N, int splits);                              // lq_gemm_tile.cu
+int tile_output_grid(int M, int N, int K, int splits);                            // lq_gemm_tile.cu
 size_t decode_tc_workspace_bytes(int M, int N, int K);                       // lq_decode_tc.cu
 int run_decode_tc(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, const void* bias,
                   const OutSpec& out, const PeerSync* sync, int out_mode, int M, int N, int K, void* ws,
@@ -66,6 +67,12 @@ int run_gemv_blob_ws(const int8_t* x, const uint8_t* blob, const float* ascale, 
                      const OutSpec& out, const PeerSync* sync, int out_dtype, int M, int N, int K, void* ws,
                      size_t ws_bytes, cudaStream_t st);  // lq_gemv_blob.cu
 int decode_tc_grid(int N, int K);                                            // lq_decode_tc.cu
+bool pair_serves(int M, int N, int K);                                       // lq_gemm_pair.cu
+size_t pair_workspace_bytes(int M, int N);                                   // lq_gemm_pair.cu
+int pair_grid(int M, int N);                                                 // lq_gemm_pair.cu
+int run_pair_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, const void* bias,
+                  const OutSpec& out, const PeerSync* sync, int out_mode, int M, int N, int K, void* ws, size_t ws_bytes,
+                  cudaStream_t st);  // lq_gemm_pair.cu
 int gemv_blob_grid(int N, int K);                                            // lq_gemv_blob.cu
 int launch_gemv_plain_f32(const int8_t* x, const uint8_t* nibbles, const uint8_t* s_u8,
                           const uint8_t* off_a, const float* ascale, const float* s1, float* y, int M,
@@ -73,17 +80,14 @@ int launch_gemv_plain_f32(const int8_t* x, const uint8_t* nibbles, const uint8_t
 
 constexpr int kTileBytes = 8704;     // weight tile in the blob: 8192 nibble bytes + 512 metadata bytes
 constexpr int kI8TileBytes = 16384;  // INT8 weight tile: 128 rows x 128 bytes
-constexpr int kRowBoxBytes = 8192;   // row-major nibble box: 128 rows x 64 bytes
 constexpr int kThreads = 512;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 constexpr int kOutI32 = 3;           // internal output mode: raw int32
 
-enum WeightSource { kBlob = 0, kRowMajor = 1, kInt8 = 2 };
+enum WeightSource { kBlob = 0, kInt8 = 1 };
 
 struct GemmArgs {
   const uint8_t* blob;     // kBlob: tile blob
-  const uint8_t* s_u8;     // kRowMajor: [N, K/64] steps
-  const uint8_t* off_a;    // kRowMajor: [N, K/64] offsets
   const float* ascale;     // [M]
   const float* s1;         // [N]
   void* out;               // [M, N] in out_mode's type
@@ -95,25 +99,12 @@ struct GemmArgs {
   int kt_total;            // K / 128
   int n_tiles, m_tiles;
   int fixed_split;         // 0: stream-K ranges; S >= 1: every tile is cut into S equal k-ranges
-  long long* trace;        // optional per-CTA cycle counters (32 per CTA) for pipeline studies, or null
-  int debug_skip;          // pipeline studies only (results become wrong): 1 = no tcgen05.st,
-                           // 2 = no epilogue global writes, 4 = no tcgen05.mma, 8 = no activation TMA
 };
-
-// Trace slots (cycles relative to the CTA's first instruction, or accumulated waits).
-enum TraceSlot {
-  kTrSetupDone = 1, kTrFirstTma = 2, kTrLastTma = 3, kTrDeqFirst = 4, kTrDeqLast = 5, kTrMmaFirst = 6,
-  kTrMmaLast = 7, kTrEpiFirst = 8, kTrEpiLast = 9, kTrExit = 10, kTrEpiWhole = 11, kTrEpiPartial = 12,
-  kTrMmaWaitA = 13, kTrMmaWaitFull = 14, kTrMmaWaitAcc = 15, kTrDeqWaitFull = 16, kTrDeqWaitFree = 17,
-  kTrProdWaitEmpty = 18, kTrEpiWaitAcc = 19, kTrSegments = 20, kTrKsteps = 21, kTrDeqCompute = 22,
-  kTrProdIssue = 23, kTrMmaIssue = 24,
-};
-#define LQ_TRACE(slot, value) do { if (args.trace) args.trace[(size_t)blockIdx.x * 32 + (slot)] = (value); } while (0)
 
 template <int BN, int NS, int NT, int NACC, int WSRC>
 struct TcCfg {
   static constexpr int kXStage = BN * 128;
-  static constexpr int kWStage = WSRC == kBlob ? kTileBytes : WSRC == kRowMajor ? kRowBoxBytes : kI8TileBytes;
+  static constexpr int kWStage = WSRC == kBlob ? kTileBytes : kI8TileBytes;
   static constexpr int kACols = WSRC == kInt8 ? 0 : 32 * NS;   // one operand stage per shared-memory stage
   static constexpr int kColsNeeded = NACC * BN + kACols;
   static constexpr int kTmemCols = kColsNeeded <= 32 ? 32 : kColsNeeded <= 64 ? 64 : kColsNeeded <= 128 ? 128
@@ -135,8 +126,6 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, int lan
 }
 
 __device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-
-#define LQ_CLK() (tracing ? clock64() : 0ll)
 
 template <int BN, int NS, int NT, int NACC, int WSRC>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -164,8 +153,6 @@ w4a8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
   volatile int* wait_flag = reinterpret_cast<volatile int*>(gen_bars + Cfg::kNumBars * 8 + 8);  // [2]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const bool tracing = args.trace != nullptr;
-  const long long t_begin = LQ_CLK();
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < NS; ++s) {
@@ -190,7 +177,6 @@ w4a8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_p;
   const uint32_t tmem_a = tmem_base + NACC * BN;   // NS operand stages of 32 columns behind the accumulators
-  if (threadIdx.x == 0) LQ_TRACE(kTrSetupDone, LQ_CLK() - t_begin);
 
   if (warp == 0 || warp == 2) {
     // ------------------------------------------------------------------ producers
@@ -198,34 +184,26 @@ w4a8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
     // and polls (a warp that stays converged costs far less than one lane spinning while 31 wait);
     // lane 0 alone announces the byte count and issues the copy.
     const bool weights = (warp == 0);
-    if ((args.debug_skip & 16) && lane != 0) goto role_done;   // experiment: single-lane producer
     SegmentWalk walk(SchedArgs{args.kt_total, args.n_tiles, args.m_tiles, args.fixed_split}, blockIdx.x, gridDim.x);
     Segment sg;
     Ring<NS> ring;
     int issued = 0;
     bool ok = true;
-    long long w_empty = 0, t_issue = 0;
     while (ok && walk.next(sg)) {
       const int nt = sg.tile % args.n_tiles, mt = sg.tile / args.n_tiles;
       const uint8_t* wsrc = WSRC == kBlob ? args.blob + ((size_t)nt * args.kt_total + sg.kb) * kTileBytes : nullptr;
       for (int kt = sg.kb; kt < sg.ke; ++kt) {
-        const long long tw0 = LQ_CLK();
         if (!ptx::mbar_wait_bounded(bar_empty + 8 * ring.s, ring.ph ^ 1u, kWaitLimitNs)) {
           atomicExch(args.status, 101);
           ok = false;
           break;
         }
-        const long long ti0 = LQ_CLK();
-        w_empty += ti0 - tw0;
-        if (issued == 0 && weights && lane == 0) LQ_TRACE(kTrFirstTma, ti0 - t_begin);
         const uint32_t full = bar_full + 8 * ring.s;
         if (lane == 0) {
           if (weights) {
             ptx::mbar_expect_tx(full, Cfg::kWStage);
             if (WSRC == kBlob) {
               ptx::bulk_load(ws + ring.s * Cfg::kWStage, wsrc, kTileBytes, full);
-            } else if (WSRC == kRowMajor) {
-              ptx::tensor_load_2d(ws + ring.s * Cfg::kWStage, &tmap_w, kt * 64, nt * 128, full);
             } else {
               ptx::tensor_load_2d(ws + ring.s * Cfg::kWStage, &tmap_w, kt * 128, nt * 128, full);
             }
@@ -235,16 +213,9 @@ w4a8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
           }
         }
         if (WSRC == kBlob) wsrc += kTileBytes;
-        t_issue += LQ_CLK() - ti0;
         ring.advance();
         ++issued;
       }
-    }
-    if (weights && lane == 0) {
-      LQ_TRACE(kTrLastTma, LQ_CLK() - t_begin);
-      LQ_TRACE(kTrProdWaitEmpty, w_empty);
-      LQ_TRACE(kTrProdIssue, t_issue);
-      LQ_TRACE(kTrKsteps, issued);
     }
     if (!ok) {
       // copies already issued still write shared memory: let them land before the CTA exits
@@ -257,72 +228,51 @@ w4a8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issue
-    // The whole warp waits; lane 0 issues.  With dequantisation the only wait per k-step is on the
+    // The whole warp walks the loop; one elected lane issues (see ptx::elect_one).  With dequantisation the only wait per k-step is on the
     // operand barrier: the dequant warps saw the stage's full barrier (weights and activations)
     // before they produced the operand, so "operand ready" implies "activations landed".
     constexpr uint32_t idesc = ptx::idesc_i8(BN);
-    if ((args.debug_skip & 32) && lane != 0) goto role_done;   // experiment: single-lane MMA role
+    const bool leader = ptx::elect_one();
     SegmentWalk walk(SchedArgs{args.kt_total, args.n_tiles, args.m_tiles, args.fixed_split}, blockIdx.x, gridDim.x);
     Segment sg;
     Ring<NS> ring;
     Ring<NACC> accring;
-    int seg = 0;
-    bool ok = true, first = true;
-    long long w_a = 0, w_acc = 0, t_mma = 0;
+    bool ok = true;
     while (ok && walk.next(sg)) {
-      const long long ta0 = LQ_CLK();
-      if (!ptx::mbar_wait_bounded(bar_accempty + 8 * accring.s, accring.ph ^ 1u, kWaitLimitNs)) {
-        atomicExch(args.status, 106);
-        ok = false;
+      ok = __all_sync(0xffffffffu, ptx::mbar_wait_bounded(bar_accempty + 8 * accring.s, accring.ph ^ 1u, kWaitLimitNs));
+      if (!ok) {
+        if (leader) atomicExch(args.status, 106);
         break;
       }
-      w_acc += LQ_CLK() - ta0;
       ptx::tc_fence_after();
       const uint32_t tmem_acc = tmem_base + accring.s * BN;
       for (int kt = sg.kb; kt < sg.ke; ++kt) {
-        const long long tf0 = LQ_CLK();
-        ok = ptx::mbar_wait_bounded((kDequant ? bar_aready : bar_full) + 8 * ring.s, ring.ph, kWaitLimitNs);
-        const long long tm0 = LQ_CLK();
-        w_a += tm0 - tf0;
+        ok = __all_sync(0xffffffffu, ptx::mbar_wait_bounded((kDequant ? bar_aready : bar_full) + 8 * ring.s, ring.ph,
+                                                            kWaitLimitNs));
         if (!ok) {
-          atomicExch(args.status, 102);
+          if (leader) atomicExch(args.status, 102);
           break;
         }
-        if (first && lane == 0) LQ_TRACE(kTrMmaFirst, tm0 - t_begin);
-        first = false;
         ptx::tc_fence_after();
-        if (lane == 0) {
-          const uint32_t xb = xs + ring.s * Cfg::kXStage;
-          if (!(args.debug_skip & 4)) {
+        const uint32_t xb = xs + ring.s * Cfg::kXStage;
+        const uint32_t ab = tmem_a + ring.s * 32;
+        const uint32_t wb = ws + ring.s * Cfg::kWStage;
+        if (leader) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const uint64_t bdesc = ptx::smem_desc_sw128(xb + j * 32);
-              const uint32_t accumulate = (kt > sg.kb || j > 0) ? 1u : 0u;
-              if (kDequant) {
-                ptx::mma_i8_ts(tmem_acc, tmem_a + ring.s * 32 + j * 8, bdesc, idesc, accumulate);
-              } else {
-                const uint64_t adesc = ptx::smem_desc_sw128(ws + ring.s * Cfg::kWStage + j * 32);
-                ptx::mma_i8_ss(tmem_acc, adesc, bdesc, idesc, accumulate);
-              }
-            }
+          for (int j = 0; j < 4; ++j) {
+            const uint64_t bdesc = ptx::smem_desc_sw128(xb + j * 32);
+            const uint32_t accumulate = (kt > sg.kb || j > 0) ? 1u : 0u;
+            if (kDequant) ptx::mma_i8_ts(tmem_acc, ab + j * 8, bdesc, idesc, accumulate);
+            else ptx::mma_i8_ss(tmem_acc, ptx::smem_desc_sw128(wb + j * 32), bdesc, idesc, accumulate);
           }
           // one commit recycles the shared-memory stage and the tensor-memory operand stage: the
           // dequant warps have finished with both before they signalled "operand ready"
           ptx::tc_commit(bar_empty + 8 * ring.s);
         }
-        t_mma += LQ_CLK() - tm0;
         ring.advance();
       }
-      if (ok && lane == 0) ptx::tc_commit(bar_accfull + 8 * accring.s);
+      if (ok && leader) ptx::tc_commit(bar_accfull + 8 * accring.s);
       accring.advance();
-      ++seg;
-    }
-    if (lane == 0) {
-      LQ_TRACE(kTrMmaLast, LQ_CLK() - t_begin);
-      LQ_TRACE(kTrMmaWaitA, w_a);
-      LQ_TRACE(kTrMmaWaitAcc, w_acc);
-      LQ_TRACE(kTrSegments, seg);
-      LQ_TRACE(kTrMmaIssue, t_mma);
     }
   } else if ((warp >= 4 && warp < 8) || warp >= 12) {
     // ------------------------------------------------------------------ dequant
@@ -333,60 +283,35 @@ w4a8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
     // that read the previous contents of both are complete and no separate "operand free"
     // barrier is needed.
     if (kDequant) {
-      const int my_parity = warp >= 12 ? 1 : 0;
-      int step_parity = 0;
+      const int my_set = warp < 8 ? 0 : 1;
+      int step_set = 0;   // set that owns the current k-step
       const int quad = warp & 3;               // TMEM lane quadrant this warp may access
       const int row = quad * 32 + lane;        // weight row inside the tile == TMEM lane
       const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
-      const int G = args.K >> 6;
       SegmentWalk walk(SchedArgs{args.kt_total, args.n_tiles, args.m_tiles, args.fixed_split}, blockIdx.x, gridDim.x);
       Segment sg;
       Ring<NS> ring;
-      bool ok = true, first = true;
-      long long w_full = 0, t_comp = 0;
-      const bool tracer = (threadIdx.x == 128);
+      bool ok = true;
       while (ok && walk.next(sg)) {
-        const int nt = sg.tile % args.n_tiles;
-        const long n = (long)nt * 128 + row;
-        const bool n_ok = n < args.N;
         for (int kt = sg.kb; kt < sg.ke; ++kt) {
-          if (step_parity != my_parity) {        // the other set's k-step
-            step_parity ^= 1;
+          const bool mine = step_set == my_set;
+          step_set ^= 1;
+          if (!mine) {                           // another set's k-step
             ring.advance();
             continue;
           }
-          step_parity ^= 1;
-          uint32_t meta = 0x80008000u;   // step 0, offset 128: reconstructs to zero
-          if (WSRC == kRowMajor && n_ok) {
-            const uint32_t sp = *reinterpret_cast<const uint16_t*>(args.s_u8 + n * G + 2 * kt);
-            const uint32_t op = *reinterpret_cast<const uint16_t*>(args.off_a + n * G + 2 * kt);
-            meta = (sp & 0xffu) | ((op & 0xffu) << 8) | ((sp >> 8) << 16) | ((op >> 8) << 24);
-          }
-          const long long td0 = LQ_CLK();
           if (!ptx::mbar_wait_bounded(bar_full + 8 * ring.s, ring.ph, kWaitLimitNs)) {
             atomicExch(args.status, 103);
             ok = false;
             break;
           }
-          const long long td1 = LQ_CLK();
-          w_full += td1 - td0;
-          if (first && tracer) LQ_TRACE(kTrDeqFirst, td1 - t_begin);
-          first = false;
           __syncwarp();   // lanes leave the poll loop one by one; tcgen05.st / wait::st need the warp converged
           ptx::tc_fence_after();
           const uint8_t* wst = smem + (ws - base) + ring.s * Cfg::kWStage;
           uint4 ch[4];
-          if (WSRC == kBlob) {
 #pragma unroll
-            for (int c = 0; c < 4; ++c) ch[c] = *reinterpret_cast<const uint4*>(wst + (c * 128 + row) * 16);
-            meta = *reinterpret_cast<const uint32_t*>(wst + 8192 + row * 4);
-          } else {
-            // 64-byte rows stored with the 64-byte swizzle: 16-byte chunk c of row r sits at
-            // chunk position c ^ ((r >> 1) & 3)
-            const int sw = (row >> 1) & 3;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) ch[c] = *reinterpret_cast<const uint4*>(wst + row * 64 + ((c ^ sw) << 4));
-          }
+          for (int c = 0; c < 4; ++c) ch[c] = *reinterpret_cast<const uint4*>(wst + (c * 128 + row) * 16);
+          const uint32_t meta = *reinterpret_cast<const uint32_t*>(wst + 8192 + row * 4);
           const uint32_t step0 = meta & 0xffu, a0 = ((meta >> 8) & 0xffu) * 0x01010101u;
           const uint32_t step1 = (meta >> 16) & 0xffu, a1 = (meta >> 24) * 0x01010101u;
           uint32_t v[32];
@@ -401,21 +326,15 @@ w4a8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
               v[8 * c + 2 * h + 1] = lqq_dequant4((pk[h] >> 4) & 0x0F0F0F0Fu, step, ab);
             }
           }
-          if (!(args.debug_skip & 1)) ptx::tmem_st32(tmem_a + lane_addr + ring.s * 32, v);
+          ptx::tmem_st32(tmem_a + lane_addr + ring.s * 32, v);
           // Publish at once: the other dequant set covers the next k-step while these stores drain.
           // (Deferring this to the set's next iteration would tie MMA i to the arrival of the TMA
           // data of k-step i + 2 and eat two stages of prefetch depth.)
           ptx::tc_wait_st();
           ptx::tc_fence_before();
           ptx::mbar_arrive(bar_aready + 8 * ring.s);
-          t_comp += LQ_CLK() - td1;
           ring.advance();
         }
-      }
-      if (tracer) {
-        LQ_TRACE(kTrDeqLast, LQ_CLK() - t_begin);
-        LQ_TRACE(kTrDeqWaitFull, w_full);
-        LQ_TRACE(kTrDeqCompute, t_comp);
       }
     }
   } else if (warp >= 8 && warp < 12) {
@@ -429,12 +348,10 @@ w4a8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
     Ring<NACC> accring;
     int seg = 0;
     bool ok = true;
-    long long w_acc = 0, t_whole = 0, t_part = 0;
     while (ok && walk.next(sg)) {
       const int b = accring.s;
       const uint32_t phb = accring.ph;
       accring.advance();
-      const long long te0 = LQ_CLK();
       // One thread performs the bounded wait and publishes the outcome, so that the 128 threads
       // always agree on it (they meet at named barriers below and must never split up).
       const int fslot = seg & 1;
@@ -450,13 +367,10 @@ w4a8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
         break;
       }
       ptx::tc_fence_after();
-      const long long te1 = LQ_CLK();
-      w_acc += te1 - te0;
-      if (seg == 1 && et == 0) LQ_TRACE(kTrEpiFirst, te1 - t_begin);
       const int nt = sg.tile % args.n_tiles, mt = sg.tile / args.n_tiles;
       const int m0 = mt * BN;
       const long n = (long)nt * 128 + row;
-      const bool n_ok = n < args.N && !(args.debug_skip & 2);
+      const bool n_ok = n < args.N;
       const int cols = (args.M - m0) < BN ? (args.M - m0) : BN;   // valid token columns of this tile
       const uint32_t tmem_acc = tmem_base + b * BN + lane_addr;
       const float w_scale = (n_ok && args.out_mode != kOutI32) ? __ldg(args.s1 + n) : 0.f;
@@ -573,21 +487,11 @@ w4a8_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
           if (et == 0) args.counters[sg.slot] = 0;
         }
       }
-      if (sg.whole) t_whole += LQ_CLK() - te1;
-      else t_part += LQ_CLK() - te1;
-    }
-    if (et == 0) {
-      LQ_TRACE(kTrEpiLast, LQ_CLK() - t_begin);
-      LQ_TRACE(kTrEpiWhole, t_whole);
-      LQ_TRACE(kTrEpiPartial, t_part);
-      LQ_TRACE(kTrEpiWaitAcc, w_acc);
     }
   }
 
-role_done:
   ptx::tc_fence_before();
   __syncthreads();
-  if (threadIdx.x == 0) LQ_TRACE(kTrExit, LQ_CLK() - t_begin);
   if (warp == 1) {
     __syncwarp();
     ptx::tc_fence_after();
@@ -638,9 +542,6 @@ int make_byte_matrix_map(CUtensorMap* map, const void* ptr, long rows, long row_
   }
   return LQ_OK;
 }
-
-static long long* g_trace_ptr = nullptr;   // set by lq_debug_set_trace (pipeline studies only)
-static int g_debug_skip = 0;
 
 static int pick_bn(int M, int K = 0) {
   (void)K;
@@ -724,9 +625,9 @@ static int dispatch_bn(int bn, const CUtensorMap& tx, const CUtensorMap& tw, con
   }
 }
 
-// x: [M,K] int8 tokens.  w: tile blob, row-major interleaved nibbles [N,K/2], or [N,K] int8 weights.
+// x: [M,K] int8 tokens.  w: tile blob, or [N,K] int8 weights.
 template <int WSRC>
-static int run_gemm(const int8_t* x, const void* w, const uint8_t* s_u8, const uint8_t* off_a, const float* ascale,
+static int run_gemm(const int8_t* x, const void* w, const float* ascale,
                     const float* s1, void* out, int out_mode, int M, int N, int K, int splitk, void* wsp,
                     size_t ws_bytes, cudaStream_t st) {
   if (int rc = lq_check_device()) return rc;
@@ -736,13 +637,10 @@ static int run_gemm(const int8_t* x, const void* w, const uint8_t* s_u8, const u
   int rc = make_byte_matrix_map(&tx, x, M, K, p.bn, 128);
   if (rc) return rc;
   if (WSRC == kBlob) tw = tx;
-  else if (WSRC == kRowMajor) rc = make_byte_matrix_map(&tw, w, N, K / 2, 128, 64);
   else rc = make_byte_matrix_map(&tw, w, N, K, 128, 128);
   if (rc) return rc;
   GemmArgs a;
   a.blob = WSRC == kBlob ? static_cast<const uint8_t*>(w) : nullptr;
-  a.s_u8 = s_u8;
-  a.off_a = off_a;
   a.ascale = ascale;
   a.s1 = s1;
   a.out = out;
@@ -758,8 +656,6 @@ static int run_gemm(const int8_t* x, const void* w, const uint8_t* s_u8, const u
   a.n_tiles = p.n_tiles;
   a.m_tiles = p.m_tiles;
   a.fixed_split = p.fixed_split;
-  a.trace = g_trace_ptr;
-  a.debug_skip = g_debug_skip;
   if (!a.status) return LQ_ERR_CUDA;
   return dispatch_bn<WSRC>(p.cfg, tx, tw, a, p.grid, st);
 }
@@ -769,14 +665,6 @@ static int run_gemm(const int8_t* x, const void* w, const uint8_t* s_u8, const u
 using namespace lq;
 
 extern "C" {
-
-// Pipeline-study hook: when set to a device buffer of 32 x 8 bytes per SM, every tensor-core GEMM
-// launch records per-CTA cycle counters there (see TraceSlot).  Pass null to switch it off.
-// `skip` switches pipeline parts off for timing experiments (see GemmArgs::debug_skip); 0 = normal.
-LQ_API void lq_debug_set_trace(void* device_buffer, int skip) {
-  g_trace_ptr = static_cast<long long*>(device_buffer);
-  g_debug_skip = skip;
-}
 
 int lq_gemm_pick_splitk(int M, int N, int K, int env_override) {
   // 0 selects stream-K scheduling, which balances any shape over the SMs; an explicit
@@ -795,6 +683,7 @@ enum RouteKind {
   kRouteTile,         // two CTAs per SM, one tile each, `splits` int32 planes + finish pass when splits > 1
   kRouteGemv,         // streaming dp4a GEMV over the blob (scaled outputs only)
   kRouteDecodeTc,     // streaming tensor-core kernel, one launch, atomic join
+  kRoutePair,         // CTA pairs, 256 channels x 192 tokens per tile (prefill)
 };
 struct Route {
   RouteKind kind;
@@ -813,6 +702,17 @@ static int decode_tc_max_m() {
     const char* e = getenv("LQ_DECODE_TC_MAX_M");
     const int n = e ? atoi(e) : 16;
     return n <= 0 ? 0 : n >= 32 ? 32 : 16;
+  }();
+  return v;
+}
+
+// From this many tokens on, shapes with whole 256-channel blocks go to the CTA-pair kernel (LQ_PAIR_MIN_M moves
+// the limit for measurements; 0 switches the kernel off).
+static int pair_min_m() {
+  static const int v = []() {
+    const char* e = getenv("LQ_PAIR_MIN_M");
+    const int n = e ? atoi(e) : 256;
+    return n <= 0 ? (1 << 30) : n < 129 ? 129 : n;
   }();
   return v;
 }
@@ -836,7 +736,10 @@ static Route route_for(int M, int N, int K, int splitk, bool scaled) {
   // Automatic choice above 128 tokens: the two-CTAs-per-SM tile kernel.  With two dequant sets it is ahead
   // of the persistent stream-K kernel at every size measured (M = 256: 2x, M = 2048: 1.1-1.3x, M = 16384 on
   // 28672 x 4096: 1.13x); the persistent kernel stays reachable through an explicit split argument.
-  if (splitk == 0) return {kRouteTile, tile_pick_splits(M, N, K)};
+  if (splitk == 0) {
+    if (M >= pair_min_m() && pair_serves(M, N, K)) return {kRoutePair, 0};
+    return {kRouteTile, tile_pick_splits(M, N, K)};
+  }
   return {kRoutePersistent, splitk};
 }
 
@@ -845,6 +748,7 @@ static size_t route_ws_bytes(const Route& r, int M, int N, int K) {
     case kRouteGemv: return gemv_blob_workspace_bytes(N, K);
     case kRouteDecodeTc: return decode_tc_workspace_bytes(M, N, K);
     case kRouteTile: return tile_workspace_bytes(M, N, r.splits);
+    case kRoutePair: return pair_workspace_bytes(M, N);
     default: return make_plan(M, N, K, r.splits).ws_bytes;
   }
 }
@@ -889,9 +793,11 @@ static int blob_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, 
     case kRouteTile:
       return run_tile_gemm(x, blob, ascale, s1, bias, single_out(out, N), nullptr, out_mode, M, N, K, r.splits, ws,
                            ws_bytes, st);
+    case kRoutePair:
+      return run_pair_gemm(x, blob, ascale, s1, bias, single_out(out, N), nullptr, out_mode, M, N, K, ws, ws_bytes, st);
     default:
       if (bias) return LQ_ERR_BAD_ARG;   // the persistent kernel has no bias epilogue
-      return run_gemm<kBlob>(x, blob, nullptr, nullptr, ascale, s1, out, out_mode, M, N, K, r.splits, ws, ws_bytes, st);
+      return run_gemm<kBlob>(x, blob, ascale, s1, out, out_mode, M, N, K, r.splits, ws, ws_bytes, st);
   }
 }
 
@@ -951,6 +857,9 @@ int lq_w4a8_gemm_fused_scatter_sync(const int8_t* x_i8, const uint8_t* blob, con
     case kRouteDecodeTc:
       return run_decode_tc(x_i8, blob, ascale, s1, nullptr, o, &ps, out_dtype, M, N, K, workspace, workspace_bytes,
                            as_stream(stream));
+    case kRoutePair:
+      return run_pair_gemm(x_i8, blob, ascale, s1, nullptr, o, &ps, out_dtype, M, N, K, workspace, workspace_bytes,
+                           as_stream(stream));
     default:
       return run_tile_gemm(x_i8, blob, ascale, s1, nullptr, o, &ps, out_dtype, M, N, K, r.splits, workspace,
                            workspace_bytes, as_stream(stream));
@@ -977,7 +886,8 @@ int lq_decode_grid(int M, int N, int K) {
   switch (r.kind) {
     case kRouteGemv: return gemv_blob_grid(N, K);
     case kRouteDecodeTc: return decode_tc_grid(N, K);
-    default: return tile_output_grid(M, N, r.splits);
+    case kRoutePair: return pair_grid(M, N);
+    default: return tile_output_grid(M, N, K, r.splits);
   }
 }
 
@@ -1005,7 +915,7 @@ int lq_w4a8_gemm_v1(const int8_t* x_i8, const uint8_t* nibbles, const uint8_t* s
   uint8_t* blob = static_cast<uint8_t*>(workspace);
   int rc = lq_repack_tiles(nibbles, LQ_SRC_NIBBLES, s_u8, offset_a, blob, N, K, group_size, stream);
   if (rc) return rc;
-  return run_gemm<kBlob>(x_i8, blob, nullptr, nullptr, ascale, s1, y, LQ_DT_F32, M, N, K, 1, nullptr, 0, st);
+  return run_gemm<kBlob>(x_i8, blob, ascale, s1, y, LQ_DT_F32, M, N, K, 1, nullptr, 0, st);
 }
 
 static int i8_common(const int8_t* a, const int8_t* b, const float* a_scale, const float* b_scale, void* out,
@@ -1015,7 +925,7 @@ static int i8_common(const int8_t* a, const int8_t* b, const float* a_scale, con
   if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) % 16) return LQ_ERR_BAD_ARG;
   if (M == 0) return LQ_OK;
   // whole-tile scheduling: the plain INT8 entry points take no workspace
-  return run_gemm<kInt8>(a, b, nullptr, nullptr, a_scale, b_scale, out, out_mode, M, N, K, 1, nullptr, 0,
+  return run_gemm<kInt8>(a, b, a_scale, b_scale, out, out_mode, M, N, K, 1, nullptr, 0,
                          as_stream(stream));
 }
 

@@ -186,36 +186,40 @@ w4a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs args
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issue
-    if (lane == 0) {
+    // The whole warp walks the loop; one elected lane issues (see ptx::elect_one).
+    {
+      const bool leader = ptx::elect_one();
       constexpr uint32_t idesc = ptx::idesc_i8(BN);
       bool ok = true;
-      for (int i = 0; i < nk && ok; ++i) {
+      for (int i = 0; i < nk; ++i) {
         const int s = i % NS;
         const uint32_t ph = (uint32_t)(i / NS) & 1u;
         const int t = i % NT;
         const uint32_t pht = (uint32_t)(i / NT) & 1u;
         ok = ptx::mbar_wait_bounded(bar_full + 8 * s, ph, kWaitLimitNs);
         if (ok && W4) ok = ptx::mbar_wait_bounded(bar_aready + 8 * t, pht, kWaitLimitNs);
+        ok = __all_sync(0xffffffffu, ok);
         if (!ok) {
-          atomicExch(args.status, 102);
+          if (leader) atomicExch(args.status, 102);
           break;
         }
         ptx::tc_fence_after();
+        const uint32_t xb = xs + s * Cfg::kXStage;
+        const uint32_t ab = tmem_a + t * 32;
+        const uint32_t wb = ws + s * Cfg::kWStage;
+        if (leader) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const uint64_t bdesc = ptx::smem_desc_sw128(xs + s * Cfg::kXStage + j * 32);
-          const uint32_t accumulate = (i > 0 || j > 0) ? 1u : 0u;
-          if (W4) {
-            ptx::mma_i8_ts(tmem_acc, tmem_a + t * 32 + j * 8, bdesc, idesc, accumulate);
-          } else {
-            const uint64_t adesc = ptx::smem_desc_sw128(ws + s * Cfg::kWStage + j * 32);
-            ptx::mma_i8_ss(tmem_acc, adesc, bdesc, idesc, accumulate);
+          for (int j = 0; j < 4; ++j) {
+            const uint64_t bdesc = ptx::smem_desc_sw128(xb + j * 32);
+            const uint32_t accumulate = (i > 0 || j > 0) ? 1u : 0u;
+            if (W4) ptx::mma_i8_ts(tmem_acc, ab + j * 8, bdesc, idesc, accumulate);
+            else ptx::mma_i8_ss(tmem_acc, ptx::smem_desc_sw128(wb + j * 32), bdesc, idesc, accumulate);
           }
+          ptx::tc_commit(bar_empty + 8 * s);
+          if (W4) ptx::tc_commit(bar_afree + 8 * t);
         }
-        ptx::tc_commit(bar_empty + 8 * s);
-        if (W4) ptx::tc_commit(bar_afree + 8 * t);
       }
-      if (ok) ptx::tc_commit(bar_acc);
+      if (ok && leader) ptx::tc_commit(bar_acc);
     }
   } else {
     // ------------------------------------------------------------------ dequant, then epilogue
@@ -400,12 +404,12 @@ static int launch_cfg(const CUtensorMap& tx, const GemmArgs& a, const MultiOut* 
 // raised an unspecified launch failure on a fourth (28672 x 4096, 8192 tokens) and in back-to-back graph
 // replays.  Reading the index arithmetic, the barrier counts and the tensor-memory budget (192 + 2 x 32 =
 // 256 columns, two CTAs per SM) did not show the cause, so the configuration is not built.
-static int tile_bn(int M) {
-  static const int narrow = []() {
-    const char* e = getenv("LQ_TILE_NARROW");   // measurement switch: 64-token tiles for 65..128 tokens
-    return e ? atoi(e) : 0;
-  }();
-  if (narrow && M > 64 && M <= 128) return 64;
+// Between 65 and 128 tokens a small matrix (up to 32 M weights: the qkv and o projections of an 8B model)
+// takes 64-token tiles: twice the CTAs, so the split factor halves and so do the int32 planes each CTA
+// writes (measured at 128 tokens: 6144 x 4096 15.7 -> 14.4 us, 4096 x 4096 13.5 -> 11.7 us; 28672 x 4096
+// and 4096 x 14336, which fill the machine without it, lose 38 % and 7 %).
+static int tile_bn(int M, int N, int K) {
+  if (M > 64 && M <= 128 && (long)N * K <= (1L << 25)) return 64;
   return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
 }
 
@@ -415,7 +419,8 @@ static int tile_bn(int M) {
 // on 6144 x 4096 at 8 tokens: S = 4 / 5 / 6 / 8 give 8.35 / 7.95 / 8.03 / 10.9 us).
 int tile_pick_splits(int M, int N, int K) {
   const int kt = K / 128;
-  const long tiles = (long)((N + 127) / 128) * ((M + tile::tile_bn(M) - 1) / tile::tile_bn(M));
+  const int bn = tile::tile_bn(M, N, K);
+  const long tiles = (long)((N + 127) / 128) * ((M + bn - 1) / bn);
   const long slots = 2L * sm_count();
   int S = 1;
   if (tiles * 2 <= slots) {
@@ -433,9 +438,9 @@ size_t tile_workspace_bytes(int M, int N, int splits) {
 
 // CTAs of the launch that writes the outputs (and signals the peers): the tile grid, or the finish pass.
 int finish_grid(int M, int N);   // lq_elementwise.cu
-int tile_output_grid(int M, int N, int splits) {
+int tile_output_grid(int M, int N, int K, int splits) {
   if (splits > 1) return finish_grid(M, N);
-  const int bn = tile::tile_bn(M);
+  const int bn = tile::tile_bn(M, N, K);
   return ((N + 127) / 128) * ((M + bn - 1) / bn);
 }
 
@@ -446,7 +451,7 @@ int run_tile_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, con
                   size_t ws_bytes, cudaStream_t st) {
   using namespace tile;
   if (splits > 1 && (!ws || ws_bytes < tile_workspace_bytes(M, N, splits))) return LQ_ERR_WORKSPACE;
-  const int bn = tile_bn(M);
+  const int bn = tile_bn(M, N, K);
   CUtensorMap tx;
   int rc = make_byte_matrix_map(&tx, x, M, K, bn, 128);
   if (rc) return rc;

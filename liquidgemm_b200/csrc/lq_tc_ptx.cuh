@@ -166,6 +166,25 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, int (&v)[16]) {
       : "memory");
 }
 
+// ---- issuing thread -------------------------------------------------------------------------------
+// One lane of the converged warp (the same one every time it is asked).  The MMA-issuing role runs its loop
+// with the WHOLE warp and lets only this lane execute the tcgen05.mma / tcgen05.commit instructions: the
+// operand descriptors then stay warp-uniform values.  Measured on B200 (148 CTAs, back-to-back 128 x N x 32
+// kind::i8 MMAs whose operand address changes every four): a loop that only thread 0 walks issues one MMA per
+// 94 cycles whatever N; the warp-uniform loop issues one per 28 / 42 / 74 / 106 / 138 cycles for
+// N = 16 / 64 / 128 / 192 / 256, which is the tensor pipe's own rate.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred = 0;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 // ---- descriptors ----------------------------------------------------------------------------------
 // Shared-memory operand descriptor for a K-major tile whose rows are 128 bytes long and stored
 // with the 128-byte swizzle (what a TMA load with SWIZZLE_128B produces): groups of 8 rows are
@@ -216,6 +235,133 @@ __device__ __forceinline__ void mma_i8_ss(uint32_t d_tmem, uint64_t a_desc, uint
       "}" ::"r"(d_tmem),
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
+}
+
+// ---- CTA pairs (cluster of two, tcgen05 ... cta_group::2) ------------------------------------------
+// One 256 x N x 32 MMA is issued by the leader CTA (cluster rank 0) for both: each CTA holds its 128 rows of A
+// and of the accumulator in its own tensor memory and N / 2 rows of B in its own shared memory, at the same
+// offsets in both CTAs.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_id_x() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%clusterid.x;" : "=r"(r));
+  return r;
+}
+// All threads of both CTAs (every warp converged).
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Address of the same shared-memory location in CTA `rank` of the cluster (shared::cluster window).
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+// Arrive on a barrier of any CTA of the cluster (address from map_to_cta), releasing at cluster scope.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// The same with the default (CTA-scope) release: what it publishes to the peer is tensor-memory and
+// async-proxy state, which the tcgen05 fences and the barriers of the copies order, not generic-proxy stores.
+// (The cluster-scope release costs the arriving thread about 1000 cycles.)
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// Bounded wait on a barrier of this CTA whose arrivals may come from the peer CTA (acquire at cluster scope).
+__device__ __forceinline__ bool mbar_wait_bounded_cluster(uint32_t bar, uint32_t parity, uint64_t limit_ns) {
+  uint32_t ok = 0;
+#pragma unroll 1
+  for (int i = 0; i < 257 && !ok; ++i) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(4000u)
+        : "memory");
+  }
+  if (ok) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  for (;;) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if ((++spins & 0x3ffu) == 0 && globaltimer_ns() - t0 > limit_ns) return false;
+  }
+}
+// Bounded wait that polls with test_wait (never parks the thread): for barriers completed from the peer CTA
+// (a remote arrive, a multicast commit).
+__device__ __forceinline__ bool mbar_spin_bounded_cluster(uint32_t bar, uint32_t parity, uint64_t limit_ns) {
+  uint32_t ok = 0;
+  uint32_t spins = 0;
+  uint64_t t0 = 0;
+  for (;;) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if ((++spins & 0x3ffu) == 0) {
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > limit_ns) return false;
+    }
+  }
+}
+// Tensor memory of the pair: one warp of EACH CTA (the same warp index) executes these.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t result_slot_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(result_slot_smem), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// Instruction descriptor as idesc_i8 for the 256-row MMA of a CTA pair (n a multiple of 32).
+__host__ __device__ constexpr uint32_t idesc_i8_pair(int n) {
+  return (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (static_cast<uint32_t>(256 >> 4) << 24);
+}
+// D[tmem of both CTAs] (+)= A[tmem of both CTAs] * B[smem halves of both CTAs]^T; leader CTA only.
+__device__ __forceinline__ void mma_i8_ts_pair(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::i8 [%0], [%1], %2, %3, p;\n\t"
+      "}" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on the barrier at this shared-memory offset in BOTH CTAs once every MMA issued so far has completed.
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+  const uint16_t mask = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+                   bar),
+               "h"(mask)
+               : "memory");
 }
 
 }  // namespace ptx

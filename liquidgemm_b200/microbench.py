@@ -2,14 +2,17 @@
 
     python -m liquidgemm_b200.build --debug           # once: the measurement kernels, a library of their own
     python -m liquidgemm_b200.microbench mma_rate     # tcgen05.mma kind::i8 issue-to-issue cost
+    python -m liquidgemm_b200.microbench mma_rate2    # the same for cta_group::2 (CTA pairs)
     python -m liquidgemm_b200.microbench sync_cost    # mbarrier / commit / bulk-copy instruction costs
     python -m liquidgemm_b200.microbench tma_stream   # HBM streaming rate of ring-buffered bulk copies
+    python -m liquidgemm_b200.microbench l2_stream    # the same stream when the data is L2-resident
+    python -m liquidgemm_b200.microbench tma_stream2  # two producer threads with a ring each in one CTA
     python -m liquidgemm_b200.microbench tma_rows     # the same with one bulk copy per weight row
 
     python -m liquidgemm_b200.build --trace           # once: the product sources with -DLQ_PIPELINE_TRACE
     python -m liquidgemm_b200.microbench decode_trace gate_up 8   # per-CTA cycle counters of the decode kernel
 
-The first four launch measurement-only kernels (``lq_debug_*`` in ``csrc/dbg/lq_debug.cu``); none of them is
+All but the last launch measurement-only kernels (``lq_debug_*`` in ``csrc/dbg/lq_debug.cu``); none of them is
 in the product library.  ``decode_trace`` runs the real decode tensor-core kernel from the trace build and
 prints where each role's cycles go.  They need a B200; every device-side wait in them is bounded.
 """
@@ -65,6 +68,16 @@ def mma_rate(iters: int = 2000) -> None:
                 issue = float(np.median(o[:, 1])) / (iters * 4)
                 print(f"ctas={ctas:3d} {'TS' if ts else 'SS'} N={n:3d}: {cyc:7.1f} cycles/MMA (issue {issue:6.1f})"
                       f"  -> {128 * n * 32 / cyc:7.0f} MAC/clk/SM", flush=True)
+    # the issue loop walked by the whole warp with one elected lane issuing, against `if (thread 0) loop`; both
+    # with an operand address that changes from group to group, as in a real main loop
+    for mode, what in [(1, "thread 0 alone"), (9, "warp-uniform loop, elected lane")]:
+        for n in (16, 64, 128, 192, 256):
+            out = torch.zeros(148 * 2, dtype=torch.int64, device="cuda")
+            for _ in range(2):
+                assert fn(n, iters, mode, 148, out.data_ptr(), _stream()) == 0
+            torch.cuda.synchronize()
+            cyc = float(np.median(out.cpu().numpy().reshape(148, 2)[:, 0])) / (iters * 4)
+            print(f"ctas=148 TS N={n:3d} {what}: {cyc:7.1f} cycles/MMA", flush=True)
     # two accumulators taken in turn: is the floor a dependent-accumulate latency?
     for n in (16, 64, 128):
         out = torch.zeros(148 * 2, dtype=torch.int64, device="cuda")
@@ -81,6 +94,57 @@ def mma_rate(iters: int = 2000) -> None:
         torch.cuda.synchronize()
         cyc = float(np.median(out.cpu().numpy().reshape(296, 2)[:, 0])) / (iters * 4)
         print(f"ctas=296 (2 per SM) TS N={n:3d}: {cyc:7.1f} cycles/MMA per CTA", flush=True)
+
+
+def mma_rate2(iters: int = 2000) -> None:
+    """The same for tcgen05.mma.cta_group::2: one 256 x N x 32 MMA per CTA pair (128 x N per SM); then what the
+    issuing thread's other per-k-step work adds: one or two multicast commits per group of four MMAs, a wait
+    on a completed barrier with its fence."""
+    fn = lib.lq_debug_mma_rate2
+    fn.argtypes, fn.restype = [_I] * 5 + [_P, _P], _I
+
+    def run(n, ts, extra, ctas):
+        out = torch.zeros(ctas * 2, dtype=torch.int64, device="cuda")
+        for _ in range(2):
+            assert fn(n, iters, ts, extra, ctas, out.data_ptr(), _stream()) == 0
+        torch.cuda.synchronize()
+        o = out.cpu().numpy().reshape(ctas, 2)
+        return float(np.median(o[:, 0])) / (iters * 4), int(o[:, 1].sum())
+
+    for ctas in (2, 148):
+        for ts in (1, 0):
+            for n in (64, 128, 192, 256):
+                cyc, bad = run(n, ts, 0, ctas)
+                print(f"ctas={ctas:3d} pair {'TS' if ts else 'SS'} N={n:3d}: {cyc:7.1f} cycles/MMA  -> "
+                      f"{128 * n * 32 / cyc:7.0f} MAC/clk/SM  (waits that ran out: {bad})", flush=True)
+    for n in (128, 192, 256):
+        for extra, what in [(0, "four MMAs"), (1, "+ one commit"), (2, "+ two commits"), (4, "+ wait and fence"),
+                            (5, "+ one commit, wait and fence"), (6, "+ two commits, wait and fence")]:
+            cyc, bad = run(n, 1, extra, 148)
+            print(f"pair TS N={n:3d} per group: {what:32s} {4 * cyc:7.1f} cycles  (waits that ran out: {bad})", flush=True)
+
+
+def tma_stream2(total_bytes: int = 2_000_000_000) -> None:
+    """Two producer threads per CTA, each with its own ring, reading L2-resident data: is the fixed cost of a
+    bulk copy paid per issuing thread or per CTA?"""
+    fn = lib.lq_debug_tma_stream2
+    fn.argtypes, fn.restype = [_P, _I, _I, _I, _I, _I, _P, _P], _I
+    src = torch.zeros(1 << 28, dtype=torch.uint8, device="cuda")
+    cyc = torch.zeros(296, dtype=torch.int64, device="cuda")
+    for stage, ns in [(8704, 8), (16384, 5), (24576, 4), (32768, 3)]:
+        wrap = max(1, (32 << 20) // (296 * stage))
+        steps = total_bytes // (296 * stage)
+        for _ in range(2):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            assert fn(src.data_ptr(), stage, ns, steps, wrap, 148, cyc.data_ptr(), None) == 0
+            e1.record()
+            torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3
+        clk = float(np.median(cyc.cpu().numpy())) / steps
+        print(f"148 CTAs x 2 rings, stage {stage:6d} B x {ns:2d} buffers: {us:8.1f} us  "
+              f"{296 * steps * stage / us / 1e6:6.2f} TB/s  {clk:6.1f} cycles per copy per ring  "
+              f"{2 * stage / clk:5.1f} B/clk/SM", flush=True)
 
 
 def sync_cost() -> None:
@@ -115,6 +179,35 @@ def tma_stream(total_bytes: int = 400_000_000) -> None:
         nbytes = 148 * steps * stage
         print(f"stage {stage:6d} B x {ns:2d} buffers: {us:8.1f} us  {nbytes / us / 1e6:6.2f} TB/s  "
               f"cycles/stage {float(np.median(cyc.cpu().numpy())) / steps:7.1f}", flush=True)
+
+
+def l2_stream(total_bytes: int = 2_000_000_000) -> None:
+    """The bulk-copy stream out of L2: every group of `share` CTAs re-reads a region small enough that all
+    regions together stay L2-resident (what the token tiles of a prefill GEMM look like to the memory system).
+    296 CTAs are two per SM: whether the cost of a copy is paid per issuing CTA or per SM."""
+    fn = lib.lq_debug_tma_stream_l2
+    fn.argtypes, fn.restype = [_P, _I, _I, _I, _I, _I, _I, _P, _P], _I
+    src = torch.zeros(1 << 28, dtype=torch.uint8, device="cuda")
+    cyc = torch.zeros(296, dtype=torch.int64, device="cuda")
+    for stage, ns, footprint_mb, share, ctas in [
+            (32768, 5, 32, 1, 148), (32768, 5, 32, 8, 148), (16384, 10, 32, 1, 148), (24576, 6, 32, 4, 148),
+            (8704, 16, 32, 1, 148), (8704, 8, 32, 1, 296), (16384, 5, 32, 1, 296), (32768, 3, 32, 1, 296),
+            (49152, 4, 32, 1, 148), (65536, 3, 32, 1, 148), (65536, 3, 32, 8, 148), (4352, 16, 32, 1, 148)]:
+        groups = -(-ctas // share)
+        wrap = max(1, (footprint_mb << 20) // (groups * stage))
+        steps = total_bytes // (ctas * stage)
+        for _ in range(2):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            assert fn(src.data_ptr(), stage, ns, steps, wrap, share, ctas, cyc.data_ptr(), None) == 0
+            e1.record()
+            torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3
+        nbytes = ctas * steps * stage
+        clk = float(np.median(cyc[:ctas].cpu().numpy())) / steps
+        print(f"{ctas} CTAs, stage {stage:6d} B x {ns:2d} buffers, {footprint_mb:3d} MB footprint, {share} CTAs per region: "
+              f"{us:8.1f} us  {nbytes / us / 1e6:6.2f} TB/s  {clk:6.1f} cycles per copy per CTA  "
+              f"{stage / clk * (ctas / 148):5.1f} B/clk/SM", flush=True)
 
 
 def tma_rows(total_bytes: int = 400_000_000) -> None:
@@ -180,7 +273,8 @@ def decode_trace(shape: str = "gate_up", M: int = 8) -> None:
               f"max {int(c.max())}")
 
 
-_CASES = {"mma_rate": mma_rate, "sync_cost": sync_cost, "tma_stream": tma_stream, "tma_rows": tma_rows}
+_CASES = {"mma_rate": mma_rate, "mma_rate2": mma_rate2, "sync_cost": sync_cost, "tma_stream": tma_stream,
+          "l2_stream": l2_stream, "tma_stream2": tma_stream2, "tma_rows": tma_rows}
 
 if __name__ == "__main__":
     torch.cuda.set_device(0)
