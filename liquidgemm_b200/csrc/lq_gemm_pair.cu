@@ -11,9 +11,10 @@
 //
 // Work.  Tile = 256 channels x 192 tokens, pair p of P takes tiles p, p + P, ... (channel blocks fastest, so
 // the pairs of a wave share one or two token tiles and walk k in step: their weight and token lines hit in
-// L2).  The tiles of the last, partial wave are laid end to end along k and cut into equal ranges, one per
-// pair; a pair that holds only part of a tile's K adds its int32 sums into a workspace slot (exact in any
-// order) and the pair whose contribution completes the tile applies the epilogue and re-zeroes the slot.
+// L2).  The tiles of the last, partial wave are taken whole by as many pairs, or, when they are long and few,
+// cut into equal k-ranges over the pairs; a pair that holds only part of a tile's K adds its int32 sums into a
+// workspace slot (exact in any order) and the pair whose contribution completes the tile applies the epilogue
+// and re-zeroes the slot.
 //
 // Per CTA (640 threads), connected by mbarrier rings; rank = CTA's rank in its pair:
 //   warp 0        weight producer: one 8704-byte bulk copy per k-step (tile 2 * block + rank of the blob)
@@ -100,10 +101,22 @@ struct Args {
   int vec_out;             // several destinations, 2-byte outputs whose rows allow 16-byte stores: stage through smem
 };
 
-// The segments of one pair: whole tiles of the full waves, then this pair's k-range of the last partial wave.
+// Split factor of the tiles of the last, partial wave (r tiles on P pairs).  Splitting a tile along k costs every
+// participating pair a pass of int32 atomics over its 192 x 128 sums plus the completing pair's read-back, about
+// as much as 20 k-steps of the main loop: it only pays when the tile is long and at least half of the pairs
+// would otherwise idle.
+__host__ __device__ inline int tail_split(int r, int P, int kt) {
+  if (r == 0 || 2 * r > P || kt < 64) return 1;
+  int S = P / r;
+  if (S > kt / 16) S = kt / 16;
+  return S < 1 ? 1 : S;
+}
+
+// The segments of one pair: whole tiles of the full waves, then at most one unit of the last partial wave (a
+// whole tile, or one of the S equal k-ranges of a tile).
 struct PairWalk {
-  int kt, P, p, full_waves, wave;
-  unsigned u, u_end;
+  int kt, P, p, full_waves, wave, tail_units, S;
+  bool tail_done;
   __device__ PairWalk(const Args& a, int pair) {
     kt = a.kt_total;
     P = a.pairs;
@@ -111,18 +124,10 @@ struct PairWalk {
     const int tiles = a.n2_tiles * a.m_tiles;
     full_waves = tiles / P;
     wave = 0;
-    const unsigned total = (unsigned)(tiles - full_waves * P) * (unsigned)kt;
-    // ranges of at least 8 k-steps: a shorter one costs more in the slot reduction than it saves
-    unsigned parts = total / 8u;
-    parts = parts < 1u ? 1u : parts > (unsigned)P ? (unsigned)P : parts;
-    const unsigned q = total / parts, r = total - q * parts;
-    const unsigned up = (unsigned)pair;
-    if (up < parts) {
-      u = up * q + (up < r ? up : r);
-      u_end = u + q + (up < r ? 1u : 0u);
-    } else {
-      u = u_end = 0;
-    }
+    const int r = tiles - full_waves * P;
+    S = tail_split(r, P, kt);
+    tail_units = r * S;
+    tail_done = false;
   }
   __device__ bool next(Segment& s) {
     if (wave < full_waves) {
@@ -134,15 +139,14 @@ struct PairWalk {
       ++wave;
       return true;
     }
-    if (u >= u_end) return false;
-    const int rt = (int)(u / (unsigned)kt);
+    if (tail_done || p >= tail_units) return false;
+    tail_done = true;
+    const int rt = p / S, part = p - rt * S;
     s.tile = full_waves * P + rt;
-    s.kb = (int)(u - (unsigned)rt * (unsigned)kt);
-    const int left = (int)(u_end - u);
-    s.ke = (kt - s.kb) < left ? kt : s.kb + left;
-    s.whole = (s.kb == 0 && s.ke == kt);
+    s.kb = (part * kt) / S;
+    s.ke = ((part + 1) * kt) / S;
+    s.whole = (S == 1);
     s.slot = rt;
-    u += (unsigned)(s.ke - s.kb);
     return true;
   }
 };
@@ -748,14 +752,15 @@ struct PairPlan {
   int n2_tiles, m_tiles, pairs, partial_tiles;
   size_t ws_bytes;
 };
-static PairPlan plan(int M, int N) {
+static PairPlan plan(int M, int N, int K) {
   PairPlan p;
   p.n2_tiles = N / 256;
   p.m_tiles = (M + kBN - 1) / kBN;
   const long tiles = (long)p.n2_tiles * p.m_tiles;
   const int cap = max_pairs();
   p.pairs = (int)(tiles < cap ? tiles : cap);
-  p.partial_tiles = (int)(tiles % p.pairs);
+  const int r = (int)(tiles % p.pairs);
+  p.partial_tiles = tail_split(r, p.pairs, K / 128) > 1 ? r : 0;   // tiles whose K is shared between pairs
   // per partial tile and rank: 192 x 128 int32 sums; then one counter each, padded to 256 bytes
   p.ws_bytes = p.partial_tiles == 0 ? 0
                                     : (size_t)p.partial_tiles * 2 * (128 * kBN * 4) +
@@ -768,10 +773,33 @@ static PairPlan plan(int M, int N) {
 // Shapes the pair kernel serves: whole 256-channel blocks.
 bool pair_serves(int M, int N, int K) { return M >= 1 && N >= 256 && N % 256 == 0 && K >= 128 && K % 128 == 0; }
 
-size_t pair_workspace_bytes(int M, int N) { return pairk::plan(M, N).ws_bytes; }
+// Whether the pair kernel is expected to beat the two-CTAs-per-SM tile kernel on this shape.  Both run whole
+// waves of tiles, so the comparison is between (waves x k-steps x time per k-step) of either, with the times
+// per k-step measured on B200 over the Llama-3.1-8B shapes at 256..8192 tokens (microseconds: pair 0.35, or
+// 0.31 for K >= 8192, plus 6 for the prologue and the last epilogue; tile 0.58, 0.48 for K >= 8192, 0.44 when
+// there is at most one CTA per SM).  The model reproduces the measured winner at every point of that sweep
+// except ties within 5 %.
+bool pair_prefers(int M, int N, int K) {
+  if (!pair_serves(M, N, K)) return false;
+  const int kt = K / 128;
+  const int sms = sm_count();
+  const long tiles_t = (long)(N / 128) * ((M + 127) / 128);
+  if (tiles_t * 2 <= 2L * sms) return false;   // the tile kernel splits K here: a small problem, it wins
+  const double waves_t = (double)((tiles_t + 2L * sms - 1) / (2L * sms));
+  const double est_tile = waves_t * kt * (tiles_t <= sms ? 0.44 : kt >= 64 ? 0.48 : 0.58);
+  const pairk::PairPlan p = pairk::plan(M, N, K);
+  const long tiles_p = (long)p.n2_tiles * p.m_tiles;
+  const int r = (int)(tiles_p % p.pairs);
+  const int S = pairk::tail_split(r, p.pairs, kt);
+  const double tail = r == 0 ? 0.0 : S > 1 ? 1.0 / S + 20.0 / kt : 1.0;
+  const double est_pair = ((double)(tiles_p / p.pairs) + tail) * kt * (kt >= 64 ? 0.31 : 0.35) + 6.0;
+  return est_pair < 0.97 * est_tile;
+}
+
+size_t pair_workspace_bytes(int M, int N, int K) { return pairk::plan(M, N, K).ws_bytes; }
 
 // CTAs of the launch (each signals the peers once in the gather-by-stores form).
-int pair_grid(int M, int N) { return 2 * pairk::plan(M, N).pairs; }
+int pair_grid(int M, int N, int K) { return 2 * pairk::plan(M, N, K).pairs; }
 
 // out_mode: LQ_DT_* or 3 (raw int32).  `ws` (all zero on entry, all zero again on exit) holds the slots of the last partial wave.
 int run_pair_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, const void* bias,
@@ -779,7 +807,7 @@ int run_pair_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, con
                   cudaStream_t st) {
   using namespace pairk;
   if (!pair_serves(M, N, K) || out_mode < 0 || out_mode > kOutI32) return LQ_ERR_BAD_ARG;
-  const PairPlan p = plan(M, N);
+  const PairPlan p = plan(M, N, K);
   if (p.ws_bytes && (!ws || ws_bytes < p.ws_bytes)) return LQ_ERR_WORKSPACE;
   CUtensorMap tx;
   if (int rc = make_byte_matrix_map(&tx, x, M, K, kHalf, 128)) return rc;

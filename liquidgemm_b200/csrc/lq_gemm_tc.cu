@@ -68,8 +68,9 @@ int run_gemv_blob_ws(const int8_t* x, const uint8_t* blob, const float* ascale, 
                      size_t ws_bytes, cudaStream_t st);  // lq_gemv_blob.cu
 int decode_tc_grid(int N, int K);                                            // lq_decode_tc.cu
 bool pair_serves(int M, int N, int K);                                       // lq_gemm_pair.cu
-size_t pair_workspace_bytes(int M, int N);                                   // lq_gemm_pair.cu
-int pair_grid(int M, int N);                                                 // lq_gemm_pair.cu
+bool pair_prefers(int M, int N, int K);                                      // lq_gemm_pair.cu
+size_t pair_workspace_bytes(int M, int N, int K);                                // lq_gemm_pair.cu
+int pair_grid(int M, int N, int K);                                              // lq_gemm_pair.cu
 int run_pair_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, const void* bias,
                   const OutSpec& out, const PeerSync* sync, int out_mode, int M, int N, int K, void* ws, size_t ws_bytes,
                   cudaStream_t st);  // lq_gemm_pair.cu
@@ -689,9 +690,10 @@ struct Route {
   RouteKind kind;
   int splits;
 };
-// Up to this many tokens the dp4a streaming GEMV over the blob beats the tensor-core kernels (measured on
-// the Llama-3.1-8B shapes: its integer pipe is full at four tokens on the small matrices and at three on the
-// large one); it only produces scaled outputs, the int32 entry point always uses tensor cores.
+// The dp4a streaming GEMV over the blob serves one and two tokens, and three or four on matrices up to 16 M
+// weights (measured on the Llama-3.1-8B shapes against the tensor-core decode kernel: 4096 x 4096 5.2 vs 5.7 us
+// at three tokens; 6144 x 4096 equal; 4096 x 14336 11.2 vs 10.5 us); it only produces scaled outputs, the
+// int32 entry point always uses tensor cores.
 constexpr int kGemvBlobMaxM = 4;
 
 // Largest decode batch of the single-launch streaming tensor-core kernel: its one-atomic-per-element
@@ -706,8 +708,8 @@ static int decode_tc_max_m() {
   return v;
 }
 
-// From this many tokens on, shapes with whole 256-channel blocks go to the CTA-pair kernel (LQ_PAIR_MIN_M moves
-// the limit for measurements; 0 switches the kernel off).
+// From this many tokens on, shapes with whole 256-channel blocks go to the CTA-pair kernel where it is expected
+// to win (pair_prefers).  LQ_PAIR_MIN_M moves the limit for measurements; 0 switches the kernel off.
 static int pair_min_m() {
   static const int v = []() {
     const char* e = getenv("LQ_PAIR_MIN_M");
@@ -717,8 +719,19 @@ static int pair_min_m() {
   return v;
 }
 
+// LQ_PAIR_ALWAYS=1: every shape the pair kernel serves goes to it (tests and measurements).
+static bool pair_forced() {   // read at every call: a test sets and clears it inside one process
+  const char* e = getenv("LQ_PAIR_ALWAYS");
+  return e && atoi(e) != 0;
+}
+
 static bool gemv_serves(int M, int N, int K) {
-  return M <= 2 || (M <= kGemvBlobMaxM && (long)N * K <= (1L << 26));
+  static const int cap = []() {   // LQ_GEMV_MAX_M (0..4) lowers the limit for measurements
+    const char* e = getenv("LQ_GEMV_MAX_M");
+    return e ? atoi(e) : kGemvBlobMaxM;
+  }();
+  if (M > cap) return false;
+  return M <= 2 || (M <= kGemvBlobMaxM && (long)N * K <= (1L << 24));
 }
 
 static Route route_for(int M, int N, int K, int splitk, bool scaled) {
@@ -737,7 +750,7 @@ static Route route_for(int M, int N, int K, int splitk, bool scaled) {
   // of the persistent stream-K kernel at every size measured (M = 256: 2x, M = 2048: 1.1-1.3x, M = 16384 on
   // 28672 x 4096: 1.13x); the persistent kernel stays reachable through an explicit split argument.
   if (splitk == 0) {
-    if (M >= pair_min_m() && pair_serves(M, N, K)) return {kRoutePair, 0};
+    if (M >= pair_min_m() && (pair_forced() ? pair_serves(M, N, K) : pair_prefers(M, N, K))) return {kRoutePair, 0};
     return {kRouteTile, tile_pick_splits(M, N, K)};
   }
   return {kRoutePersistent, splitk};
@@ -748,7 +761,7 @@ static size_t route_ws_bytes(const Route& r, int M, int N, int K) {
     case kRouteGemv: return gemv_blob_workspace_bytes(N, K);
     case kRouteDecodeTc: return decode_tc_workspace_bytes(M, N, K);
     case kRouteTile: return tile_workspace_bytes(M, N, r.splits);
-    case kRoutePair: return pair_workspace_bytes(M, N);
+    case kRoutePair: return pair_workspace_bytes(M, N, K);
     default: return make_plan(M, N, K, r.splits).ws_bytes;
   }
 }
@@ -886,7 +899,7 @@ int lq_decode_grid(int M, int N, int K) {
   switch (r.kind) {
     case kRouteGemv: return gemv_blob_grid(N, K);
     case kRouteDecodeTc: return decode_tc_grid(N, K);
-    case kRoutePair: return pair_grid(M, N);
+    case kRoutePair: return pair_grid(M, N, K);
     default: return tile_output_grid(M, N, K, r.splits);
   }
 }

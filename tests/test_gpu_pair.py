@@ -1,7 +1,6 @@
 """The CTA-pair prefill kernel (tcgen05.mma.cta_group::2, 256 channels x 192 tokens per tile) against the CPU
-oracle, through the reference's operators: the automatic dispatch sends 256 tokens and more to it whenever the
-layer has whole 256-channel blocks.  Cases cover a single tile, ragged token counts, several waves of tiles, the
-last partial wave (split along k, summed through the workspace slots), every output type, the bias and the
+oracle, through the reference's operators (256 tokens and more, layers with whole 256-channel blocks).  Cases cover a single tile, ragged token counts, several waves of tiles, the
+last partial wave (whole tiles, or long tiles split along k and summed through the workspace slots), every output type, the bias and the
 multi-destination epilogue; full benchmark sizes are compared with cuBLASLt's exact INT8 GEMM."""
 
 import numpy as np
@@ -21,12 +20,19 @@ def ops():
     return _ops
 
 
+@pytest.fixture(autouse=True)
+def _every_served_shape_takes_the_pair_kernel(monkeypatch):
+    """The automatic dispatch sends a shape to the pair kernel only where it expects it to beat the tile kernel
+    (large problems); the library reads this switch at every call, so the small cases below run on it too."""
+    monkeypatch.setenv("LQ_PAIR_ALWAYS", "1")
+
+
 def _acc(x, qw):
     return O.int_accumulate(x, O.dequantize_i8(qw))
 
 
 # (M, N, K): one tile; ragged tokens; K with an odd number of k-steps; two full waves and a partial one
-# (2 x 80 tiles on 74 pairs); a partial wave whose tiles are cut along k between several pairs
+# (2 x 80 tiles on 74 pairs); one tile more than a wave
 CASES = [(256, 256, 128), (257, 512, 1024), (383, 256, 2176), (385, 768, 512), (7680, 512, 512), (1000, 2560, 1536),
          (14400, 256, 384)]
 
@@ -73,19 +79,25 @@ def test_bias_is_added_to_the_rounded_output(ops, out_dtype):
     ops.poll_status()
 
 
-def test_two_calls_leave_the_workspace_clean(ops):
-    """The slots of the partial wave are re-zeroed by the pair that completes a tile: a second call on the same
-    cached workspace gives the same bits, and so does a decode call (which shares that workspace) afterwards."""
-    M, N, K = 7680, 512, 512
+def test_split_tail_and_clean_workspace(ops):
+    """80 long tiles on 74 pairs: the six tiles of the last wave are cut along k between the pairs and summed
+    through the workspace slots, which the completing pair re-zeroes: a second call on the same cached workspace
+    gives the same bits, and so does a decode call (which shares that workspace) afterwards."""
+    M, N, K = 15360, 256, 8192
     qw = random_lqq(N, K, 64, seed=21)
     tq = to_torch_qw(qw)
     x, ascale = random_tokens(M, K, seed=5)
     xt, at = torch.from_numpy(x).cuda(), torch.from_numpy(ascale).cuda()
     w = ops.repack_rs_weight(tq)
+    ref = torch._int_mm(xt, ops.dequant_weight_i8(tq).t())
+    acc = torch.ops.liquidgemm.w4a8_wgmma_rs(xt, w, tq.s_u8, tq.s_u8, tq.offset_a, N, K, 64, True)
+    assert torch.equal(acc, ref)
+    want = torch.ops.liquidgemm.scale_epilogue(ref, at, tq.s1, 0)
     y1 = torch.ops.liquidgemm.w4a8_wgmma_rs_fused(xt, w, tq.s_u8, tq.offset_a, at, tq.s1, N, K, 64, 0)
     y2 = torch.ops.liquidgemm.w4a8_wgmma_rs_fused(xt, w, tq.s_u8, tq.offset_a, at, tq.s1, N, K, 64, 0)
-    assert torch.equal(y1, y2)
-    assert_bits_equal(y1[:32], O.w4a8_matmul(x[:32], ascale[:32], qw), 0, "first rows")
+    assert torch.equal(y1, want) and torch.equal(y2, want)
+    for rows in (slice(0, 16), slice(M - 16, M)):      # first tile and a tile of the split wave against the CPU oracle
+        assert_bits_equal(y1[rows], O.w4a8_matmul(x[rows], ascale[rows], qw), 0, "rows against the oracle")
     y8 = torch.ops.liquidgemm.w4a8_wgmma_rs_fused(xt[:8].contiguous(), w, tq.s_u8, tq.offset_a, at[:8].contiguous(), tq.s1,
                                                   N, K, 64, 0)
     assert_bits_equal(y8, O.w4a8_matmul(x[:8], ascale[:8], qw), 0, "decode call after the pair kernel")
