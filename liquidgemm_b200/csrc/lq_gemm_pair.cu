@@ -791,7 +791,7 @@ bool pair_prefers(int M, int N, int K) {
   const long tiles_p = (long)p.n2_tiles * p.m_tiles;
   const int r = (int)(tiles_p % p.pairs);
   const int S = pairk::tail_split(r, p.pairs, kt);
-  const double tail = r == 0 ? 0.0 : S > 1 ? 1.0 / S + 20.0 / kt : 1.0;
+  const double tail = r == 0 ? 0.0 : S > 1 ? 1.0 / S + 40.0 / kt : 1.0;   // a split tile costs its reduction too
   const double est_pair = ((double)(tiles_p / p.pairs) + tail) * kt * (kt >= 64 ? 0.31 : 0.35) + 6.0;
   return est_pair < 0.97 * est_tile;
 }
