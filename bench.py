@@ -482,7 +482,10 @@ def main():
                        "summary": summary},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_RATIO * abytes,
-                         "of": peaks["source"], "kernel": "w4a8_decode_tc_kernel (M = 8, 16; gate_up at M = 4) + gemv_blob_kernel (M = 1, 4): the 12-op sweep, one launch per linear",
+                         "of": peaks["source"], "traffic_source": f"ncu DRAM bytes / algorithmic bytes = {NCU_TRAFFIC_RATIO} on single launches "
+                                           "(profiles/decode_kernels_ncu_full.md) x this step's algorithmic bytes",
+                         "kernel": "w4a8_tile_kernel (gate_up and down at M = 4, 8, 16; down with finish_kernel), "
+                                   "w4a8_decode_tc_kernel (qkv at M = 4, 8, 16), gemv_blob_kernel (M = 1): the 12-op sweep",
                          "algorithmic_bytes_per_step": abytes},
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": UNIT,

@@ -740,7 +740,10 @@ static Route route_for(int M, int N, int K, int splitk, bool scaled) {
   if (M <= 128) {
     if (splitk == 0) {
       if (scaled && gemv_serves(M, N, K)) return {kRouteGemv, 0};
-      if (M <= decode_tc_max_m()) return {kRouteDecodeTc, 0};
+      // Small matrices (up to 32 M weights) only: on larger ones the tile kernel's whole tiles (or its planes
+      // and finish pass) are ahead since the MMA issue became cheap (28672 x 4096 at 8 tokens: 14.7 vs 16.7 us,
+      // 4096 x 14336: 10.4 vs 10.8 us; 6144 x 4096: 7.3 vs 7.0 us, 4096 x 4096: 6.6 vs 6.0 us).
+      if (M <= decode_tc_max_m() && (long)N * K <= (1L << 25)) return {kRouteDecodeTc, 0};
     }
     int S = splitk > 0 ? splitk : tile_pick_splits(M, N, K);
     if (S > kt) S = kt;
