@@ -523,7 +523,7 @@ mma_rate2_kernel(int n, int iters, int a_in_tmem, int extra, long long* out) {
     ptx::fence_mbar_init();
     ptx::mbar_arrive(smem_u32(&side_bar[2]));   // phase 0 of [2] is complete
   }
-  for (int i = threadIdx.x; i < (16384 + 16384) / 4; i += blockDim.x)
+  for (int i = threadIdx.x; i < (1024 + 16384 + 16384) / 4; i += blockDim.x)
     reinterpret_cast<uint32_t*>(smem_raw + (base - raw_addr))[i] = 0x01020304u * (i + 1);
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   if (threadIdx.x < 32) {
@@ -536,40 +536,38 @@ mma_rate2_kernel(int n, int iters, int a_in_tmem, int extra, long long* out) {
   ptx::tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
   long long t0 = clock64();
-  if (rank == 0 && threadIdx.x == 0) {
-    const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((256u >> 4) << 24);
+  if (rank == 0 && threadIdx.x < 32) {
+    // the whole warp walks the loop, one elected lane issues (see ptx::elect_one)
+    const bool leader = ptx::elect_one();
+    const uint32_t idesc = ptx::idesc_i8_pair(n);
     t0 = clock64();
     for (int i = 0; i < iters; ++i) {
+      const uint32_t sbase = base + (uint32_t)(i & 1) * 1024u;   // a stage-dependent operand address
+      if (leader) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const uint64_t bdesc = ptx::smem_desc_sw128(base + j * 32);
-        if (a_in_tmem) {
-          asm volatile(
-              "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-              "tcgen05.mma.cta_group::2.kind::i8 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_base),
-              "r"(tmem_base + 256u + j * 8), "l"(bdesc), "r"(idesc), "r"(1u)
-              : "memory");
-        } else {
-          const uint64_t adesc = ptx::smem_desc_sw128(base + 16384 + j * 32);
-          asm volatile(
-              "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-              "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_base),
-              "l"(adesc), "l"(bdesc), "r"(idesc), "r"(1u)
-              : "memory");
+        for (int j = 0; j < 4; ++j) {
+          const uint64_t bdesc = ptx::smem_desc_sw128(sbase + j * 32);
+          if (a_in_tmem) {
+            ptx::mma_i8_ts_pair(tmem_base, tmem_base + 256u + j * 8, bdesc, idesc, 1u);
+          } else {
+            const uint64_t adesc = ptx::smem_desc_sw128(sbase + 16384 + j * 32);
+            asm volatile(
+                "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_base),
+                "l"(adesc), "l"(bdesc), "r"(idesc), "r"(1u)
+                : "memory");
+          }
         }
+        if (extra & 3) ptx::tc_commit_pair(smem_u32(&side_bar[0]));
+        if (extra & 2) ptx::tc_commit_pair(smem_u32(&side_bar[1]));
       }
-      if (extra & 3) ptx::tc_commit_pair(smem_u32(&side_bar[0]));
-      if (extra & 2) ptx::tc_commit_pair(smem_u32(&side_bar[1]));
       if (extra & 4) {
         ptx::mbar_wait_bounded(smem_u32(&side_bar[2]), 0u, 1000000ull);
         ptx::tc_fence_after();
       }
+      __syncwarp();
     }
-    const uint16_t mask = 3;
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
-                     bar_addr),
-                 "h"(mask)
-                 : "memory");
+    if (leader) ptx::tc_commit_pair(bar_addr);
   }
   if (threadIdx.x == 0) {
     const bool ok = ptx::mbar_wait_bounded(bar_addr, 0u, 2000000000ull);
@@ -588,7 +586,7 @@ mma_rate2_kernel(int n, int iters, int a_in_tmem, int extra, long long* out) {
 extern "C" LQ_API int lq_debug_mma_rate2(int n, int iters, int a_in_tmem, int extra, int ctas, long long* out,
                                          void* stream) {
   if (n < 32 || n > 256 || n % 32 || iters <= 0 || ctas <= 0 || (ctas & 1) || !out) return LQ_ERR_BAD_ARG;
-  const int smem = 1024 + 16384 + 16384;
+  const int smem = 2048 + 16384 + 16384;
   cudaFuncSetAttribute(lq::mma_rate2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   lq::mma_rate2_kernel<<<ctas, 128, smem, lq::as_stream(stream)>>>(n, iters, a_in_tmem, extra, out);
   return lq::check_launch("mma_rate2_kernel");

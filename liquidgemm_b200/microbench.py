@@ -11,10 +11,11 @@
 
     python -m liquidgemm_b200.build --trace           # once: the product sources with -DLQ_PIPELINE_TRACE
     python -m liquidgemm_b200.microbench decode_trace gate_up 8   # per-CTA cycle counters of the decode kernel
+    python -m liquidgemm_b200.microbench pair_trace gate_up 8192  # the same for the CTA-pair prefill kernel
 
 All but the last launch measurement-only kernels (``lq_debug_*`` in ``csrc/dbg/lq_debug.cu``); none of them is
-in the product library.  ``decode_trace`` runs the real decode tensor-core kernel from the trace build and
-prints where each role's cycles go.  They need a B200; every device-side wait in them is bounded.
+in the product library.  ``decode_trace`` and ``pair_trace`` run the real decode tensor-core kernel and the CTA-pair prefill kernel
+from the trace build and print where each role's cycles go.  They need a B200; every device-side wait in them is bounded.
 """
 
 from __future__ import annotations
@@ -273,13 +274,59 @@ def decode_trace(shape: str = "gate_up", M: int = 8) -> None:
               f"max {int(c.max())}")
 
 
+def pair_trace(shape: str = "gate_up", M: int = 8192) -> None:
+    """Per-CTA cycle counters of ``w4a8_pair_kernel`` (trace build of the library) on one Llama-3.1-8B shape:
+    median / min / max over the CTAs of either rank of the last launch.  Counters are sums over the k-steps
+    (or tiles) a role handled; divide by the k-steps the MMA warp reports."""
+    if os.environ.get("LIQUIDGEMM_B200_TRACE") != "1":
+        import subprocess
+        env = dict(os.environ, LIQUIDGEMM_B200_TRACE="1", LQ_PAIR_ALWAYS="1")
+        sys.exit(subprocess.call([sys.executable, "-m", "liquidgemm_b200.microbench", "pair_trace", shape, str(M)],
+                                 env=env))
+    from . import benchlib as B
+    from ._lib import lib as plib
+    N, K = B.SHAPES[shape]
+    layer = B.device_lqq(N, K, seed=1, want_gp=False)
+    x, sc = B.device_tokens(M, K, seed=M)
+    for _ in range(3):
+        B.linear_call(layer, x, sc, M)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    B.linear_call(layer, x, sc, M)
+    e1.record()
+    torch.cuda.synchronize()
+    buf = (ctypes.c_longlong * (256 * 32))()
+    plib.lq_debug_read_pair_trace.argtypes = [ctypes.c_void_p]
+    assert plib.lq_debug_read_pair_trace(buf) == 0
+    a = np.frombuffer(buf, dtype=np.int64).reshape(256, 32)[:plib.lq_decode_grid(M, N, K)]
+    names = {0: "weight producer: waiting for a free stage", 1: "weight producer: whole loop",
+             2: "token producer: waiting for a free stage", 3: "token producer: whole loop",
+             4: "MMA warp: waiting for a free accumulator", 5: "MMA warp: waiting for operands",
+             6: "MMA warp: issuing 4 MMAs", 7: "MMA warp: commits", 8: "MMA warp: whole loop", 9: "MMA warp: k-steps",
+             10: "dequant thread: waiting for the stage", 11: "dequant thread: shared loads + unpack",
+             12: "dequant thread: waiting for the operand stage", 13: "dequant thread: tcgen05.st + wait::st + arrive",
+             14: "dequant thread: whole role", 16: "epilogue thread: waiting for an accumulator",
+             19: "epilogue thread: token scales + barrier", 21: "epilogue thread: tcgen05.ld, convert, store",
+             17: "epilogue thread: whole role", 18: "epilogue thread: tiles"}
+    print(f"{shape} {N}x{K}, M = {M}: {e0.elapsed_time(e1) * 1e3:.1f} us (trace build), {len(a)} CTAs; cycles per CTA")
+    for rank in (0, 1):
+        rows = a[rank::2]
+        print(f"rank {rank} of the pair")
+        for slot, label in names.items():
+            col = rows[:, slot]
+            if col.any():
+                print(f"  {label:48s} median {int(np.median(col)):9d}   min {int(col.min()):9d}   max {int(col.max()):9d}")
+
+
 _CASES = {"mma_rate": mma_rate, "mma_rate2": mma_rate2, "sync_cost": sync_cost, "tma_stream": tma_stream,
           "l2_stream": l2_stream, "tma_stream2": tma_stream2, "tma_rows": tma_rows}
 
 if __name__ == "__main__":
     torch.cuda.set_device(0)
-    if len(sys.argv) > 1 and sys.argv[1] == "decode_trace":
-        decode_trace(*(sys.argv[2:3] or ["gate_up"]), *(int(v) for v in sys.argv[3:4]))
+    if len(sys.argv) > 1 and sys.argv[1] in ("decode_trace", "pair_trace"):
+        fn = decode_trace if sys.argv[1] == "decode_trace" else pair_trace
+        fn(*(sys.argv[2:3] or ["gate_up"]), *(int(v) for v in sys.argv[3:4]))
         sys.exit(0)
     which = sys.argv[1:] or list(_CASES)
     for name in which:
