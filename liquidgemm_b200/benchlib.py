@@ -159,6 +159,19 @@ def _symmetric_outputs(world, M, names):
         return None
 
 
+def _symmetric_flags(words):
+    """A uint32 flag array in symmetric memory (every rank's kernels can add to every rank's words).  Returns
+    (tensor, handle) or None."""
+    import torch.distributed as dist
+    try:
+        import torch.distributed._symmetric_memory as symm_mem
+        t = symm_mem.empty(max(words, 64), dtype=torch.int32, device=torch.device("cuda", torch.cuda.current_device()))
+        t.zero_()
+        return t, symm_mem.rendezvous(t, dist.group.WORLD.group_name)
+    except Exception:
+        return None
+
+
 def run_tp70b(world, rank, Ms=(1, 64, 2048), layers_in_stack=80, distinct_layers=3):
     """80-layer stack of the four 70B-shape linears, each column-sharded along N over `world` ranks, timed
     (CUDA events around graph replays, max over ranks) in up to four ways:
@@ -170,7 +183,14 @@ def run_tp70b(world, rank, Ms=(1, 64, 2048), layers_in_stack=80, distinct_layers
     * ``stores``        gather by stores: the linear's own epilogue writes its slice into every rank's
                         full-width output over NVLink (plain peer stores into symmetric memory), and the
                         ranks are ordered ONCE PER LAYER by a symmetric-memory barrier on the stream, i.e.
-                        the four outputs of a layer are complete on every rank when the next layer starts.
+                        the four outputs of a layer are complete on every rank when the next layer starts;
+    * ``stores_flags``  the same stores ordered by the kernels' own flags instead of a barrier per layer: every
+                        writing CTA of layer l adds 1 to word l of every rank's flag array after its last store,
+                        and the first linear of layer l + 1 waits (bounded) until its own word l has reached the
+                        number of writing CTAs of all ranks before it reads its tokens.  Outputs alternate
+                        between two sets of buffers by layer parity (a rank starts the stores of layer l + 2 only
+                        after every rank has finished the kernels of layer l + 1, which are the readers of layer
+                        l's buffers); the flags are cleared, between two barriers, once per stack.
 
     On one rank the unsharded stack is ``single_gpu_ms``; with more ranks every rank also times that
     unsharded stack on its own GPU, so that the strong-scaling efficiency t1 / (N * tN) of each mode comes
@@ -192,16 +212,32 @@ def run_tp70b(world, rank, Ms=(1, 64, 2048), layers_in_stack=80, distinct_layers
         gathered = {n: torch.empty((world * M, SHAPES_70B[n][0] // world), dtype=torch.bfloat16, device="cuda")
                     for n in names} if world > 1 else None
         symm = _symmetric_outputs(world, M, names) if world > 1 else None
+        symm2 = _symmetric_outputs(world, M, names) if symm is not None else None
+        flags = _symmetric_flags(layers_in_stack) if symm2 is not None else None
+        layer_ctas = world * sum(ops.decode_grid(M, SHAPES_70B[n][0] // world, SHAPES_70B[n][1]) for n in names) \
+            if flags is not None else 0
         comm = torch.cuda.Stream() if world > 1 else None
 
         def one_stack(mode):
             lays = full_stack if mode == "single" else stack
             done = []
+            if mode == "stores_flags":
+                symm[names[0]][1].barrier(channel=1)    # every rank is done with the previous stack's flags
+                flags[0].zero_()
+                symm[names[0]][1].barrier(channel=1)    # every rank's flags are clear before anyone signals
             for l in range(layers_in_stack):
                 lay = lays[l % distinct_layers]
-                for n in names:
+                for i, n in enumerate(names):
                     L = lay[n]
-                    if mode == "stores":
+                    if mode == "stores_flags":
+                        full, hdl = (symm if (layers_in_stack - 1 - l) % 2 == 0 else symm2)[n]   # the last layer writes `symm`
+                        first = i == 0 and l > 0
+                        ops.gemm_fused_scatter(toks[n][0], L["rs"], toks[n][1], L["s1"], hdl.buffer_ptrs, full.shape[1],
+                                               rank * L["N"], L["N"], L["K"], 0, flag_ptrs=flags[1].buffer_ptrs,
+                                               flag_index=l,
+                                               wait_ptr=(flags[0].data_ptr() + 4 * (l - 1)) if first else None,
+                                               wait_value=layer_ctas if first else 0)
+                    elif mode == "stores":
                         full, hdl = symm[n]
                         ops.gemm_fused_scatter(toks[n][0], L["rs"], toks[n][1], L["s1"], hdl.buffer_ptrs, full.shape[1],
                                                rank * L["N"], L["N"], L["K"], 0)
@@ -221,13 +257,15 @@ def run_tp70b(world, rank, Ms=(1, 64, 2048), layers_in_stack=80, distinct_layers
                                 done.pop(0)
                 if mode == "stores":
                     symm[names[0]][1].barrier(channel=0)   # one ordering point per layer
+            if mode == "stores_flags":
+                symm[names[0]][1].barrier(channel=1)    # the last layer's outputs are complete everywhere
             if mode == "nccl_overlap":
                 torch.cuda.current_stream().wait_stream(comm)
 
         res = {"M": M}
         modes = (["no_gather"] if world > 1 else ["single"]) + \
                 (["nccl"] if world > 1 else []) + (["nccl_overlap"] if world > 1 and M >= 512 else []) + \
-                (["stores"] if symm is not None else []) + \
+                (["stores"] if symm is not None else []) + (["stores_flags"] if flags is not None else []) + \
                 (["single"] if world > 1 else [])
         for mode in modes:
             s = torch.cuda.Stream()
@@ -265,7 +303,7 @@ def run_tp70b(world, rank, Ms=(1, 64, 2048), layers_in_stack=80, distinct_layers
                 res[mode + "_graph"] = False
         if world > 1:
             t1 = res["single_ms"]
-            for mode in ("no_gather", "nccl", "nccl_overlap", "stores"):
+            for mode in ("no_gather", "nccl", "nccl_overlap", "stores", "stores_flags"):
                 if mode + "_ms" in res:
                     res[mode + "_eff"] = round(t1 / (world * res[mode + "_ms"]), 3)
         if symm is not None:
@@ -278,8 +316,17 @@ def run_tp70b(world, rank, Ms=(1, 64, 2048), layers_in_stack=80, distinct_layers
                 dist.all_gather(parts, y)
                 ok = ok and torch.equal(torch.cat(parts, dim=1), symm[n][0])
             res["stores_match_nccl"] = bool(ok)
+            if flags is not None:
+                # the flag-ordered stack ran last (its final layer's outputs are what was just compared with NCCL):
+                # every layer's flag word holds exactly the writing CTAs of all ranks, no bounded wait ran out
+                ok2 = bool((flags[0][:layers_in_stack] == layer_ctas).all())
+                try:
+                    ops.poll_status()
+                except Exception:
+                    ok2 = False
+                res["stores_flags_ok"] = bool(ok2)
         rows.append(res)
-        del symm, gathered
+        del symm, symm2, flags, gathered
         torch.cuda.empty_cache()
     return rows
 
