@@ -489,6 +489,9 @@ int run_tile_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, con
     mop = &mo;
   }
   switch (bn) {
+    // 16 tokens: 8 stages, 4 operand stages (95 KB, two CTAs per SM).  Five stages and two operand stages, so
+    // that three CTAs fit an SM and the next launch's CTAs can start beside this one's, measured 30 % slower
+    // on 28672 x 4096 (19.2 vs 14.8 us) and 9 % slower on 4096 x 14336.
     case 16: rc = launch_cfg<16, 8, 4, true>(tx, a, mop, splits, st); break;
     case 32: rc = launch_cfg<32, 8, 4, true>(tx, a, mop, splits, st); break;
     case 64: rc = launch_cfg<64, 6, 4, true>(tx, a, mop, splits, st); break;
