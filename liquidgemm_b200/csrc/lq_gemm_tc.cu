@@ -690,10 +690,11 @@ struct Route {
   RouteKind kind;
   int splits;
 };
-// The dp4a streaming GEMV over the blob serves one and two tokens, and three or four on matrices up to 16 M
-// weights (measured on the Llama-3.1-8B shapes against the tensor-core decode kernel: 4096 x 4096 5.2 vs 5.7 us
-// at three tokens; 6144 x 4096 equal; 4096 x 14336 11.2 vs 10.5 us); it only produces scaled outputs, the
-// int32 entry point always uses tensor cores.
+// The dp4a streaming GEMV over the blob serves one token, two on matrices up to 64 M weights (28672 x 4096 at two
+// tokens: 15.7 us against the tile kernel's 14.8) and three or four on matrices up to 16 M weights (measured on
+// the Llama-3.1-8B shapes against the tensor-core decode kernel: 4096 x 4096 5.2 vs 5.7 us at three tokens;
+// 6144 x 4096 equal; 4096 x 14336 11.2 vs 10.5 us); it only produces scaled outputs, the int32 entry point always
+// uses tensor cores.
 constexpr int kGemvBlobMaxM = 4;
 
 // Largest decode batch of the single-launch streaming tensor-core kernel: its one-atomic-per-element
@@ -731,7 +732,8 @@ static bool gemv_serves(int M, int N, int K) {
     return e ? atoi(e) : kGemvBlobMaxM;
   }();
   if (M > cap) return false;
-  return M <= 2 || (M <= kGemvBlobMaxM && (long)N * K <= (1L << 24));
+  const long w = (long)N * K;
+  return M == 1 || (M == 2 && w <= (1L << 26)) || (M <= kGemvBlobMaxM && w <= (1L << 24));
 }
 
 static Route route_for(int M, int N, int K, int splitk, bool scaled) {
