@@ -16,17 +16,18 @@
 // workspace slot (exact in any order) and the pair whose contribution completes the tile applies the epilogue
 // and re-zeroes the slot.
 //
-// Per CTA (640 threads), connected by mbarrier rings; rank = CTA's rank in its pair:
+// Per CTA (768 threads), connected by mbarrier rings; rank = CTA's rank in its pair:
 //   warp 0        weight producer: one 8704-byte bulk copy per k-step (tile 2 * block + rank of the blob)
 //   warp 2        token producer: one 96-row x 128-byte tensor-map box per k-step (rows 96 * rank ...)
 //   warp 1        tensor-memory allocation; on rank 0 it issues (one elected lane) four 256 x 192 x 32 MMAs per k-step
 //                 (A from the tensor memory of both CTAs, B from the shared memory of both) and commits to the
 //                 barriers of BOTH CTAs (stage free, operand free, accumulator full)
-//   warps 8..15   two dequant sets taking alternate k-steps: thread r owns weight row r of its CTA's tile,
+//   warps 8..19   three dequant sets taking the k-steps in turn (two measured 3-4 % slower: a set spends half of
+//                 its k-step in the tensor-memory store and its wait): thread r owns weight row r of its CTA's tile,
 //                 unpacks 128 INT8 into tensor-memory lane r, then arrives on rank 0's "operand ready"
 //                 barrier (one arrival per warp, both CTAs)
 //   warps 4..7,   epilogue of the CTA's 128 channels, two groups sharing every tile's token chunks: tcgen05.ld,
-//   16..19        scale, optional bias, stores (straight to global memory for one destination, staged through
+//   20..23        scale, optional bias, stores (straight to global memory for one destination, staged through
 //                 shared memory as 16-byte stores for several), while the MMAs of the next tile fill the other
 //                 accumulator; every warp arrives on rank 0's "accumulator free" barrier
 // Tensor memory (512 columns per CTA): two 192-column accumulators + four 32-column operand stages.
@@ -52,7 +53,8 @@ namespace pairk {
 constexpr int kTileBytes = 8704;
 constexpr int kBN = 192;                 // tokens per tile
 constexpr int kHalf = kBN / 2;           // token rows staged by each CTA
-constexpr int kThreads = 640;            // 20 warps: see the role list above
+constexpr int kSets = 3;                 // dequant sets of four warps, taking the k-steps in turn
+constexpr int kThreads = 256 + 128 * kSets + 128;   // 24 warps: see the role list above
 constexpr int kNS = 9;                   // shared-memory stages (weights + token half)
 constexpr int kNT = 4;                   // operand stages in tensor memory
 constexpr int kXStage = kHalf * 128;     // 12288
@@ -382,9 +384,9 @@ w4a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args,
         TR_SET(9, tr_steps);
       }
     }
-  } else if (warp >= 8 && warp < 16) {
-    // ------------------------------------------------------------------ dequant (two sets, alternate k-steps)
-    const int my_set = warp < 12 ? 0 : 1;
+  } else if (warp >= 8 && warp < 8 + 4 * kSets) {
+    // ------------------------------------------------------------------ dequant (kSets sets, k-steps in turn)
+    const int my_set = (warp - 8) >> 2;
     int step_set = 0;
     const int quad = warp & 3;               // TMEM lane quadrant this warp may access
     const int row = quad * 32 + lane;        // weight row inside the CTA's tile == TMEM lane
@@ -402,7 +404,7 @@ w4a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args,
     while (ok && walk.next(sg)) {
       for (int kt = sg.kb; kt < sg.ke; ++kt) {
         const bool mine = step_set == my_set;
-        step_set ^= 1;
+        step_set = step_set + 1 == kSets ? 0 : step_set + 1;
         if (!mine) {
           ring.advance();
           tring.advance();
@@ -478,11 +480,11 @@ w4a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args,
       TR_SET(14, TR_NOW() - tr_d0);
     }
   } else if (warp >= 4) {
-    // ------------------------------------------------------------------ epilogue (warps 4..7 and 16..19)
+    // ------------------------------------------------------------------ epilogue (warps 4..7 and 20..23)
     // Two groups of four warps share every tile: group g takes the 16-token chunks g, g + 2, ...  (One warp
     // converting and storing runs at a fraction of an instruction per cycle; the tile's 192 x 128 outputs need
     // eight of them to finish inside the next tile's main loop.)
-    const int g = warp >= 16 ? 1 : 0;
+    const int g = warp >= 8 + 4 * kSets ? 1 : 0;
     const int quad = warp & 3;
     const int row = quad * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
