@@ -43,6 +43,19 @@ constexpr int kThreads = 64 + 128 * kSets;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 constexpr int kOutI32 = 3;
 
+// Pipeline studies (-DLQ_PIPELINE_TRACE, a build of its own): %globaltimer stamps of every CTA's milestones, read
+// back with lq_debug_read_tile_trace().  The product build compiles none of it.
+#ifdef LQ_PIPELINE_TRACE
+__device__ long long g_trace[1024 * 8];
+#define TT_STAMP(slot)                                                                              \
+  do {                                                                                              \
+    const unsigned cta_ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);           \
+    if (cta_ < 1024u) g_trace[cta_ * 8 + (slot)] = (long long)ptx::globaltimer_ns();               \
+  } while (0)
+#else
+#define TT_STAMP(slot) ((void)0)
+#endif
+
 struct GemmArgs {
   const uint8_t* blob;   // W4: tile blob
   const float* ascale;   // [M]
@@ -112,6 +125,7 @@ w4a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs args
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nt = blockIdx.x, mt = blockIdx.y, z = blockIdx.z, splits = gridDim.z;
+  if (threadIdx.x == 0) TT_STAMP(0);   // CTA start
   const int kt_begin = (int)(((long)z * args.kt_total) / splits);
   const int kt_end = (int)(((long)(z + 1) * args.kt_total) / splits);
   const int nk = kt_end - kt_begin;
@@ -156,7 +170,9 @@ w4a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs args
         const uint8_t* src = args.blob + ((size_t)nt * args.kt_total + kt_begin + i) * kTileBytes;
         ptx::bulk_load(ws + i * Cfg::kWStage, src, kTileBytes, bar_full + 8 * i);
       }
+      TT_STAMP(1);   // first weight copies issued
       dependency_wait();
+      TT_STAMP(2);   // the previous kernel is complete
       if constexpr (MULTI) {
         if (!peer_wait(multi.sync, 1000000000ull)) atomicExch(args.status, 109);   // tokens gathered from peers
       }
@@ -239,6 +255,8 @@ w4a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs args
           ok = false;
           break;
         }
+        if (i == 0 && threadIdx.x == 64) TT_STAMP(3);   // first stage (weights and tokens) landed
+        if (i + kSets >= nk && (threadIdx.x & 127) == 64 % 128 && set == ((nk - 1) % kSets)) TT_STAMP(4);   // last stage landed
         const uint8_t* wst = smem + (ws - base) + s * Cfg::kWStage;
         uint4 ch[4];
 #pragma unroll
@@ -283,6 +301,7 @@ w4a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs args
       ok = false;
     }
     __syncwarp();
+    if (threadIdx.x == 64) TT_STAMP(5);   // accumulator final
     dependency_wait();   // outputs, planes and token scales belong to earlier kernels until here
     if (ok) {
       ptx::tc_fence_after();
@@ -359,6 +378,7 @@ w4a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs args
 
   ptx::tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) TT_STAMP(6);   // all roles done
   if (warp == 1) {
     __syncwarp();
     ptx::tc_fence_after();
@@ -508,3 +528,10 @@ int run_tile_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, con
 }
 
 }  // namespace lq
+
+#ifdef LQ_PIPELINE_TRACE
+// Copies the per-CTA stamps of the last launch (1024 CTAs x 8 slots of int64) to host memory.
+extern "C" LQ_API int lq_debug_read_tile_trace(long long* host_dst) {
+  return cudaMemcpyFromSymbol(host_dst, lq::tile::g_trace, sizeof(long long) * 1024 * 8) == cudaSuccess ? 0 : -4;
+}
+#endif

@@ -12,6 +12,7 @@
     python -m liquidgemm_b200.build --trace           # once: the product sources with -DLQ_PIPELINE_TRACE
     python -m liquidgemm_b200.microbench decode_trace gate_up 8   # per-CTA cycle counters of the decode kernel
     python -m liquidgemm_b200.microbench pair_trace gate_up 8192  # the same for the CTA-pair prefill kernel
+    python -m liquidgemm_b200.microbench tile_trace gate_up 8     # time stamps of every CTA of the tile kernel
 
 All but the last launch measurement-only kernels (``lq_debug_*`` in ``csrc/dbg/lq_debug.cu``); none of them is
 in the product library.  ``decode_trace`` and ``pair_trace`` run the real decode tensor-core kernel and the CTA-pair prefill kernel
@@ -274,6 +275,43 @@ def decode_trace(shape: str = "gate_up", M: int = 8) -> None:
               f"max {int(c.max())}")
 
 
+def tile_trace(shape: str = "gate_up", M: int = 8) -> None:
+    """%globaltimer stamps of every CTA of ``w4a8_tile_kernel`` (trace build) for the last launch of a graph of
+    back-to-back launches over rotating weight copies: nanoseconds after the launch's first CTA started."""
+    if os.environ.get("LIQUIDGEMM_B200_TRACE") != "1":
+        import subprocess
+        env = dict(os.environ, LIQUIDGEMM_B200_TRACE="1")
+        sys.exit(subprocess.call([sys.executable, "-m", "liquidgemm_b200.microbench", "tile_trace", shape, str(M)],
+                                 env=env))
+    from . import benchlib as B
+    from ._lib import lib as plib
+    N, K = B.SHAPES[shape]
+    C = 6
+    layers = [B.device_lqq(N, K, seed=31 * c + 1, want_gp=False) for c in range(C)]
+    x, sc = B.device_tokens(M, K, seed=M)
+    t = B.graph_time_us(lambda i: B.linear_call(layers[i % C], x, sc, M), C, 3)
+    buf = (ctypes.c_longlong * (1024 * 8))()
+    plib.lq_debug_read_tile_trace.argtypes = [ctypes.c_void_p]
+    assert plib.lq_debug_read_tile_trace(buf) == 0
+    a = np.frombuffer(buf, dtype=np.int64).reshape(1024, 8)
+    a = a[a[:, 0] > 0]
+    t0 = a[:, 0].min()
+    names = {0: "CTA start", 1: "first weight copies issued", 2: "previous kernel complete (griddepcontrol.wait returned)",
+             3: "first stage landed (weights + tokens)", 4: "last stage landed", 5: "accumulator final",
+             6: "all roles done"}
+    print(f"{shape} {N}x{K}, M = {M}: {t:.2f} us per launch (trace build), {len(a)} CTAs; ns after the first CTA's start")
+    for slot, label in names.items():
+        col = a[:, slot] - t0
+        print(f"  {label:58s} min {int(col.min()):6d}   median {int(np.median(col)):6d}   p90 {int(np.percentile(col, 90)):6d}"
+              f"   max {int(col.max()):6d}")
+    for (i, j), label in {(0, 2): "start -> previous kernel complete", (2, 3): "-> first stage landed",
+                          (3, 4): "-> last stage landed (the stream)", (4, 5): "-> accumulator final",
+                          (5, 6): "-> done (epilogue)"}.items():
+        d = a[:, j] - a[:, i]
+        print(f"  per CTA {label:40s} median {int(np.median(d)):6d}   p10 {int(np.percentile(d, 10)):6d}   p90 "
+              f"{int(np.percentile(d, 90)):6d}")
+
+
 def pair_trace(shape: str = "gate_up", M: int = 8192) -> None:
     """Per-CTA cycle counters of ``w4a8_pair_kernel`` (trace build of the library) on one Llama-3.1-8B shape:
     median / min / max over the CTAs of either rank of the last launch.  Counters are sums over the k-steps
@@ -324,8 +362,8 @@ _CASES = {"mma_rate": mma_rate, "mma_rate2": mma_rate2, "sync_cost": sync_cost, 
 
 if __name__ == "__main__":
     torch.cuda.set_device(0)
-    if len(sys.argv) > 1 and sys.argv[1] in ("decode_trace", "pair_trace"):
-        fn = decode_trace if sys.argv[1] == "decode_trace" else pair_trace
+    if len(sys.argv) > 1 and sys.argv[1] in ("decode_trace", "pair_trace", "tile_trace"):
+        fn = {"decode_trace": decode_trace, "pair_trace": pair_trace, "tile_trace": tile_trace}[sys.argv[1]]
         fn(*(sys.argv[2:3] or ["gate_up"]), *(int(v) for v in sys.argv[3:4]))
         sys.exit(0)
     which = sys.argv[1:] or list(_CASES)
