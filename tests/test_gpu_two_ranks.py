@@ -1,7 +1,7 @@
 """Every GPU of the host as one rank: the N-sharded linear whose epilogue stores its slice into every rank's
 full-width output (symmetric memory, plain peer stores, no multicast objects) against the unsharded CPU
 oracle -- through each kernel route of the dispatch (dp4a GEMV, one-launch tensor-core decode kernel, tile
-kernel with split-K planes + finish pass, tile kernel with the fused epilogue), with a barrier between the
+kernel with split-K planes + finish pass, tile kernel with the fused epilogue, CTA-pair kernel), with a barrier between the
 ranks and with the kernels' own flags.  Skipped on hosts with fewer than two GPUs; no rank leaves early and
 nothing here can wait on a rank that is gone."""
 
@@ -40,6 +40,12 @@ def _worker(rank, world, port, cases, q):
         fh = symm_mem.rendezvous(flags, dist.group.WORLD.group_name)
         results = []
         for M, N, K in cases:
+            # the last case runs on the CTA-pair kernel wherever the shard has whole 256-channel blocks (the
+            # library reads the switch at every call)
+            if (M, N, K) == cases[-1]:
+                os.environ["LQ_PAIR_ALWAYS"] = "1"
+            else:
+                os.environ.pop("LQ_PAIR_ALWAYS", None)
             qw = random_lqq(N, K, 64, seed=5 + M)                  # the same full layer on every rank
             x, ascale = random_tokens(M, K, seed=6 + M)
             lo, hi = shard_range(N, rank, world)
@@ -94,8 +100,9 @@ def test_sharded_linear_gathers_by_stores_on_every_gpu():
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    # token counts that take the GEMV, the decode tensor-core kernel, tile + finish, and the fused tile epilogue
-    cases = [(1, 1024, 2048), (8, 1024, 2048), (64, 1024, 2048), (300, 2048, 512)]
+    # token counts that take the GEMV, the decode tensor-core kernel, tile + finish, the fused tile epilogue, and
+    # the CTA-pair kernel's multi-destination epilogue
+    cases = [(1, 1024, 2048), (8, 1024, 2048), (64, 1024, 2048), (300, 2048, 512), (600, 1024, 1024)]
     procs = [ctx.Process(target=_worker, args=(r, world, port, cases, q)) for r in range(world)]
     for p in procs:
         p.start()
