@@ -1,4 +1,5 @@
-// W4A8 tensor-core linear for decode batches (up to 32 tokens): HBM-bound, so built like a streaming
+// W4A8 tensor-core linear for decode batches (up to 32 tokens; the dispatch uses it for 3..16 tokens on matrices
+// up to 32 M weights, where its single launch beats the tile kernel's planes + finish pass): HBM-bound, so built like a streaming
 // copy with tensor cores attached, in ONE launch.  Replaces the reference's split-K WGMMA path for small
 // M (csrc/liquid_gemm/w4a8_wgmma.cu:333-503 with the split rule at :523-534 and the finish kernel :39-56).
 //
@@ -17,7 +18,7 @@
 //  * warps 2..9  two dequant sets taking alternate k-tiles; thread r of a set owns weight row r:
 //            64 bytes of nibbles -> 128 INT8 (AND / SHR+AND / IMAD / XOR on 4-lane words) ->
 //            tcgen05.st into tensor-memory lane r (the MMA's A operand, 4 consecutive k per column).
-//  * warp 1  MMA: one thread issues four 128 x BN x 32 tcgen05.mma kind::i8 per k-tile (A from tensor
+//  * warp 1  MMA: the warp walks the loop, one elected lane issues four 128 x BN x 32 tcgen05.mma kind::i8 per k-tile (A from tensor
 //            memory, B = tokens through a shared-memory descriptor); its commit recycles the operand
 //            stage (NT stages: 32 tensor-memory columns + the token slice in shared memory).
 //  * Two accumulators in tensor memory, taken in turn by the segments (tile, k-range) of the CTA's

@@ -1,7 +1,10 @@
-// Tile W4A8 GEMM (M >= 17; up to 128 tokens per tile): one 128-channel x BN-token tile per CTA, two CTAs per SM.
+// Tile W4A8 GEMM (3 tokens and more; up to 128 tokens per tile): one 128-channel x BN-token tile per CTA, two CTAs
+// per SM.  Serves decode on the large matrices (whole 16-token tiles of a 28672-channel layer stream at 0.65 of
+// the HBM rate with no cross-CTA join at all), every batch from 17 tokens, and prefill where the CTA-pair kernel's
+// large tiles quantise badly.
 //
 // The persistent stream-K kernel keeps one CTA per SM; for a handful of k-steps per CTA its
-// single MMA-issuing thread and the cross-CTA reduction tail dominate.  With small token tiles the
+// cross-CTA reduction tail dominates.  With small token tiles the
 // shared-memory and tensor-memory footprint of a tile is small enough for two CTAs per SM, whose
 // load, dequant, MMA-issue and epilogue latencies overlap each other, which measured 1.5-2x
 // faster in this range.  Long-K shapes are cut into `splits` k-ranges (blockIdx.z); each CTA then
@@ -10,7 +13,8 @@
 // 523-534); with one split the epilogue is fused in the GEMM kernel.
 //
 // Per CTA: warp 0 = TMA producer (8704-byte bulk copy of the weight tile + BN x 128 token box per
-// k-step), warp 1 = TMEM allocation and tcgen05.mma issue (A operand from tensor memory), warps
+// k-step), warp 1 = TMEM allocation and tcgen05.mma issue (the warp walks the loop, one elected lane issues; A
+// operand from tensor memory), warps
 // 2..5 and 6..9 = two dequant sets taking alternate k-steps (thread r of a set owns weight row r ->
 // TMEM lane r; one set alone needs ~800 cycles per k-step, more than the MMAs of two CTAs), then
 // epilogue, the sets sharing the accumulator's columns.  All waits are bounded.
