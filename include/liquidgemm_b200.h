@@ -204,10 +204,13 @@ LQ_API int lq_quantize_weight(const void* w, int w_dtype, int N, int K, int grou
 
 /* Scheduling of the tensor-core GEMM, selected by the `splitk` argument of the calls below.
  *   splitk = 0 (automatic):
- *     M <= 2, and M <= 4 on matrices up to 64 M weights: streaming dp4a GEMV over the tile blob;
- *     M <= 16  (and int32 output at any small M): the streaming tensor-core kernel, ONE launch:
+ *     one token, two tokens on matrices up to 64 M weights, three or four on matrices up to 16 M weights
+ *              (scaled outputs only): streaming dp4a GEMV over the tile blob;
+ *     up to 16 tokens on matrices up to 32 M weights: the streaming tensor-core kernel, ONE launch:
  *              stream-K over two CTAs per SM, one 64-bit atomic per element joins cut tiles;
- *     larger   tile kernel: one 128-channel x up-to-128-token tile per CTA, two CTAs per SM, every
+ *     256 tokens and more on layers with whole 256-channel blocks, where a cost model expects it to win
+ *              (large M x N): the CTA-pair kernel, tcgen05.mma.cta_group::2 on 256-channel x 192-token tiles;
+ *     otherwise tile kernel: one 128-channel x up-to-128-token tile per CTA, two CTAs per SM, every
  *              tile cut into S k-ranges (S from the SM count) whose int32 partial planes one finish
  *              kernel reduces, scales and casts -- the split-K design of the reference
  *              (csrc/liquid_gemm/w4a8_wgmma.cu:39-56, 523-534); S = 1 fuses the epilogue.
@@ -219,7 +222,7 @@ LQ_API int lq_quantize_weight(const void* w, int w_dtype, int N, int K, int grou
  * the reference the override only applies to M <= 128 and is clamped to K/128; otherwise 0. */
 LQ_API int lq_gemm_pick_splitk(int M, int N, int K, int env_override);
 /* Workspace bytes for (M,N,K,splitk) and its kind: 0 = none, 1 = scratch (any contents; the
- * tile kernel's planes), 2 = reduction buffer of the streaming and persistent kernels, which must be ALL ZERO when
+ * tile kernel's planes), 2 = reduction buffer of the streaming, pair and persistent kernels, which must be ALL ZERO when
  * a call starts and is all zero again when its kernel ends (the kernel cleans up after itself), so
  * one zero-filled buffer serves any number of successive calls on a stream; calls that overlap on
  * the GPU need separate buffers, and after a LQ_ERR_TIMEOUT the caller must clear it. */

@@ -751,9 +751,9 @@ static Route route_for(int M, int N, int K, int splitk, bool scaled) {
     if (S > kt) S = kt;
     return {kRouteTile, S < 1 ? 1 : S};
   }
-  // Automatic choice above 128 tokens: the two-CTAs-per-SM tile kernel.  With two dequant sets it is ahead
-  // of the persistent stream-K kernel at every size measured (M = 256: 2x, M = 2048: 1.1-1.3x, M = 16384 on
-  // 28672 x 4096: 1.13x); the persistent kernel stays reachable through an explicit split argument.
+  // Automatic choice above 128 tokens: the CTA-pair kernel where its cost model expects it to win (large
+  // M x N on layers with whole 256-channel blocks), else the two-CTAs-per-SM tile kernel; the persistent
+  // stream-K kernel stays reachable through an explicit split argument.
   if (splitk == 0) {
     if (M >= pair_min_m() && (pair_forced() ? pair_serves(M, N, K) : pair_prefers(M, N, K))) return {kRoutePair, 0};
     return {kRouteTile, tile_pick_splits(M, N, K)};
