@@ -591,3 +591,71 @@ extern "C" LQ_API int lq_debug_mma_rate2(int n, int iters, int a_in_tmem, int ex
   lq::mma_rate2_kernel<<<ctas, 128, smem, lq::as_stream(stream)>>>(n, iters, a_in_tmem, extra, out);
   return lq::check_launch("mma_rate2_kernel");
 }
+
+namespace lq {
+// Hand-over between two kernels launched with programmatic stream serialisation: kernel "first" (one CTA per SM)
+// optionally allocates tensor memory and writes `out_bytes_per_cta` bytes, stamps %globaltimer just before it
+// ends; kernel "second" stamps %globaltimer when griddepcontrol.wait returns.  stamps[0] = latest end stamp of the
+// first kernel (atomicMax), stamps[1] = earliest return of the wait in the second (atomicMin).
+__global__ void __launch_bounds__(320, 1)
+handover_first_kernel(int use_tmem, int out_bytes_per_cta, uint8_t* out, unsigned long long* stamps, int smem_dummy) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint32_t tmem_slot;
+  (void)smem_dummy;
+  allow_dependents();
+  dependency_wait();
+  uint32_t tmem_base = 0;
+  if (use_tmem) {
+    if (threadIdx.x < 32) {
+      ptx::tmem_alloc(smem_u32(&tmem_slot), 256);
+      ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    tmem_base = tmem_slot;
+  }
+  // some work: stream the CTA's share of `out`
+  uint4* dst = reinterpret_cast<uint4*>(out + (size_t)blockIdx.x * out_bytes_per_cta);
+  for (int i = threadIdx.x; i < out_bytes_per_cta / 16; i += blockDim.x) dst[i] = make_uint4(i, i, i, i);
+  if (smem_raw[threadIdx.x] == 0xff) dst[0] = make_uint4(0, 0, 0, 0);   // keeps the dynamic shared memory referenced
+  __syncthreads();
+  if (threadIdx.x == 0) atomicMax(stamps, (unsigned long long)ptx::globaltimer_ns());
+  if (use_tmem) {
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      ptx::tc_fence_after();
+      ptx::tmem_dealloc(tmem_base, 256);
+    }
+  }
+}
+__global__ void __launch_bounds__(320, 1) handover_second_kernel(unsigned long long* stamps, int smem_dummy) {
+  extern __shared__ uint8_t smem_raw[];
+  (void)smem_dummy;
+  allow_dependents();
+  dependency_wait();
+  if (threadIdx.x == 0) atomicMin(stamps + 1, (unsigned long long)ptx::globaltimer_ns());
+  if (smem_raw[threadIdx.x] == 0xff) stamps[2] = 1;
+}
+}  // namespace lq
+
+// Launches first + second `pairs` times back to back; after each pair the host reads nothing - the caller reads
+// stamps[0..1] after synchronising (they hold the LAST pair's values only if it resets them between pairs, so
+// the Python side launches one pair at a time after a warm-up).  smem_bytes: dynamic shared memory per CTA of
+// both kernels (occupancy: with more than half of the SM's shared memory the second kernel's CTAs cannot be
+// resident beside the first's).
+extern "C" LQ_API int lq_debug_handover(int use_tmem, int out_bytes_per_cta, int smem_bytes, int ctas, void* out,
+                                        unsigned long long* stamps, void* stream) {
+  if (ctas <= 0 || out_bytes_per_cta % 16 || smem_bytes < 512 || smem_bytes > 200 * 1024 || !out || !stamps)
+    return LQ_ERR_BAD_ARG;
+  cudaStream_t st = lq::as_stream(stream);
+  cudaFuncSetAttribute(lq::handover_first_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 201 * 1024);
+  cudaFuncSetAttribute(lq::handover_second_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 201 * 1024);
+  cudaError_t e = lq::launch_overlapped(lq::handover_first_kernel, dim3(ctas), dim3(320), (size_t)smem_bytes, st, use_tmem,
+                                        out_bytes_per_cta, static_cast<uint8_t*>(out), stamps, 0);
+  if (e != cudaSuccess) return LQ_ERR_CUDA;
+  e = lq::launch_overlapped(lq::handover_second_kernel, dim3(ctas), dim3(320), (size_t)smem_bytes, st, stamps, 0);
+  if (e != cudaSuccess) return LQ_ERR_CUDA;
+  return lq::check_launch("handover kernels");
+}

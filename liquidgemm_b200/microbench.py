@@ -4,6 +4,7 @@
     python -m liquidgemm_b200.microbench mma_rate     # tcgen05.mma kind::i8 issue-to-issue cost
     python -m liquidgemm_b200.microbench mma_rate2    # the same for cta_group::2 (CTA pairs)
     python -m liquidgemm_b200.microbench sync_cost    # mbarrier / commit / bulk-copy instruction costs
+    python -m liquidgemm_b200.microbench handover     # end of one kernel -> griddepcontrol.wait returns in the next
     python -m liquidgemm_b200.microbench tma_stream   # HBM streaming rate of ring-buffered bulk copies
     python -m liquidgemm_b200.microbench l2_stream    # the same stream when the data is L2-resident
     python -m liquidgemm_b200.microbench tma_stream2  # two producer threads with a ring each in one CTA
@@ -147,6 +148,34 @@ def tma_stream2(total_bytes: int = 2_000_000_000) -> None:
         print(f"148 CTAs x 2 rings, stage {stage:6d} B x {ns:2d} buffers: {us:8.1f} us  "
               f"{296 * steps * stage / us / 1e6:6.2f} TB/s  {clk:6.1f} cycles per copy per ring  "
               f"{2 * stage / clk:5.1f} B/clk/SM", flush=True)
+
+
+def handover() -> None:
+    """Time from the end of a kernel's last CTA to the return of griddepcontrol.wait in the next kernel of the
+    stream (both launched with programmatic stream serialisation), with and without tensor memory in the first
+    kernel, for several output sizes and shared-memory footprints."""
+    fn = lib.lq_debug_handover
+    fn.argtypes, fn.restype = [_I, _I, _I, _I, _P, _P, _P], _I
+    out = torch.zeros(148 * (1 << 20), dtype=torch.uint8, device="cuda")
+    stamps = torch.zeros(4, dtype=torch.int64, device="cuda")
+    big = torch.iinfo(torch.int64).max
+    for smem_kb in (95, 150):
+        for use_tmem in (0, 1):
+            for out_kb in (0, 4, 64, 1024):
+                ctas = 296 if smem_kb < 110 else 148
+                gaps = []
+                for rep in range(12):
+                    stamps.copy_(torch.tensor([0, big, 0, 0], dtype=torch.int64))
+                    torch.cuda.synchronize()
+                    assert fn(use_tmem, out_kb * 1024 // 2 if ctas == 296 else out_kb * 1024, smem_kb * 1024, ctas,
+                              out.data_ptr(), stamps.data_ptr(), _stream()) == 0
+                    torch.cuda.synchronize()
+                    s = stamps.cpu().numpy()
+                    if rep >= 2:
+                        gaps.append(int(s[1]) - int(s[0]))
+                print(f"{ctas} CTAs, {smem_kb:3d} KB shared memory per CTA, tensor memory {'yes' if use_tmem else 'no '}, "
+                      f"{out_kb:5d} KB written per SM: last CTA's end -> wait returns: median {int(np.median(gaps)):6d} ns  "
+                      f"(min {min(gaps)}, max {max(gaps)})", flush=True)
 
 
 def sync_cost() -> None:
@@ -357,7 +386,7 @@ def pair_trace(shape: str = "gate_up", M: int = 8192) -> None:
                 print(f"  {label:48s} median {int(np.median(col)):9d}   min {int(col.min()):9d}   max {int(col.max()):9d}")
 
 
-_CASES = {"mma_rate": mma_rate, "mma_rate2": mma_rate2, "sync_cost": sync_cost, "tma_stream": tma_stream,
+_CASES = {"mma_rate": mma_rate, "mma_rate2": mma_rate2, "sync_cost": sync_cost, "handover": handover, "tma_stream": tma_stream,
           "l2_stream": l2_stream, "tma_stream2": tma_stream2, "tma_rows": tma_rows}
 
 if __name__ == "__main__":
