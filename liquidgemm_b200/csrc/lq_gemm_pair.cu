@@ -3,8 +3,8 @@
 // Why pairs.  A 128-channel x 192-token tile needs, per 128-wide k-step, 8.7 KB of packed weights and 24 KB
 // of tokens for 424 cycles of tensor-core work: 78 bytes per clock into every SM, which is what the L2 of
 // this part delivers to 148 SMs that all read different lines (measured with the library's bulk-copy
-// stream: 75 B/clk/SM out of L2, 18 TB/s in total).  The one-CTA kernels therefore stall on their token
-// boxes at half of the tensor-core rate.  Two CTAs on neighbouring SMs that issue ONE 256-channel x 192-token
+// stream: 75 B/clk/SM out of L2, 18 TB/s in total).  A one-CTA kernel would sit on that limit as soon as its
+// tensor cores ran at their full rate.  Two CTAs on neighbouring SMs that issue ONE 256-channel x 192-token
 // MMA share the token tile: each stages only 96 of the 192 token rows (12 KB per k-step) and the tensor
 // cores of both read both halves, so the traffic per SM drops to 49 B/clk at the same tensor-core rate
 // (measured: 106 cycles per 256 x 192 x 32 MMA, the same as the one-CTA 128 x 192 x 32).
