@@ -12,9 +12,9 @@
 // Work.  Tile = 256 channels x 192 tokens, pair p of P takes tiles p, p + P, ... (channel blocks fastest, so
 // the pairs of a wave share one or two token tiles and walk k in step: their weight and token lines hit in
 // L2).  The tiles of the last, partial wave are taken whole by as many pairs, or, when they are long and few,
-// cut into equal k-ranges over the pairs; a pair that holds only part of a tile's K adds its int32 sums into a
-// workspace slot (exact in any order) and the pair whose contribution completes the tile applies the epilogue
-// and re-zeroes the slot.
+// cut into equal k-ranges over the pairs; a pair that holds one of the first k-ranges of a tile takes that unit
+// FIRST and writes its int32 sums to a plane of the workspace; the pair with the last k-range takes it last, adds
+// the planes (exact in any order) to the sums in its tensor memory, applies the epilogue and re-zeroes them.
 //
 // Per CTA (768 threads), connected by mbarrier rings; rank = CTA's rank in its pair:
 //   warp 0        weight producer: one 8704-byte bulk copy per k-step (tile 2 * block + rank of the blob)
@@ -92,33 +92,38 @@ struct Args {
   const float* s1;         // [N]
   const void* bias;        // [N] in the output dtype, or null
   void* out;               // [M, N] in out_mode's type (single destination)
-  int32_t* slots;          // workspace: per (partial tile, rank) 192 x 128 int32 sums, all zero between launches
-  int32_t* counters;       // workspace: per (partial tile, rank) k-steps received so far, all zero between launches
+  int32_t* slots;          // workspace: per (partial tile, k-range but the last, rank) a plane of 192 x 128 int32 sums, all zero between launches
+  int32_t* counters;       // workspace: per (partial tile, rank, epilogue group) planes written so far, all zero between launches
   int* status;
   int out_mode;            // LQ_DT_* or kOutI32
   int M, N, K;
   int kt_total;            // K / 128
   int n2_tiles, m_tiles;   // 256-channel blocks, 192-token blocks
   int pairs;               // CTA pairs of the launch
+  int tail_s;              // k-ranges each tile of the last, partial wave is cut into (1: whole tiles)
   int vec_out;             // several destinations, 2-byte outputs whose rows allow 16-byte stores: stage through smem
 };
 
-// Split factor of the tiles of the last, partial wave (r tiles on P pairs).  Splitting a tile along k costs every
-// participating pair a pass of int32 atomics over its 192 x 128 sums plus the completing pair's read-back, about
-// as much as 20 k-steps of the main loop: it only pays when the tile is long and at least half of the pairs
+// Split factor of the tiles of the last, partial wave (r tiles on P pairs).  A tile cut along k costs the pair
+// that completes it a read of the other pairs' sums in its last, exposed epilogue, and more pairs working in the
+// last wave run at a lower clock under the power limit than the few that would otherwise finish it alone:
+// measured on 4096 x 14336 (112 k-steps) the cut saves 13 % at 1024 tokens, 5 % at 2048 and 2 % at 8192; on
+// layers of 32 k-steps it loses 2-4 %.  So only long tiles are cut, and only when at least half of the pairs
 // would otherwise idle.
-__host__ __device__ inline int tail_split(int r, int P, int kt) {
+inline int tail_split(int r, int P, int kt) {
   if (r == 0 || 2 * r > P || kt < 64) return 1;
   int S = P / r;
   if (S > kt / 16) S = kt / 16;
   return S < 1 ? 1 : S;
 }
 
-// The segments of one pair: whole tiles of the full waves, then at most one unit of the last partial wave (a
-// whole tile, or one of the S equal k-ranges of a tile).
+// The segments of one pair: the whole tiles of the full waves and at most one unit of the last, partial wave (a
+// whole tile, or one of the S equal k-ranges of a tile).  The pair with the last k-range of a split tile completes
+// it from the other pairs' sums; it takes that unit last, the others take theirs FIRST, so that their sums are in
+// memory long before they are wanted and nobody's last segment waits for anybody else's.
 struct PairWalk {
-  int kt, P, p, full_waves, wave, tail_units, S;
-  bool tail_done;
+  int kt, P, p, full_waves, wave, S, rt, part;
+  bool tail_left, tail_first;
   __device__ PairWalk(const Args& a, int pair) {
     kt = a.kt_total;
     P = a.pairs;
@@ -127,11 +132,25 @@ struct PairWalk {
     full_waves = tiles / P;
     wave = 0;
     const int r = tiles - full_waves * P;
-    S = tail_split(r, P, kt);
-    tail_units = r * S;
-    tail_done = false;
+    S = a.tail_s;
+    tail_left = p < r * S;
+    rt = p / S;
+    part = p - rt * S;
+    tail_first = tail_left && part < S - 1;
+  }
+  __device__ void tail(Segment& s) {
+    tail_left = false;
+    s.tile = full_waves * P + rt;
+    s.kb = (part * kt) / S;
+    s.ke = ((part + 1) * kt) / S;
+    s.whole = (S == 1);
+    s.slot = p;   // unit index: tile rt, k-range part
   }
   __device__ bool next(Segment& s) {
+    if (tail_first && tail_left) {
+      tail(s);
+      return true;
+    }
     if (wave < full_waves) {
       s.tile = wave * P + p;
       s.kb = 0;
@@ -141,14 +160,8 @@ struct PairWalk {
       ++wave;
       return true;
     }
-    if (tail_done || p >= tail_units) return false;
-    tail_done = true;
-    const int rt = p / S, part = p - rt * S;
-    s.tile = full_waves * P + rt;
-    s.kb = (part * kt) / S;
-    s.ke = ((part + 1) * kt) / S;
-    s.whole = (S == 1);
-    s.slot = rt;
+    if (!tail_left) return false;
+    tail(s);
     return true;
   }
 };
@@ -220,8 +233,8 @@ w4a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args,
   const uint32_t tmem_slot = bar_accfree + 2 * 8;
   uint8_t* gen_bars = smem + (bars - base);
   volatile uint32_t* tmem_slot_p = reinterpret_cast<volatile uint32_t*>(gen_bars + kNumBars * 8);
-  volatile int* last_flag = reinterpret_cast<volatile int*>(gen_bars + kNumBars * 8 + 4);
   volatile int* wait_flag = reinterpret_cast<volatile int*>(gen_bars + kNumBars * 8 + 8);   // [group][2]
+  volatile int* last_flag = reinterpret_cast<volatile int*>(gen_bars + kNumBars * 8 + 24);  // [group]
   uint8_t* out_stage = gen_bars + ((kBarBytes + 15) & ~15);
   float* tok_scale = reinterpret_cast<float*>(out_stage + 2 * kOutStage);   // [group][2][kBN]
 
@@ -502,6 +515,8 @@ w4a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args,
     TR_VAR(tr_accfull);
     TR_VAR(tr_tsc);
     TR_VAR(tr_out);
+    TR_VAR(tr_p1);
+    TR_VAR(tr_psync);
     const long long tr_g0 = TR_NOW();
     while (ok && walk.next(sg)) {
       const int b = accring.s;
@@ -533,7 +548,17 @@ w4a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args,
       const uint32_t tmem_acc = tmem_base + b * kBN + lane_addr;
       const float w_scale = (n_ok && !raw) ? __ldg(args.s1 + n) : 0.f;
       const float bias = (has_bias && n_ok) ? load_bias(args.bias, n, args.out_mode) : 0.f;
-      if (sg.whole) {
+      // A tile cut along k between S pairs: every pair but the one with the last k-range writes its sums to a
+      // plane of its own in the workspace (plain 16-byte stores; int32 atomics on whole tiles from every pair at
+      // once were measured at a fraction of that rate) and counts itself in; the pair with the last k-range
+      // adds those planes to the sums it holds in tensor memory, applies the epilogue and leaves planes and
+      // counter zero again.  The two groups work on their own chunks with a counter each.
+      constexpr size_t kPlane4 = (size_t)128 * kBN / 4;   // int4 units: [token / 4][channel]
+      const int S = walk.S;
+      const bool completes = !sg.whole && walk.part == S - 1;
+      int4* planes = reinterpret_cast<int4*>(args.slots) + ((size_t)walk.rt * (S - 1) * 2 + rank) * kPlane4;   // k-range q: + q * 2 * kPlane4
+      int32_t* counter = args.counters + 2 * ((size_t)walk.rt * 2 + rank) + g;
+      if (sg.whole || completes) {
         // Token scales of the tile, once, through shared memory (two buffers per group: a warp may be one tile
         // ahead of the slowest; this barrier is the only one of a tile whose outputs go straight to global memory).
         float* tsc = tok_scale + (2 * g + fslot) * kBN;
@@ -541,13 +566,54 @@ w4a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args,
         if (!raw) {
           for (int i = et; i < kBN; i += 128) tsc[i] = (i < cols) ? __ldg(args.ascale + m0 + i) : 0.f;
         }
+        if (completes && et == 0) {
+          // the other pairs took their k-ranges first of all: their sums have been there for a long time
+          const uint64_t t0 = ptx::globaltimer_ns();
+          bool there = true;
+          for (;;) {
+            int have;
+            asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(have) : "l"(counter) : "memory");
+            if (have >= S - 1) break;
+            if (ptx::globaltimer_ns() - t0 > kWaitLimitNs) {
+              there = false;
+              break;
+            }
+            __nanosleep(100);
+          }
+          if (!there) atomicExch(args.status, 130);
+          last_flag[g] = there ? 1 : 0;
+        }
         group_barrier(g);
+        if (completes) {
+          if (last_flag[g] == 0) {
+            ok = false;
+            break;
+          }
+          __threadfence();
+        }
         TR_ADD(tr_tsc, tr_t0);
         const long long tr_o0 = TR_NOW();
 #pragma unroll 1
         for (int c0 = 16 * g; c0 < cols; c0 += 32) {
           int v[16];
           ptx::tmem_ld16(tmem_acc + c0, v);
+          if (completes) {
+            // (Loading these one chunk ahead was measured: it saves a microsecond here and costs every whole tile
+            // of short-K layers 8 % through the registers it holds.)
+            ptx::tc_wait_ld();
+#pragma unroll 1
+            for (int q = 0; q < S - 1; ++q) {
+              int4* pl = planes + (size_t)q * 2 * kPlane4 + (size_t)(c0 >> 2) * 128 + row;
+              int4 t[4];
+#pragma unroll
+              for (int jj = 0; jj < 4; ++jj) t[jj] = (c0 + 4 * jj < cols) ? __ldcg(pl + jj * 128) : make_int4(0, 0, 0, 0);
+#pragma unroll
+              for (int jj = 0; jj < 4; ++jj) {
+                v[4 * jj] += t[jj].x; v[4 * jj + 1] += t[jj].y; v[4 * jj + 2] += t[jj].z; v[4 * jj + 3] += t[jj].w;
+                if (c0 + 4 * jj < cols) __stcg(pl + jj * 128, make_int4(0, 0, 0, 0));
+              }
+            }
+          }
           float sc[16];
 #pragma unroll
           for (int q4 = 0; q4 < 4; ++q4) {
@@ -613,75 +679,33 @@ w4a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args,
           else ptx::mbar_arrive_remote(leader_accfree + 8 * b);
         }
         TR_ADD(tr_out, tr_o0);
-      } else if (g == 1) {
-        // part of a tile's K: group 0 does the slot reduction alone; this group only releases the accumulator
+        if (completes && et == 0) *counter = 0;
+      } else {
+        // One of the first S - 1 k-ranges of a split tile: sums to this pair's plane.
+        int4* own = planes + (size_t)walk.part * 2 * kPlane4 + row;
+        const long long tr_a0 = TR_NOW();
+#pragma unroll 1
+        for (int c0 = 16 * g; c0 < cols; c0 += 32) {
+          int v[16];
+          ptx::tmem_ld16(tmem_acc + c0, v);
+          ptx::tc_wait_ld();
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj)
+            if (c0 + 4 * jj < cols)
+              __stcg(own + (size_t)((c0 >> 2) + jj) * 128, make_int4(v[4 * jj], v[4 * jj + 1], v[4 * jj + 2], v[4 * jj + 3]));
+        }
+        TR_ADD(tr_p1, tr_a0);
+        ptx::tc_fence_before();
         __syncwarp();
         if (lane == 0) {
           if (rank == 0) ptx::mbar_arrive(bar_accfree + 8 * b);
           else ptx::mbar_arrive_remote(leader_accfree + 8 * b);
         }
-      } else {
-        // part of a tile's K: add into the slot; whoever completes the tile applies the epilogue
-        const size_t sidx = (size_t)sg.slot * 2 + rank;
-        int32_t* slot = args.slots + sidx * (size_t)(128 * kBN);
-#pragma unroll 1
-        for (int c0 = 0; c0 < cols; c0 += 16) {
-          int v[16];
-          ptx::tmem_ld16(tmem_acc + c0, v);
-          ptx::tc_wait_ld();
-          if (c0 + 16 >= cols) {
-            ptx::tc_fence_before();
-            __syncwarp();
-            if (lane == 0) {
-              if (rank == 0) ptx::mbar_arrive(bar_accfree + 8 * b);
-              else ptx::mbar_arrive_remote(leader_accfree + 8 * b);
-            }
-          }
-          if (n_ok) {
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-              if (c0 + j < cols) atomicAdd(slot + (c0 + j) * 128 + row, v[j]);
-          }
-        }
+        const long long tr_b0 = TR_NOW();
         __threadfence();
-        group_barrier(0);
-        if (et == 0) {
-          const int add = sg.ke - sg.kb;
-          const int before = atomicAdd(args.counters + sidx, add);
-          *last_flag = (before + add == args.kt_total) ? 1 : 0;
-        }
-        group_barrier(0);
-        const bool last = *last_flag != 0;
-        group_barrier(0);                        // everyone has read the flag before it can be rewritten
-        if (last) {
-          __threadfence();
-          if (n_ok) {
-#pragma unroll 1
-            for (int c0 = 0; c0 < cols; c0 += 16) {
-              int v[16];
-              float sc[16];
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {       // all loads of the chunk first: one L2 round trip
-                v[j] = (c0 + j < cols) ? __ldcg(slot + (c0 + j) * 128 + row) : 0;
-                sc[j] = (c0 + j < cols && !raw) ? __ldg(args.ascale + m0 + c0 + j) : 0.f;
-              }
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                if (c0 + j < cols) {
-                  __stcg(slot + (c0 + j) * 128 + row, 0);
-                  const int m = m0 + c0 + j;
-                  if (raw) reinterpret_cast<int32_t*>(args.out)[(size_t)m * args.N + n] = v[j];
-                  else if constexpr (MULTI)
-                    store_out_all(multi.out, m, n, lqq_scale(v[j], sc[j], w_scale), bias, has_bias, args.out_mode);
-                  else
-                    store_out_bias(args.out, (size_t)m * args.N + n, lqq_scale(v[j], sc[j], w_scale), bias, has_bias,
-                                   args.out_mode);
-                }
-              }
-            }
-          }
-          if (et == 0) args.counters[sidx] = 0;
-        }
+        group_barrier(g);
+        if (et == 0) atomicAdd(counter, 1);
+        TR_ADD(tr_psync, tr_b0);
       }
     }
     if (et == 0 && g == 0) {
@@ -690,6 +714,8 @@ w4a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args,
       TR_SET(18, seg);
       TR_SET(19, tr_tsc);
       TR_SET(21, tr_out);
+      TR_SET(22, tr_p1);
+      TR_SET(23, tr_psync);
     }
     if constexpr (MULTI) {
       // every output store of this CTA, peer memory included, is ordered before the flags (see lq_common.cuh):
@@ -754,7 +780,7 @@ static int launch(const CUtensorMap& tx, const Args& a, const MultiOut* multi, c
 }
 
 struct PairPlan {
-  int n2_tiles, m_tiles, pairs, partial_tiles;
+  int n2_tiles, m_tiles, pairs, partial_tiles, tail_s;
   size_t ws_bytes;
 };
 static PairPlan plan(int M, int N, int K) {
@@ -765,11 +791,13 @@ static PairPlan plan(int M, int N, int K) {
   const int cap = max_pairs();
   p.pairs = (int)(tiles < cap ? tiles : cap);
   const int r = (int)(tiles % p.pairs);
-  p.partial_tiles = tail_split(r, p.pairs, K / 128) > 1 ? r : 0;   // tiles whose K is shared between pairs
-  // per partial tile and rank: 192 x 128 int32 sums; then one counter each, padded to 256 bytes
+  p.tail_s = tail_split(r, p.pairs, K / 128);
+  p.partial_tiles = p.tail_s > 1 ? r : 0;   // tiles whose K is shared between pairs
+  // per partial tile, k-range but the last and rank: 192 x 128 int32 sums; then one counter per tile, rank and
+  // epilogue group, padded to 256 bytes
   p.ws_bytes = p.partial_tiles == 0 ? 0
-                                    : (size_t)p.partial_tiles * 2 * (128 * kBN * 4) +
-                                          (((size_t)p.partial_tiles * 2 * 4 + 255) / 256) * 256;
+                                    : (size_t)p.partial_tiles * (p.tail_s - 1) * 2 * (128 * kBN * 4) +
+                                          (((size_t)p.partial_tiles * 2 * 2 * 4 + 255) / 256) * 256;
   return p;
 }
 
@@ -780,10 +808,10 @@ bool pair_serves(int M, int N, int K) { return M >= 1 && N >= 256 && N % 256 == 
 
 // Whether the pair kernel is expected to beat the two-CTAs-per-SM tile kernel on this shape.  Both run whole
 // waves of tiles, so the comparison is between (waves x k-steps x time per k-step) of either, with the times
-// per k-step measured on B200 over the Llama-3.1-8B shapes at 256..8192 tokens (microseconds: pair 0.35, or
-// 0.31 for K >= 8192, plus 6 for the prologue and the last epilogue; tile 0.58, 0.48 for K >= 8192, 0.44 when
-// there is at most one CTA per SM).  The model reproduces the measured winner at every point of that sweep
-// except ties within 5 %.
+// per k-step measured on B200 over the Llama-3.1-8B shapes at 256..8192 tokens (microseconds: pair 0.325, or
+// 0.285 for K >= 8192, plus 9.5 for the prologue and the last epilogue, a tile cut in S costing 1/S of a wave
+// plus 27 k-steps; tile 0.58, 0.48 for K >= 8192, 0.44 when there is at most one CTA per SM).  The model
+// reproduces the measured winner at every point of that sweep except ties within 4 %.
 bool pair_prefers(int M, int N, int K) {
   if (!pair_serves(M, N, K)) return false;
   const int kt = K / 128;
@@ -795,9 +823,9 @@ bool pair_prefers(int M, int N, int K) {
   const pairk::PairPlan p = pairk::plan(M, N, K);
   const long tiles_p = (long)p.n2_tiles * p.m_tiles;
   const int r = (int)(tiles_p % p.pairs);
-  const int S = pairk::tail_split(r, p.pairs, kt);
-  const double tail = r == 0 ? 0.0 : S > 1 ? 1.0 / S + 40.0 / kt : 1.0;   // a split tile costs its reduction too
-  const double est_pair = ((double)(tiles_p / p.pairs) + tail) * kt * (kt >= 64 ? 0.31 : 0.35) + 6.0;
+  const int S = p.tail_s;
+  const double tail = r == 0 ? 0.0 : S > 1 ? 1.0 / S + 27.0 / kt : 1.0;   // a split tile costs its reduction too
+  const double est_pair = ((double)(tiles_p / p.pairs) + tail) * kt * (kt >= 64 ? 0.285 : 0.325) + 9.5;
   return est_pair < 0.97 * est_tile;
 }
 
@@ -826,7 +854,7 @@ int run_pair_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, con
   a.out = out.ptr[0];
   a.slots = static_cast<int32_t*>(ws);
   a.counters = p.ws_bytes ? reinterpret_cast<int32_t*>(static_cast<uint8_t*>(ws) +
-                                                      (size_t)p.partial_tiles * 2 * (128 * kBN * 4))
+                                                      (size_t)p.partial_tiles * (p.tail_s - 1) * 2 * (128 * kBN * 4))
                           : nullptr;
   a.status = status_word();
   a.out_mode = out_mode;
@@ -837,6 +865,7 @@ int run_pair_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, con
   a.n2_tiles = p.n2_tiles;
   a.m_tiles = p.m_tiles;
   a.pairs = p.pairs;
+  a.tail_s = p.tail_s;
   // staged 16-byte stores for the gather-by-stores form; one local destination is written directly
   bool vec = multi && (out_mode == LQ_DT_BF16 || out_mode == LQ_DT_F16) && out.ld % 8 == 0 && out.col0 % 8 == 0;
   for (int r = 0; r < out.n; ++r) vec = vec && (reinterpret_cast<uintptr_t>(out.ptr[r]) % 16 == 0);

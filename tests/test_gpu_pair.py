@@ -79,11 +79,13 @@ def test_bias_is_added_to_the_rounded_output(ops, out_dtype):
     ops.poll_status()
 
 
-def test_split_tail_and_clean_workspace(ops):
-    """80 long tiles on 74 pairs: the six tiles of the last wave are cut along k between the pairs and summed
-    through the workspace slots, which the completing pair re-zeroes: a second call on the same cached workspace
-    gives the same bits, and so does a decode call (which shares that workspace) afterwards."""
-    M, N, K = 15360, 256, 8192
+@pytest.mark.parametrize("M", [15360, 19918])
+def test_split_tail_and_clean_workspace(ops, M):
+    """80 long tiles on 74 pairs: the six tiles of the last wave are cut along k between the pairs (four ranges
+    each; 104 tiles, the last one ragged: thirty tiles in two ranges each) and summed through the workspace
+    planes, which the completing pair re-zeroes: a second call on the same cached workspace gives the same bits,
+    and so does a decode call (which shares that workspace) afterwards."""
+    N, K = 256, 8192
     qw = random_lqq(N, K, 64, seed=21)
     tq = to_torch_qw(qw)
     x, ascale = random_tokens(M, K, seed=5)
