@@ -375,7 +375,8 @@ def pair_trace(shape: str = "gate_up", M: int = 8192) -> None:
              12: "dequant thread: waiting for the operand stage", 13: "dequant thread: tcgen05.st + wait::st + arrive",
              14: "dequant thread: whole role", 16: "epilogue thread: waiting for an accumulator",
              19: "epilogue thread: token scales + barrier", 21: "epilogue thread: tcgen05.ld, convert, store",
-             17: "epilogue thread: whole role", 18: "epilogue thread: tiles"}
+             17: "epilogue thread: whole role", 18: "epilogue thread: tiles",
+             22: "epilogue thread, first k-range of a cut tile: sums to the plane", 23: "... fence, barrier, counter"}
     print(f"{shape} {N}x{K}, M = {M}: {e0.elapsed_time(e1) * 1e3:.1f} us (trace build), {len(a)} CTAs; cycles per CTA")
     for rank in (0, 1):
         rows = a[rank::2]
