@@ -123,7 +123,7 @@ inline int tail_split(int r, int P, int kt) {
 // memory long before they are wanted and nobody's last segment waits for anybody else's.
 struct PairWalk {
   int kt, P, p, full_waves, wave, S, rt, part;
-  bool tail_left, tail_first;
+  bool has_tail, tail_left, tail_first;
   __device__ PairWalk(const Args& a, int pair) {
     kt = a.kt_total;
     P = a.pairs;
@@ -133,11 +133,19 @@ struct PairWalk {
     wave = 0;
     const int r = tiles - full_waves * P;
     S = a.tail_s;
-    tail_left = p < r * S;
+    has_tail = tail_left = p < r * S;
     rt = p / S;
     part = p - rt * S;
     tail_first = tail_left && part < S - 1;
   }
+  __device__ int segments() const { return full_waves + (has_tail ? 1 : 0); }
+  // Whether the dequant warps share the epilogue of the pair's last segment: a whole tile, and long enough that a
+  // dequant warp done with it (at most kNT + kSets k-steps ahead of the MMA warp) cannot meet the accumulator
+  // barrier a whole use behind, where the parity it waits for would read as complete.  (Sharing the completion of
+  // a cut tile as well was measured: 5 us faster with three k-ranges, 1-5 us slower with two; not kept.)
+  __device__ bool last_shared() const { return kt >= 8 && ((has_tail && !tail_first) ? S == 1 : full_waves > 0); }
+  // whether this pair holds the last k-range of a cut tile
+  __device__ bool completes_tile() const { return has_tail && S > 1 && part == S - 1; }
   __device__ void tail(Segment& s) {
     tail_left = false;
     s.tile = full_waves * P + rt;
@@ -165,6 +173,11 @@ struct PairWalk {
     return true;
   }
 };
+
+__device__ __forceinline__ void store_cols_any(void* out, int out_mode, size_t idx0, long ld, const int (&v)[16],
+                                               const float (&sc)[16], float w_scale, float bias, bool has_bias, int valid);
+
+constexpr int kGroupsLast = 2 + kSets;   // warps groups sharing the epilogue of a pair's last tile
 
 __device__ __forceinline__ uint16_t out_bits16(float v, float bias, bool has_bias, int out_mode) {
   if (out_mode == LQ_DT_BF16) {
@@ -202,6 +215,45 @@ __device__ __forceinline__ void store_cols(void* out, size_t idx0, long ld, cons
           reinterpret_cast<float*>(out)[idx] = has_bias ? __fadd_rn(y, bias) : y;
         }
       }
+    }
+  }
+}
+
+__device__ __forceinline__ void store_cols_any(void* out, int out_mode, size_t idx0, long ld, const int (&v)[16],
+                                               const float (&sc)[16], float w_scale, float bias, bool has_bias, int valid) {
+  if (out_mode == LQ_DT_BF16) store_cols<LQ_DT_BF16>(out, idx0, ld, v, sc, w_scale, bias, has_bias, valid);
+  else if (out_mode == LQ_DT_F16) store_cols<LQ_DT_F16>(out, idx0, ld, v, sc, w_scale, bias, has_bias, valid);
+  else if (out_mode == LQ_DT_F32) store_cols<LQ_DT_F32>(out, idx0, ld, v, sc, w_scale, bias, has_bias, valid);
+  else store_cols<kOutI32>(out, idx0, ld, v, sc, w_scale, bias, has_bias, valid);
+}
+
+// Bounded wait for the planes of a cut tile: both epilogue groups of each of the `need` other pairs have counted
+// themselves in.  Relaxed polls; the caller fences before it reads the planes.
+__device__ __forceinline__ bool planes_ready(const int32_t* counters2, int need, uint64_t limit_ns) {
+  const uint64_t t0 = ptx::globaltimer_ns();
+  for (;;) {
+    int a, b;
+    asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(a) : "l"(counters2) : "memory");
+    asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(b) : "l"(counters2 + 1) : "memory");
+    if (a >= need && b >= need) return true;
+    if (ptx::globaltimer_ns() - t0 > limit_ns) return false;
+    __nanosleep(100);
+  }
+}
+
+// Adds the other pairs' sums of one 16-token chunk (planes of int4: [token / 4][channel]) and zeroes them.
+__device__ __forceinline__ void add_planes(int (&v)[16], int4* planes, size_t plane_stride, int others, int c0, int cols,
+                                           int row) {
+#pragma unroll 1
+  for (int q = 0; q < others; ++q) {
+    int4* pl = planes + (size_t)q * plane_stride + (size_t)(c0 >> 2) * 128 + row;
+    int4 t[4];
+#pragma unroll
+    for (int jj = 0; jj < 4; ++jj) t[jj] = (c0 + 4 * jj < cols) ? __ldcg(pl + jj * 128) : make_int4(0, 0, 0, 0);
+#pragma unroll
+    for (int jj = 0; jj < 4; ++jj) {
+      v[4 * jj] += t[jj].x; v[4 * jj + 1] += t[jj].y; v[4 * jj + 2] += t[jj].z; v[4 * jj + 3] += t[jj].w;
+      if (c0 + 4 * jj < cols) __stcg(pl + jj * 128, make_int4(0, 0, 0, 0));
     }
   }
 }
@@ -485,6 +537,45 @@ w4a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args,
         tring.advance();
       }
     }
+    // The pair's last tile: nothing is left to unpack, and the two epilogue groups alone would take as long over
+    // it as over any other (a converting, storing warp gets a memory instruction through per ~130 cycles; this
+    // last epilogue is the one nothing hides).  The dequant sets join as groups 2..4 of kGroupsLast, with the
+    // direct-store form only (one destination, or rows that do not allow 16-byte stores).
+    if (!MULTI && args.vec_out == 0 && ok && walk.last_shared()) {
+      const int last = walk.segments() - 1;            // sg still holds that segment
+      const int b = last & 1;
+      const uint32_t phb = (uint32_t)(last >> 1) & 1u;
+      bool done = true;
+      if (lane == 0) {
+        done = ptx::mbar_wait_bounded(bar_accfull + 8 * b, phb, kWaitLimitNs);
+        if (!done) atomicExch(args.status, 126);
+      }
+      done = __shfl_sync(0xffffffffu, done ? 1 : 0, 0) != 0;
+      if (done) {
+        ptx::tc_fence_after();
+        const bool raw = args.out_mode == kOutI32;
+        const bool has_bias = !raw && args.bias != nullptr;
+        const int n2 = sg.tile % args.n2_tiles, mt = sg.tile / args.n2_tiles;
+        const int m0 = mt * kBN;
+        const long n = (long)(2 * n2 + (int)rank) * 128 + row;
+        const int cols = (args.M - m0) < kBN ? (args.M - m0) : kBN;
+        const uint32_t tmem_acc = tmem_base + b * kBN + lane_addr;
+        const float w_scale = raw ? 0.f : __ldg(args.s1 + n);
+        const float bias = has_bias ? load_bias(args.bias, n, args.out_mode) : 0.f;
+#pragma unroll 1
+        for (int c0 = 16 * (2 + my_set); c0 < cols; c0 += 16 * kGroupsLast) {
+          int v[16];
+          ptx::tmem_ld16(tmem_acc + c0, v);
+          float sc[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) sc[j] = (!raw && c0 + j < cols) ? __ldg(args.ascale + m0 + c0 + j) : 0.f;
+          ptx::tc_wait_ld();
+          store_cols_any(args.out, args.out_mode, (size_t)(m0 + c0) * args.N + n, args.N, v, sc, w_scale, bias, has_bias,
+                         cols - c0);
+        }
+        ptx::tc_fence_before();
+      }
+    }
     if (threadIdx.x == 256) {
       TR_SET(10, tr_full);
       TR_SET(11, tr_unpack);
@@ -508,6 +599,8 @@ w4a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args,
     uint8_t* stage = out_stage + g * kOutStage;
     volatile int* wflag = wait_flag + 2 * g;
     PairWalk walk(args, pair);
+    const int nseg = walk.segments();
+    const bool helped = !MULTI && !vec && walk.last_shared();
     Segment sg;
     Ring<2> accring;
     int seg = 0;
@@ -551,13 +644,13 @@ w4a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args,
       // A tile cut along k between S pairs: every pair but the one with the last k-range writes its sums to a
       // plane of its own in the workspace (plain 16-byte stores; int32 atomics on whole tiles from every pair at
       // once were measured at a fraction of that rate) and counts itself in; the pair with the last k-range
-      // adds those planes to the sums it holds in tensor memory, applies the epilogue and leaves planes and
-      // counter zero again.  The two groups work on their own chunks with a counter each.
+      // adds those planes to the sums it holds in tensor memory, applies the epilogue and leaves the planes zero
+      // again (the counters are cleared at the end of the kernel).  The writers' two groups count separately.
       constexpr size_t kPlane4 = (size_t)128 * kBN / 4;   // int4 units: [token / 4][channel]
       const int S = walk.S;
       const bool completes = !sg.whole && walk.part == S - 1;
       int4* planes = reinterpret_cast<int4*>(args.slots) + ((size_t)walk.rt * (S - 1) * 2 + rank) * kPlane4;   // k-range q: + q * 2 * kPlane4
-      int32_t* counter = args.counters + 2 * ((size_t)walk.rt * 2 + rank) + g;
+      int32_t* counters2 = args.counters + 2 * ((size_t)walk.rt * 2 + rank);   // one per epilogue group of the writers
       if (sg.whole || completes) {
         // Token scales of the tile, once, through shared memory (two buffers per group: a warp may be one tile
         // ahead of the slowest; this barrier is the only one of a tile whose outputs go straight to global memory).
@@ -568,18 +661,7 @@ w4a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args,
         }
         if (completes && et == 0) {
           // the other pairs took their k-ranges first of all: their sums have been there for a long time
-          const uint64_t t0 = ptx::globaltimer_ns();
-          bool there = true;
-          for (;;) {
-            int have;
-            asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(have) : "l"(counter) : "memory");
-            if (have >= S - 1) break;
-            if (ptx::globaltimer_ns() - t0 > kWaitLimitNs) {
-              there = false;
-              break;
-            }
-            __nanosleep(100);
-          }
+          const bool there = planes_ready(counters2, S - 1, kWaitLimitNs);
           if (!there) atomicExch(args.status, 130);
           last_flag[g] = there ? 1 : 0;
         }
@@ -593,26 +675,17 @@ w4a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args,
         }
         TR_ADD(tr_tsc, tr_t0);
         const long long tr_o0 = TR_NOW();
+        // the pair's last tile, its main loop over: the dequant warps take three of every five chunks (below)
+        const int cstep = (helped && seg == nseg) ? 16 * kGroupsLast : 32;
 #pragma unroll 1
-        for (int c0 = 16 * g; c0 < cols; c0 += 32) {
+        for (int c0 = 16 * g; c0 < cols; c0 += cstep) {
           int v[16];
           ptx::tmem_ld16(tmem_acc + c0, v);
           if (completes) {
             // (Loading these one chunk ahead was measured: it saves a microsecond here and costs every whole tile
             // of short-K layers 8 % through the registers it holds.)
             ptx::tc_wait_ld();
-#pragma unroll 1
-            for (int q = 0; q < S - 1; ++q) {
-              int4* pl = planes + (size_t)q * 2 * kPlane4 + (size_t)(c0 >> 2) * 128 + row;
-              int4 t[4];
-#pragma unroll
-              for (int jj = 0; jj < 4; ++jj) t[jj] = (c0 + 4 * jj < cols) ? __ldcg(pl + jj * 128) : make_int4(0, 0, 0, 0);
-#pragma unroll
-              for (int jj = 0; jj < 4; ++jj) {
-                v[4 * jj] += t[jj].x; v[4 * jj + 1] += t[jj].y; v[4 * jj + 2] += t[jj].z; v[4 * jj + 3] += t[jj].w;
-                if (c0 + 4 * jj < cols) __stcg(pl + jj * 128, make_int4(0, 0, 0, 0));
-              }
-            }
+            add_planes(v, planes, 2 * kPlane4, S - 1, c0, cols, row);
           }
           float sc[16];
 #pragma unroll
@@ -632,14 +705,8 @@ w4a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args,
                 for (int j = 0; j < 16; ++j)
                   if (j < valid)
                     store_out_all(multi.out, m0 + c0 + j, n, lqq_scale(v[j], sc[j], w_scale), bias, has_bias, args.out_mode);
-              } else if (args.out_mode == LQ_DT_BF16) {
-                store_cols<LQ_DT_BF16>(args.out, idx0, args.N, v, sc, w_scale, bias, has_bias, valid);
-              } else if (args.out_mode == LQ_DT_F16) {
-                store_cols<LQ_DT_F16>(args.out, idx0, args.N, v, sc, w_scale, bias, has_bias, valid);
-              } else if (args.out_mode == LQ_DT_F32) {
-                store_cols<LQ_DT_F32>(args.out, idx0, args.N, v, sc, w_scale, bias, has_bias, valid);
               } else {
-                store_cols<kOutI32>(args.out, idx0, args.N, v, sc, w_scale, bias, has_bias, valid);
+                store_cols_any(args.out, args.out_mode, idx0, args.N, v, sc, w_scale, bias, has_bias, valid);
               }
             }
           } else {
@@ -679,7 +746,6 @@ w4a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args,
           else ptx::mbar_arrive_remote(leader_accfree + 8 * b);
         }
         TR_ADD(tr_out, tr_o0);
-        if (completes && et == 0) *counter = 0;
       } else {
         // One of the first S - 1 k-ranges of a split tile: sums to this pair's plane.
         int4* own = planes + (size_t)walk.part * 2 * kPlane4 + row;
@@ -704,7 +770,7 @@ w4a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args,
         const long long tr_b0 = TR_NOW();
         __threadfence();
         group_barrier(g);
-        if (et == 0) atomicAdd(counter, 1);
+        if (et == 0) atomicAdd(counters2 + g, 1);
         TR_ADD(tr_psync, tr_b0);
       }
     }
@@ -729,6 +795,15 @@ w4a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args,
   __syncwarp();
   ptx::tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) {
+    // every warp of this CTA is done with the planes of the tile it completed: the counters are zero for the next launch
+    const PairWalk w(args, pair);
+    if (w.completes_tile()) {
+      int32_t* c = args.counters + 2 * ((size_t)w.rt * 2 + rank);
+      c[0] = 0;
+      c[1] = 0;
+    }
+  }
   ptx::cluster_sync_all();
   if (warp == 1) {
     ptx::tc_fence_after();
@@ -809,7 +884,7 @@ bool pair_serves(int M, int N, int K) { return M >= 1 && N >= 256 && N % 256 == 
 // Whether the pair kernel is expected to beat the two-CTAs-per-SM tile kernel on this shape.  Both run whole
 // waves of tiles, so the comparison is between (waves x k-steps x time per k-step) of either, with the times
 // per k-step measured on B200 over the Llama-3.1-8B shapes at 256..8192 tokens (microseconds: pair 0.325, or
-// 0.285 for K >= 8192, plus 9.5 for the prologue and the last epilogue, a tile cut in S costing 1/S of a wave
+// 0.285 for K >= 8192, plus 7.5 for the prologue and the last epilogue, a tile cut in S costing 1/S of a wave
 // plus 27 k-steps; tile 0.58, 0.48 for K >= 8192, 0.44 when there is at most one CTA per SM).  The model
 // reproduces the measured winner at every point of that sweep except ties within 4 %.
 bool pair_prefers(int M, int N, int K) {
@@ -825,7 +900,7 @@ bool pair_prefers(int M, int N, int K) {
   const int r = (int)(tiles_p % p.pairs);
   const int S = p.tail_s;
   const double tail = r == 0 ? 0.0 : S > 1 ? 1.0 / S + 27.0 / kt : 1.0;   // a split tile costs its reduction too
-  const double est_pair = ((double)(tiles_p / p.pairs) + tail) * kt * (kt >= 64 ? 0.285 : 0.325) + 9.5;
+  const double est_pair = ((double)(tiles_p / p.pairs) + tail) * kt * (kt >= 64 ? 0.285 : 0.325) + 7.5;
   return est_pair < 0.97 * est_tile;
 }
 
