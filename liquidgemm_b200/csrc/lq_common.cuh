@@ -92,6 +92,87 @@ __device__ __forceinline__ void store_out_bias(void* y, size_t idx, float v, flo
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Epilogue of the tensor-core kernels, sixteen accumulator columns (tokens) of one channel at a time.  These
+// kernels are bound by instruction issue, and an epilogue that decides the output type, the bias and the
+// ragged edge per element and forms every address with 64-bit arithmetic was measured to cost the CTA-pair
+// kernel 16 % on layers with K = 4096: here the decisions are made once per sixteen elements and an address
+// is one 32 x 32 + 64-bit multiply-add.  kEpiI32 selects raw int32 outputs.
+constexpr int kEpiI32 = 3;
+
+template <int DT, bool BIAS>
+__device__ __forceinline__ uint16_t epi_bits16(int acc, float a_scale, float w_scale, float bias) {
+  const float y = lqq_scale(acc, a_scale, w_scale);
+  if (DT == LQ_DT_BF16) {
+    __nv_bfloat16 t = __float2bfloat16_rn(y);
+    if (BIAS) t = __float2bfloat16_rn(__fadd_rn(__bfloat162float(t), bias));
+    return *reinterpret_cast<uint16_t*>(&t);
+  }
+  __half t = __float2half_rn(y);
+  if (BIAS) t = __float2half_rn(__fadd_rn(__half2float(t), bias));
+  return *reinterpret_cast<uint16_t*>(&t);
+}
+
+// Straight to global memory: element j goes to out + (idx0 + j * ld) elements.
+template <int DT, bool BIAS, bool FULL>
+__device__ __forceinline__ void epi_store_cols_t(void* out, size_t idx0, long ld, const int (&v)[16], const float (&sc)[16],
+                                                 float w_scale, float bias, int valid) {
+  constexpr int ES = (DT == LQ_DT_BF16 || DT == LQ_DT_F16) ? 2 : 4;
+  char* p = static_cast<char*>(out) + idx0 * ES;
+  const uint32_t pitch = (uint32_t)ld * ES;   // a row pitch below 4 GB
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    if (FULL || j < valid) {
+      char* q = p + (uint64_t)pitch * (uint32_t)j;
+      if (DT == kEpiI32) *reinterpret_cast<int32_t*>(q) = v[j];
+      else if (DT == LQ_DT_F32) {
+        const float y = lqq_scale(v[j], sc[j], w_scale);
+        *reinterpret_cast<float*>(q) = BIAS ? __fadd_rn(y, bias) : y;
+      } else {
+        *reinterpret_cast<uint16_t*>(q) = epi_bits16<DT, BIAS>(v[j], sc[j], w_scale, bias);
+      }
+    }
+  }
+}
+template <int DT>
+__device__ __forceinline__ void epi_store_cols_dt(void* out, size_t idx0, long ld, const int (&v)[16], const float (&sc)[16],
+                                                  float w_scale, float bias, bool has_bias, int valid) {
+  if (valid >= 16) {
+    if (has_bias) epi_store_cols_t<DT, true, true>(out, idx0, ld, v, sc, w_scale, bias, valid);
+    else epi_store_cols_t<DT, false, true>(out, idx0, ld, v, sc, w_scale, bias, valid);
+  } else {
+    if (has_bias) epi_store_cols_t<DT, true, false>(out, idx0, ld, v, sc, w_scale, bias, valid);
+    else epi_store_cols_t<DT, false, false>(out, idx0, ld, v, sc, w_scale, bias, valid);
+  }
+}
+// out_mode: LQ_DT_* or kEpiI32; `valid` of the sixteen elements exist (the ragged last token chunk).
+__device__ __forceinline__ void epi_store_cols(void* out, int out_mode, size_t idx0, long ld, const int (&v)[16],
+                                               const float (&sc)[16], float w_scale, float bias, bool has_bias, int valid) {
+  if (out_mode == LQ_DT_BF16) epi_store_cols_dt<LQ_DT_BF16>(out, idx0, ld, v, sc, w_scale, bias, has_bias, valid);
+  else if (out_mode == LQ_DT_F16) epi_store_cols_dt<LQ_DT_F16>(out, idx0, ld, v, sc, w_scale, bias, has_bias, valid);
+  else if (out_mode == LQ_DT_F32) epi_store_cols_dt<LQ_DT_F32>(out, idx0, ld, v, sc, w_scale, bias, has_bias, valid);
+  else epi_store_cols_dt<kEpiI32>(out, idx0, ld, v, sc, w_scale, bias, false, valid);
+}
+
+// Into a shared-memory stage of 2-byte outputs: element j goes to col[j * 128] (the thread's channel column of a
+// [16 tokens][128 channels] block).  out_mode: LQ_DT_BF16 or LQ_DT_F16.
+template <int DT, bool BIAS>
+__device__ __forceinline__ void epi_stage_cols_t(uint16_t* col, const int (&v)[16], const float (&sc)[16], float w_scale,
+                                                 float bias) {
+#pragma unroll
+  for (int j = 0; j < 16; ++j) col[j * 128] = epi_bits16<DT, BIAS>(v[j], sc[j], w_scale, bias);
+}
+__device__ __forceinline__ void epi_stage_cols(uint16_t* col, int out_mode, const int (&v)[16], const float (&sc)[16],
+                                               float w_scale, float bias, bool has_bias) {
+  if (out_mode == LQ_DT_BF16) {
+    if (has_bias) epi_stage_cols_t<LQ_DT_BF16, true>(col, v, sc, w_scale, bias);
+    else epi_stage_cols_t<LQ_DT_BF16, false>(col, v, sc, w_scale, bias);
+  } else {
+    if (has_bias) epi_stage_cols_t<LQ_DT_F16, true>(col, v, sc, w_scale, bias);
+    else epi_stage_cols_t<LQ_DT_F16, false>(col, v, sc, w_scale, bias);
+  }
+}
+
 // Where a kernel's outputs go: the same [M, N] block is written into up to 8 row-major matrices with
 // row stride `ld` elements at column offset `col0`.  One destination with ld = N, col0 = 0 is the
 // ordinary output; several destinations (this GPU's and its peers' full-width output, mapped into this

@@ -67,7 +67,7 @@ constexpr int kScaleBytes = 4 * kBN * 4;  // token scales of the current and the
 constexpr int kSmemBytes = 1024 /* alignment slack */ + kNS * (kXStage + kWStage) + ((kBarBytes + 15) & ~15) + 2 * kOutStage +
                            kScaleBytes;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
-constexpr int kOutI32 = 3;              // internal output mode: raw int32
+constexpr int kOutI32 = kEpiI32;              // internal output mode: raw int32
 static_assert(kSmemBytes <= 232448, "shared memory budget exceeded");
 static_assert(2 * kBN + 32 * kNT <= kTmemCols, "tensor memory budget exceeded");
 
@@ -174,58 +174,7 @@ struct PairWalk {
   }
 };
 
-__device__ __forceinline__ void store_cols_any(void* out, int out_mode, size_t idx0, long ld, const int (&v)[16],
-                                               const float (&sc)[16], float w_scale, float bias, bool has_bias, int valid);
-
 constexpr int kGroupsLast = 2 + kSets;   // warps groups sharing the epilogue of a pair's last tile
-
-__device__ __forceinline__ uint16_t out_bits16(float v, float bias, bool has_bias, int out_mode) {
-  if (out_mode == LQ_DT_BF16) {
-    __nv_bfloat16 t = __float2bfloat16_rn(v);
-    if (has_bias) t = __float2bfloat16_rn(__fadd_rn(__bfloat162float(t), bias));
-    return *reinterpret_cast<uint16_t*>(&t);
-  }
-  __half t = __float2half_rn(v);
-  if (has_bias) t = __float2half_rn(__fadd_rn(__half2float(t), bias));
-  return *reinterpret_cast<uint16_t*>(&t);
-}
-
-// 16 token columns of one channel, straight to global memory: lane = channel, so a warp's store covers 32
-// consecutive channels of one token row (64 contiguous bytes for 2-byte outputs).  DT: LQ_DT_* or kOutI32.
-template <int DT>
-__device__ __forceinline__ void store_cols(void* out, size_t idx0, long ld, const int (&v)[16], const float* sc,
-                                           float w_scale, float bias, bool has_bias, int valid) {
-#pragma unroll
-  for (int j = 0; j < 16; ++j) {
-    if (j < valid) {
-      const size_t idx = idx0 + (size_t)j * ld;
-      if (DT == kOutI32) {
-        reinterpret_cast<int32_t*>(out)[idx] = v[j];
-      } else {
-        const float y = lqq_scale(v[j], sc[j], w_scale);
-        if (DT == LQ_DT_BF16) {
-          __nv_bfloat16 t = __float2bfloat16_rn(y);
-          if (has_bias) t = __float2bfloat16_rn(__fadd_rn(__bfloat162float(t), bias));
-          reinterpret_cast<__nv_bfloat16*>(out)[idx] = t;
-        } else if (DT == LQ_DT_F16) {
-          __half t = __float2half_rn(y);
-          if (has_bias) t = __float2half_rn(__fadd_rn(__half2float(t), bias));
-          reinterpret_cast<__half*>(out)[idx] = t;
-        } else {
-          reinterpret_cast<float*>(out)[idx] = has_bias ? __fadd_rn(y, bias) : y;
-        }
-      }
-    }
-  }
-}
-
-__device__ __forceinline__ void store_cols_any(void* out, int out_mode, size_t idx0, long ld, const int (&v)[16],
-                                               const float (&sc)[16], float w_scale, float bias, bool has_bias, int valid) {
-  if (out_mode == LQ_DT_BF16) store_cols<LQ_DT_BF16>(out, idx0, ld, v, sc, w_scale, bias, has_bias, valid);
-  else if (out_mode == LQ_DT_F16) store_cols<LQ_DT_F16>(out, idx0, ld, v, sc, w_scale, bias, has_bias, valid);
-  else if (out_mode == LQ_DT_F32) store_cols<LQ_DT_F32>(out, idx0, ld, v, sc, w_scale, bias, has_bias, valid);
-  else store_cols<kOutI32>(out, idx0, ld, v, sc, w_scale, bias, has_bias, valid);
-}
 
 // Bounded wait for the planes of a cut tile: both epilogue groups of each of the `need` other pairs have counted
 // themselves in.  Relaxed polls; the caller fences before it reads the planes.
@@ -570,7 +519,7 @@ w4a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args,
 #pragma unroll
           for (int j = 0; j < 16; ++j) sc[j] = (!raw && c0 + j < cols) ? __ldg(args.ascale + m0 + c0 + j) : 0.f;
           ptx::tc_wait_ld();
-          store_cols_any(args.out, args.out_mode, (size_t)(m0 + c0) * args.N + n, args.N, v, sc, w_scale, bias, has_bias,
+          epi_store_cols(args.out, args.out_mode, (size_t)(m0 + c0) * args.N + n, args.N, v, sc, w_scale, bias, has_bias,
                          cols - c0);
         }
         ptx::tc_fence_before();
@@ -706,16 +655,13 @@ w4a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args,
                   if (j < valid)
                     store_out_all(multi.out, m0 + c0 + j, n, lqq_scale(v[j], sc[j], w_scale), bias, has_bias, args.out_mode);
               } else {
-                store_cols_any(args.out, args.out_mode, idx0, args.N, v, sc, w_scale, bias, has_bias, valid);
+                epi_store_cols(args.out, args.out_mode, idx0, args.N, v, sc, w_scale, bias, has_bias, valid);
               }
             }
           } else {
             // Several destinations (peers over NVLink prefer whole 256-byte rows written with 16-byte stores):
             // through shared memory.  A thread holds 16 tokens of ONE channel, the output rows run along the channels.
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-              reinterpret_cast<uint16_t*>(stage)[j * 128 + row] =
-                  n_ok ? out_bits16(lqq_scale(v[j], sc[j], w_scale), bias, has_bias, args.out_mode) : (uint16_t)0;
+            epi_stage_cols(reinterpret_cast<uint16_t*>(stage) + row, args.out_mode, v, sc, w_scale, bias, has_bias);
             group_barrier(g);
 #pragma unroll
             for (int q = 0; q < 2; ++q) {
@@ -883,10 +829,10 @@ bool pair_serves(int M, int N, int K) { return M >= 1 && N >= 256 && N % 256 == 
 
 // Whether the pair kernel is expected to beat the two-CTAs-per-SM tile kernel on this shape.  Both run whole
 // waves of tiles, so the comparison is between (waves x k-steps x time per k-step) of either, with the times
-// per k-step measured on B200 over the Llama-3.1-8B shapes at 256..8192 tokens (microseconds: pair 0.325, or
-// 0.285 for K >= 8192, plus 7.5 for the prologue and the last epilogue, a tile cut in S costing 1/S of a wave
-// plus 27 k-steps; tile 0.58, 0.48 for K >= 8192, 0.44 when there is at most one CTA per SM).  The model
-// reproduces the measured winner at every point of that sweep except ties within 4 %.
+// per k-step measured on B200 over the Llama-3.1-8B shapes at 256..8192 tokens in one run (microseconds: pair
+// 0.335, or 0.30 for K >= 8192, plus 3 for the prologue and the last epilogue, a tile cut in S costing 1/S of
+// a wave plus 27 k-steps; tile 0.53, 0.45 for K >= 8192, 0.40 when there is at most one CTA per SM).  The
+// model reproduces the measured winner at every point of that sweep except ties within 4 %.
 bool pair_prefers(int M, int N, int K) {
   if (!pair_serves(M, N, K)) return false;
   const int kt = K / 128;
@@ -894,13 +840,13 @@ bool pair_prefers(int M, int N, int K) {
   const long tiles_t = (long)(N / 128) * ((M + 127) / 128);
   if (tiles_t * 2 <= 2L * sms) return false;   // the tile kernel splits K here: a small problem, it wins
   const double waves_t = (double)((tiles_t + 2L * sms - 1) / (2L * sms));
-  const double est_tile = waves_t * kt * (tiles_t <= sms ? 0.44 : kt >= 64 ? 0.48 : 0.58);
+  const double est_tile = waves_t * kt * (tiles_t <= sms ? 0.40 : kt >= 64 ? 0.45 : 0.53);
   const pairk::PairPlan p = pairk::plan(M, N, K);
   const long tiles_p = (long)p.n2_tiles * p.m_tiles;
   const int r = (int)(tiles_p % p.pairs);
   const int S = p.tail_s;
   const double tail = r == 0 ? 0.0 : S > 1 ? 1.0 / S + 27.0 / kt : 1.0;   // a split tile costs its reduction too
-  const double est_pair = ((double)(tiles_p / p.pairs) + tail) * kt * (kt >= 64 ? 0.285 : 0.325) + 7.5;
+  const double est_pair = ((double)(tiles_p / p.pairs) + tail) * kt * (kt >= 64 ? 0.30 : 0.335) + 3.0;
   return est_pair < 0.97 * est_tile;
 }
 

@@ -45,7 +45,7 @@ constexpr int kI8TileBytes = 16384;
 constexpr int kSets = 2;
 constexpr int kThreads = 64 + 128 * kSets;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
-constexpr int kOutI32 = 3;
+constexpr int kOutI32 = kEpiI32;
 
 // Pipeline studies (-DLQ_PIPELINE_TRACE, a build of its own): %globaltimer stamps of every CTA's milestones, read
 // back with lq_debug_read_tile_trace().  The product build compiles none of it.
@@ -88,18 +88,6 @@ struct TcCfg {
                                     kSets * kOutStage;
   static_assert(kColsNeeded <= 512, "tensor memory budget exceeded");
 };
-
-// Round to the output type (with the optional bias added to the rounded value) and return the 16 bits.
-__device__ __forceinline__ uint16_t out_bits16(float v, float bias, bool has_bias, int out_mode) {
-  if (out_mode == LQ_DT_BF16) {
-    __nv_bfloat16 t = __float2bfloat16_rn(v);
-    if (has_bias) t = __float2bfloat16_rn(__fadd_rn(__bfloat162float(t), bias));
-    return *reinterpret_cast<uint16_t*>(&t);
-  }
-  __half t = __float2half_rn(v);
-  if (has_bias) t = __float2half_rn(__fadd_rn(__half2float(t), bias));
-  return *reinterpret_cast<uint16_t*>(&t);
-}
 
 template <int BN, int NS, int NT, bool W4, bool MULTI>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -332,10 +320,8 @@ w4a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs args
           // A thread holds 16 tokens of ONE channel, the output rows run along the channels: stored
           // directly, a warp writes 64 contiguous bytes per token.  Through shared memory the set writes
           // whole 256-byte rows with 16-byte stores instead (local HBM and NVLink alike prefer those).
-#pragma unroll
-          for (int j = 0; j < 16; ++j)
-            reinterpret_cast<uint16_t*>(stage)[j * 128 + row] =
-                n_ok ? out_bits16(lqq_scale(v[j], sc[j], w_scale), bias, has_bias, args.out_mode) : (uint16_t)0;
+          // (rows past N hold values nobody copies out: w_scale and bias are zero there)
+          epi_stage_cols(reinterpret_cast<uint16_t*>(stage) + row, args.out_mode, v, sc, w_scale, bias, has_bias);
           if (set == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
           else asm volatile("bar.sync 2, 128;" ::: "memory");
 #pragma unroll
@@ -359,16 +345,17 @@ w4a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs args
           if (set == 0) asm volatile("bar.sync 1, 128;" ::: "memory");   // the stage is rewritten by the next chunk
           else asm volatile("bar.sync 2, 128;" ::: "memory");
         } else if (n_ok) {
+          const size_t idx0 = (size_t)(m0 + c0) * args.N + n;
+          const int valid = args.M - (m0 + c0);
+          if (args.out_mode == kOutI32) {
+            epi_store_cols(plane, kEpiI32, idx0, args.N, v, sc, w_scale, bias, false, valid);
+          } else if constexpr (MULTI) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int m = m0 + c0 + j;
-            if (m < args.M) {
-              const size_t idx = (size_t)m * args.N + n;
-              if (args.out_mode == kOutI32) plane[idx] = v[j];
-              else if constexpr (MULTI)
-                store_out_all(multi.out, m, n, lqq_scale(v[j], sc[j], w_scale), bias, has_bias, args.out_mode);
-              else store_out_bias(args.out, idx, lqq_scale(v[j], sc[j], w_scale), bias, has_bias, args.out_mode);
-            }
+            for (int j = 0; j < 16; ++j)
+              if (j < valid)
+                store_out_all(multi.out, m0 + c0 + j, n, lqq_scale(v[j], sc[j], w_scale), bias, has_bias, args.out_mode);
+          } else {
+            epi_store_cols(args.out, args.out_mode, idx0, args.N, v, sc, w_scale, bias, has_bias, valid);
           }
         }
       }
