@@ -104,14 +104,14 @@ struct Args {
   int vec_out;             // several destinations, 2-byte outputs whose rows allow 16-byte stores: stage through smem
 };
 
-// Split factor of the tiles of the last, partial wave (r tiles on P pairs).  A tile cut along k costs the pair
-// that completes it a read of the other pairs' sums in its last, exposed epilogue, and more pairs working in the
-// last wave run at a lower clock under the power limit than the few that would otherwise finish it alone:
-// measured on 4096 x 14336 (112 k-steps) the cut saves 13 % at 1024 tokens, 5 % at 2048 and 2 % at 8192; on
-// layers of 32 k-steps it loses 2-4 %.  So only long tiles are cut, and only when at least half of the pairs
-// would otherwise idle.
+// Split factor of the tiles of the last, partial wave (r tiles on P pairs): when at least half of the pairs would
+// otherwise idle, each tile is cut into equal k-ranges of 16 k-steps or more.  A cut costs the pair that
+// completes the tile a read of the other pairs' sums in its last, exposed epilogue, and more pairs working in
+// the last wave run at a lower clock under the power limit than the few that would otherwise finish it alone.
+// Measured against whole tiles: 4096 x 14336 (112 k-steps) 16 % faster at 1024 tokens, 6 % at 2048, 4 % at 3072
+// and 8192; layers of 32 k-steps 1-3 % faster where it applies.
 inline int tail_split(int r, int P, int kt) {
-  if (r == 0 || 2 * r > P || kt < 64) return 1;
+  if (r == 0 || 2 * r > P || kt < 32) return 1;
   int S = P / r;
   if (S > kt / 16) S = kt / 16;
   return S < 1 ? 1 : S;
@@ -139,11 +139,11 @@ struct PairWalk {
     tail_first = tail_left && part < S - 1;
   }
   __device__ int segments() const { return full_waves + (has_tail ? 1 : 0); }
-  // Whether the dequant warps share the epilogue of the pair's last segment: a whole tile, and long enough that a
-  // dequant warp done with it (at most kNT + kSets k-steps ahead of the MMA warp) cannot meet the accumulator
-  // barrier a whole use behind, where the parity it waits for would read as complete.  (Sharing the completion of
-  // a cut tile as well was measured: 5 us faster with three k-ranges, 1-5 us slower with two; not kept.)
-  __device__ bool last_shared() const { return kt >= 8 && ((has_tail && !tail_first) ? S == 1 : full_waves > 0); }
+  // Whether the dequant warps share the epilogue of the pair's last segment: a whole tile or the last k-range of
+  // a cut one (at least 16 k-steps), long enough that a dequant warp done with it (at most kNT + kSets k-steps
+  // ahead of the MMA warp) cannot meet the accumulator barrier a whole use behind, where the parity it waits
+  // for would read as complete.
+  __device__ bool last_shared() const { return kt >= 8 && ((has_tail && !tail_first) || full_waves > 0); }
   // whether this pair holds the last k-range of a cut tile
   __device__ bool completes_tile() const { return has_tail && S > 1 && part == S - 1; }
   __device__ void tail(Segment& s) {
@@ -190,20 +190,31 @@ __device__ __forceinline__ bool planes_ready(const int32_t* counters2, int need,
   }
 }
 
-// Adds the other pairs' sums of one 16-token chunk (planes of int4: [token / 4][channel]) and zeroes them.
-__device__ __forceinline__ void add_planes(int (&v)[16], int4* planes, size_t plane_stride, int others, int c0, int cols,
-                                           int row) {
+// Adds the other pairs' sums of one 16-token chunk (planes of int4: [token / 4][channel]).  The planes are zeroed
+// in a pass of their own afterwards (zero_planes): a load issued behind a store to the same plane waited for
+// it, chunk after chunk, which made the completing epilogue 2.5 times as long as an ordinary one (trace build:
+// 79 000 cycles against 30 000 without the loads and 36 000 without the stores).
+__device__ __forceinline__ void add_planes(int (&v)[16], const int4* planes, size_t plane_stride, int others, int c0,
+                                           int cols, int row) {
 #pragma unroll 1
   for (int q = 0; q < others; ++q) {
-    int4* pl = planes + (size_t)q * plane_stride + (size_t)(c0 >> 2) * 128 + row;
+    const int4* pl = planes + (size_t)q * plane_stride + (size_t)(c0 >> 2) * 128 + row;
     int4 t[4];
 #pragma unroll
     for (int jj = 0; jj < 4; ++jj) t[jj] = (c0 + 4 * jj < cols) ? __ldcg(pl + jj * 128) : make_int4(0, 0, 0, 0);
 #pragma unroll
     for (int jj = 0; jj < 4; ++jj) {
       v[4 * jj] += t[jj].x; v[4 * jj + 1] += t[jj].y; v[4 * jj + 2] += t[jj].z; v[4 * jj + 3] += t[jj].w;
-      if (c0 + 4 * jj < cols) __stcg(pl + jj * 128, make_int4(0, 0, 0, 0));
     }
+  }
+}
+__device__ __forceinline__ void zero_planes(int4* planes, size_t plane_stride, int others, int c0, int cols, int row) {
+#pragma unroll 1
+  for (int q = 0; q < others; ++q) {
+    int4* pl = planes + (size_t)q * plane_stride + (size_t)(c0 >> 2) * 128 + row;
+#pragma unroll
+    for (int jj = 0; jj < 4; ++jj)
+      if (c0 + 4 * jj < cols) __stcg(pl + jj * 128, make_int4(0, 0, 0, 0));
   }
 }
 
@@ -499,8 +510,17 @@ w4a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args,
         done = ptx::mbar_wait_bounded(bar_accfull + 8 * b, phb, kWaitLimitNs);
         if (!done) atomicExch(args.status, 126);
       }
+      constexpr size_t kPlane4 = (size_t)128 * kBN / 4;
+      const int S = walk.S;
+      const bool completes = !sg.whole;                // the last k-range of a cut tile: add the other pairs' planes
+      int4* planes = reinterpret_cast<int4*>(args.slots) + ((size_t)walk.rt * (S - 1) * 2 + rank) * kPlane4;
+      if (done && completes && lane == 0) {
+        done = planes_ready(args.counters + 2 * ((size_t)walk.rt * 2 + rank), S - 1, kWaitLimitNs);
+        if (!done) atomicExch(args.status, 130);
+      }
       done = __shfl_sync(0xffffffffu, done ? 1 : 0, 0) != 0;
       if (done) {
+        if (completes) __threadfence();
         ptx::tc_fence_after();
         const bool raw = args.out_mode == kOutI32;
         const bool has_bias = !raw && args.bias != nullptr;
@@ -519,8 +539,13 @@ w4a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args,
 #pragma unroll
           for (int j = 0; j < 16; ++j) sc[j] = (!raw && c0 + j < cols) ? __ldg(args.ascale + m0 + c0 + j) : 0.f;
           ptx::tc_wait_ld();
+          if (completes) add_planes(v, planes, 2 * kPlane4, S - 1, c0, cols, row);
           epi_store_cols(args.out, args.out_mode, (size_t)(m0 + c0) * args.N + n, args.N, v, sc, w_scale, bias, has_bias,
                          cols - c0);
+        }
+        if (completes) {
+#pragma unroll 1
+          for (int c0 = 16 * (2 + my_set); c0 < cols; c0 += 16 * kGroupsLast) zero_planes(planes, 2 * kPlane4, S - 1, c0, cols, row);
         }
         ptx::tc_fence_before();
       }
@@ -691,6 +716,10 @@ w4a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const Args args,
           if (rank == 0) ptx::mbar_arrive(bar_accfree + 8 * b);
           else ptx::mbar_arrive_remote(leader_accfree + 8 * b);
         }
+        if (completes) {
+#pragma unroll 1
+          for (int c0 = 16 * g; c0 < cols; c0 += cstep) zero_planes(planes, 2 * kPlane4, S - 1, c0, cols, row);
+        }
         TR_ADD(tr_out, tr_o0);
       } else {
         // One of the first S - 1 k-ranges of a split tile: sums to this pair's plane.
@@ -831,7 +860,7 @@ bool pair_serves(int M, int N, int K) { return M >= 1 && N >= 256 && N % 256 == 
 // waves of tiles, so the comparison is between (waves x k-steps x time per k-step) of either, with the times
 // per k-step measured on B200 over the Llama-3.1-8B shapes at 256..8192 tokens in one run (microseconds: pair
 // 0.335, or 0.30 for K >= 8192, plus 3 for the prologue and the last epilogue, a tile cut in S costing 1/S of
-// a wave plus 27 k-steps; tile 0.53, 0.45 for K >= 8192, 0.40 when there is at most one CTA per SM).  The
+// a wave plus 20 k-steps; tile 0.53, 0.45 for K >= 8192, 0.40 when there is at most one CTA per SM).  The
 // model reproduces the measured winner at every point of that sweep except ties within 4 %.
 bool pair_prefers(int M, int N, int K) {
   if (!pair_serves(M, N, K)) return false;
@@ -845,7 +874,7 @@ bool pair_prefers(int M, int N, int K) {
   const long tiles_p = (long)p.n2_tiles * p.m_tiles;
   const int r = (int)(tiles_p % p.pairs);
   const int S = p.tail_s;
-  const double tail = r == 0 ? 0.0 : S > 1 ? 1.0 / S + 27.0 / kt : 1.0;   // a split tile costs its reduction too
+  const double tail = r == 0 ? 0.0 : S > 1 ? 1.0 / S + 20.0 / kt : 1.0;   // a split tile costs its reduction too
   const double est_pair = ((double)(tiles_p / p.pairs) + tail) * kt * (kt >= 64 ? 0.30 : 0.335) + 3.0;
   return est_pair < 0.97 * est_tile;
 }
