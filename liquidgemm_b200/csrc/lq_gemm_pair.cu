@@ -860,7 +860,7 @@ bool pair_serves(int M, int N, int K) { return M >= 1 && N >= 256 && N % 256 == 
 // waves of tiles, so the comparison is between (waves x k-steps x time per k-step) of either, with the times
 // per k-step measured on B200 over the Llama-3.1-8B shapes at 256..8192 tokens in one run (microseconds: pair
 // 0.335, or 0.30 for K >= 8192, plus 3 for the prologue and the last epilogue, a tile cut in S costing 1/S of
-// a wave plus 20 k-steps; tile 0.53, 0.45 for K >= 8192, 0.40 when there is at most one CTA per SM).  The
+// a wave plus 20 k-steps (8 for K < 8192); tile 0.53, 0.45 for K >= 8192, 0.40 when there is at most one CTA per SM).  The
 // model reproduces the measured winner at every point of that sweep except ties within 4 %.
 bool pair_prefers(int M, int N, int K) {
   if (!pair_serves(M, N, K)) return false;
@@ -874,7 +874,7 @@ bool pair_prefers(int M, int N, int K) {
   const long tiles_p = (long)p.n2_tiles * p.m_tiles;
   const int r = (int)(tiles_p % p.pairs);
   const int S = p.tail_s;
-  const double tail = r == 0 ? 0.0 : S > 1 ? 1.0 / S + 20.0 / kt : 1.0;   // a split tile costs its reduction too
+  const double tail = r == 0 ? 0.0 : S > 1 ? 1.0 / S + (kt >= 64 ? 20.0 : 8.0) / kt : 1.0;   // a split tile costs its reduction too
   const double est_pair = ((double)(tiles_p / p.pairs) + tail) * kt * (kt >= 64 ? 0.30 : 0.335) + 3.0;
   return est_pair < 0.97 * est_tile;
 }

@@ -79,13 +79,13 @@ def test_bias_is_added_to_the_rounded_output(ops, out_dtype):
     ops.poll_status()
 
 
-@pytest.mark.parametrize("M", [15360, 19918])
-def test_split_tail_and_clean_workspace(ops, M):
+@pytest.mark.parametrize("M,K", [(15360, 8192), (19918, 8192), (19918, 4096)])
+def test_split_tail_and_clean_workspace(ops, M, K):
     """80 long tiles on 74 pairs: the six tiles of the last wave are cut along k between the pairs (four ranges
-    each; 104 tiles, the last one ragged: thirty tiles in two ranges each) and summed through the workspace
-    planes, which the completing pair re-zeroes: a second call on the same cached workspace gives the same bits,
-    and so does a decode call (which shares that workspace) afterwards."""
-    N, K = 256, 8192
+    each; 104 tiles, the last one ragged: thirty tiles in two ranges each, also with the shortest K that is cut)
+    and summed through the workspace planes, which the completing pair re-zeroes: a second call on the same
+    cached workspace gives the same bits, and so does a decode call (which shares that workspace) afterwards."""
+    N = 256
     qw = random_lqq(N, K, 64, seed=21)
     tq = to_torch_qw(qw)
     x, ascale = random_tokens(M, K, seed=5)
