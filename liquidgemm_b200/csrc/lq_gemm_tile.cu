@@ -304,6 +304,7 @@ w4a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs args
       const float bias = (has_bias && n_ok) ? load_bias(args.bias, n, args.out_mode) : 0.f;
       int32_t* plane = reinterpret_cast<int32_t*>(args.out) + (size_t)z * args.M * args.N;
       const bool vec = args.vec_out != 0;   // uniform over the CTA
+      const bool sc_vec = (reinterpret_cast<uintptr_t>(args.ascale) & 15u) == 0;   // 16-byte loads of the token scales
       const int q_in_set = (threadIdx.x - 64) & 127;
       uint8_t* stage = out_stage + set * Cfg::kOutStage;
 #pragma unroll 1
@@ -311,11 +312,23 @@ w4a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs args
         if (m0 + c0 >= args.M) break;  // uniform over the set
         int v[16];
         ptx::tmem_ld16(tmem_acc + lane_addr + c0, v);
-        ptx::tc_wait_ld();
+        // token scales of the chunk, fetched while the tensor-memory load is in flight
         float sc[16];
+        if (args.out_mode == kOutI32) {
 #pragma unroll
-        for (int j = 0; j < 16; ++j)   // all loads of the chunk first: one round trip
-          sc[j] = (args.out_mode != kOutI32 && m0 + c0 + j < args.M) ? __ldg(args.ascale + m0 + c0 + j) : 0.f;
+          for (int j = 0; j < 16; ++j) sc[j] = 0.f;
+        } else if (sc_vec && m0 + c0 + 16 <= args.M) {
+          const float4* sp = reinterpret_cast<const float4*>(args.ascale + m0 + c0);
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            const float4 f = __ldg(sp + q4);
+            sc[4 * q4] = f.x; sc[4 * q4 + 1] = f.y; sc[4 * q4 + 2] = f.z; sc[4 * q4 + 3] = f.w;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) sc[j] = (m0 + c0 + j < args.M) ? __ldg(args.ascale + m0 + c0 + j) : 0.f;
+        }
+        ptx::tc_wait_ld();
         if (vec) {
           // A thread holds 16 tokens of ONE channel, the output rows run along the channels: stored
           // directly, a warp writes 64 contiguous bytes per token.  Through shared memory the set writes
