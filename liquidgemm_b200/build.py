@@ -14,8 +14,8 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
-SOURCES = ["lq_api.cu", "lq_elementwise.cu", "lq_gemv.cu", "lq_gemm_tc.cu", "lq_gemm_tile.cu", "lq_gemv_blob.cu", "lq_decode_tc.cu", "lq_gemm_pair.cu", "lq_quantize.cu", "lq_host.cu"]
-HEADERS = ["lq_common.cuh", "lq_tc_ptx.cuh", "lq_sched.cuh", os.path.join("..", "..", "include", "liquidgemm_b200.h")]
+SOURCES = ["lq_api.cu", "lq_elementwise.cu", "lq_gemv.cu", "lq_gemm_tc.cu", "lq_gemm_tile.cu", "lq_gemv_blob.cu", "lq_decode_tc.cu", "lq_gemm_pair.cu", "lq_i8_pair.cu", "lq_quantize.cu", "lq_host.cu"]
+HEADERS = ["lq_common.cuh", "lq_tc_ptx.cuh", "lq_sched.cuh", "lq_pair_common.cuh", os.path.join("..", "..", "include", "liquidgemm_b200.h")]
 LIB_PATH = os.path.join(HERE, "_lq_b200.so")
 # Measurement-only kernels (building-block rates; nothing in the product calls them): a library of their own,
 # built on request with ``python -m liquidgemm_b200.build --debug`` and loaded by liquidgemm_b200.microbench.

@@ -68,6 +68,9 @@ int run_gemv_blob_ws(const int8_t* x, const uint8_t* blob, const float* ascale, 
                      size_t ws_bytes, cudaStream_t st);  // lq_gemv_blob.cu
 int decode_tc_grid(int N, int K);                                            // lq_decode_tc.cu
 bool pair_serves(int M, int N, int K);                                       // lq_gemm_pair.cu
+bool i8_pair_serves(int M, int N, int K);                                    // lq_i8_pair.cu
+int run_i8_pair_gemm(const int8_t* x, const int8_t* w, const float* ascale, const float* s1, void* out, int out_mode,
+                     int M, int N, int K, cudaStream_t st);
 bool pair_prefers(int M, int N, int K);                                      // lq_gemm_pair.cu
 size_t pair_workspace_bytes(int M, int N, int K);                                // lq_gemm_pair.cu
 int pair_grid(int M, int N, int K);                                              // lq_gemm_pair.cu
@@ -907,6 +910,12 @@ int lq_w4a8_gemm_v1(const int8_t* x_i8, const uint8_t* nibbles, const uint8_t* s
   return run_gemm<kBlob>(x_i8, blob, ascale, s1, y, LQ_DT_F32, M, N, K, 1, nullptr, 0, st);
 }
 
+// LQ_I8_PAIR=0 keeps every INT8 GEMM on the one-CTA persistent kernel (read at every call: a measurement switch).
+static bool i8_pair_enabled() {
+  const char* e = getenv("LQ_I8_PAIR");
+  return !(e && e[0] == '0');
+}
+
 static int i8_common(const int8_t* a, const int8_t* b, const float* a_scale, const float* b_scale, void* out,
                      int out_mode, int M, int N, int K, void* stream) {
   if (!a || !b || !out || M < 0 || N <= 0 || K <= 0) return LQ_ERR_BAD_ARG;
@@ -914,6 +923,8 @@ static int i8_common(const int8_t* a, const int8_t* b, const float* a_scale, con
   if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) % 16) return LQ_ERR_BAD_ARG;
   if (M == 0) return LQ_OK;
   // whole-tile scheduling: the plain INT8 entry points take no workspace
+  if (i8_pair_serves(M, N, K) && i8_pair_enabled())
+    return run_i8_pair_gemm(a, b, a_scale, b_scale, out, out_mode, M, N, K, as_stream(stream));
   return run_gemm<kInt8>(a, b, a_scale, b_scale, out, out_mode, M, N, K, 1, nullptr, 0,
                          as_stream(stream));
 }

@@ -355,6 +355,18 @@ __device__ __forceinline__ void mma_i8_ts_pair(uint32_t d_tmem, uint32_t a_tmem,
       "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// The same with A read from shared memory: each CTA holds its 128 rows of A at the same offset.
+__device__ __forceinline__ void mma_i8_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t"
+      "}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // Arrive on the barrier at this shared-memory offset in BOTH CTAs once every MMA issued so far has completed.
 __device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
   const uint16_t mask = 3;

@@ -79,10 +79,11 @@ def test_bias_is_added_to_the_rounded_output(ops, out_dtype):
     ops.poll_status()
 
 
-@pytest.mark.parametrize("M,K", [(15360, 8192), (19918, 8192), (19918, 4096)])
+@pytest.mark.parametrize("M,K", [(15360, 8192), (19918, 8192), (19918, 4096), (18816, 8192), (15644, 14336)])
 def test_split_tail_and_clean_workspace(ops, M, K):
     """80 long tiles on 74 pairs: the six tiles of the last wave are cut along k between the pairs (four ranges
-    each; 104 tiles, the last one ragged: thirty tiles in two ranges each, also with the shortest K that is cut)
+    each; 104 tiles, the last one ragged: thirty tiles in two ranges each, also with the shortest K that is cut;
+    98 tiles: three ranges; 82 tiles of 112 k-steps, the last one ragged: seven ranges)
     and summed through the workspace planes, which the completing pair re-zeroes: a second call on the same
     cached workspace gives the same bits, and so does a decode call (which shares that workspace) afterwards."""
     N = 256
@@ -103,6 +104,40 @@ def test_split_tail_and_clean_workspace(ops, M, K):
     y8 = torch.ops.liquidgemm.w4a8_wgmma_rs_fused(xt[:8].contiguous(), w, tq.s_u8, tq.offset_a, at[:8].contiguous(), tq.s1,
                                                   N, K, 64, 0)
     assert_bits_equal(y8, O.w4a8_matmul(x[:8], ascale[:8], qw), 0, "decode call after the pair kernel")
+    ops.poll_status()
+
+
+@pytest.mark.parametrize("out_dtype", [0, 2])
+def test_cut_tiles_with_bias_and_two_destinations(ops, out_dtype):
+    """The completing pair's epilogue in its other forms: bias, float32 outputs, and the gather-by-stores form
+    (two destinations; 2-byte outputs go through the staged 16-byte stores, float32 through the direct ones)."""
+    M, N, K = 19918, 256, 4096
+    qw = random_lqq(N, K, 64, seed=17)
+    tq = to_torch_qw(qw)
+    x, ascale = random_tokens(M, K, seed=9)
+    xt, at = torch.from_numpy(x).cuda(), torch.from_numpy(ascale).cuda()
+    rng = np.random.default_rng(6)
+    dt = [torch.bfloat16, torch.float16, torch.float32][out_dtype]
+    bias = torch.from_numpy(rng.standard_normal(N).astype(np.float32)).to(dt)
+    blob = ops.repack_rs_weight(tq).reshape(-1)
+    ref = torch._int_mm(xt, ops.dequant_weight_i8(tq).t())
+    want = torch.ops.liquidgemm.scale_epilogue(ref, at, tq.s1, out_dtype)
+    y = torch.ops.liquidgemm.w4a8_linear_bias(xt, blob, at, tq.s1, bias.cuda(), N, K, out_dtype)
+    rows = slice(M - 40, M)                                   # the ragged last tile is one of the cut ones
+    assert_bits_equal(y[rows], with_bias_f32(O.w4a8_matmul(x[rows], ascale[rows], qw), bits(bias), out_dtype), out_dtype,
+                      "cut tile with bias")
+    if out_dtype == 2:
+        assert torch.equal(y, want + bias.cuda())             # float32: one addition, exact against torch
+    NF, col0 = 768, 256
+    outs = [torch.full((M, NF), -1.0, dtype=dt, device="cuda") for _ in range(2)]
+    ops.gemm_fused_scatter(xt, blob, at, tq.s1, [o.data_ptr() for o in outs], NF, col0, N, K, out_dtype)
+    torch.cuda.synchronize()
+    for o in outs:
+        assert torch.equal(o[:, col0:col0 + N], want)
+        assert bool((o[:, :col0] == -1).all()) and bool((o[:, col0 + N:] == -1).all())
+    y8 = torch.ops.liquidgemm.w4a8_wgmma_rs_fused(xt[:8].contiguous(), ops.repack_rs_weight(tq), tq.s_u8, tq.offset_a,
+                                                  at[:8].contiguous(), tq.s1, N, K, 64, 0)
+    assert_bits_equal(y8, O.w4a8_matmul(x[:8], ascale[:8], qw), 0, "decode call on the shared workspace afterwards")
     ops.poll_status()
 
 
