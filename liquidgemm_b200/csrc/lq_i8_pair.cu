@@ -66,20 +66,6 @@ struct Args {
   int tail_s;              // always 1: whole tiles
 };
 
-// Tile index -> (channel block, token tile).  Tiles are numbered in groups of kGroupM token tiles, token tiles
-// fastest inside a group, so that the 74 tiles the pairs work on at one time share 8 token tiles and about 9
-// channel blocks: 17 MB of operands per wave instead of the 75 MB of a wave along one token tile (INT8 weights
-// of a wide layer do not stay in L2 beside the outputs: 28672 x 4096 ran DRAM-bound at 2.57 POPS before).
-constexpr int kGroupM = 8;
-__device__ __forceinline__ void tile_coords(int tile, int n2_tiles, int m_tiles, int& n2, int& mt) {
-  const int per_group = kGroupM * n2_tiles;
-  const int group = tile / per_group, in_group = tile - group * per_group;
-  const int first = group * kGroupM;
-  const int gm = (m_tiles - first) < kGroupM ? (m_tiles - first) : kGroupM;
-  mt = first + in_group % gm;
-  n2 = in_group / gm;
-}
-
 __device__ __forceinline__ void group_bar(int g) { asm volatile("bar.sync %0, 128;" ::"r"(g + 1) : "memory"); }
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
@@ -144,7 +130,7 @@ i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
       bool ok = true;
       while (ok && walk.next(sg)) {
         int n2, mt;
-        tile_coords(sg.tile, args.n2_tiles, args.m_tiles, n2, mt);
+        tile_coords(sg.tile, args.n2_tiles, args.m_tiles, kGroupM, n2, mt);
         const int row0 = weights ? (2 * n2 + (int)rank) * 128 : mt * kBN + (int)rank * kHalf;
         for (int kt = sg.kb; kt < sg.ke; ++kt) {
           if (!ptx::mbar_wait_bounded(bar_empty + 8 * ring.s, ring.ph ^ 1u, kWaitLimitNs)) {
@@ -265,7 +251,7 @@ i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
         wflag[fslot] = done ? 1 : 0;
       }
       int n2, mt;
-      tile_coords(sg.tile, args.n2_tiles, args.m_tiles, n2, mt);
+      tile_coords(sg.tile, args.n2_tiles, args.m_tiles, kGroupM, n2, mt);
       const int m0 = mt * kBN;
       const long n = (long)(2 * n2 + (int)rank) * 128 + row;
       const int cols = (args.M - m0) < kBN ? (args.M - m0) : kBN;   // valid token columns of this tile

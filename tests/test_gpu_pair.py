@@ -161,6 +161,25 @@ def test_multi_destination_epilogue(ops):
     ops.poll_status()
 
 
+def test_grouped_tile_order_with_a_cut_last_wave(ops):
+    """Weights too large to stay in L2 are walked in groups of eight token tiles (here 4096 x 28672: 58.7 MB of
+    4-bit tiles, 160 tiles of which the last twelve are cut in six k-ranges each)."""
+    M, N, K = 1920, 4096, 28672
+    qw = random_lqq(N, K, 64, seed=5)
+    tq = to_torch_qw(qw)
+    x, ascale = random_tokens(M, K, seed=7)
+    xt, at = torch.from_numpy(x).cuda(), torch.from_numpy(ascale).cuda()
+    w = ops.repack_rs_weight(tq)
+    ref = torch._int_mm(xt, ops.dequant_weight_i8(tq).t())
+    acc = torch.ops.liquidgemm.w4a8_wgmma_rs(xt, w, tq.s_u8, tq.s_u8, tq.offset_a, N, K, 64, True)
+    assert torch.equal(acc, ref)
+    y = torch.ops.liquidgemm.w4a8_wgmma_rs_fused(xt, w, tq.s_u8, tq.offset_a, at, tq.s1, N, K, 64, 0)
+    assert torch.equal(y, torch.ops.liquidgemm.scale_epilogue(ref, at, tq.s1, 0))
+    rows = slice(M - 8, M)
+    assert_bits_equal(y[rows], O.w4a8_matmul(x[rows], ascale[rows], qw), 0, "rows of a cut tile against the oracle")
+    ops.poll_status()
+
+
 @pytest.mark.parametrize("name,M", [("qkv", 2048), ("o", 512), ("gate_up", 2048), ("down", 8192)])
 def test_full_size_against_exact_int8_gemm(ops, name, M):
     N, K = LLAMA8B[name]
