@@ -352,15 +352,36 @@ def run_one(name, M, reps=3):
             "alg_GBps": round(algorithmic_bytes(M, N, K) / t / 1e3, 1)}
 
 
+def run_one_i8(name, M, reps=3):
+    """One (shape, M) point of the INT8 x INT8 operator (``i8_gemm_scaled``, the plugin's INT8-weights mode) beside
+    cuBLASLt's INT8 GEMM (``torch._int_mm``: int32 outputs, no scaling): microseconds and TOPS of either."""
+    N, K = SHAPES[name]
+    a = torch.randint(-127, 128, (M, K), dtype=torch.int8, device="cuda")
+    ws = [torch.randint(-127, 128, (N, K), dtype=torch.int8, device="cuda") for _ in range(3)]
+    sa = torch.rand(M, device="cuda") + 0.5
+    sb = torch.rand(N, device="cuda") + 0.5
+    t = graph_time_us(lambda i: torch.ops.liquidgemm.i8_gemm_scaled(a, ws[i % 3], sa, sb, 0), 3, reps)
+    wt = [w.t() for w in ws]
+    t2 = graph_time_us(lambda i: torch._int_mm(a, wt[i % 3]), 3, reps)
+    ops_ = 2.0 * M * N * K / 1e6
+    return {"shape": name, "M": M, "us": round(t, 2), "TOPS": round(ops_ / t, 1), "cublaslt_int8_us": round(t2, 2),
+            "cublaslt_int8_TOPS": round(ops_ / t2, 1)}
+
+
 if __name__ == "__main__":
     # ``python -m liquidgemm_b200.benchlib <hbm_gbs>``: single-GPU extras as one JSON object on stdout
     # (bench.py runs this in a child process so that the headline numbers never depend on it);
-    # ``python -m liquidgemm_b200.benchlib one <qkv|gate_up|down> <M>``: a single point of the sweep.
+    # ``python -m liquidgemm_b200.benchlib one <qkv|gate_up|down> <M>``: a single point of the sweep;
+    # ``... one_i8 <shape> <M>``: the same for the INT8 x INT8 operator beside cuBLASLt's INT8 GEMM.
     import json
     import sys
     torch.cuda.set_device(0)
     if len(sys.argv) > 1 and sys.argv[1] == "one":
         print(json.dumps(run_one(sys.argv[2], int(sys.argv[3]))))
+        sys.exit(0)
+    if len(sys.argv) > 1 and sys.argv[1] == "one_i8":
+        from . import ops as _ops  # noqa: F401  (registers torch.ops.liquidgemm)
+        print(json.dumps(run_one_i8(sys.argv[2], int(sys.argv[3]))))
         sys.exit(0)
     print(json.dumps(run_extras(1, 0, 0, {"hbm_gbs": float(sys.argv[1]) if len(sys.argv) > 1 else 6451.8,
                                           "bf16_tflops": float(sys.argv[2]) if len(sys.argv) > 2 else 1685.0})))
