@@ -254,7 +254,10 @@ LQ_API int lq_w4a8_linear_bias(const int8_t* x_i8, const uint8_t* blob, const fl
 
 /* Plain INT8 x INT8 -> INT32 tensor-core GEMM c[M,N] = a[M,K] @ b[N,K]^T.
  * Replaces torch.ops.liquidgemm.wgmma_i8_gemm (reference csrc/liquid_gemm/w4a8_wgmma.cu:648-694).
- * K % 128 == 0; M and N are arbitrary here (the reference needs multiples of 128). */
+ * K % 128 == 0; M and N are arbitrary here (the reference needs multiples of 128).
+ * Dispatch: from 256 tokens, on layers with whole 256-channel blocks and at least 60 tiles of 256 x 256, a
+ * CTA-pair kernel (tcgen05.mma.cta_group::2, both operands from shared memory); otherwise a persistent one-CTA
+ * kernel.  LQ_I8_PAIR=0 in the environment keeps every call on the latter (a measurement switch). */
 LQ_API int lq_i8_gemm_i32(const int8_t* a, const int8_t* b, int32_t* c, int M, int N, int K,
                    void* stream);
 
