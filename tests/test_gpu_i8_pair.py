@@ -63,3 +63,28 @@ def test_scaled_outputs_are_bit_exact(ops, M, N, K, out_dtype, monkeypatch):
     monkeypatch.setenv("LQ_I8_PAIR", "0")
     assert torch.equal(torch.ops.liquidgemm.i8_gemm_scaled(at, bt, sat, sbt, out_dtype), got)
     ops.poll_status()
+
+
+def _seeded_shapes(count, seed):
+    rng = np.random.default_rng(seed)
+    out = []
+    while len(out) < count:
+        N = 256 * int(rng.integers(1, 40))
+        K = 128 * int(rng.integers(1, 48))
+        M = int(rng.integers(256, 6000))
+        if (N // 256) * ((M + 255) // 256) >= 60 and M * K + N * K < 300_000_000:
+            out.append((M, N, K))
+    return out
+
+
+@pytest.mark.parametrize("M,N,K", _seeded_shapes(16, seed=2024))
+def test_seeded_shapes_against_cublaslt(ops, M, N, K):
+    """Sixteen seeded shapes the pair kernel serves (ragged token counts, one to 47 k-steps, one to 39 channel
+    blocks, partial last waves): int32 sums equal to cuBLASLt's exact INT8 GEMM, one after the other on one
+    context."""
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    a = torch.randint(-127, 128, (M, K), dtype=torch.int8, device="cuda", generator=g)
+    b = torch.randint(-128, 128, (N, K), dtype=torch.int8, device="cuda", generator=g)
+    got = torch.ops.liquidgemm.wgmma_i8_gemm(a, b)
+    assert torch.equal(got, torch._int_mm(a, b.t()))
+    ops.poll_status()
