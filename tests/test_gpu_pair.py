@@ -195,3 +195,27 @@ def test_full_size_against_exact_int8_gemm(ops, name, M):
     assert torch.equal(y, torch.ops.liquidgemm.scale_epilogue(ref, at, tq.s1, 0))
     assert np.array_equal(acc[:16].cpu().numpy(), _acc(x[:16], qw))
     ops.poll_status()
+
+
+def _seeded_shapes(count, seed):
+    rng = np.random.default_rng(seed)
+    return [(int(rng.integers(256, 5000)), 256 * int(rng.integers(1, 17)), 128 * int(rng.integers(1, 33)))
+            for _ in range(count)]
+
+
+@pytest.mark.parametrize("M,N,K", _seeded_shapes(10, seed=77))
+def test_seeded_shapes_against_cublaslt(ops, M, N, K):
+    """Ten seeded shapes (ragged token counts, 1..32 k-steps, 1..16 channel blocks; whole, partial and cut last
+    waves as they fall): int32 sums equal to cuBLASLt's exact INT8 GEMM on the dequantised weights, and the fused
+    bf16 output equal to the epilogue applied to them."""
+    qw = random_lqq(N, K, 64, seed=M)
+    tq = to_torch_qw(qw)
+    x, ascale = random_tokens(M, K, seed=N)
+    xt, at = torch.from_numpy(x).cuda(), torch.from_numpy(ascale).cuda()
+    w = ops.repack_rs_weight(tq)
+    ref = torch._int_mm(xt, ops.dequant_weight_i8(tq).t())
+    acc = torch.ops.liquidgemm.w4a8_wgmma_rs(xt, w, tq.s_u8, tq.s_u8, tq.offset_a, N, K, 64, True)
+    assert torch.equal(acc, ref)
+    y = torch.ops.liquidgemm.w4a8_wgmma_rs_fused(xt, w, tq.s_u8, tq.offset_a, at, tq.s1, N, K, 64, 0)
+    assert torch.equal(y, torch.ops.liquidgemm.scale_epilogue(ref, at, tq.s1, 0))
+    ops.poll_status()
