@@ -457,6 +457,10 @@ def main():
             summary["decode_us"] = {f'{r["shape"]}:{r["M"]}': [r["us"], r["hbm_frac"], r["speedup_vs_cublas_bf16"]]
                                     for r in extras["sweep"] if r["M"] <= 128}
             summary["decode_us_columns"] = ["us per launch", "fraction of measured HBM rate", "x cuBLAS bf16"]
+        if "int8_mode" in extras:
+            # the plugin's INT8-weights mode (i8_gemm_scaled) beside cuBLASLt's INT8 GEMM: [TOPS, cuBLASLt TOPS]
+            summary["int8_mode_tops"] = {f'{r["shape"]}:{r["M"]}': [r["TOPS"], r["cublaslt_int8_TOPS"]]
+                                         for r in extras["int8_mode"]}
         if "tp70b" in extras:
             summary["tp70b_stack_ms"] = extras["tp70b"]["rows"]
     except Exception as exc:

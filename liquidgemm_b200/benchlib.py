@@ -337,6 +337,7 @@ def run_extras(world, rank, local_rank, peaks):
         out["sweep"] = run_sweep(peaks)
         out["splitk"] = run_splitk(peaks)
         out["quant_per_token"] = run_quant(peaks)
+        out["int8_mode"] = [run_one_i8(name, M) for name in SHAPES for M in (2048, 8192)]
     out["tp70b"] = {"ranks": world, "layers": 80, "rows": run_tp70b(world, rank)}
     return out
 
