@@ -123,6 +123,46 @@ quant_per_token_kernel(const T* __restrict__ x, int8_t* __restrict__ xq, float* 
 }
 
 // ---------------------------------------------------------------------------------------------
+// Tile blob -> row-major INT8 weights [N, K] (the level-2 dequantisation of the whole matrix), for very large
+// token counts where unpacking once and running the INT8 x INT8 pair kernel beats unpacking inside the main
+// loop.  One CTA of 128 threads per 128 x 128 tile; thread = weight row, which it writes as one 128-byte line.
+__global__ void __launch_bounds__(128)
+unpack_blob_i8_kernel(const uint8_t* __restrict__ blob, int8_t* __restrict__ w, int N, int K) {
+  const int kt = blockIdx.x, nt = blockIdx.y, row = threadIdx.x;
+  const uint8_t* tile = blob + ((size_t)nt * (K / 128) + kt) * 8704;
+  uint4 ch[4];
+#pragma unroll
+  for (int c = 0; c < 4; ++c) ch[c] = __ldg(reinterpret_cast<const uint4*>(tile + (c * 128 + row) * 16));
+  const uint32_t meta = __ldg(reinterpret_cast<const uint32_t*>(tile + 8192 + row * 4));
+  const uint32_t step0 = meta & 0xffu, a0 = ((meta >> 8) & 0xffu) * 0x01010101u;
+  const uint32_t step1 = (meta >> 16) & 0xffu, a1 = (meta >> 24) * 0x01010101u;
+  const long n = (long)nt * 128 + row;
+  if (n >= N) return;
+  uint4* dst = reinterpret_cast<uint4*>(w + n * K + (long)kt * 128);
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const uint32_t step = c < 2 ? step0 : step1;
+    const uint32_t ab = c < 2 ? a0 : a1;
+    const uint32_t pk[4] = {ch[c].x, ch[c].y, ch[c].z, ch[c].w};
+    uint32_t v[8];
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {
+      v[2 * h] = lqq_dequant4(pk[h] & 0x0F0F0F0Fu, step, ab);
+      v[2 * h + 1] = lqq_dequant4((pk[h] >> 4) & 0x0F0F0F0Fu, step, ab);
+    }
+    dst[2 * c] = make_uint4(v[0], v[1], v[2], v[3]);
+    dst[2 * c + 1] = make_uint4(v[4], v[5], v[6], v[7]);
+  }
+}
+
+// Enqueue the unpack of a whole blob (N a multiple of 128 rows in the blob; K % 128 == 0; `w` 16-byte aligned).
+int run_unpack_blob_i8(const uint8_t* blob, int8_t* w, int N, int K, cudaStream_t st) {
+  dim3 grid(K / 128, (N + 127) / 128);
+  unpack_blob_i8_kernel<<<grid, 128, 0, st>>>(blob, w, N, K);
+  return check_launch("unpack_blob_i8_kernel");
+}
+
+// ---------------------------------------------------------------------------------------------
 // scale_epilogue and split-K finish
 // ---------------------------------------------------------------------------------------------
 // out_dtype 0..2 select the scaled output type; 3 writes the exact int32 sum of the planes.

@@ -69,8 +69,9 @@ int run_gemv_blob_ws(const int8_t* x, const uint8_t* blob, const float* ascale, 
 int decode_tc_grid(int N, int K);                                            // lq_decode_tc.cu
 bool pair_serves(int M, int N, int K);                                       // lq_gemm_pair.cu
 bool i8_pair_serves(int M, int N, int K);                                    // lq_i8_pair.cu
-int run_i8_pair_gemm(const int8_t* x, const int8_t* w, const float* ascale, const float* s1, void* out, int out_mode,
-                     int M, int N, int K, cudaStream_t st);
+int run_i8_pair_gemm(const int8_t* x, const int8_t* w, const float* ascale, const float* s1, const void* bias, void* out,
+                     int out_mode, int M, int N, int K, cudaStream_t st);
+int run_unpack_blob_i8(const uint8_t* blob, int8_t* w, int N, int K, cudaStream_t st);   // lq_elementwise.cu
 bool pair_prefers(int M, int N, int K);                                      // lq_gemm_pair.cu
 size_t pair_workspace_bytes(int M, int N, int K);                                // lq_gemm_pair.cu
 int pair_grid(int M, int N, int K);                                              // lq_gemm_pair.cu
@@ -659,6 +660,7 @@ enum RouteKind {
   kRouteGemv,         // streaming dp4a GEMV over the blob (scaled outputs only)
   kRouteDecodeTc,     // streaming tensor-core kernel, one launch, atomic join
   kRoutePair,         // CTA pairs, 256 channels x 192 tokens per tile (prefill)
+  kRouteUnpackI8,     // very large token counts: unpack the blob to INT8 once, then the INT8 x INT8 pair kernel
 };
 struct Route {
   RouteKind kind;
@@ -710,7 +712,23 @@ static bool gemv_serves(int M, int N, int K) {
   return M == 1 || (M == 2 && w <= (1L << 26)) || (M <= kGemvBlobMaxM && w <= (1L << 24));
 }
 
-static Route route_for(int M, int N, int K, int splitk, bool scaled) {
+// Very large token counts on layers the INT8 pair kernel serves: unpacking the whole blob to INT8 once (a pass over
+// N x K bytes of scratch: 38 us for 28672 x 4096) and running the INT8 x INT8 pair kernel, which keeps the tensor
+// pipe 95 % busy, beats unpacking inside the main loop (71 %).  Measured at 8192 tokens: qkv 153 -> 144 us, o 107
+// -> 95, gate_up 722 -> 681, down (K = 14336, where the W4 kernel's epilogues weigh least) level: layers with
+// K >= 8192 stay on the W4 pair kernel; at 4096 tokens 0-6 %, below that the pass costs more than it saves.
+// LQ_UNPACK_I8_MIN_M moves the limit (0 switches the route off); layers above 256 MB of INT8 weights stay on the
+// W4 pair kernel (the scratch would be larger than that).
+static int unpack_i8_min_m() {
+  const char* e = getenv("LQ_UNPACK_I8_MIN_M");   // read at every call: a measurement switch
+  return e ? atoi(e) : 6144;
+}
+static bool unpack_i8_serves(int M, int N, int K) {
+  const int lim = unpack_i8_min_m();
+  return lim > 0 && M >= lim && K < 8192 && (size_t)N * K <= ((size_t)256 << 20) && i8_pair_serves(M, N, K);
+}
+
+static Route route_for(int M, int N, int K, int splitk, bool scaled, bool single_dest = true) {
   const int kt = K / 128;
   if (splitk == -1) return {kRoutePersistent, 0};
   if (M <= 128) {
@@ -729,6 +747,7 @@ static Route route_for(int M, int N, int K, int splitk, bool scaled) {
   // M x N on layers with whole 256-channel blocks), else the two-CTAs-per-SM tile kernel; the persistent
   // stream-K kernel stays reachable through an explicit split argument.
   if (splitk == 0) {
+    if (single_dest && !pair_forced() && unpack_i8_serves(M, N, K)) return {kRouteUnpackI8, 0};
     if (M >= pair_min_m() && (pair_forced() ? pair_serves(M, N, K) : pair_prefers(M, N, K))) return {kRoutePair, 0};
     return {kRouteTile, tile_pick_splits(M, N, K)};
   }
@@ -741,6 +760,7 @@ static size_t route_ws_bytes(const Route& r, int M, int N, int K) {
     case kRouteDecodeTc: return decode_tc_workspace_bytes(M, N, K);
     case kRouteTile: return tile_workspace_bytes(M, N, r.splits);
     case kRoutePair: return pair_workspace_bytes(M, N, K);
+    case kRouteUnpackI8: return (size_t)N * K;   // scratch: the INT8 weights
     default: return make_plan(M, N, K, r.splits).ws_bytes;
   }
 }
@@ -756,14 +776,15 @@ size_t lq_gemm_workspace_bytes(int M, int N, int K, int splitk) {
 // 0: none, 1: scratch (split-K planes; any content), 2: the shared buffer that is all zero between calls.
 int lq_gemm_workspace_kind(int M, int N, int K, int splitk) {
   if (lq_gemm_workspace_bytes(M, N, K, splitk) == 0) return 0;
-  return route_for(M, N, K, splitk, true).kind == kRouteTile ? 1 : 2;
+  const RouteKind k = route_for(M, N, K, splitk, true).kind;
+  return (k == kRouteTile || k == kRouteUnpackI8) ? 1 : 2;   // 1: scratch, 2: all-zero reduction buffer
 }
 
 // Kernel launches one call makes (for callers that count them).
 int lq_gemm_launches(int M, int N, int K, int splitk) {
   if (M <= 0 || N <= 0 || K < 128) return 0;
   const Route r = route_for(M, N, K, splitk, true);
-  return (r.kind == kRouteTile && r.splits > 1) ? 2 : 1;
+  return ((r.kind == kRouteTile && r.splits > 1) || r.kind == kRouteUnpackI8) ? 2 : 1;
 }
 
 static int blob_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, const float* s1, const void* bias,
@@ -787,6 +808,12 @@ static int blob_gemm(const int8_t* x, const uint8_t* blob, const float* ascale, 
                            ws_bytes, st);
     case kRoutePair:
       return run_pair_gemm(x, blob, ascale, s1, bias, single_out(out, N), nullptr, out_mode, M, N, K, ws, ws_bytes, st);
+    case kRouteUnpackI8: {
+      if (!ws || ws_bytes < (size_t)N * K || (reinterpret_cast<uintptr_t>(ws) & 15)) return LQ_ERR_WORKSPACE;
+      int8_t* w8 = static_cast<int8_t*>(ws);
+      if (int rc = run_unpack_blob_i8(blob, w8, N, K, st)) return rc;
+      return run_i8_pair_gemm(x, w8, ascale, s1, bias, out, out_mode, M, N, K, st);
+    }
     default:
       if (bias) return LQ_ERR_BAD_ARG;   // the persistent kernel has no bias epilogue
       return run_gemm<kBlob>(x, blob, ascale, s1, out, out_mode, M, N, K, r.splits, ws, ws_bytes, st);
@@ -841,7 +868,7 @@ int lq_w4a8_gemm_fused_scatter_sync(const int8_t* x_i8, const uint8_t* blob, con
   ps.wait = wait_flag;
   ps.wait_value = wait_value;
   if (int rc = lq_check_device()) return rc;
-  const Route r = route_for(M, N, K, 0, true);
+  const Route r = route_for(M, N, K, 0, true, false);
   switch (r.kind) {
     case kRouteGemv:
       return run_gemv_blob_ws(x_i8, blob, ascale, s1, nullptr, o, &ps, out_dtype, M, N, K, workspace, workspace_bytes,
@@ -867,14 +894,17 @@ int lq_w4a8_gemm_fused_scatter(const int8_t* x_i8, const uint8_t* blob, const fl
 
 size_t lq_scatter_workspace_bytes(int M, int N, int K) {
   if (M < 1 || N <= 0 || K < 128 || K % 128) return 0;
-  return route_ws_bytes(route_for(M, N, K, 0, true), M, N, K);
+  return route_ws_bytes(route_for(M, N, K, 0, true, false), M, N, K);
 }
 
-int lq_scatter_workspace_kind(int M, int N, int K) { return lq_gemm_workspace_kind(M, N, K, 0); }
+int lq_scatter_workspace_kind(int M, int N, int K) {
+  if (lq_scatter_workspace_bytes(M, N, K) == 0) return 0;
+  return route_for(M, N, K, 0, true, false).kind == kRouteTile ? 1 : 2;
+}
 
 int lq_decode_grid(int M, int N, int K) {
   if (M < 1 || N <= 0 || K < 128 || K % 128) return 0;
-  const Route r = route_for(M, N, K, 0, true);
+  const Route r = route_for(M, N, K, 0, true, false);
   switch (r.kind) {
     case kRouteGemv: return gemv_blob_grid(N, K);
     case kRouteDecodeTc: return decode_tc_grid(N, K);
@@ -924,7 +954,7 @@ static int i8_common(const int8_t* a, const int8_t* b, const float* a_scale, con
   if (M == 0) return LQ_OK;
   // whole-tile scheduling: the plain INT8 entry points take no workspace
   if (i8_pair_serves(M, N, K) && i8_pair_enabled())
-    return run_i8_pair_gemm(a, b, a_scale, b_scale, out, out_mode, M, N, K, as_stream(stream));
+    return run_i8_pair_gemm(a, b, a_scale, b_scale, nullptr, out, out_mode, M, N, K, as_stream(stream));
   return run_gemm<kInt8>(a, b, a_scale, b_scale, out, out_mode, M, N, K, 1, nullptr, 0,
                          as_stream(stream));
 }

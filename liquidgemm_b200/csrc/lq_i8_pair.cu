@@ -56,6 +56,7 @@ constexpr int kOutI32 = kEpiI32;
 struct Args {
   const float* ascale;     // [M] or null (raw int32)
   const float* s1;         // [N] or null
+  const void* bias;        // [N] in the output dtype, or null
   void* out;               // [M, N]
   int* status;
   int out_mode;            // LQ_DT_* or kOutI32
@@ -231,6 +232,7 @@ i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
     const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
     const int et = (threadIdx.x & 127);        // 0..127 inside the group (the groups start at multiples of 128)
     const bool raw = args.out_mode == kOutI32;
+    const bool has_bias = !raw && args.bias != nullptr;
     volatile int* wflag = wait_flag + 2 * g;
     PairWalk walk(args, pair);
     Segment sg;
@@ -267,6 +269,7 @@ i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
       ptx::tc_fence_after();
       const uint32_t tmem_acc = tmem_base + b * kBN + lane_addr;
       const float w_scale = raw ? 0.f : __ldg(args.s1 + n);
+      const float bias = has_bias ? load_bias(args.bias, n, args.out_mode) : 0.f;
 #pragma unroll 1
       for (int c0 = 16 * g; c0 < cols; c0 += 16 * kGroups) {
         int v[16];
@@ -279,7 +282,7 @@ i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
         }
         ptx::tc_wait_ld();
         // lane = channel: a warp's store covers 32 consecutive channels of one token row
-        epi_store_cols(args.out, args.out_mode, (size_t)(m0 + c0) * args.N + n, args.N, v, sc, w_scale, 0.f, false,
+        epi_store_cols(args.out, args.out_mode, (size_t)(m0 + c0) * args.N + n, args.N, v, sc, w_scale, bias, has_bias,
                        cols - c0);
       }
       // this warp's reads of the accumulator are complete: the MMA warp may reuse it
@@ -338,8 +341,8 @@ bool i8_pair_serves(int M, int N, int K) {
   return tiles >= 60;
 }
 
-int run_i8_pair_gemm(const int8_t* x, const int8_t* w, const float* ascale, const float* s1, void* out, int out_mode, int M,
-                     int N, int K, cudaStream_t st) {
+int run_i8_pair_gemm(const int8_t* x, const int8_t* w, const float* ascale, const float* s1, const void* bias, void* out,
+                     int out_mode, int M, int N, int K, cudaStream_t st) {
   using namespace i8pair;
   if (out_mode < 0 || out_mode > kOutI32) return LQ_ERR_BAD_ARG;
   CUtensorMap tx, tw;
@@ -348,6 +351,7 @@ int run_i8_pair_gemm(const int8_t* x, const int8_t* w, const float* ascale, cons
   Args a;
   a.ascale = ascale;
   a.s1 = s1;
+  a.bias = bias;
   a.out = out;
   a.status = status_word();
   a.out_mode = out_mode;
