@@ -712,19 +712,17 @@ static bool gemv_serves(int M, int N, int K) {
   return M == 1 || (M == 2 && w <= (1L << 26)) || (M <= kGemvBlobMaxM && w <= (1L << 24));
 }
 
-// Very large token counts on layers the INT8 pair kernel serves: unpacking the whole blob to INT8 once (a pass over
+// Large token counts on layers the INT8 pair kernel serves: unpacking the whole blob to INT8 once (a pass over
 // N x K bytes of scratch: 38 us for 28672 x 4096) and running the INT8 x INT8 pair kernel, which keeps the tensor
-// pipe 95 % busy, beats unpacking inside the main loop (71 %).  Measured at 8192 tokens: qkv 153 -> 144 us, o 107
-// -> 95, gate_up 722 -> 681, down (K = 14336, where the W4 kernel's epilogues weigh least) level: layers with
-// K >= 8192 stay on the W4 pair kernel; at 4096 tokens 0-6 %, below that the pass costs more than it saves.
-// LQ_UNPACK_I8_MIN_M moves the limit (0 switches the route off); layers above 256 MB of INT8 weights stay on the
-// W4 pair kernel (the scratch would be larger than that).
-static int unpack_i8_min_m() {
-  const char* e = getenv("LQ_UNPACK_I8_MIN_M");   // read at every call: a measurement switch
-  return e ? atoi(e) : 6144;
-}
+// pipe 95 % busy, beats unpacking inside the main loop (71 %).  Measured in one process: at 8192 tokens qkv 158.6
+// -> 144.0 us, o 108.9 -> 93.8, gate_up 720.6 -> 660.4; at 5120 tokens 6 / 3 / 2.5 %; at 3072 tokens qkv 6 %, o
+// 2 %, gate_up 5 % slower; at 2048 all slower.  down (K = 14336, where the W4 kernel's epilogues weigh least) is
+// level at every size: layers with K >= 8192 stay on the W4 pair kernel, and so do layers above 256 MB of INT8
+// weights (the scratch would be larger than that).  LQ_UNPACK_I8_MIN_M replaces both limits (0 switches the route
+// off).
 static bool unpack_i8_serves(int M, int N, int K) {
-  const int lim = unpack_i8_min_m();
+  const char* e = getenv("LQ_UNPACK_I8_MIN_M");   // read at every call: a measurement switch
+  const int lim = e ? atoi(e) : ((size_t)N * K <= ((size_t)1 << 25) ? 3072 : 5120);
   return lim > 0 && M >= lim && K < 8192 && (size_t)N * K <= ((size_t)256 << 20) && i8_pair_serves(M, N, K);
 }
 

@@ -48,7 +48,7 @@ def test_size_helpers_without_gpu():
     assert lib.lq_gemm_workspace_kind(8, 6144, 4096, 0) == 2         # streaming tensor-core kernel, atomic join
     assert lib.lq_gemm_workspace_kind(8, 4096, 14336, 0) == 1        # larger matrix: tile kernel with split-K planes
     assert lib.lq_gemm_workspace_kind(64, 4096, 14336, 0) == 1       # tile kernel with split-K planes
-    assert lib.lq_gemm_workspace_kind(4096, 6144, 4096, 0) == 2      # pair kernel, last wave split along k
+    assert lib.lq_gemm_workspace_kind(4096, 28672, 4096, 0) == 2     # pair kernel, last wave split along k
     assert lib.lq_gemm_workspace_kind(8192, 6144, 4096, 0) == 1      # unpack to INT8 scratch, then the INT8 pair kernel
     assert lib.lq_gemm_workspace_bytes(8192, 6144, 4096, 0) == 6144 * 4096
     assert lib.lq_gemm_launches(8192, 6144, 4096, 0) == 2
