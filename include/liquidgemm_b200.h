@@ -208,6 +208,10 @@ LQ_API int lq_quantize_weight(const void* w, int w_dtype, int N, int K, int grou
  *              (scaled outputs only): streaming dp4a GEMV over the tile blob;
  *     up to 16 tokens on matrices up to 32 M weights: the streaming tensor-core kernel, ONE launch:
  *              stream-K over two CTAs per SM, one 64-bit atomic per element joins cut tiles;
+ *     3072 tokens and more (5120 on matrices above 32 M weights) on layers with K < 8192, whole 256-channel
+ *              blocks and at most 256 M weights, one destination: the blob is unpacked to INT8 in the workspace
+ *              (scratch, N x K bytes) and the INT8 x INT8 CTA-pair kernel does the GEMM, TWO launches
+ *              (LQ_UNPACK_I8_MIN_M in the environment moves the limit, 0 switches the route off);
  *     256 tokens and more on layers with whole 256-channel blocks, where a cost model expects it to win
  *              (large M x N): the CTA-pair kernel, tcgen05.mma.cta_group::2 on 256-channel x 192-token tiles;
  *     otherwise tile kernel: one 128-channel x up-to-128-token tile per CTA, two CTAs per SM, every
@@ -222,13 +226,14 @@ LQ_API int lq_quantize_weight(const void* w, int w_dtype, int N, int K, int grou
  * the reference the override only applies to M <= 128 and is clamped to K/128; otherwise 0. */
 LQ_API int lq_gemm_pick_splitk(int M, int N, int K, int env_override);
 /* Workspace bytes for (M,N,K,splitk) and its kind: 0 = none, 1 = scratch (any contents; the
- * tile kernel's planes), 2 = reduction buffer of the streaming, pair and persistent kernels, which must be ALL ZERO when
+ * tile kernel's planes, or the INT8 weights of the unpack route: 16-byte aligned), 2 = reduction buffer of the streaming, pair and persistent kernels, which must be ALL ZERO when
  * a call starts and is all zero again when its kernel ends (the kernel cleans up after itself), so
  * one zero-filled buffer serves any number of successive calls on a stream; calls that overlap on
  * the GPU need separate buffers, and after a LQ_ERR_TIMEOUT the caller must clear it. */
 LQ_API size_t lq_gemm_workspace_bytes(int M, int N, int K, int splitk);
 LQ_API int lq_gemm_workspace_kind(int M, int N, int K, int splitk);
-/* Kernel launches one fused call with these arguments makes (2 when the tile kernel splits K). */
+/* Kernel launches one fused call with these arguments makes (2 when the tile kernel splits K or the unpack
+ * route is taken). */
 LQ_API int lq_gemm_launches(int M, int N, int K, int splitk);
 
 /* W4A8 tensor-core GEMM, exact int32 accumulators acc[M,N] = x_i8 @ q_hat^T.
