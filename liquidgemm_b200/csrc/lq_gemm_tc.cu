@@ -719,7 +719,9 @@ static bool gemv_serves(int M, int N, int K) {
 // 2 %, gate_up 5 % slower; at 2048 all slower.  down (K = 14336, where the W4 kernel's epilogues weigh least) is
 // level at every size: layers with K >= 8192 stay on the W4 pair kernel, and so do layers above 256 MB of INT8
 // weights (the scratch would be larger than that).  LQ_UNPACK_I8_MIN_M replaces both limits (0 switches the route
-// off).
+// off).  Running the two kernels overlapped (the GEMM launched programmatically behind a persistent unpack kernel,
+// waiting per channel block on counts of finished tiles) was measured as well: bit-exact, 3-7 % SLOWER than one after
+// the other (the unpack's memory traffic slows the GEMM it runs beside); not kept.
 static bool unpack_i8_serves(int M, int N, int K) {
   const char* e = getenv("LQ_UNPACK_I8_MIN_M");   // read at every call: a measurement switch
   const int lim = e ? atoi(e) : ((size_t)N * K <= ((size_t)1 << 25) ? 3072 : 5120);
