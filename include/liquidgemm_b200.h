@@ -150,10 +150,13 @@ LQ_API int lq_w4a8_gemm_fused_scatter_sync(const int8_t* x_i8, const uint8_t* bl
                                            unsigned* const* peer_flags, int flag_index,
                                            const unsigned* wait_flag, unsigned wait_value,
                                            void* workspace, size_t workspace_bytes, void* stream);
-/* CTAs a gather-by-stores launch (M <= 16) of this shape uses on the current device, and the bytes of
- * its workspace (ALL ZERO on entry, left all zero; may be shared with the other zeroed workspaces). */
+/* CTAs a gather-by-stores launch of this shape uses on the current device, and the bytes and kind of its
+ * workspace (kinds as for lq_gemm_workspace_kind: 1 = scratch, the tile kernel's planes; 2 = ALL ZERO on entry,
+ * left all zero, may be shared with the other zeroed workspaces).  These differ from the single-destination
+ * queries where that call would take a route the gather-by-stores form does not have. */
 LQ_API int lq_decode_grid(int M, int N, int K);
 LQ_API size_t lq_scatter_workspace_bytes(int M, int N, int K);
+LQ_API int lq_scatter_workspace_kind(int M, int N, int K);
 
 /* One whole linear layer for HOST activations and a HOST output: upload, per-token quantise, fused
  * W4A8 linear from the tile blob (automatic kernel choice by M), download, all enqueued on `stream`

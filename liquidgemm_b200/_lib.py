@@ -42,6 +42,7 @@ _SIGNATURES = {
                                                 c_int, P, c_int, P, ctypes.c_uint, P, c_size_t, P]),
     "lq_decode_grid": (c_int, [c_int, c_int, c_int]),
     "lq_scatter_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "lq_scatter_workspace_kind": (c_int, [c_int, c_int, c_int]),
     "lq_linear_host_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "lq_w4a8_linear_host": (c_int, [P, c_int, P, P, P, c_int, c_int, c_int, c_int, P, c_size_t, P, c_size_t, P]),
     "lq_gemm_v1_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),

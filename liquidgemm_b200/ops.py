@@ -420,7 +420,7 @@ def gemm_fused_scatter(x_i8, blob, ascale, s1, out_ptrs, ld_out, col0, N, K, out
         flags = (ctypes.c_void_p * len(flag_ptrs))(*[int(p) for p in flag_ptrs])
     with _dev_ctx(x_i8):
         nbytes = lib.lq_scatter_workspace_bytes(M, N, K)
-        kind = lib.lq_gemm_workspace_kind(M, N, K, 0)
+        kind = lib.lq_scatter_workspace_kind(M, N, K)
         if kind == 1:
             ws = torch.empty((nbytes,), dtype=torch.uint8, device=x_i8.device)   # split-K planes: plain scratch
         else:

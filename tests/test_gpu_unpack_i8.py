@@ -73,3 +73,30 @@ def test_bias_is_added_to_the_rounded_output(ops, out_dtype):
     want = with_bias_f32(O.w4a8_matmul(x[rows], ascale[rows], qw), bits(bias), out_dtype)
     assert_bits_equal(y[rows], want, out_dtype, "unpack route with bias")
     ops.poll_status()
+
+
+def test_gather_by_stores_keeps_its_own_route_and_workspace(ops):
+    """The multi-destination form has no unpack route: for a shape whose single-destination call takes it, the
+    scatter call runs the W4 kernels on the zeroed reduction workspace (kind from lq_scatter_workspace_kind) and
+    leaves it zero: the same call twice and a decode call afterwards are exact."""
+    from liquidgemm_b200._lib import lib
+    M, N, K, NF, col0 = 3200, 2560, 512, 5120, 2560
+    assert lib.lq_gemm_workspace_kind(M, N, K, 0) == 1
+    assert lib.lq_scatter_workspace_kind(M, N, K) in (0, 2)
+    qw = random_lqq(N, K, 64, seed=3)
+    tq = to_torch_qw(qw)
+    x, ascale = random_tokens(M, K, seed=4)
+    xt, at = torch.from_numpy(x).cuda(), torch.from_numpy(ascale).cuda()
+    blob = ops.repack_rs_weight(tq).reshape(-1)
+    want = torch.ops.liquidgemm.scale_epilogue(torch._int_mm(xt, ops.dequant_weight_i8(tq).t()), at, tq.s1, 0)
+    for _ in range(2):
+        outs = [torch.full((M, NF), -1.0, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+        ops.gemm_fused_scatter(xt, blob, at, tq.s1, [o.data_ptr() for o in outs], NF, col0, N, K, 0)
+        torch.cuda.synchronize()
+        for o in outs:
+            assert torch.equal(o[:, col0:col0 + N], want)
+            assert bool((o[:, :col0] == -1).all())
+    y8 = torch.ops.liquidgemm.w4a8_wgmma_rs_fused(xt[:8].contiguous(), ops.repack_rs_weight(tq), tq.s_u8, tq.offset_a,
+                                                  at[:8].contiguous(), tq.s1, N, K, 64, 0)
+    assert_bits_equal(y8, O.w4a8_matmul(x[:8], ascale[:8], qw), 0, "decode call on the shared workspace afterwards")
+    ops.poll_status()
