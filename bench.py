@@ -453,7 +453,7 @@ def main():
             summary["prefill"] = [
                 {"shape": r["shape"], "M": r["M"], "TOPS": r["TOPS"], "of_4500": r["int8_frac_of_4500"],
                  "of_2x_measured_bf16": r.get("int8_frac_of_2x_bf16"), "x_cublas_bf16": r["speedup_vs_cublas_bf16"]}
-                for r in extras["sweep"] if r["M"] in (2048, 8192)]
+                for r in extras["sweep"] if r["M"] in (512, 2048, 8192)]
             summary["decode_us"] = {f'{r["shape"]}:{r["M"]}': [r["us"], r["hbm_frac"], r["speedup_vs_cublas_bf16"]]
                                     for r in extras["sweep"] if r["M"] <= 128}
             summary["decode_us_columns"] = ["us per launch", "fraction of measured HBM rate", "x cuBLAS bf16"]

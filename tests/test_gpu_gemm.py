@@ -310,3 +310,24 @@ def test_peer_wait_gives_up_and_reports(ops):
     assert_bits_equal(out, O.w4a8_matmul(x, ascale, qw), 1, "after timeout")
     got = ops.gemm_fused(xd, blob, sd, tq.s1, N, K, 1)
     assert_bits_equal(got, O.w4a8_matmul(x, ascale, qw), 1, "next call")
+
+
+@pytest.mark.parametrize("name,M", [("o", 512), ("qkv", 384), ("o", 384), ("qkv", 512), ("o", 257)])
+def test_medium_token_counts(ops, name, M):
+    """A few hundred tokens on the small matrices, where the dispatch switches between 64-token tiles in one wave
+    and 128-token tiles cut along k: int32 sums equal to cuBLASLt's exact INT8 GEMM on the dequantised weights,
+    fused output equal to the epilogue applied to them, last rows against the CPU oracle."""
+    N, K = LLAMA8B[name]
+    qw = random_lqq(N, K, 64, seed=M)
+    tq = to_torch_qw(qw)
+    x, ascale = random_tokens(M, K, seed=M + 1)
+    xt, at = torch.from_numpy(x).cuda(), torch.from_numpy(ascale).cuda()
+    w = ops.repack_rs_weight(tq)
+    acc = torch.ops.liquidgemm.w4a8_wgmma_rs(xt, w, tq.s_u8, tq.s_u8, tq.offset_a, N, K, 64, True)
+    ref = torch._int_mm(xt, ops.dequant_weight_i8(tq).t()) if M > 16 else None
+    assert torch.equal(acc, ref)
+    y = torch.ops.liquidgemm.w4a8_wgmma_rs_fused(xt, w, tq.s_u8, tq.offset_a, at, tq.s1, N, K, 64, 0)
+    assert torch.equal(y, torch.ops.liquidgemm.scale_epilogue(ref, at, tq.s1, 0))
+    rows = slice(M - 5, M)
+    assert_bits_equal(y[rows], O.w4a8_matmul(x[rows], ascale[rows], qw), 0, "medium token counts")
+    ops.poll_status()
