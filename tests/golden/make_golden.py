@@ -2,7 +2,7 @@
 
 Usage (only where the reference tree is mounted; the fixtures themselves are committed):
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <root of the reference tree>
 
 The reference's ``liquidgemm.quant`` / ``liquidgemm.pack`` are pure PyTorch and import as they
 are.  ``liquidgemm.ops`` imports a compiled ``_C`` module and attaches fake kernels to ops that
